@@ -1,0 +1,176 @@
+// Hccl* collectives over NCCL, for gathering column-sharded matmul outputs across the GPUs of a
+// box (NVLink 5 / NVSwitch).  Same contract as the reference's cuda/src/hccl.cu:47-172: the root
+// info blob carries the NCCL unique id, one NCCL communicator per HcclComm, every collective is
+// enqueued on the caller's stream.
+//
+// NCCL is bound at first use, not at load time: a process that already holds an NCCL (for example
+// the one bundled with PyTorch) keeps using that copy, and merely loading this library pulls no
+// second NCCL into the process.
+#include <cuda_runtime.h>
+#include <dlfcn.h>
+#include <nccl.h>
+
+#include <cstdio>
+#include <cstring>
+
+#include "hccl/hccl.h"
+
+namespace {
+static_assert(sizeof(ncclUniqueId) <= HCCL_ROOT_INFO_BYTES, "root info must hold the NCCL unique id");
+
+struct Nccl {
+    decltype(&::ncclGetUniqueId) GetUniqueId = nullptr;
+    decltype(&::ncclCommInitRank) CommInitRank = nullptr;
+    decltype(&::ncclCommDestroy) CommDestroy = nullptr;
+    decltype(&::ncclAllReduce) AllReduce = nullptr;
+    decltype(&::ncclAllGather) AllGather = nullptr;
+    decltype(&::ncclReduceScatter) ReduceScatter = nullptr;
+    decltype(&::ncclBroadcast) Broadcast = nullptr;
+    decltype(&::ncclCommCount) CommCount = nullptr;
+    decltype(&::ncclCommUserRank) CommUserRank = nullptr;
+    bool ok = false;
+};
+
+const Nccl &nccl() {
+    static Nccl n = [] {
+        Nccl t;
+        void *h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD);  // a copy the process already holds
+        if (!h) h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+        if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+        if (!h) {
+            fprintf(stderr, "[b200-hccl] NCCL not found: %s\n", dlerror());
+            return t;
+        }
+#define BIND(name) t.name = reinterpret_cast<decltype(t.name)>(dlsym(h, "nccl" #name))
+        BIND(GetUniqueId); BIND(CommInitRank); BIND(CommDestroy); BIND(AllReduce); BIND(AllGather);
+        BIND(ReduceScatter); BIND(Broadcast); BIND(CommCount); BIND(CommUserRank);
+#undef BIND
+        t.ok = t.GetUniqueId && t.CommInitRank && t.CommDestroy && t.AllReduce && t.AllGather && t.ReduceScatter &&
+               t.Broadcast && t.CommCount && t.CommUserRank;
+        return t;
+    }();
+    return n;
+}
+#define NEED_NCCL() do { if (!nccl().ok) return HCCL_E_UNAVAIL; } while (0)
+
+bool to_nccl(HcclDataType t, ncclDataType_t *o) {
+    switch (t) {
+        case HCCL_DATA_TYPE_INT8: *o = ncclInt8; return true;
+        case HCCL_DATA_TYPE_UINT8: *o = ncclUint8; return true;
+        case HCCL_DATA_TYPE_INT32: *o = ncclInt32; return true;
+        case HCCL_DATA_TYPE_UINT32: *o = ncclUint32; return true;
+        case HCCL_DATA_TYPE_INT64: *o = ncclInt64; return true;
+        case HCCL_DATA_TYPE_UINT64: *o = ncclUint64; return true;
+        case HCCL_DATA_TYPE_FP16: *o = ncclFloat16; return true;
+        case HCCL_DATA_TYPE_FP32: *o = ncclFloat32; return true;
+        case HCCL_DATA_TYPE_FP64: *o = ncclFloat64; return true;
+        case HCCL_DATA_TYPE_BFP16: *o = ncclBfloat16; return true;
+        default: return false;
+    }
+}
+bool to_nccl(HcclReduceOp op, ncclRedOp_t *o) {
+    switch (op) {
+        case HCCL_REDUCE_SUM: *o = ncclSum; return true;
+        case HCCL_REDUCE_PROD: *o = ncclProd; return true;
+        case HCCL_REDUCE_MAX: *o = ncclMax; return true;
+        case HCCL_REDUCE_MIN: *o = ncclMin; return true;
+    }
+    return false;
+}
+HcclResult from_nccl(ncclResult_t r) {
+    switch (r) {
+        case ncclSuccess: return HCCL_SUCCESS;
+        case ncclInvalidArgument: case ncclInvalidUsage: return HCCL_E_PARA;
+        case ncclSystemError: case ncclRemoteError: return HCCL_E_NETWORK;
+        default: return HCCL_E_INTERNAL;
+    }
+}
+}  // namespace
+
+extern "C" {
+
+HcclResult HcclGetRootInfo(HcclRootInfo *rootInfo) {
+    NEED_NCCL();
+    if (!rootInfo) return HCCL_E_PTR;
+    ncclUniqueId id;
+    ncclResult_t r = nccl().GetUniqueId(&id);
+    if (r != ncclSuccess) return from_nccl(r);
+    memset(rootInfo->internal, 0, sizeof(rootInfo->internal));
+    memcpy(rootInfo->internal, &id, sizeof(id));
+    return HCCL_SUCCESS;
+}
+
+HcclResult HcclCommInitRootInfo(uint32_t nRanks, const HcclRootInfo *rootInfo, uint32_t rank, HcclComm *comm) {
+    NEED_NCCL();
+    if (!rootInfo || !comm) return HCCL_E_PTR;
+    if (nRanks == 0 || rank >= nRanks) return HCCL_E_PARA;
+    ncclUniqueId id;
+    memcpy(&id, rootInfo->internal, sizeof(id));
+    ncclComm_t c = nullptr;
+    ncclResult_t r = nccl().CommInitRank(&c, (int)nRanks, id, (int)rank);
+    if (r != ncclSuccess) return from_nccl(r);
+    *comm = (HcclComm)c;
+    return HCCL_SUCCESS;
+}
+
+HcclResult HcclCommDestroy(HcclComm comm) {
+    NEED_NCCL();
+    if (!comm) return HCCL_E_PTR;
+    return from_nccl(nccl().CommDestroy((ncclComm_t)comm));
+}
+
+HcclResult HcclAllReduce(void *sendBuf, void *recvBuf, uint64_t count, HcclDataType dataType, HcclReduceOp op,
+                         HcclComm comm, aclrtStreamH stream) {
+    NEED_NCCL();
+    ncclDataType_t dt; ncclRedOp_t ro;
+    if (!sendBuf || !recvBuf || !comm) return HCCL_E_PTR;
+    if (!to_nccl(dataType, &dt) || !to_nccl(op, &ro)) return HCCL_E_NOT_SUPPORT;
+    return from_nccl(nccl().AllReduce(sendBuf, recvBuf, count, dt, ro, (ncclComm_t)comm, (cudaStream_t)stream));
+}
+
+HcclResult HcclAllGather(void *sendBuf, void *recvBuf, uint64_t sendCount, HcclDataType dataType, HcclComm comm,
+                         aclrtStreamH stream) {
+    NEED_NCCL();
+    ncclDataType_t dt;
+    if (!sendBuf || !recvBuf || !comm) return HCCL_E_PTR;
+    if (!to_nccl(dataType, &dt)) return HCCL_E_NOT_SUPPORT;
+    return from_nccl(nccl().AllGather(sendBuf, recvBuf, sendCount, dt, (ncclComm_t)comm, (cudaStream_t)stream));
+}
+
+HcclResult HcclReduceScatter(void *sendBuf, void *recvBuf, uint64_t recvCount, HcclDataType dataType, HcclReduceOp op,
+                             HcclComm comm, aclrtStreamH stream) {
+    NEED_NCCL();
+    ncclDataType_t dt; ncclRedOp_t ro;
+    if (!sendBuf || !recvBuf || !comm) return HCCL_E_PTR;
+    if (!to_nccl(dataType, &dt) || !to_nccl(op, &ro)) return HCCL_E_NOT_SUPPORT;
+    return from_nccl(nccl().ReduceScatter(sendBuf, recvBuf, recvCount, dt, ro, (ncclComm_t)comm, (cudaStream_t)stream));
+}
+
+HcclResult HcclBroadcast(void *buf, uint64_t count, HcclDataType dataType, uint32_t root, HcclComm comm,
+                         aclrtStreamH stream) {
+    NEED_NCCL();
+    ncclDataType_t dt;
+    if (!buf || !comm) return HCCL_E_PTR;
+    if (!to_nccl(dataType, &dt)) return HCCL_E_NOT_SUPPORT;
+    return from_nccl(nccl().Broadcast(buf, buf, count, dt, (int)root, (ncclComm_t)comm, (cudaStream_t)stream));
+}
+
+HcclResult HcclGetRankSize(HcclComm comm, uint32_t *rankSize) {
+    NEED_NCCL();
+    if (!comm || !rankSize) return HCCL_E_PTR;
+    int n = 0;
+    ncclResult_t r = nccl().CommCount((ncclComm_t)comm, &n);
+    *rankSize = (uint32_t)n;
+    return from_nccl(r);
+}
+
+HcclResult HcclGetRankId(HcclComm comm, uint32_t *rank) {
+    NEED_NCCL();
+    if (!comm || !rank) return HCCL_E_PTR;
+    int n = 0;
+    ncclResult_t r = nccl().CommUserRank((ncclComm_t)comm, &n);
+    *rank = (uint32_t)n;
+    return from_nccl(r);
+}
+
+}  // extern "C"

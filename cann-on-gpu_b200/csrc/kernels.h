@@ -1,0 +1,84 @@
+// Launch interface between the operator layer (ops_api.cu) and the kernel files.
+// Plain pointers and sizes only; every launcher enqueues on the given stream and returns the
+// launch status without synchronising.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cstdint>
+
+namespace qmm {
+
+// Element encodings understood by the kernels.
+enum ElemType : int {
+    ET_F32 = 0, ET_F16, ET_BF16, ET_I8, ET_I4, ET_I32, ET_E4M3, ET_E5M2, ET_E2M1, ET_E8M0, ET_U8, ET_NONE = -1
+};
+
+__host__ __device__ inline int elem_bits(int t) {
+    switch (t) {
+        case ET_F32: case ET_I32: return 32;
+        case ET_F16: case ET_BF16: return 16;
+        case ET_I4: case ET_E2M1: return 4;
+        default: return 8;
+    }
+}
+
+enum Epilogue : int {
+    EPI_PLAIN = 0,   // out = acc (+ bias[n])                          (weight-only and MX matmuls)
+    EPI_DEQ_I32,     // out = float(acc + bias_i32[n]) * scale[n] (* pertoken[m])   (W8A8)
+    EPI_RAW_I32,     // out = acc (int32)                              (W8A8 accumulator dump)
+};
+
+// One matmul problem: out[b][M,N] = A[b][M,K] (x) B[b][K,N] with the dequantisation rules of the
+// operator family selected by the element types.
+struct MatmulArgs {
+    const void *a = nullptr;       // [M,K] row-major
+    const void *b = nullptr;       // [K,N] row-major (or [N,K] when b_transposed)
+    void *out = nullptr;           // [M,N] row-major
+    int a_type = ET_NONE, b_type = ET_NONE, out_type = ET_NONE;
+    // weight-only: scale/offset [G,N] of sc_type, G = K/group.  W8A8: scale [N] of sc_type.
+    const void *scale = nullptr;
+    const void *offset = nullptr;
+    int sc_type = ET_NONE;
+    // MX: a_scale [M,K/32], b_scale [K/32,N], e8m0 bytes.
+    const uint8_t *a_scale = nullptr;
+    const uint8_t *b_scale = nullptr;
+    const void *bias = nullptr;    // [N]; bias_type ET_I32 for W8A8, activation type otherwise
+    int bias_type = ET_NONE;
+    const float *pertoken = nullptr;  // [M] fp32 (W8A8)
+    int epilogue = EPI_PLAIN;
+    int64_t batch = 1, M = 0, N = 0, K = 0, group = 0;
+    int64_t a_batch_stride = 0, b_batch_stride = 0, out_batch_stride = 0;  // elements
+    bool b_transposed = false;
+    bool accumulate = false;       // out = T(float(out) + float(T(result)))
+    int split_k = 1;
+    void *workspace = nullptr;
+    uint64_t workspace_bytes = 0;
+};
+
+// Generic CUDA-core tile kernel: any shape, any supported type mix.  No workspace.
+cudaError_t launch_generic(const MatmulArgs &p, cudaStream_t s);
+
+// Streaming decode kernel for weight-only matmul at M <= gemv_max_m(): split-K over the grid,
+// fp32 partials in `workspace`, reduced by a second kernel that applies bias and the output cast.
+int gemv_max_m();
+bool gemv_supported(const MatmulArgs &p);
+int gemv_pick_split_k(const MatmulArgs &p);
+uint64_t gemv_workspace_bytes(const MatmulArgs &p);
+cudaError_t launch_gemv(const MatmulArgs &p, cudaStream_t s);
+
+// tcgen05 tensor-core kernel family.
+bool tc_supported(const MatmulArgs &p);
+void tc_plan(MatmulArgs &p);                 // fills split_k
+uint64_t tc_workspace_bytes(const MatmulArgs &p);
+cudaError_t launch_tc(const MatmulArgs &p, cudaStream_t s);
+
+// Host-side tally of kernels this library has launched (diagnostics for benchmarks).
+void count_launch(int n = 1);
+uint64_t launch_count();
+
+// Small element-wise helpers.
+cudaError_t launch_int4_pack(const int8_t *in, uint8_t *out, int64_t n_out, cudaStream_t s);
+cudaError_t launch_fill_i64(int64_t *out, int64_t value, cudaStream_t s);
+cudaError_t launch_cast(const void *in, int in_type, void *out, int out_type, int64_t n, cudaStream_t s);
+
+}  // namespace qmm

@@ -1,0 +1,409 @@
+// The aclnn two-phase operator surface of the quantized-matmul family: argument validation, plan
+// construction (kernel path, split-K, workspace bytes) and execution on the caller's stream.
+//
+// Call contract follows the reference (cuda/src/ops/matmul.cu:758-859, cuda/src/ops/quant.cu:196-326):
+// phase 1 is host-only and returns 161001 for null arguments and 161002 for unsupported types or
+// shapes; phase 2 enqueues on the stream, never synchronises or allocates, reports launch errors as
+// 361001 and consumes the executor.
+#include <cstring>
+#include <new>
+
+#include "aclnnop/aclnn_quant_matmul.h"
+#include "executor.h"
+#include "kernels.h"
+
+using namespace qmm;
+
+namespace {
+
+int elem_type(aclDataType t) {
+    switch (t) {
+        case ACL_FLOAT: return ET_F32;
+        case ACL_FLOAT16: return ET_F16;
+        case ACL_BF16: return ET_BF16;
+        case ACL_INT8: return ET_I8;
+        case ACL_UINT8: return ET_U8;
+        case ACL_INT4: return ET_I4;
+        case ACL_INT32: return ET_I32;
+        case ACL_FLOAT8_E4M3FN: return ET_E4M3;
+        case ACL_FLOAT8_E5M2: return ET_E5M2;
+        case ACL_FLOAT4_E2M1: return ET_E2M1;
+        case ACL_FLOAT8_E8M0: return ET_E8M0;
+        default: return ET_NONE;
+    }
+}
+bool is_float_act(aclDataType t) { return t == ACL_FLOAT || t == ACL_FLOAT16 || t == ACL_BF16; }
+
+// Path override for A/B measurements: B200_QMM_PATH=generic|gemv|tc (unset = automatic).
+int forced_path() {
+    const char *e = getenv("B200_QMM_PATH");
+    if (!e) return -1;
+    if (!strcmp(e, "generic")) return PATH_GENERIC;
+    if (!strcmp(e, "gemv")) return PATH_GEMV;
+    if (!strcmp(e, "tc")) return PATH_TC;
+    return -1;
+}
+bool debug_on() {
+    static const bool on = getenv("B200_QMM_DBG") != nullptr;
+    return on;
+}
+
+const void *data_of(const aclTensor *t) {
+    if (!t || !t->data) return nullptr;
+    // Sub-byte tensors cannot carry an odd element offset; validated in phase 1.
+    return (const char *)t->data + t->offset * (int64_t)elem_bits(elem_type(t->dtype)) / 8;
+}
+
+// MatmulArgs of a plan with the tensors' current data pointers.
+MatmulArgs args_of(const aclOpExecutor *e, void *ws, uint64_t ws_bytes) {
+    MatmulArgs p;
+    p.a = data_of(e->a); p.b = data_of(e->b); p.out = const_cast<void *>(data_of(e->out));
+    p.a_type = elem_type(e->a->dtype); p.b_type = elem_type(e->b->dtype); p.out_type = elem_type(e->out->dtype);
+    p.batch = e->batch; p.M = e->m; p.N = e->n; p.K = e->k; p.group = e->group;
+    p.a_batch_stride = e->m * e->k; p.b_batch_stride = e->k * e->n; p.out_batch_stride = e->m * e->n;
+    p.b_transposed = e->b_transposed; p.accumulate = e->accumulate;
+    p.split_k = e->split_k; p.workspace = ws; p.workspace_bytes = ws_bytes;
+    if (e->bias) { p.bias = data_of(e->bias); p.bias_type = elem_type(e->bias->dtype); }
+    switch (e->op) {
+        case PLAN_WQBMM:
+            p.epilogue = EPI_PLAIN;
+            p.scale = data_of(e->scale); p.sc_type = elem_type(e->scale->dtype);
+            p.offset = e->scale2 ? data_of(e->scale2) : nullptr;
+            break;
+        case PLAN_QMM:
+            if (e->scale) {
+                p.epilogue = EPI_DEQ_I32;
+                p.scale = data_of(e->scale); p.sc_type = elem_type(e->scale->dtype);
+                p.pertoken = e->pertoken ? (const float *)data_of(e->pertoken) : nullptr;
+            } else {
+                p.epilogue = EPI_RAW_I32;
+            }
+            break;
+        case PLAN_MX:
+            p.epilogue = EPI_PLAIN;
+            p.a_scale = (const uint8_t *)data_of(e->scale);
+            p.b_scale = (const uint8_t *)data_of(e->scale2);
+            break;
+        default: break;
+    }
+    return p;
+}
+
+// Chooses the kernel family for a plan and sizes its workspace.
+void choose_path(aclOpExecutor *e, uint64_t *ws) {
+    MatmulArgs p = args_of(e, nullptr, 0);
+    int want = forced_path();
+    e->path = PATH_GENERIC; e->split_k = 1; e->ws_bytes = 0;
+    const bool tc_ok = tc_supported(p), gemv_ok = gemv_supported(p);
+    if (want == PATH_TC && tc_ok) e->path = PATH_TC;
+    else if (want == PATH_GEMV && gemv_ok) e->path = PATH_GEMV;
+    else if (want == PATH_GENERIC) e->path = PATH_GENERIC;
+    else if (gemv_ok && e->m <= 2) e->path = PATH_GEMV;
+    else if (tc_ok) e->path = PATH_TC;
+    else if (gemv_ok) e->path = PATH_GEMV;
+    if (e->path == PATH_GEMV) {
+        p.split_k = e->split_k = gemv_pick_split_k(p);
+        e->ws_bytes = gemv_workspace_bytes(p);
+    } else if (e->path == PATH_TC) {
+        tc_plan(p);
+        e->split_k = p.split_k;
+        e->ws_bytes = tc_workspace_bytes(p);
+    }
+    *ws = e->ws_bytes;
+    if (debug_on())
+        fprintf(stderr, "[b200-qmm] op=%d M=%ld N=%ld K=%ld group=%ld path=%d split_k=%d ws=%lu\n", (int)e->op, (long)e->m,
+                (long)e->n, (long)e->k, (long)e->group, (int)e->path, e->split_k, (unsigned long)e->ws_bytes);
+}
+
+aclnnStatus run_matmul(void *ws, uint64_t ws_bytes, aclOpExecutor *e, aclrtStream stream) {
+    if (!e) return ACLNN_ERR_PARAM_NULLPTR;
+    aclnnStatus st = ACLNN_SUCCESS;
+    if (e->ws_bytes > 0 && (!ws || ws_bytes < e->ws_bytes)) {
+        st = ACLNN_ERR_PARAM_INVALID;  // undersized workspace is rejected before anything is launched
+    } else {
+        MatmulArgs p = args_of(e, ws, ws_bytes);
+        if (!p.a || !p.b || !p.out) st = ACLNN_ERR_PARAM_NULLPTR;
+        else {
+            cudaStream_t s = (cudaStream_t)stream;
+            cudaError_t err;
+            switch (e->path) {
+                case PATH_GEMV: err = launch_gemv(p, s); break;
+                case PATH_TC: err = launch_tc(p, s); break;
+                default: err = launch_generic(p, s); break;
+            }
+            if (err != cudaSuccess) {
+                fprintf(stderr, "[b200-qmm] launch failed: %s\n", cudaGetErrorString(err));
+                st = ACLNN_ERR_RUNTIME_ERROR;
+            }
+        }
+    }
+    delete e;
+    return st;
+}
+
+bool shape_is(const aclTensor *t, std::initializer_list<int64_t> dims) {
+    if (t->viewDims.size() != dims.size()) return false;
+    size_t i = 0;
+    for (auto d : dims) if (t->viewDims[i++] != d) return false;
+    return true;
+}
+bool dense(const aclTensor *t) { return t->contiguous(); }
+
+// ---- weight-only quantized matmul ------------------------------------------------------------------
+aclnnStatus wqbmm_plan(const aclTensor *x, const aclTensor *weight, const aclTensor *scale, const aclTensor *offset,
+                       const aclTensor *bias, int64_t groupSize, aclTensor *out, uint64_t *ws, aclOpExecutor **ex) {
+    if (!x || !weight || !scale || !out || !ws || !ex) return ACLNN_ERR_PARAM_NULLPTR;
+    if (!is_float_act(x->dtype) || out->dtype != x->dtype) return ACLNN_ERR_PARAM_INVALID;
+    if (weight->dtype != ACL_INT8 && weight->dtype != ACL_INT4) return ACLNN_ERR_PARAM_INVALID;
+    if (scale->dtype != x->dtype || (offset && offset->dtype != x->dtype) || (bias && bias->dtype != x->dtype))
+        return ACLNN_ERR_PARAM_INVALID;
+    if (x->rank() != 2 || weight->rank() != 2 || out->rank() != 2) return ACLNN_ERR_PARAM_INVALID;
+    const int64_t M = x->viewDims[0], K = x->viewDims[1], N = weight->viewDims[1];
+    if (weight->viewDims[0] != K || !shape_is(out, {M, N}) || K <= 0 || N <= 0 || M < 0) return ACLNN_ERR_PARAM_INVALID;
+    int64_t G = 1;
+    if (scale->rank() == 1) { if (scale->viewDims[0] != N) return ACLNN_ERR_PARAM_INVALID; }
+    else if (scale->rank() == 2) { G = scale->viewDims[0]; if (scale->viewDims[1] != N || G <= 0 || K % G != 0) return ACLNN_ERR_PARAM_INVALID; }
+    else return ACLNN_ERR_PARAM_INVALID;
+    if (offset && offset->viewDims != scale->viewDims) return ACLNN_ERR_PARAM_INVALID;
+    if (bias && !shape_is(bias, {N})) return ACLNN_ERR_PARAM_INVALID;
+    if (groupSize < 0 || (groupSize > 0 && G > 1 && groupSize != K / G)) return ACLNN_ERR_PARAM_INVALID;
+    if (groupSize > 0 && G == 1 && groupSize < K) return ACLNN_ERR_PARAM_INVALID;
+    if (weight->dtype == ACL_INT4 && (((K * N) & 1) || (weight->offset & 1))) return ACLNN_ERR_PARAM_INVALID;
+    for (const aclTensor *t : {x, weight, scale, offset, bias, (const aclTensor *)out})
+        if (t && !dense(t)) return ACLNN_ERR_PARAM_INVALID;
+    auto *e = new (std::nothrow) aclOpExecutor();
+    if (!e) return ACLNN_ERR_RUNTIME_ERROR;
+    e->op = PLAN_WQBMM; e->a = x; e->b = weight; e->scale = scale; e->scale2 = offset; e->bias = bias; e->out = out;
+    e->m = M; e->n = N; e->k = K; e->group = K / G;
+    choose_path(e, ws);
+    *ex = e;
+    return ACLNN_SUCCESS;
+}
+
+// ---- W8A8 quantized matmul -------------------------------------------------------------------------
+struct QmmOpts { bool transposed = false, accumulate = false, batched = false; };
+
+aclnnStatus qmm_plan(const aclTensor *x, const aclTensor *weight, const aclTensor *scale, const aclTensor *pertoken,
+                     const aclTensor *bias, aclTensor *out, QmmOpts o, uint64_t *ws, aclOpExecutor **ex) {
+    if (!x || !weight || !out || !ws || !ex) return ACLNN_ERR_PARAM_NULLPTR;
+    if (!scale && out->dtype != ACL_INT32) return ACLNN_ERR_PARAM_NULLPTR;
+    if (x->dtype != ACL_INT8 || weight->dtype != ACL_INT8) return ACLNN_ERR_PARAM_INVALID;
+    if (scale && (!is_float_act(scale->dtype) || !is_float_act(out->dtype))) return ACLNN_ERR_PARAM_INVALID;
+    if (!scale && (pertoken || o.accumulate)) return ACLNN_ERR_PARAM_INVALID;
+    if (pertoken && pertoken->dtype != ACL_FLOAT) return ACLNN_ERR_PARAM_INVALID;
+    if (bias && bias->dtype != ACL_INT32) return ACLNN_ERR_PARAM_INVALID;
+    int64_t B = 1, M, K, N;
+    if (o.batched) {
+        if (x->rank() != 3 || weight->rank() != 3 || out->rank() != 3) return ACLNN_ERR_PARAM_INVALID;
+        B = x->viewDims[0]; M = x->viewDims[1]; K = x->viewDims[2]; N = weight->viewDims[2];
+        if (weight->viewDims[0] != B || weight->viewDims[1] != K || !shape_is(out, {B, M, N})) return ACLNN_ERR_PARAM_INVALID;
+    } else {
+        if (x->rank() != 2 || weight->rank() != 2 || out->rank() != 2) return ACLNN_ERR_PARAM_INVALID;
+        M = x->viewDims[0]; K = x->viewDims[1];
+        N = o.transposed ? weight->viewDims[0] : weight->viewDims[1];
+        if ((o.transposed ? weight->viewDims[1] : weight->viewDims[0]) != K || !shape_is(out, {M, N})) return ACLNN_ERR_PARAM_INVALID;
+    }
+    if (K <= 0 || N <= 0 || M < 0 || B <= 0) return ACLNN_ERR_PARAM_INVALID;
+    if (scale && !shape_is(scale, {N})) return ACLNN_ERR_PARAM_INVALID;
+    if (pertoken && !shape_is(pertoken, {M})) return ACLNN_ERR_PARAM_INVALID;
+    if (bias && !shape_is(bias, {N})) return ACLNN_ERR_PARAM_INVALID;
+    // int32 accumulation is exact while K * 128 * 128 stays below 2^31.
+    if (K > 131071) return ACLNN_ERR_PARAM_INVALID;
+    for (const aclTensor *t : {x, weight, scale, pertoken, bias, (const aclTensor *)out})
+        if (t && !dense(t)) return ACLNN_ERR_PARAM_INVALID;
+    auto *e = new (std::nothrow) aclOpExecutor();
+    if (!e) return ACLNN_ERR_RUNTIME_ERROR;
+    e->op = PLAN_QMM; e->a = x; e->b = weight; e->scale = scale; e->pertoken = pertoken; e->bias = bias; e->out = out;
+    e->batch = B; e->m = M; e->n = N; e->k = K; e->group = K;
+    e->b_transposed = o.transposed; e->accumulate = o.accumulate;
+    choose_path(e, ws);
+    *ex = e;
+    return ACLNN_SUCCESS;
+}
+
+// ---- MX block-scaled matmul ------------------------------------------------------------------------
+bool is_mx_operand(aclDataType t) { return t == ACL_FLOAT8_E4M3FN || t == ACL_FLOAT8_E5M2 || t == ACL_FLOAT4_E2M1; }
+
+aclnnStatus mx_plan(const aclTensor *self, const aclTensor *selfScale, const aclTensor *other, const aclTensor *otherScale,
+                    aclTensor *out, uint64_t *ws, aclOpExecutor **ex) {
+    if (!self || !selfScale || !other || !otherScale || !out || !ws || !ex) return ACLNN_ERR_PARAM_NULLPTR;
+    if (!self->data || !other->data || !selfScale->data || !otherScale->data || !out->data) return ACLNN_ERR_PARAM_NULLPTR;
+    if (!is_mx_operand(self->dtype) || !is_mx_operand(other->dtype)) return ACLNN_ERR_PARAM_INVALID;
+    if (selfScale->dtype != ACL_FLOAT8_E8M0 || otherScale->dtype != ACL_FLOAT8_E8M0) return ACLNN_ERR_PARAM_INVALID;
+    if (!is_float_act(out->dtype)) return ACLNN_ERR_PARAM_INVALID;
+    if (self->rank() != 2 || other->rank() != 2 || out->rank() != 2) return ACLNN_ERR_PARAM_INVALID;
+    const int64_t M = self->viewDims[0], K = self->viewDims[1], N = other->viewDims[1];
+    if (other->viewDims[0] != K || !shape_is(out, {M, N}) || K <= 0 || N <= 0 || M < 0) return ACLNN_ERR_PARAM_INVALID;
+    if (K % 32 != 0) return ACLNN_ERR_PARAM_INVALID;
+    if (!shape_is(selfScale, {M, K / 32}) || !shape_is(otherScale, {K / 32, N})) return ACLNN_ERR_PARAM_INVALID;
+    if (other->dtype == ACL_FLOAT4_E2M1 && (N & 1)) return ACLNN_ERR_PARAM_INVALID;
+    if ((self->dtype == ACL_FLOAT4_E2M1 && (self->offset & 1)) || (other->dtype == ACL_FLOAT4_E2M1 && (other->offset & 1)))
+        return ACLNN_ERR_PARAM_INVALID;
+    for (const aclTensor *t : {self, selfScale, other, otherScale, (const aclTensor *)out})
+        if (!dense(t)) return ACLNN_ERR_PARAM_INVALID;
+    auto *e = new (std::nothrow) aclOpExecutor();
+    if (!e) return ACLNN_ERR_RUNTIME_ERROR;
+    e->op = PLAN_MX; e->a = self; e->b = other; e->scale = selfScale; e->scale2 = otherScale; e->out = out;
+    e->m = M; e->n = N; e->k = K; e->group = 32;
+    choose_path(e, ws);
+    *ex = e;
+    return ACLNN_SUCCESS;
+}
+
+aclnnStatus run_simple(aclOpExecutor *e, aclrtStream stream) {
+    if (!e) return ACLNN_ERR_PARAM_NULLPTR;
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t err = cudaSuccess;
+    switch (e->op) {
+        case PLAN_INT4_PACK:
+            err = launch_int4_pack((const int8_t *)data_of(e->a), (uint8_t *)const_cast<void *>(data_of(e->out)), e->n, s);
+            break;
+        case PLAN_COPY:
+            err = cudaMemcpyAsync(const_cast<void *>(data_of(e->out)), data_of(e->a), (size_t)e->n, cudaMemcpyDeviceToDevice, s);
+            break;
+        case PLAN_WEIGHT_SIZE:
+            err = launch_fill_i64((int64_t *)const_cast<void *>(data_of(e->out)), e->n, s);
+            break;
+        case PLAN_CAST:
+            err = launch_cast(data_of(e->a), elem_type(e->a->dtype), const_cast<void *>(data_of(e->out)), elem_type(e->cast_to),
+                              e->n, s);
+            break;
+        default: err = cudaErrorInvalidValue;
+    }
+    delete e;
+    return err == cudaSuccess ? ACLNN_SUCCESS : ACLNN_ERR_RUNTIME_ERROR;
+}
+
+}  // namespace
+
+extern "C" {
+
+uint64_t aclnnB200KernelLaunchCount(void) { return qmm::launch_count(); }
+
+#define RUN_MATMUL(NAME) \
+    aclnnStatus NAME(void *ws, uint64_t wsz, aclOpExecutor *e, aclrtStream s) { return run_matmul(ws, wsz, e, s); }
+
+#define WQBMM_ALIAS(NAME)                                                                                             \
+    aclnnStatus NAME##GetWorkspaceSize(const aclTensor *x, const aclTensor *weight, const aclTensor *antiquantScale, \
+                                       const aclTensor *antiquantOffset, aclTensor *out, uint64_t *ws, aclOpExecutor **ex) { \
+        return wqbmm_plan(x, weight, antiquantScale, antiquantOffset, nullptr, 0, out, ws, ex);                       \
+    }                                                                                                                 \
+    RUN_MATMUL(NAME)
+WQBMM_ALIAS(aclnnWeightQuantBatchMatmul)
+WQBMM_ALIAS(aclnnWeightQuantBatchMatmulV2)
+WQBMM_ALIAS(aclnnWeightQuantBatchMatmulV3)
+WQBMM_ALIAS(aclnnWeightQuantBatchMatmulNz)
+
+aclnnStatus aclnnWeightQuantBatchMatmulV2ExGetWorkspaceSize(const aclTensor *x, const aclTensor *weight,
+        const aclTensor *antiquantScale, const aclTensor *antiquantOffsetOptional, const aclTensor *biasOptional,
+        int64_t antiquantGroupSize, aclTensor *out, uint64_t *ws, aclOpExecutor **ex) {
+    return wqbmm_plan(x, weight, antiquantScale, antiquantOffsetOptional, biasOptional, antiquantGroupSize, out, ws, ex);
+}
+RUN_MATMUL(aclnnWeightQuantBatchMatmulV2Ex)
+
+#define QMM_ALIAS(NAME, OPTS)                                                                                        \
+    aclnnStatus NAME##GetWorkspaceSize(const aclTensor *x, const aclTensor *weight, const aclTensor *scale,          \
+                                       aclTensor *out, uint64_t *ws, aclOpExecutor **ex) {                           \
+        if (!scale) return ACLNN_ERR_PARAM_NULLPTR;                                                                  \
+        return qmm_plan(x, weight, scale, nullptr, nullptr, out, OPTS, ws, ex);                                      \
+    }                                                                                                                \
+    RUN_MATMUL(NAME)
+QMM_ALIAS(aclnnQuantMatmul, QmmOpts{})
+QMM_ALIAS(aclnnQuantMatmulV2, QmmOpts{})
+QMM_ALIAS(aclnnQuantMatmulV3, QmmOpts{})
+QMM_ALIAS(aclnnQuantMatmulV4, QmmOpts{})
+QMM_ALIAS(aclnnQuantMatmulV5, QmmOpts{})
+QMM_ALIAS(aclnnQuantMatmulDequant, QmmOpts{})
+QMM_ALIAS(aclnnQuantMatmulWeightNz, QmmOpts{})
+QMM_ALIAS(aclnnFusedQuantMatmul, QmmOpts{})
+QMM_ALIAS(aclnnFusedQuantMatmulWeightNz, QmmOpts{})
+QMM_ALIAS(aclnnMatmulCompressDequant, QmmOpts{})
+QMM_ALIAS(aclnnSparse4to2QuantMatmulWeightNz, QmmOpts{})
+QMM_ALIAS(aclnnDualLevelQuantMatmulWeightNz, QmmOpts{})
+QMM_ALIAS(aclnnQuantBatchMatmulInplaceAdd, (QmmOpts{false, true, false}))
+QMM_ALIAS(aclnnTransposeQuantBatchMatMul, (QmmOpts{true, false, false}))
+QMM_ALIAS(aclnnBatchMatmulQuant, (QmmOpts{false, false, true}))
+
+aclnnStatus aclnnQuantMatmulV4ExGetWorkspaceSize(const aclTensor *x1, const aclTensor *x2, const aclTensor *scale,
+        const aclTensor *offsetOptional, const aclTensor *pertokenScaleOptional, const aclTensor *biasOptional,
+        aclTensor *out, uint64_t *ws, aclOpExecutor **ex) {
+    if (offsetOptional) return ACLNN_ERR_PARAM_INVALID;
+    return qmm_plan(x1, x2, scale, pertokenScaleOptional, biasOptional, out, QmmOpts{}, ws, ex);
+}
+RUN_MATMUL(aclnnQuantMatmulV4Ex)
+
+#define MX_ALIAS(NAME)                                                                                               \
+    aclnnStatus NAME##GetWorkspaceSize(const aclTensor *self, const aclTensor *selfScale, const aclTensor *other,    \
+                                       const aclTensor *otherScale, aclTensor *out, uint64_t *ws, aclOpExecutor **ex) { \
+        return mx_plan(self, selfScale, other, otherScale, out, ws, ex);                                             \
+    }                                                                                                                \
+    RUN_MATMUL(NAME)
+MX_ALIAS(aclnnMatmulMxFp8)
+MX_ALIAS(aclnnMatmulMxFp8Hw)
+MX_ALIAS(aclnnMatmulMxFp4)
+MX_ALIAS(aclnnMatmulMxFp4Hw)
+
+#define RUN_SIMPLE(NAME) \
+    aclnnStatus NAME(void *, uint64_t, aclOpExecutor *e, aclrtStream s) { return run_simple(e, s); }
+
+aclnnStatus aclnnConvertWeightToINT4PackGetWorkspaceSize(const aclTensor *weight, aclTensor *out, uint64_t *ws, aclOpExecutor **ex) {
+    if (!weight || !out || !ws || !ex) return ACLNN_ERR_PARAM_NULLPTR;
+    if (!weight->data || !out->data) return ACLNN_ERR_PARAM_NULLPTR;
+    if (weight->dtype != ACL_INT8 || !dense(weight) || !dense(out)) return ACLNN_ERR_PARAM_INVALID;
+    if (weight->numel() & 1) return ACLNN_ERR_PARAM_INVALID;
+    // out holds numel/2 bytes: an int8/uint8 tensor of half the elements, or an ACL_INT4 tensor of all of them.
+    const int64_t n_out = weight->numel() / 2;
+    const int64_t out_bytes = out->dtype == ACL_INT4 ? out->numel() / 2 : out->numel() * (int64_t)dtype_size(out->dtype);
+    if (out_bytes != n_out) return ACLNN_ERR_PARAM_INVALID;
+    auto *e = new aclOpExecutor();
+    e->op = PLAN_INT4_PACK; e->a = weight; e->out = out; e->n = n_out;
+    *ws = 0; *ex = e;
+    return ACLNN_SUCCESS;
+}
+RUN_SIMPLE(aclnnConvertWeightToINT4Pack)
+
+aclnnStatus aclnnTransMatmulWeightGetWorkspaceSize(const aclTensor *weight, aclTensor *out, uint64_t *ws, aclOpExecutor **ex) {
+    if (!weight || !out || !ws || !ex) return ACLNN_ERR_PARAM_NULLPTR;
+    if (!weight->data || !out->data) return ACLNN_ERR_PARAM_NULLPTR;
+    if (weight->dtype != out->dtype || weight->numel() != out->numel() || !dense(weight) || !dense(out)) return ACLNN_ERR_PARAM_INVALID;
+    auto *e = new aclOpExecutor();
+    e->op = PLAN_COPY; e->a = weight; e->out = out;
+    e->n = (weight->numel() * elem_bits(elem_type(weight->dtype)) + 7) / 8;
+    *ws = 0; *ex = e;
+    return ACLNN_SUCCESS;
+}
+RUN_SIMPLE(aclnnTransMatmulWeight)
+
+static aclnnStatus weight_size_plan(const aclIntArray *shape, aclTensor *out, uint64_t *ws, aclOpExecutor **ex) {
+    if (!shape || !out || !ws || !ex) return ACLNN_ERR_PARAM_NULLPTR;
+    if (!out->data) return ACLNN_ERR_PARAM_NULLPTR;
+    if (out->dtype != ACL_INT64 || out->numel() < 1) return ACLNN_ERR_PARAM_INVALID;
+    auto *e = new aclOpExecutor();
+    e->op = PLAN_WEIGHT_SIZE; e->out = out; e->n = 1;
+    for (auto d : shape->v) e->n *= d;
+    *ws = 0; *ex = e;
+    return ACLNN_SUCCESS;
+}
+aclnnStatus aclnnCalculateMatmulWeightSizeGetWorkspaceSize(const aclIntArray *weightShape, aclTensor *out, uint64_t *ws, aclOpExecutor **ex) {
+    return weight_size_plan(weightShape, out, ws, ex);
+}
+RUN_SIMPLE(aclnnCalculateMatmulWeightSize)
+aclnnStatus aclnnCalculateMatmulWeightSizeV2GetWorkspaceSize(const aclIntArray *weightShape, int64_t, aclTensor *out, uint64_t *ws, aclOpExecutor **ex) {
+    return weight_size_plan(weightShape, out, ws, ex);
+}
+RUN_SIMPLE(aclnnCalculateMatmulWeightSizeV2)
+
+aclnnStatus aclnnCastGetWorkspaceSize(const aclTensor *self, aclDataType dtype, aclTensor *out, uint64_t *ws, aclOpExecutor **ex) {
+    if (!self || !out || !ws || !ex) return ACLNN_ERR_PARAM_NULLPTR;
+    if (out->dtype != dtype || self->viewDims != out->viewDims) return ACLNN_ERR_PARAM_INVALID;
+    if (!dense(self) || !dense(out)) return ACLNN_ERR_PARAM_INVALID;
+    const int st = elem_type(self->dtype), dt = elem_type(dtype);
+    if (st == ET_NONE || dt == ET_NONE || st == ET_I4 || dt == ET_I4 || dt == ET_E8M0) return ACLNN_ERR_PARAM_INVALID;
+    auto *e = new aclOpExecutor();
+    e->op = PLAN_CAST; e->a = self; e->out = out; e->cast_to = dtype; e->n = self->numel();
+    *ws = 0; *ex = e;
+    return ACLNN_SUCCESS;
+}
+RUN_SIMPLE(aclnnCast)
+
+}  // extern "C"

@@ -1,0 +1,149 @@
+/*
+ * aclnn_quant_matmul.h -- the quantized-matmul family of the aclnn two-phase operator ABI,
+ * implemented with hand-written sm_100a kernels.
+ *
+ * Every operator is a pair
+ *     aclnnStatus aclnnXxxGetWorkspaceSize(<tensors...>, uint64_t *workspaceSize, aclOpExecutor **executor);
+ *     aclnnStatus aclnnXxx(void *workspace, uint64_t workspaceSize, aclOpExecutor *executor, aclrtStream stream);
+ * Phase 1 runs on the host only, validates, and returns the scratch bytes the caller must provide.
+ * Phase 2 enqueues kernels on `stream` (a cudaStream_t), never synchronises or allocates, and
+ * consumes the executor (one executor = one launch).  Status codes: 0 ok, 161001 null pointer,
+ * 161002 invalid parameter, 361001 runtime error.
+ *
+ * Each declaration cites the reference interface it replaces (paths inside Cryspia/cann-on-gpu).
+ */
+#ifndef B200_ACLNN_QUANT_MATMUL_H
+#define B200_ACLNN_QUANT_MATMUL_H
+
+#include "aclnn/acl_meta.h"
+
+/* aclnn status codes (same values as the reference's cuda/src/internal.h:16-19). */
+#ifndef ACLNN_SUCCESS
+#define ACLNN_SUCCESS 0
+#define ACLNN_ERR_PARAM_NULLPTR 161001
+#define ACLNN_ERR_PARAM_INVALID 161002
+#define ACLNN_ERR_RUNTIME_ERROR 361001
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_ACLNN_RUN(NAME) \
+    ACL_FUNC_VISIBILITY aclnnStatus NAME(void *workspace, uint64_t workspaceSize, aclOpExecutor *executor, aclrtStream stream);
+
+/* ---- Weight-only quantized matmul (W8A16 / W4A16) ---------------------------------------------
+ * out[M,N] = x[M,K] @ ((weight[K,N] - antiquantOffset) * antiquantScale)
+ * weight: ACL_INT8, or ACL_INT4 packed two per byte (linear index k*N+n; even index = low nibble,
+ * two's complement).  antiquantScale / antiquantOffset: [N] (per channel) or [K/g, N] (group-wise,
+ * g = K / rows).  x/out/scale/offset: ACL_FLOAT16, ACL_BF16 or ACL_FLOAT (all the same type).
+ * Replaces include/aclnnop/aclnn_ops.h:1041-1043 and the V2/V3 aliases at :1052-1062
+ * (implementation cuda/src/ops/matmul.cu:758-796, cuda/src/ops/quant.cu:216-223);
+ * ...Nz replaces cuda/src/ops/matmul.cu:1450-1454. */
+#define B200_ACLNN_WQBMM(NAME) \
+    ACL_FUNC_VISIBILITY aclnnStatus NAME##GetWorkspaceSize(const aclTensor *x, const aclTensor *weight, \
+        const aclTensor *antiquantScale, const aclTensor *antiquantOffset, aclTensor *out, \
+        uint64_t *workspaceSize, aclOpExecutor **executor); \
+    B200_ACLNN_RUN(NAME)
+B200_ACLNN_WQBMM(aclnnWeightQuantBatchMatmul)
+B200_ACLNN_WQBMM(aclnnWeightQuantBatchMatmulV2)
+B200_ACLNN_WQBMM(aclnnWeightQuantBatchMatmulV3)
+B200_ACLNN_WQBMM(aclnnWeightQuantBatchMatmulNz)
+
+/* Extended form: adds the optional bias [N] (same type as x) and an explicit group size
+ * (0 = infer from antiquantScale's shape).  The reference ABI has no slot for these
+ * (cuda/src/ops/matmul.cu:761-767 rejects them); the old names forward here with nulls. */
+ACL_FUNC_VISIBILITY aclnnStatus aclnnWeightQuantBatchMatmulV2ExGetWorkspaceSize(const aclTensor *x, const aclTensor *weight,
+    const aclTensor *antiquantScale, const aclTensor *antiquantOffsetOptional, const aclTensor *biasOptional,
+    int64_t antiquantGroupSize, aclTensor *out, uint64_t *workspaceSize, aclOpExecutor **executor);
+B200_ACLNN_RUN(aclnnWeightQuantBatchMatmulV2Ex)
+
+/* ---- W8A8 quantized matmul ----------------------------------------------------------------------
+ * acc[M,N] = int32( x[M,K] int8 @ weight[K,N] int8 )            (exact)
+ * out      = T( float(acc) * scale[n] )                          (reference epilogue, matmul.cu:327-330)
+ * scale: [N], ACL_FLOAT16 / ACL_BF16 / ACL_FLOAT.  out: ACL_FLOAT16 / ACL_BF16 / ACL_FLOAT.
+ * Replaces include/aclnnop/aclnn_ops.h:1044-1060 (cuda/src/ops/matmul.cu:799-859 and the aliases at
+ * cuda/src/ops/quant.cu:204-213,226-230; WeightNz cuda/src/ops/matmul.cu:1457-1461; Fused* and
+ * MatmulCompressDequant cuda/src/ops/matmul.cu:1156-1161; Sparse4to2* / DualLevel*
+ * include/aclnnop/aclnn_mc2.h:92-95). */
+#define B200_ACLNN_QMM(NAME) \
+    ACL_FUNC_VISIBILITY aclnnStatus NAME##GetWorkspaceSize(const aclTensor *x, const aclTensor *weight, \
+        const aclTensor *scale, aclTensor *out, uint64_t *workspaceSize, aclOpExecutor **executor); \
+    B200_ACLNN_RUN(NAME)
+B200_ACLNN_QMM(aclnnQuantMatmul)
+B200_ACLNN_QMM(aclnnQuantMatmulV2)
+B200_ACLNN_QMM(aclnnQuantMatmulV3)
+B200_ACLNN_QMM(aclnnQuantMatmulV4)
+B200_ACLNN_QMM(aclnnQuantMatmulV5)
+B200_ACLNN_QMM(aclnnQuantMatmulDequant)
+B200_ACLNN_QMM(aclnnQuantMatmulWeightNz)
+B200_ACLNN_QMM(aclnnFusedQuantMatmul)
+B200_ACLNN_QMM(aclnnFusedQuantMatmulWeightNz)
+B200_ACLNN_QMM(aclnnMatmulCompressDequant)
+B200_ACLNN_QMM(aclnnSparse4to2QuantMatmulWeightNz)
+B200_ACLNN_QMM(aclnnDualLevelQuantMatmulWeightNz)
+/* out += dequant(x @ weight, scale)  -- replaces aclnn_ops.h:1067-1069 (cuda/src/ops/quant.cu:273-299). */
+B200_ACLNN_QMM(aclnnQuantBatchMatmulInplaceAdd)
+/* weight given as [N,K]  -- replaces cuda/src/ops/quant.cu:303-326. */
+B200_ACLNN_QMM(aclnnTransposeQuantBatchMatMul)
+/* batched int8: self[B,M,K] @ other[B,K,N] * scale[N]  -- replaces aclnn_ops.h:1997-1998
+ * (cuda/src/ops/matmul.cu:1097-1149). */
+B200_ACLNN_QMM(aclnnBatchMatmulQuant)
+
+/* Extended form: out = T( float(acc + bias[n]) * scale[n] * pertokenScale[m] ).
+ * bias: ACL_INT32 [N] (added to the exact accumulator); pertokenScale: ACL_FLOAT [M];
+ * offsetOptional is accepted for signature compatibility and must be null.
+ * With scale == null and out of type ACL_INT32 the raw accumulators are written (the bit-exact
+ * check; on the reference they sit in the caller's workspace at byte offset N*K, matmul.cu:821). */
+ACL_FUNC_VISIBILITY aclnnStatus aclnnQuantMatmulV4ExGetWorkspaceSize(const aclTensor *x1, const aclTensor *x2,
+    const aclTensor *scale, const aclTensor *offsetOptional, const aclTensor *pertokenScaleOptional,
+    const aclTensor *biasOptional, aclTensor *out, uint64_t *workspaceSize, aclOpExecutor **executor);
+B200_ACLNN_RUN(aclnnQuantMatmulV4Ex)
+
+/* ---- MX block-scaled matmul ---------------------------------------------------------------------
+ * out[M,N] = sum_k self[m,k]*2^(selfScale[m,k/32]-127) * other[k,n]*2^(otherScale[k/32,n]-127)
+ * self [M,K], other [K,N]: fp8 e4m3/e5m2 (one byte each) or fp4 e2m1 (two per byte, element 0 =
+ * low nibble); the two operands may differ (MXFP8 x MXFP4).  Scales ACL_FLOAT8_E8M0.
+ * out: ACL_FLOAT16 / ACL_BF16 / ACL_FLOAT.  All four names run the same native kernels.
+ * Replaces include/aclnnop/aclnn_ops.h:1021-1038 (cuda/src/ops/matmul.cu:432-518,538-597,657-730). */
+#define B200_ACLNN_MX(NAME) \
+    ACL_FUNC_VISIBILITY aclnnStatus NAME##GetWorkspaceSize(const aclTensor *self, const aclTensor *selfScale, \
+        const aclTensor *other, const aclTensor *otherScale, aclTensor *out, \
+        uint64_t *workspaceSize, aclOpExecutor **executor); \
+    B200_ACLNN_RUN(NAME)
+B200_ACLNN_MX(aclnnMatmulMxFp8)
+B200_ACLNN_MX(aclnnMatmulMxFp8Hw)
+B200_ACLNN_MX(aclnnMatmulMxFp4)
+B200_ACLNN_MX(aclnnMatmulMxFp4Hw)
+
+/* ---- Weight pre-pack and test-support operators ------------------------------------------------ */
+/* Two int8 values in [-8,7] -> one byte (hi<<4 | lo&0xF), low nibble first.
+ * Replaces aclnn_ops.h:1790-1791 (cuda/src/ops/conv.cu:588-591,788-794). */
+ACL_FUNC_VISIBILITY aclnnStatus aclnnConvertWeightToINT4PackGetWorkspaceSize(const aclTensor *weight, aclTensor *out,
+    uint64_t *workspaceSize, aclOpExecutor **executor);
+B200_ACLNN_RUN(aclnnConvertWeightToINT4Pack)
+/* Weight copy into the on-device format (identity layout, like the reference) and its size query.
+ * Replaces aclnn_ops.h:2009-2014 (cuda/src/ops/matmul.cu:1162-1170). */
+ACL_FUNC_VISIBILITY aclnnStatus aclnnTransMatmulWeightGetWorkspaceSize(const aclTensor *weight, aclTensor *out,
+    uint64_t *workspaceSize, aclOpExecutor **executor);
+B200_ACLNN_RUN(aclnnTransMatmulWeight)
+ACL_FUNC_VISIBILITY aclnnStatus aclnnCalculateMatmulWeightSizeGetWorkspaceSize(const aclIntArray *weightShape, aclTensor *out,
+    uint64_t *workspaceSize, aclOpExecutor **executor);
+B200_ACLNN_RUN(aclnnCalculateMatmulWeightSize)
+ACL_FUNC_VISIBILITY aclnnStatus aclnnCalculateMatmulWeightSizeV2GetWorkspaceSize(const aclIntArray *weightShape, int64_t dtype,
+    aclTensor *out, uint64_t *workspaceSize, aclOpExecutor **executor);
+B200_ACLNN_RUN(aclnnCalculateMatmulWeightSizeV2)
+/* Element-wise cast between ACL_FLOAT and {fp16, bf16, fp8 e4m3/e5m2, fp4 e2m1, int8, int32}; the MX
+ * tests build their operands with it.  Replaces aclnn_ops.h:116-118 (cuda/src/ops/cast.cu:157-202). */
+ACL_FUNC_VISIBILITY aclnnStatus aclnnCastGetWorkspaceSize(const aclTensor *self, aclDataType dtype, aclTensor *out,
+    uint64_t *workspaceSize, aclOpExecutor **executor);
+B200_ACLNN_RUN(aclnnCast)
+
+/* Diagnostics (no counterpart in the reference): number of kernels this library has launched in the
+ * calling process so far.  Benchmarks use the difference around a timed region. */
+ACL_FUNC_VISIBILITY uint64_t aclnnB200KernelLaunchCount(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

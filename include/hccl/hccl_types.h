@@ -1,0 +1,58 @@
+/*
+ * hccl/hccl_types.h -- minimal, self-declared HCCL types used by the N-sharded matmul path
+ * (reference users: cuda/src/hccl.cu:1-60, include/hccl/hccl.h of the reference).
+ */
+#ifndef B200_HCCL_TYPES_H
+#define B200_HCCL_TYPES_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void *HcclComm;
+
+#define HCCL_ROOT_INFO_BYTES 4108
+typedef struct HcclRootInfoDef {
+    char internal[HCCL_ROOT_INFO_BYTES];
+} HcclRootInfo;
+
+typedef enum {
+    HCCL_SUCCESS = 0,
+    HCCL_E_PARA = 1,
+    HCCL_E_PTR = 2,
+    HCCL_E_MEMORY = 3,
+    HCCL_E_INTERNAL = 4,
+    HCCL_E_NOT_SUPPORT = 5,
+    HCCL_E_NOT_FOUND = 6,
+    HCCL_E_UNAVAIL = 7,
+    HCCL_E_NETWORK = 19
+} HcclResult;
+
+typedef enum {
+    HCCL_REDUCE_SUM = 0,
+    HCCL_REDUCE_PROD = 1,
+    HCCL_REDUCE_MAX = 2,
+    HCCL_REDUCE_MIN = 3
+} HcclReduceOp;
+
+typedef enum {
+    HCCL_DATA_TYPE_INT8 = 0,
+    HCCL_DATA_TYPE_INT16 = 1,
+    HCCL_DATA_TYPE_INT32 = 2,
+    HCCL_DATA_TYPE_FP16 = 3,
+    HCCL_DATA_TYPE_FP32 = 4,
+    HCCL_DATA_TYPE_INT64 = 5,
+    HCCL_DATA_TYPE_UINT64 = 6,
+    HCCL_DATA_TYPE_UINT8 = 7,
+    HCCL_DATA_TYPE_UINT16 = 8,
+    HCCL_DATA_TYPE_UINT32 = 9,
+    HCCL_DATA_TYPE_FP64 = 10,
+    HCCL_DATA_TYPE_BFP16 = 11
+} HcclDataType;
+
+#ifdef __cplusplus
+}
+#endif
+#endif

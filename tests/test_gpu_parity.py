@@ -1,0 +1,315 @@
+"""GPU parity tests: every operator of the family, through the C ABI, against the CPU checker on
+identical seeded inputs -- bit-exact for integer work, within the stated tolerance for fp outputs."""
+import ctypes
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from util import assert_close, dev_or_none, errors, f32, to_np
+
+pytestmark = pytest.mark.gpu
+
+
+class forced_path:
+    """Pin the kernel family (generic | gemv | tc) for the calls inside the block."""
+
+    def __init__(self, path):
+        self.path = path
+
+    def __enter__(self):
+        self.prev = os.environ.get("B200_QMM_PATH")
+        if self.path:
+            os.environ["B200_QMM_PATH"] = self.path
+        elif self.prev is not None:
+            del os.environ["B200_QMM_PATH"]
+
+    def __exit__(self, *a):
+        if self.prev is None:
+            os.environ.pop("B200_QMM_PATH", None)
+        else:
+            os.environ["B200_QMM_PATH"] = self.prev
+
+
+def run_wq(pkg, d, dev, name="aclnnWeightQuantBatchMatmulV2Ex"):
+    out = pkg.weight_quant_matmul(d["x"].to(dev), d["w"].to(dev), d["scale"].to(dev), dev_or_none(d["offset"], dev),
+                                  dev_or_none(d["bias"], dev), int4=d["int4"], group=d["group"], name=name)
+    torch.cuda.synchronize()
+    return out
+
+
+def ref_wq(oracle, d):
+    return oracle.wqbmm_fast(f32(d["x"]), d["w"].numpy(), d["int4"], f32(d["scale"]), f32(d["offset"]), f32(d["bias"]),
+                             d["M"], d["K"], d["N"], d["group"])
+
+
+# ------------------------------------------------------------------ weight-only quantized matmul
+@pytest.mark.parametrize("path", ["generic", "gemv", "tc", None])
+@pytest.mark.parametrize("M", [1, 2, 3, 4, 16, 128])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_w4a16_groupwise(pkg, oracle, workloads, dev, path, M, dtype):
+    d = workloads.w4a16(M=M, K=1024, N=512, group=128, dtype=dtype, seed=3000 + M)
+    with forced_path(path):
+        out = run_wq(pkg, d, dev)
+    assert_close(to_np(out), ref_wq(oracle, d), f"W4A16 g128 M={M} {dtype} path={path}")
+
+
+@pytest.mark.parametrize("path", ["generic", "gemv", "tc", None])
+@pytest.mark.parametrize("int4", [False, True])
+@pytest.mark.parametrize("M", [1, 4, 128])
+def test_wqmm_reference_test_shapes(pkg, oracle, workloads, dev, path, int4, M):
+    """The reference's t_wqmm cases (tests/test_matmul_conv.cpp:621-640,971-974): fp16, per-channel scale
+    0.02+0.01*(n%5), offset (n%3)-1, K=256, N=64; its tolerance is 2e-2, ours is tighter."""
+    K, N = 256, 64
+    d = (workloads.w4a16(M=M, K=K, N=N, dtype=torch.float16, per_channel=True, with_bias=False, seed=11) if int4
+         else workloads.w8a16(M=M, K=K, N=N, dtype=torch.float16, with_offset=True, seed=11))
+    n = torch.arange(N)
+    d["scale"] = (0.02 + 0.01 * (n % 5)).to(torch.float16)
+    d["offset"] = ((n % 3) - 1).to(torch.float16)
+    with forced_path(path):
+        out = run_wq(pkg, d, dev, name="aclnnWeightQuantBatchMatmul")
+    assert_close(to_np(out), ref_wq(oracle, d), f"t_wqmm int4={int4} M={M} path={path}")
+
+
+def test_config0_w8a16_full_size(pkg, oracle, workloads, dev):
+    d = workloads.w8a16()  # M=1, K=1024, N=3072, fp16, per-channel
+    for name in ("aclnnWeightQuantBatchMatmul", "aclnnWeightQuantBatchMatmulV2", "aclnnWeightQuantBatchMatmulV3",
+                 "aclnnWeightQuantBatchMatmulNz"):
+        out = run_wq(pkg, d, dev, name=name)
+        assert_close(to_np(out), ref_wq(oracle, d), name)
+
+
+@pytest.mark.parametrize("M", [1, 16, 128])
+def test_config1_w4a16_full_size(pkg, oracle, workloads, dev, M):
+    d = workloads.w4a16(M=M)  # K=4096, N=4096, g128, bf16, offset + bias
+    out = run_wq(pkg, d, dev)
+    assert_close(to_np(out), ref_wq(oracle, d), f"config1 M={M}")
+    # without the optional arguments
+    d2 = workloads.w4a16(M=M, with_offset=False, with_bias=False)
+    assert_close(to_np(run_wq(pkg, d2, dev)), ref_wq(oracle, d2), f"config1 no offset/bias M={M}")
+
+
+def test_wq_fp32_and_ragged_shapes(pkg, oracle, workloads, dev):
+    """fp32 activations (tests/test_quant_parity.cpp:405-413, tol 1e-4) and shapes off every tile size."""
+    for (M, K, N) in [(5, 8, 6), (3, 40, 50), (17, 72, 34)]:
+        d = workloads.w8a16(M=M, K=K, N=N, dtype=torch.float32, with_offset=True, seed=5)
+        out = run_wq(pkg, d, dev, name="aclnnWeightQuantBatchMatmulV2")
+        mx, _ = errors(to_np(out), ref_wq(oracle, d))
+        assert mx <= 1e-4, (M, K, N, mx)
+    d = workloads.w4a16(M=3, K=40, N=50, group=8, dtype=torch.float16, seed=6)
+    assert_close(to_np(run_wq(pkg, d, dev)), ref_wq(oracle, d), "ragged int4 g8")
+
+
+def test_empty_m(pkg, dev):
+    x = torch.empty((0, 64), dtype=torch.float16, device=dev)
+    w = torch.zeros((64, 32), dtype=torch.int8, device=dev)
+    sc = torch.ones(32, dtype=torch.float16, device=dev)
+    out = pkg.weight_quant_matmul(x, w, sc, name="aclnnWeightQuantBatchMatmul")
+    torch.cuda.synchronize()
+    assert out.shape == (0, 32)
+
+
+# ------------------------------------------------------------------ W8A8
+def ref_qmm(oracle, d, out_dtype):
+    acc = oracle.qmm_acc_fast(d["x"].numpy(), d["w"].numpy(), d["M"], d["K"], d["N"])
+    v = oracle.qmm_epilogue_fast(acc, f32(d["scale"]), f32(d["pertoken"]),
+                                 None if d["bias"] is None else d["bias"].numpy())
+    return acc, torch.from_numpy(v).to(out_dtype)
+
+
+@pytest.mark.parametrize("path", ["generic", "tc", None])
+@pytest.mark.parametrize("M", [1, 8, 100, 256])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_w8a8_bit_exact(pkg, oracle, workloads, dev, path, M, out_dtype):
+    d = workloads.w8a8(M=M, K=512, N=384, seed=4000 + M, out_dtype=out_dtype)
+    x, w = d["x"].to(dev), d["w"].to(dev)
+    with forced_path(path):
+        acc = pkg.quant_matmul(x, w, None)
+        out = pkg.quant_matmul(x, w, d["scale"].to(dev), d["pertoken"].to(dev), d["bias"].to(dev), out_dtype=out_dtype)
+    torch.cuda.synchronize()
+    ref_acc, ref_out = ref_qmm(oracle, d, out_dtype)
+    assert np.array_equal(acc.cpu().numpy(), ref_acc), "int32 accumulators must be bit-exact"
+    assert torch.equal(out.cpu(), ref_out), "epilogue is a fixed fp32 sequence: output must be bit-exact"
+
+
+def test_w8a8_aliases_and_reference_test_case(pkg, oracle, workloads, dev):
+    """t_qmm / t_qmm_v of the reference (tests/test_matmul_conv.cpp:641-673): M128 K256 N64, fp16 scale
+    0.001*(1+n%7), fp16 out; plus the parity-test shape M8 K16 N8 with fp32 out through every alias name
+    (tests/test_quant_parity.cpp:362-370,540-552)."""
+    names = ["aclnnQuantMatmul", "aclnnQuantMatmulV2", "aclnnQuantMatmulV3", "aclnnQuantMatmulV4", "aclnnQuantMatmulV5",
+             "aclnnQuantMatmulDequant", "aclnnQuantMatmulWeightNz", "aclnnFusedQuantMatmul", "aclnnFusedQuantMatmulWeightNz",
+             "aclnnMatmulCompressDequant", "aclnnSparse4to2QuantMatmulWeightNz", "aclnnDualLevelQuantMatmulWeightNz"]
+    for (M, K, N, odt) in [(128, 256, 64, torch.float16), (8, 16, 8, torch.float32)]:
+        d = workloads.w8a8(M=M, K=K, N=N, seed=11, with_pertoken=False, with_bias=False)
+        d["scale"] = (0.001 * (1 + torch.arange(N) % 7)).to(torch.float16)
+        _, ref_out = ref_qmm(oracle, d, odt)
+        for name in names:
+            out = pkg.quant_matmul(d["x"].to(dev), d["w"].to(dev), d["scale"].to(dev), out_dtype=odt, name=name)
+            torch.cuda.synchronize()
+            assert torch.equal(out.cpu(), ref_out), name
+
+
+def test_w8a8_wrappers(pkg, oracle, workloads, dev):
+    # out += dequant(x @ w): the product is rounded to the output type before the add, like the
+    # reference's temp buffer (cuda/src/ops/quant.cu:286-297); t_qmm_iadd shape 64x128x48.
+    d = workloads.w8a8(M=64, K=128, N=48, seed=12, with_pertoken=False, with_bias=False, scale_dtype=torch.float16)
+    _, prod = ref_qmm(oracle, d, torch.float16)
+    acc0 = (0.5 * ((torch.arange(64 * 48) % 11) - 5)).to(torch.float16).reshape(64, 48)
+    out = acc0.clone().to(dev)
+    pkg.quant_matmul(d["x"].to(dev), d["w"].to(dev), d["scale"].to(dev), name="aclnnQuantBatchMatmulInplaceAdd", out=out)
+    torch.cuda.synchronize()
+    assert torch.equal(out.cpu(), (acc0.float() + prod.float()).to(torch.float16))
+    # weight stored [N,K] (cuda/src/ops/quant.cu:303-326; test 32x64x48)
+    d = workloads.w8a8(M=32, K=64, N=48, seed=13, with_pertoken=False, with_bias=False, scale_dtype=torch.float16)
+    _, want = ref_qmm(oracle, d, torch.float16)
+    wt = d["w"].t().contiguous()
+    out = pkg.quant_matmul(d["x"].to(dev), wt.to(dev), d["scale"].to(dev), out_dtype=torch.float16,
+                           name="aclnnTransposeQuantBatchMatMul")
+    torch.cuda.synchronize()
+    assert torch.equal(out.cpu(), want)
+    # batched (tests/test_matmul_conv.cpp:1034-1043: 2x3x4x5, fp32 scale and output)
+    B, M, K, N = 2, 3, 4, 5
+    g = torch.Generator(); g.manual_seed(14)
+    a = torch.randint(-127, 128, (B, M, K), generator=g, dtype=torch.int8)
+    b = torch.randint(-127, 128, (B, K, N), generator=g, dtype=torch.int8)
+    sc = torch.rand(N, generator=g) * 0.01
+    out = pkg.quant_matmul(a.to(dev), b.to(dev), sc.to(dev), out_dtype=torch.float32, name="aclnnBatchMatmulQuant")
+    torch.cuda.synchronize()
+    want = torch.stack([torch.from_numpy(oracle.qmm_epilogue_fast(
+        oracle.qmm_acc_fast(a[i].numpy(), b[i].numpy(), M, K, N), sc.numpy())) for i in range(B)])
+    assert torch.equal(out.cpu(), want)
+
+
+def test_config2_w8a8_full_size(pkg, oracle, workloads, dev):
+    """M=2048, K=4096, N=14336 with per-token scale, per-channel scale and int32 bias, bf16 out."""
+    d = workloads.w8a8()
+    x, w = d["x"].to(dev), d["w"].to(dev)
+    acc = pkg.quant_matmul(x, w, None)
+    out = pkg.quant_matmul(x, w, d["scale"].to(dev), d["pertoken"].to(dev), d["bias"].to(dev), out_dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+    # the CPU checker on a seeded sample of 96 rows (the full product is 240 GFLOP in float64)
+    g = torch.Generator(); g.manual_seed(1)
+    rows = torch.randperm(d["M"], generator=g)[:96].sort().values
+    sub = dict(d, x=d["x"][rows], pertoken=d["pertoken"][rows], M=96)
+    ref_acc, ref_out = ref_qmm(oracle, sub, torch.bfloat16)
+    assert np.array_equal(acc[rows.to(dev)].cpu().numpy(), ref_acc)
+    assert torch.equal(out[rows.to(dev)].cpu(), ref_out)
+    # size-independent property over the whole output: column sums of the exact accumulators
+    colsum = acc.to(torch.int64).sum(dim=0).cpu().numpy()
+    want = d["x"].to(torch.float64).sum(dim=0).numpy() @ d["w"].to(torch.float64).numpy()
+    assert np.array_equal(colsum, np.rint(want).astype(np.int64))
+
+
+# ------------------------------------------------------------------ MX
+def run_mx(pkg, d, dev, out_dtype, name):
+    ak = pkg.ACL_FLOAT4_E2M1 if d["a_fp4"] else pkg.ACL_FLOAT8_E4M3FN
+    bk = pkg.ACL_FLOAT4_E2M1 if d["b_fp4"] else pkg.ACL_FLOAT8_E4M3FN
+    out = pkg.mx_matmul(d["a"].reshape(-1).to(dev), ak, d["sa"].to(dev), d["b"].reshape(-1).to(dev), bk, d["sb"].to(dev),
+                        d["M"], d["K"], d["N"], out_dtype=out_dtype, name=name)
+    torch.cuda.synchronize()
+    return out
+
+
+def ref_mx(oracle, d, rows=None):
+    ak = oracle.MXK_E2M1 if d["a_fp4"] else oracle.MXK_E4M3
+    bk = oracle.MXK_E2M1 if d["b_fp4"] else oracle.MXK_E4M3
+    return oracle.mx_matmul_fast(d["a"].numpy(), ak, d["sa"].numpy(), d["b"].numpy(), bk, d["sb"].numpy(),
+                                 d["M"], d["K"], d["N"])
+
+
+@pytest.mark.parametrize("path", ["generic", "tc", None])
+@pytest.mark.parametrize("kinds", [(False, False), (False, True), (True, True)])
+@pytest.mark.parametrize("shape", [(128, 256, 64), (64, 512, 128), (256, 256, 128)])
+def test_mx_matmul(pkg, oracle, workloads, dev, path, kinds, shape):
+    """Shapes of the reference's MX tests (tests/test_matmul_conv.cpp:965-970,994-995); its tolerances are
+    5e-2 / 8e-2, ours are the family's 1e-2 / 2e-3."""
+    M, K, N = shape
+    d = workloads.mx(M=M, K=K, N=N, a_fp4=kinds[0], b_fp4=kinds[1], seed=5000 + M + K)
+    want = ref_mx(oracle, d)
+    for name in ("aclnnMatmulMxFp8", "aclnnMatmulMxFp8Hw", "aclnnMatmulMxFp4", "aclnnMatmulMxFp4Hw"):
+        for odt in (torch.float32, torch.bfloat16):
+            with forced_path(path):
+                out = run_mx(pkg, d, dev, odt, name)
+            assert_close(to_np(out), want, f"{name} {kinds} {shape} {odt} path={path}")
+
+
+# ------------------------------------------------------------------ helpers of the family
+def test_int4_pack_known_answer_and_bulk(pkg, oracle, dev):
+    vals = torch.tensor([1, 2, -3, 7, -8, 0, 5, -1], dtype=torch.int8, device=dev)
+    out = torch.empty(4, dtype=torch.int8, device=dev)
+    pkg.call("aclnnConvertWeightToINT4Pack", pkg.AclTensor(vals), pkg.AclTensor(out))
+    torch.cuda.synchronize()
+    assert (out.cpu().numpy().view(np.uint8)).tolist() == [33, 125, 8, 245]
+    g = torch.Generator(); g.manual_seed(3)
+    for n in (2, 6, 10, 4098, 1 << 16):
+        v = torch.randint(-8, 8, (n,), generator=g, dtype=torch.int8)
+        o = torch.empty(n // 2, dtype=torch.uint8, device=dev)
+        pkg.call("aclnnConvertWeightToINT4Pack", pkg.AclTensor(v.to(dev)), pkg.AclTensor(o))
+        torch.cuda.synchronize()
+        assert np.array_equal(o.cpu().numpy(), oracle.int4_pack(v.numpy()))
+
+
+def test_cast_codecs(pkg, oracle, dev):
+    import cases
+    x = cases.cast_input()
+    got = pkg.cast(x.to(dev), pkg.ACL_FLOAT, pkg.ACL_FLOAT4_E2M1, x.numel())
+    torch.cuda.synchronize()
+    want_codes = oracle.e2m1_encode_fast(x.numpy())
+    assert np.array_equal(got.cpu().numpy(), oracle.pack_nibbles(want_codes))
+    back = pkg.cast(got, pkg.ACL_FLOAT4_E2M1, pkg.ACL_FLOAT, x.numel())
+    torch.cuda.synchronize()
+    assert np.array_equal(back.cpu().numpy(), oracle.decode_table(oracle.MXK_E2M1)[want_codes])
+    got8 = pkg.cast((x * 64).to(dev), pkg.ACL_FLOAT, pkg.ACL_FLOAT8_E4M3FN, x.numel())
+    torch.cuda.synchronize()
+    assert np.array_equal(got8.cpu().numpy(), oracle.e4m3_encode_fast((x * 64).numpy()))
+    back8 = pkg.cast(got8, pkg.ACL_FLOAT8_E4M3FN, pkg.ACL_FLOAT, x.numel())
+    torch.cuda.synchronize()
+    assert np.array_equal(back8.cpu().numpy(), oracle.decode_table(oracle.MXK_E4M3)[got8.cpu().numpy()])
+
+
+def test_weight_size_and_copy(pkg, dev):
+    lib = pkg.load()
+    shp = (ctypes.c_int64 * 2)(4096, 14336)
+    ia = lib.aclCreateIntArray(shp, 2)
+    out = torch.zeros(1, dtype=torch.int64, device=dev)
+    pkg.call("aclnnCalculateMatmulWeightSize", ctypes.c_void_p(ia), pkg.AclTensor(out), device=dev)
+    torch.cuda.synchronize()
+    assert out.item() == 4096 * 14336
+    lib.aclDestroyIntArray(ctypes.c_void_p(ia))
+    w = torch.randint(-128, 128, (64, 48), dtype=torch.int8, device=dev)
+    o = torch.empty_like(w)
+    pkg.call("aclnnTransMatmulWeight", pkg.AclTensor(w), pkg.AclTensor(o))
+    torch.cuda.synchronize()
+    assert torch.equal(w, o)
+
+
+# ------------------------------------------------------------------ against the reference's recorded outputs
+def test_against_reference_backend_outputs(pkg, oracle, workloads, dev):
+    """This library's kernels against outputs the reference's own CUDA backend produced on a B200 for
+    the same seeded inputs (tests/golden/ref_b200_outputs.npz)."""
+    import cases
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "ref_b200_outputs.npz")
+    if not os.path.exists(path):
+        pytest.skip("reference outputs not recorded yet")
+    ref = np.load(path)
+    for name, (gen, kw) in cases.WQ_CASES.items():
+        d = getattr(workloads, gen)(**kw)
+        out = run_wq(pkg, d, dev, name="aclnnWeightQuantBatchMatmul")
+        want = oracle.f16_bits_to_f32(ref[name]).reshape(d["M"], d["N"])
+        assert_close(to_np(out), want, name)
+    for name, kw in cases.QMM_CASES.items():
+        d = workloads.w8a8(**kw)
+        acc = pkg.quant_matmul(d["x"].to(dev), d["w"].to(dev), None)
+        out = pkg.quant_matmul(d["x"].to(dev), d["w"].to(dev), d["scale"].to(dev), out_dtype=kw["out_dtype"],
+                               name="aclnnQuantMatmulV4")
+        torch.cuda.synchronize()
+        assert np.array_equal(acc.cpu().numpy(), ref[name + "_acc"]), name
+        got = out.cpu()
+        got_bits = got.view(torch.int16).numpy().view(np.uint16) if got.dtype == torch.float16 else got.numpy().view(np.uint32)
+        want_bits = ref[name] if got.dtype == torch.float16 else ref[name].view(np.uint32)
+        assert np.array_equal(got_bits, want_bits.reshape(got_bits.shape)), name
+    for name, (entry, kw) in cases.MX_CASES.items():
+        d = workloads.mx(**kw)
+        out = run_mx(pkg, d, dev, torch.float32, entry)
+        assert_close(to_np(out), ref[name].astype(np.float64), name)

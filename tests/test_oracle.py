@@ -1,0 +1,200 @@
+"""CPU tests of the checker itself: the C restatement against every known answer the reference's
+tests hold for this path, and the BLAS-backed versions against the C restatement."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+@pytest.fixture(scope="module")
+def known():
+    with open(os.path.join(GOLD, "reference_known_answers.json")) as f:
+        return json.load(f)
+
+
+def test_int4_pack_known_answer(oracle, known):
+    k = known["int4_pack"]
+    got = oracle.int4_pack(np.array(k["input"], dtype=np.int8))
+    assert got.tolist() == k["output"]
+    # and unpacking gives the signed values back
+    assert oracle.int4_unpack(got, 8).tolist() == k["input"]
+
+
+def test_e2m1_decode_table(oracle, known):
+    bits = [int(b, 16) for b in known["e2m1_decode_bits"]["fp32_bits"]]
+    want = np.array(bits, dtype=np.uint32).view(np.float32)
+    got = np.array([oracle.C().oracle_e2m1_decode(i) for i in range(16)], dtype=np.float32)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+def test_e2m1_encode_boundaries(oracle, known):
+    b = np.array(known["e2m1_encode_bounds"]["min_abs_for_code"], dtype=np.float32)
+    lib = oracle.C()
+    for c in range(1, 8):
+        assert lib.oracle_e2m1_encode(float(b[c])) == c
+        below = np.nextafter(b[c], np.float32(0))
+        assert lib.oracle_e2m1_encode(float(below)) == c - 1
+        assert lib.oracle_e2m1_encode(-float(b[c])) == (c | 8)
+    assert lib.oracle_e2m1_encode(100.0) == 7 and lib.oracle_e2m1_encode(-100.0) == 15
+    assert lib.oracle_e2m1_encode(float("nan")) == 0
+    rng = np.random.default_rng(23)
+    x = (rng.random(5000) * 14 - 7).astype(np.float32)
+    scalar = np.array([lib.oracle_e2m1_encode(float(v)) for v in x], dtype=np.uint8)
+    assert np.array_equal(scalar, oracle.e2m1_encode_fast(x))
+
+
+def test_e8m0_and_swizzle(oracle, known):
+    a = np.zeros((1, 32), dtype=np.uint8) + 0x38  # e4m3 1.0
+    b = np.zeros((32, 1), dtype=np.uint8) + 0x38
+    for e, v in known["e8m0"]["samples"].items():
+        out = oracle.mx_matmul(a, oracle.MXK_E4M3, np.array([[int(e)]], np.uint8), b, oracle.MXK_E4M3,
+                               np.array([[127]], np.uint8), 1, 32, 1)
+        assert out[0, 0] == 32 * v
+    for r, blk, nb, want in known["scale_swizzle"]["samples"]:
+        assert oracle.scale_swizzle_index(r, blk, nb) == want
+
+
+def test_fp8_codecs_against_torch(oracle):
+    torch = pytest.importorskip("torch")
+    codes = torch.arange(256, dtype=torch.uint8)
+    for kind, tdt in ((oracle.MXK_E4M3, torch.float8_e4m3fn), (oracle.MXK_E5M2, torch.float8_e5m2)):
+        want = codes.view(tdt).float().numpy()
+        got = oracle.decode_table(kind)
+        assert np.array_equal(np.isnan(want), np.isnan(got))
+        assert np.array_equal(want[~np.isnan(want)], got[~np.isnan(got)])
+    rng = np.random.default_rng(0)
+    x = np.concatenate([rng.standard_normal(4000).astype(np.float32) * s for s in (1e-3, 0.02, 1, 30, 200)])
+    x = np.clip(x, -448, 448)
+    want = torch.from_numpy(x).to(torch.float8_e4m3fn).view(torch.uint8).numpy()
+    assert np.array_equal(oracle.e4m3_encode_fast(x), want)
+    assert np.array_equal(oracle.e4m3_encode(x[:2000]), want[:2000])
+    assert oracle.C().oracle_e4m3_encode(1e9) == 0x7E and oracle.C().oracle_e4m3_encode(-1e9) == 0xFE
+    xb = rng.standard_normal(5000).astype(np.float32)
+    assert np.array_equal(oracle.f32_to_bf16_bits(xb),
+                          torch.from_numpy(xb).to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16))
+
+
+def _rand_wq(rng, M, K, N, int4, G):
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    vals = rng.integers(-8, 8, (K, N)).astype(np.int8) if int4 else rng.integers(-128, 128, (K, N)).astype(np.int8)
+    w = None
+    sc = rng.uniform(0.002, 0.02, (G, N)).astype(np.float32)
+    of = rng.uniform(-1, 1, (G, N)).astype(np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    return x, vals, w, sc, of, bias
+
+
+@pytest.mark.parametrize("int4", [False, True])
+@pytest.mark.parametrize("G", [1, 4])
+def test_wqbmm_matches_reference_test_formula(oracle, int4, G):
+    """The reference's in-test CPU reference (tests/test_matmul_conv.cpp:632-634):
+    acc += x * ((w - off[n]) * scale[n]) in double."""
+    rng = np.random.default_rng(11)
+    M, K, N = 5, 64, 24
+    x, vals, _, sc, of, bias = _rand_wq(rng, M, K, N, int4, G)
+    w = oracle.int4_pack(vals.reshape(-1)) if int4 else vals.view(np.uint8)
+    group = K // G
+    want = np.zeros((M, N))
+    for m in range(M):
+        for n in range(N):
+            acc = 0.0
+            for k in range(K):
+                acc += float(x[m, k]) * ((float(vals[k, n]) - float(of[k // group, n])) * float(sc[k // group, n]))
+            want[m, n] = acc + float(bias[n])
+    got = oracle.wqbmm(x, w, int4, sc, of, bias, M, K, N, group)
+    assert np.allclose(got, want, rtol=1e-12, atol=1e-12)
+    fast = oracle.wqbmm_fast(x, w, int4, sc, of, bias, M, K, N, group)
+    assert np.allclose(fast, want, rtol=1e-10, atol=1e-10)
+    # empty offset / bias
+    got2 = oracle.wqbmm(x, w, int4, sc, None, None, M, K, N, group)
+    fast2 = oracle.wqbmm_fast(x, w, int4, sc, None, None, M, K, N, group)
+    assert np.allclose(got2, fast2, rtol=1e-10, atol=1e-10)
+
+
+def test_qmm_exact_and_epilogue(oracle):
+    rng = np.random.default_rng(12)
+    M, K, N = 9, 80, 33
+    x = rng.integers(-127, 128, (M, K)).astype(np.int8)
+    w = rng.integers(-127, 128, (K, N)).astype(np.int8)
+    want = x.astype(np.int64) @ w.astype(np.int64)
+    acc = oracle.qmm_acc(x, w, M, K, N)
+    assert np.array_equal(acc, want)
+    assert np.array_equal(oracle.qmm_acc_fast(x, w, M, K, N), want)
+    sc = rng.uniform(0.001, 0.01, N).astype(np.float32)
+    pt = rng.uniform(0.001, 0.01, M).astype(np.float32)
+    bias = rng.integers(-1000, 1001, N).astype(np.int32)
+    a = oracle.qmm_epilogue(acc, sc, pt, bias)
+    b = oracle.qmm_epilogue_fast(acc, sc, pt, bias)
+    assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+    # the reference's formula: float(acc) * scale (cuda/src/ops/matmul.cu:327-330)
+    c = oracle.qmm_epilogue(acc, sc)
+    assert np.array_equal(c, acc.astype(np.float32) * sc[None, :])
+    # extreme values stay exact
+    xe = np.full((2, 4096), -128, np.int8); we = np.full((4096, 3), -128, np.int8)
+    assert np.array_equal(oracle.qmm_acc_fast(xe, we, 2, 4096, 3), np.full((2, 3), 4096 * 16384, np.int32))
+
+
+@pytest.mark.parametrize("kinds", [(0, 0), (0, 2), (2, 2), (1, 0)])
+def test_mx_fast_matches_scalar(oracle, kinds):
+    rng = np.random.default_rng(13)
+    M, K, N = 6, 64, 10
+    ak, bk = kinds
+
+    def operand(kind, count):
+        if kind == oracle.MXK_E2M1:
+            return rng.integers(0, 256, count // 2).astype(np.uint8)
+        b = rng.integers(0, 256, count).astype(np.uint8)
+        b[(b & 0x7F) == 0x7F] = 0x38  # no NaN codes (e4m3) / keep finite
+        if kind == oracle.MXK_E5M2:
+            b[(b & 0x7C) == 0x7C] = 0x3C
+        return b
+
+    a, b = operand(ak, M * K), operand(bk, K * N)
+    sa = rng.integers(120, 135, (M, K // 32)).astype(np.uint8)
+    sb = rng.integers(120, 135, (K // 32, N)).astype(np.uint8)
+    want = oracle.mx_matmul(a, ak, sa, b, bk, sb, M, K, N)
+    got = oracle.mx_matmul_fast(a, ak, sa, b, bk, sb, M, K, N)
+    assert np.allclose(got, want, rtol=1e-12, atol=1e-12)
+
+
+def test_reference_backend_outputs_pin_the_oracle(oracle, workloads):
+    """Outputs of the reference's own CUDA backend, recorded on a B200 (tests/golden/make_ref_fixtures.py),
+    against the CPU checker on the same seeded inputs."""
+    import torch
+    import cases
+    path = os.path.join(GOLD, "ref_b200_outputs.npz")
+    if not os.path.exists(path):
+        pytest.skip("reference outputs not recorded yet")
+    ref = np.load(path)
+
+    def nerr(got, want):
+        return np.abs(got - want).max() / (np.abs(want).max() + 1e-9)
+
+    for name, (gen, kw) in cases.WQ_CASES.items():
+        d = getattr(workloads, gen)(**kw)
+        want = oracle.wqbmm_fast(d["x"].float().numpy(), d["w"].numpy(), d["int4"], d["scale"].float().numpy(),
+                                 None if d["offset"] is None else d["offset"].float().numpy(), None, d["M"], d["K"], d["N"])
+        got = oracle.f16_bits_to_f32(ref[name]).astype(np.float64).reshape(d["M"], d["N"])
+        assert nerr(got, want) <= 2e-3, name  # fp16 output rounding (+ fp16 weight rounding on the large-M path)
+    for name, kw in cases.QMM_CASES.items():
+        d = workloads.w8a8(**kw)
+        acc = oracle.qmm_acc_fast(d["x"].numpy(), d["w"].numpy(), d["M"], d["K"], d["N"])
+        assert np.array_equal(ref[name + "_acc"], acc), name  # int32 accumulators: bit-exact
+        want = oracle.qmm_epilogue_fast(acc, d["scale"].float().numpy())
+        if kw["out_dtype"] == torch.float32:
+            assert np.array_equal(ref[name].view(np.uint32), want.view(np.uint32)), name
+        else:
+            assert np.array_equal(ref[name], oracle.f32_to_f16_bits(want).reshape(ref[name].shape)), name
+    for name, (entry, kw) in cases.MX_CASES.items():
+        d = workloads.mx(**kw)
+        ak = oracle.MXK_E2M1 if kw["a_fp4"] else oracle.MXK_E4M3
+        bk = oracle.MXK_E2M1 if kw["b_fp4"] else oracle.MXK_E4M3
+        want = oracle.mx_matmul_fast(d["a"].numpy(), ak, d["sa"].numpy(), d["b"].numpy(), bk, d["sb"].numpy(),
+                                     d["M"], d["K"], d["N"])
+        assert nerr(ref[name].astype(np.float64), want) <= 2e-3, name  # fp16 operand rounding in the functional path
+    x = cases.cast_input().numpy()
+    assert np.array_equal(ref["cast_e2m1"], oracle.pack_nibbles(oracle.e2m1_encode_fast(x)))
+    assert np.array_equal(ref["cast_e4m3"], oracle.e4m3_encode_fast(x * 64))
