@@ -118,7 +118,9 @@ void choose_path(aclOpExecutor *e, uint64_t *ws) {
 aclnnStatus run_matmul(void *ws, uint64_t ws_bytes, aclOpExecutor *e, aclrtStream stream) {
     if (!e) return ACLNN_ERR_PARAM_NULLPTR;
     aclnnStatus st = ACLNN_SUCCESS;
-    if (e->ws_bytes > 0 && (!ws || ws_bytes < e->ws_bytes)) {
+    if (e->m == 0 || e->n == 0) {
+        // empty output: nothing to launch
+    } else if (e->ws_bytes > 0 && (!ws || ws_bytes < e->ws_bytes)) {
         st = ACLNN_ERR_PARAM_INVALID;  // undersized workspace is rejected before anything is launched
     } else {
         MatmulArgs p = args_of(e, ws, ws_bytes);
