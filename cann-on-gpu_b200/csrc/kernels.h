@@ -71,6 +71,8 @@ bool tc_supported(const MatmulArgs &p);
 void tc_plan(MatmulArgs &p);                 // fills split_k
 uint64_t tc_workspace_bytes(const MatmulArgs &p);
 cudaError_t launch_tc(const MatmulArgs &p, cudaStream_t s);
+// 0, or the code of the first bounded wait that gave up on the current device (synchronises).
+unsigned int tc_device_status();
 
 // Host-side tally of kernels this library has launched (diagnostics for benchmarks).
 void count_launch(int n = 1);

@@ -281,6 +281,7 @@ aclnnStatus run_simple(aclOpExecutor *e, aclrtStream stream) {
 extern "C" {
 
 uint64_t aclnnB200KernelLaunchCount(void) { return qmm::launch_count(); }
+uint32_t aclnnB200DeviceStatus(void) { return qmm::tc_device_status(); }
 
 #define RUN_MATMUL(NAME) \
     aclnnStatus NAME(void *ws, uint64_t wsz, aclOpExecutor *e, aclrtStream s) { return run_matmul(ws, wsz, e, s); }

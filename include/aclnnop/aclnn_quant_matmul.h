@@ -142,6 +142,9 @@ B200_ACLNN_RUN(aclnnCast)
 /* Diagnostics (no counterpart in the reference): number of kernels this library has launched in the
  * calling process so far.  Benchmarks use the difference around a timed region. */
 ACL_FUNC_VISIBILITY uint64_t aclnnB200KernelLaunchCount(void);
+/* Diagnostics (no counterpart in the reference): 0, or the code of the first bounded wait inside a
+ * tensor-core kernel that gave up on the current device.  Synchronises the device. */
+ACL_FUNC_VISIBILITY uint32_t aclnnB200DeviceStatus(void);
 
 #ifdef __cplusplus
 }

@@ -21,6 +21,8 @@ def declared_symbols():
     for m in re.finditer(r"aclnnStatus (\w+GetWorkspaceSize)\(", body):
         if "##" not in m.group(0) and m.group(1) != "GetWorkspaceSize":
             names.add(m.group(1))
+    for m in re.finditer(r"^ACL_FUNC_VISIBILITY u?int\d+_t (\w+)\(", body, re.M):
+        names.add(m.group(1))
     for h in ("acl/acl.h", "aclnn/acl_meta.h"):
         for m in re.finditer(r"^ACL_FUNC_VISIBILITY\s+[\w ]+?\*?\s*\*?(\w+)\(", open(os.path.join(INC, h)).read(), re.M):
             names.add(m.group(1))

@@ -313,3 +313,12 @@ def test_against_reference_backend_outputs(pkg, oracle, workloads, dev):
         d = workloads.mx(**kw)
         out = run_mx(pkg, d, dev, torch.float32, entry)
         assert_close(to_np(out), ref[name].astype(np.float64), name)
+
+
+def test_zz_no_bounded_wait_gave_up(pkg, dev):
+    """Every spin inside the tensor-core kernels is bounded and records a code when it gives up;
+    after the whole suite the device status word must still be 0."""
+    lib = pkg.load()
+    lib.aclnnB200DeviceStatus.restype = ctypes.c_uint32
+    torch.cuda.synchronize()
+    assert lib.aclnnB200DeviceStatus() == 0
