@@ -284,4 +284,59 @@ cudaError_t launch_gemv(const MatmulArgs &p, cudaStream_t s) {
     return e;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Decode matmul for callers that cannot hand over scratch memory.
+//
+// The split-K partial sums of the streaming kernel normally live in the caller's workspace.  Some
+// programs written against the reference have no workspace to give on this path: the reference
+// reports 0 workspace bytes for M <= 16 (cuda/src/ops/matmul.cu:773-774), so their decode loop was
+// built without one, and it runs at a point where device memory can no longer be requested (the
+// device arena was carved up at start-up and allocation calls are forbidden in the serving loop).
+// For them the partial sums go into the fixed array below, which every GPU that loads this library
+// holds until the process exits.
+//
+// The array is shared by all calls and keeps the previous call's contents.  The kernels overwrite
+// every element they later read, so nothing has to be cleared; two calls whose kernels overlap on
+// the GPU (different streams, different threads) would race on it and must be serialised by the
+// caller.
+constexpr size_t NOALLOC_SCRATCH_FLOATS = 512 * 1024;  // 2 MiB per GPU
+static __device__ __align__(256) float g_noalloc_scratch[NOALLOC_SCRATCH_FLOATS];
+
+size_t noalloc_scratch_bytes() { return NOALLOC_SCRATCH_FLOATS * sizeof(float); }
+
+// Device address of the scratch array on the current device.  In host code the array's name is
+// only a handle for the runtime, not a device pointer, so the address is looked up once per device
+// (with that device current) and cached.
+static cudaError_t noalloc_scratch_ptr(float **out) {
+    static float *cached[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (!cached[dev]) {
+        float *ptr = nullptr;
+        e = cudaGetSymbolAddress((void **)&ptr, g_noalloc_scratch);
+        if (e != cudaSuccess) return e;
+        cached[dev] = ptr;
+    }
+    *out = cached[dev];
+    return cudaSuccess;
+}
+
+cudaError_t launch_gemv_noalloc(MatmulArgs p, cudaStream_t s, bool *too_large) {
+    *too_large = false;
+    p.split_k = gemv_pick_split_k(p);
+    const uint64_t need = gemv_workspace_bytes(p);
+    if (need > noalloc_scratch_bytes()) {
+        *too_large = true;
+        return cudaErrorInvalidValue;
+    }
+    float *scratch = nullptr;
+    cudaError_t e = noalloc_scratch_ptr(&scratch);
+    if (e != cudaSuccess) return e;
+    p.workspace = scratch;
+    p.workspace_bytes = noalloc_scratch_bytes();
+    return launch_gemv(p, s);
+}
+
 }  // namespace qmm

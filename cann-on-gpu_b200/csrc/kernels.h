@@ -66,6 +66,11 @@ int gemv_pick_split_k(const MatmulArgs &p);
 uint64_t gemv_workspace_bytes(const MatmulArgs &p);
 cudaError_t launch_gemv(const MatmulArgs &p, cudaStream_t s);
 
+// The same kernel with its split-K partial sums in a fixed array inside the library instead of a
+// caller workspace (no allocation anywhere).  *too_large is set when the partial sums would not fit.
+size_t noalloc_scratch_bytes();
+cudaError_t launch_gemv_noalloc(MatmulArgs p, cudaStream_t s, bool *too_large);
+
 // tcgen05 tensor-core kernel family.
 bool tc_supported(const MatmulArgs &p);
 void tc_plan(MatmulArgs &p);                 // fills split_k

@@ -346,6 +346,41 @@ MX_ALIAS(aclnnMatmulMxFp8Hw)
 MX_ALIAS(aclnnMatmulMxFp4)
 MX_ALIAS(aclnnMatmulMxFp4Hw)
 
+// Single-call decode matmul that allocates nothing and takes no workspace (see gemv.cu).
+aclnnStatus aclnnB200WeightQuantMatmulNoAlloc(const void *x, const void *weight, const void *antiquantScale,
+        const void *antiquantOffsetOptional, const void *biasOptional, void *out, int64_t m, int64_t k, int64_t n,
+        int64_t antiquantGroupSize, aclDataType xType, aclDataType weightType, aclrtStream stream) {
+    if (!x || !weight || !antiquantScale || !out) return ACLNN_ERR_PARAM_NULLPTR;
+    if (m < 1 || k < 1 || n < 1 || antiquantGroupSize < 0) return ACLNN_ERR_PARAM_INVALID;
+    if (antiquantGroupSize > 0 && k % antiquantGroupSize != 0) return ACLNN_ERR_PARAM_INVALID;
+    MatmulArgs p;
+    p.a = x; p.b = weight; p.out = out; p.scale = antiquantScale; p.offset = antiquantOffsetOptional; p.bias = biasOptional;
+    p.a_type = p.out_type = p.sc_type = elem_type(xType);
+    p.bias_type = biasOptional ? p.a_type : (int)ET_NONE;
+    p.b_type = elem_type(weightType);
+    p.epilogue = EPI_PLAIN;
+    p.M = m; p.N = n; p.K = k;
+    p.group = (antiquantGroupSize == 0 || antiquantGroupSize >= k) ? k : antiquantGroupSize;
+    if (!gemv_supported(p)) {
+        fprintf(stderr, "[b200-qmm] aclnnB200WeightQuantMatmulNoAlloc: unsupported problem (needs M <= %d, fp16/bf16/fp32 "
+                        "activations, int8/int4 weights, N %% 32 == 0, K a multiple of the group size)\n", gemv_max_m());
+        return ACLNN_ERR_PARAM_INVALID;
+    }
+    bool too_large = false;
+    cudaError_t err = launch_gemv_noalloc(p, (cudaStream_t)stream, &too_large);
+    if (too_large) {
+        fprintf(stderr, "[b200-qmm] aclnnB200WeightQuantMatmulNoAlloc: M=%ld N=%ld K=%ld needs more than the %zu bytes of "
+                        "built-in scratch; use aclnnWeightQuantBatchMatmulV2 with a workspace\n", (long)m, (long)n, (long)k,
+                noalloc_scratch_bytes());
+        return ACLNN_ERR_PARAM_INVALID;
+    }
+    if (err != cudaSuccess) {
+        fprintf(stderr, "[b200-qmm] aclnnB200WeightQuantMatmulNoAlloc: %s\n", cudaGetErrorString(err));
+        return ACLNN_ERR_RUNTIME_ERROR;
+    }
+    return ACLNN_SUCCESS;
+}
+
 #define RUN_SIMPLE(NAME) \
     aclnnStatus NAME(void *, uint64_t, aclOpExecutor *e, aclrtStream s) { return run_simple(e, s); }
 

@@ -139,6 +139,24 @@ ACL_FUNC_VISIBILITY aclnnStatus aclnnCastGetWorkspaceSize(const aclTensor *self,
     uint64_t *workspaceSize, aclOpExecutor **executor);
 B200_ACLNN_RUN(aclnnCast)
 
+/* Decode-shaped weight-only matmul in ONE call that allocates nothing and takes no workspace.
+ * It has no counterpart in the reference.  It exists for programs whose decode path was written
+ * against the reference's "0 workspace bytes for M <= 16" (cuda/src/ops/matmul.cu:773-774) and that run
+ * where device memory can no longer be requested (arena fixed at start-up, no allocation calls in the
+ * serving loop): the split-K partial sums live in a 2 MiB array inside the library, held by every GPU
+ * that loads it.
+ *   out[m,n] = x[m,k] @ ((weight - offset) * scale) + bias, same semantics and layouts as
+ *   aclnnWeightQuantBatchMatmulV2Ex; x/scale/offset/bias/out are all of xType (ACL_FLOAT16, ACL_BF16 or
+ *   ACL_FLOAT), weightType is ACL_INT8 or ACL_INT4, antiquantGroupSize 0 = per-channel [N] scales.
+ * Limits: M <= 4, N a multiple of 32, and split * M * N partial sums must fit the 2 MiB (larger
+ * problems return 161002 with a message on stderr).  The first call on each device looks up the
+ * array's device address (make that call before any stream capture).  All calls share the array:
+ * calls whose kernels could overlap on the GPU must be serialised by the caller. */
+ACL_FUNC_VISIBILITY aclnnStatus aclnnB200WeightQuantMatmulNoAlloc(const void *x, const void *weight,
+    const void *antiquantScale, const void *antiquantOffsetOptional, const void *biasOptional, void *out,
+    int64_t m, int64_t k, int64_t n, int64_t antiquantGroupSize, aclDataType xType, aclDataType weightType,
+    aclrtStream stream);
+
 /* Diagnostics (no counterpart in the reference): number of kernels this library has launched in the
  * calling process so far.  Benchmarks use the difference around a timed region. */
 ACL_FUNC_VISIBILITY uint64_t aclnnB200KernelLaunchCount(void);
