@@ -76,6 +76,11 @@ bool tc_supported(const MatmulArgs &p);
 void tc_plan(MatmulArgs &p);                 // fills split_k
 uint64_t tc_workspace_bytes(const MatmulArgs &p);
 cudaError_t launch_tc(const MatmulArgs &p, cudaStream_t s);
+// Persistent stream-K tensor-core kernel for weight-only matmuls (wq_tc.cu).
+bool wq_tc_supported(const MatmulArgs &p);
+uint64_t wq_tc_workspace_bytes(const MatmulArgs &p);
+cudaError_t launch_wq_tc(const MatmulArgs &p, cudaStream_t s);
+unsigned int wq_tc_device_status();
 // 0, or the code of the first bounded wait that gave up on the current device (synchronises).
 unsigned int tc_device_status();
 

@@ -27,20 +27,13 @@
 //     workspace and a small second kernel reduces them and applies bias / dequant / cast.
 //   * Every wait is bounded: after about a second a thread records a code in a status word, raises
 //     a CTA-wide abort flag and all roles fall through to the common exit, which frees the TMEM.
-#include <cuda.h>
-
+#include <cstring>
 #include <mutex>
 
-#include "device_utils.cuh"
+#include "tc_common.cuh"
 
 namespace qmm {
 namespace {
-
-inline uint64_t align_up_u64(uint64_t x, uint64_t a) { return (x + a - 1) / a * a; }
-
-// ------------------------------------------------------------------------------------------------
-// Device status word (0 = no kernel of this library has hit a bounded-wait limit on this device).
-__device__ unsigned int g_tc_status = 0;
 
 enum WMode : int {
     W_I8 = 0,    // int8 weights by TMA straight into kind::i8
@@ -60,7 +53,6 @@ template <> struct WTraits<W_Q8_F16>  { static constexpr int BK = 64,  STAGE_W =
 constexpr int TILE_N = 128;          // output columns per CTA = MMA M
 constexpr int W_TILE_BYTES = 16384;  // MMA-ready weight tile per stage (128 n x 128 B of K, or 2 x 64 k x 128 B)
 constexpr int MAX_UNITS = 64;        // scale groups (fold units) per CTA
-constexpr unsigned long long WAIT_LIMIT_NS = 1000000000ull;
 
 struct TcParams {
     void *out;
@@ -77,114 +69,6 @@ struct TcParams {
     int kb_per_unit;          // K blocks per fold unit (scale group); kb_per_split for per-channel scales
     int grouped;              // scale rows per group (1) or one row for all of K (0)
 };
-
-// ------------------------------------------------------------------------------------------------ PTX
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ unsigned long long global_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-// Bounded wait.  Returns false when the CTA has been (or now is) aborted; `code` lands in the device
-// status word so the host can report which hand-over gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, unsigned code) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = global_ns();
-    unsigned it = 0;
-    while (true) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((++it & 63u) == 0) {
-            if (*abort_flag) return false;
-            if (global_ns() - t0 > WAIT_LIMIT_NS) {
-                *abort_flag = 1;
-                atomicCAS(&g_tc_status, 0u, code);
-                return false;
-            }
-        }
-    }
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *tm, uint32_t bar, int x, int y) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"(tm), "r"(bar), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-template <bool INT8>
-__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    if constexpr (INT8) {
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-            "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-    } else {
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-    }
-}
-// 16 consecutive TMEM columns of this thread's lane.
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr) : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1 (Blackwell).
-// lbo/sbo in bytes: for a K-major operand sbo is the pitch between 8-row groups (lbo unused); for an
-// MN-major operand lbo is the pitch between 128-byte-wide column blocks and sbo the pitch between
-// groups of 8 K-rows.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
-    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(sbo >> 4) << 32) |
-           (1ull << 46) | (2ull << 61);
-}
-// Instruction descriptor: dense, D format (1 = f32, 2 = s32), A/B formats, A (weights) MN-major,
-// B (activations) K-major, N >> 3 at bit 17, M >> 4 at bit 24.
-__host__ __device__ constexpr uint32_t instr_desc(int c_fmt, int ab_fmt, int m, int n) {
-    return ((uint32_t)c_fmt << 4) | ((uint32_t)ab_fmt << 7) | ((uint32_t)ab_fmt << 10) | (1u << 15) | (0u << 16) |
-           ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-
-// Output column of accumulator lane r.  The int4 converter keeps the nibble pairs that one lop3
-// extracts together, so inside every run of 8 lanes the columns appear as 0,4,1,5,2,6,3,7.
-template <bool Q4> __device__ __forceinline__ int col_of_lane(int r) {
-    if constexpr (Q4) return (r & ~7) | ((r & 1) << 2) | ((r & 7) >> 1);
-    return r;
-}
 
 // ------------------------------------------------------------------------------------------------ kernel
 template <int WMODE, int MT, int STAGES>
@@ -506,33 +390,6 @@ __global__ void tc_finalize_kernel(TcParams p, int split) {
 }
 
 // ------------------------------------------------------------------------------------------------ host
-using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-                              const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeFn encode_fn() {
-    static EncodeFn fn = [] {
-        void *f = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess) return (EncodeFn) nullptr;
-        return q == cudaDriverEntryPointSuccess ? (EncodeFn)f : (EncodeFn) nullptr;
-    }();
-    return fn;
-}
-
-// 2-D row-major tensor map: `cols` contiguous elements per row, `rows` rows, row pitch in bytes.
-bool make_map(CUtensorMap *tm, const void *ptr, CUtensorMapDataType dt, uint64_t cols, uint64_t rows, uint64_t pitch_bytes,
-              uint32_t box_cols, uint32_t box_rows, CUtensorMapSwizzle sw) {
-    EncodeFn fn = encode_fn();
-    if (!fn) return false;
-    cuuint64_t dims[2] = {cols, rows};
-    cuuint64_t strides[1] = {pitch_bytes};
-    cuuint32_t box[2] = {box_cols, box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    return fn(tm, dt, 2, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
-              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 bool device_is_sm100() {
     static int cached[64];
     static std::once_flag once;
@@ -631,8 +488,17 @@ cudaError_t dispatch_mt(int mt, const CUtensorMap &tx, const CUtensorMap &tw, co
 
 }  // namespace
 
+// Weight-only matmuls go to the persistent stream-K kernel (wq_tc.cu) unless B200_QMM_WQ=legacy.
+static bool use_stream_wq(const MatmulArgs &p) {
+    if (p.epilogue != EPI_PLAIN || !p.scale) return false;
+    const char *e = getenv("B200_QMM_WQ");
+    if (e && !strcmp(e, "legacy")) return false;
+    return wq_tc_supported(p);
+}
+
 bool tc_supported(const MatmulArgs &p) {
     if (!device_is_sm100() || !encode_fn()) return false;
+    if (use_stream_wq(p)) return true;
     if (p.batch != 1 || p.b_transposed || p.accumulate || p.M < 1) return false;
     if (p.M > (1 << 24) || p.N > (1 << 24) || p.K > (1 << 24)) return false;
     auto aligned16 = [](const void *q) { return q == nullptr || (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
@@ -653,14 +519,16 @@ bool tc_supported(const MatmulArgs &p) {
     return false;
 }
 
-void tc_plan(MatmulArgs &p) { p.split_k = make_plan(p).split; }
+void tc_plan(MatmulArgs &p) { p.split_k = use_stream_wq(p) ? 1 : make_plan(p).split; }
 
 uint64_t tc_workspace_bytes(const MatmulArgs &p) {
+    if (use_stream_wq(p)) return wq_tc_workspace_bytes(p);
     TcPlan pl = make_plan(p);
     return pl.xsum_bytes + pl.partial_bytes;
 }
 
 cudaError_t launch_tc(const MatmulArgs &p, cudaStream_t s) {
+    if (use_stream_wq(p)) return launch_wq_tc(p, s);
     const TcPlan pl = make_plan(p);
     if (p.workspace_bytes < pl.xsum_bytes + pl.partial_bytes) return cudaErrorInvalidValue;
     if ((reinterpret_cast<uintptr_t>(p.a) & 15) || (reinterpret_cast<uintptr_t>(p.b) & 15)) return cudaErrorMisalignedAddress;
@@ -720,7 +588,8 @@ cudaError_t launch_tc(const MatmulArgs &p, cudaStream_t s) {
 unsigned int tc_device_status() {
     unsigned int v = 0;
     if (cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(v)) != cudaSuccess) return 0xFFFFFFFFu;
-    return v;
+    const unsigned int w = wq_tc_device_status();
+    return v ? v : w;
 }
 
 }  // namespace qmm

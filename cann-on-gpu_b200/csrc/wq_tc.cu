@@ -1,0 +1,697 @@
+// Weight-only quantized matmul (W4A16 / W8A16) on tcgen05: persistent, stream-K, fused dequant.
+//
+// Per CTA (one per SM, 16 warps).  The unit of work is a "super-block" of 128 rows of K for one
+// 128-column tile; even and odd super-blocks run on two independent lanes of the pipeline:
+//   warp 0        weight producer: TMA of the PACKED rows [128 k][128 n] (64 B or 128 B per row) into
+//                 a ring of staging slots -- this is what keeps tens of KB per SM in flight from HBM.
+//   warp 15       activation producer: TMA of the tile [MT m][128 k] into the MMA ring slot.
+//   warps 6-9 /   two converter teams (even / odd super-blocks): read a staged slot, expand it in
+//   warps 10-13   registers to bf16/fp16 INTEGERS (exact), write the tensor core's canonical MN-major
+//                 128-byte-swizzled layout into the MMA ring slot, release the staging slot.
+//   warps 1, 14   two MMA issuers (even / odd super-blocks): 8 x tcgen05.mma kind::f16 per super-block,
+//                 weights on the M side (128 columns n), activations on the N side (MT rows m), fp32
+//                 accumulators in TMEM, ONE tcgen05.commit per super-block (it releases the ring slot
+//                 and publishes the accumulator at once).
+//   warps 2-5     epilogue: per scale group, fold the finished accumulator(s) into fp32 registers with
+//                 the reference's algebra  tot += s_g[n] * (sum x*q - off_g[n] * sum_g x)
+//                 (cuda/src/ops/matmul.cu:334-335), then write the tile or its partial sums.
+// Two issuers and two converter teams exist because the costs that matter at decode shapes are
+// per-instruction latencies (an mbarrier wait ~100 cycles, a commit ~200, an MMA issue ~50, a
+// converter task ~400), not throughput; running two super-blocks side by side hides them.
+//
+// Work split: the (tile, K) iteration space is cut into P = gridDim.x equal contiguous shares
+// ("stream-K"), so every SM streams the same number of weight bytes whatever N and K are.  Whole
+// tiles are written straight to the output; pieces go to fp32 slots in the workspace that
+// wq_finalize_kernel sums.  Shares are cut at scale-group boundaries.
+//
+// Replaces the reference's k_wq_fused (matmul.cu:337-352) and its dequant + GEMM path
+// (matmul.cu:734-747,790-795).
+#include <mutex>
+
+#include "tc_common.cuh"
+
+namespace qmm {
+namespace {
+
+constexpr int TILE_N = 128;     // output columns per tile = MMA M
+constexpr int SBK = 128;        // K rows per super-block
+constexpr int W_TILE = 16384;   // MMA-ready weights of 64 K rows: 2 column halves x 64 k x 128 B
+constexpr int W_HALF = 8192;
+constexpr int ND = 8;           // "super-block done" barriers (more than any ring is deep)
+
+#ifdef WQ_PROFILE
+// Cycle counters of CTA 0 (development aid, compiled only with -DWQ_PROFILE).
+__device__ unsigned long long g_prof[32];
+__device__ unsigned int g_dbg_flags;
+#define PROF_T0() const long long _t0 = clock64()
+#define PROF_ADD(i) do { pc[i] += clock64() - _t0; } while (0)
+#define DBG(bit) ((g_dbg_flags >> (bit)) & 1u)
+#else
+#define DBG(bit) 0
+#define PROF_T0() do {} while (0)
+#define PROF_ADD(i) do {} while (0)
+#endif
+
+struct WqParams {
+    void *out;
+    float *slots;            // [tiles + P][MT][128] fp32 partial tiles
+    const void *scale, *offset, *bias;
+    const float *xtab;       // grouped: [K/g][M] sums of x per group; per-channel: [num_sb+1][M] prefix sums per super-block
+    int sc_type, out_type;
+    int M, N, K;
+    int m_tiles;             // tiles are numbered n_tile * m_tiles + m_tile
+    int num_sb;              // super-blocks of 128 K rows
+    int sbq;                 // super-blocks per quantum (= per scale group; 1 for per-channel scales)
+    int qpt;                 // quanta per tile
+    long long total_q;       // tiles * qpt
+    int grouped;
+};
+
+template <bool Q4, int MT, int NS, int NR>
+struct WqSmem {
+    static constexpr int STAGE = Q4 ? 8192 : 16384;          // packed rows of one super-block
+    static constexpr int X_BYTES = 2 * MT * 128;             // activations of one super-block (two 64-k boxes)
+    static constexpr int SLOT = 2 * W_TILE + X_BYTES;        // MMA ring slot
+    static constexpr int RING_OFF = NS * STAGE;
+    static constexpr int BAR_OFF = RING_OFF + NR * SLOT;
+    static constexpr int NUM_BARS = 2 * NS + NR + ND + 4;
+    static constexpr int MISC_OFF = BAR_OFF + NUM_BARS * 8;
+    static constexpr int TOTAL = MISC_OFF + 16 + 1024;
+};
+
+// Share of CTA c: quanta [c*T/P, (c+1)*T/P).
+__host__ __device__ inline long long share_begin(long long c, long long total_q, int P) { return c * total_q / P; }
+// CTA that owns quantum q.
+__host__ __device__ inline int share_owner(long long q, long long total_q, int P) {
+    return (int)(((q + 1) * P - 1) / total_q);
+}
+
+// One 16-byte chunk of packed weights -> MMA-ready 16-bit integers, written to the swizzled tile.
+//   Q4: 32 columns of one K row -> four chunks of 8 integers (lane order 0,4,1,5,2,6,3,7 inside a chunk)
+//   Q8: 16 columns of one K row -> two chunks of 8 integers (natural order)
+template <bool Q4, bool BF16>
+__device__ __forceinline__ void convert_chunk(const uint32_t (&w)[4], uint32_t dst, int k, int part) {
+    if constexpr (Q4) {
+        // (nibble ^ 8) | magic == (x & 0x000F000F) ^ MAGIC_X: value + 8 + 128 (bf16) or + 1024 (fp16), exact
+        constexpr uint32_t MAGIC_X = BF16 ? 0x43084308u : 0x64086408u;
+        constexpr uint32_t BIAS = BF16 ? 0x43084308u : 0x64086408u;  // 136.0 | 1032.0
+#pragma unroll
+        for (int jw = 0; jw < 4; ++jw) {
+            uint32_t o[4];
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+                const uint32_t pair = ((w[jw] >> (4 * h)) & 0x000F000Fu) ^ MAGIC_X;
+                if constexpr (BF16) {
+                    __nv_bfloat162 d = __hsub2(*reinterpret_cast<const __nv_bfloat162 *>(&pair),
+                                               *reinterpret_cast<const __nv_bfloat162 *>(&BIAS));
+                    o[h] = *reinterpret_cast<uint32_t *>(&d);
+                } else {
+                    __half2 d = __hsub2(*reinterpret_cast<const __half2 *>(&pair), *reinterpret_cast<const __half2 *>(&BIAS));
+                    o[h] = *reinterpret_cast<uint32_t *>(&d);
+                }
+            }
+            const int n8 = part * 4 + jw;
+            const uint32_t da = dst + (n8 >> 3) * W_HALF + k * 128 + (((n8 & 7) ^ (k & 7)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(da), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
+        }
+    } else {
+#pragma unroll
+        for (int jw = 0; jw < 2; ++jw) {
+            uint32_t o[4];
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+                const uint32_t ub = w[2 * jw + (h >> 1)] ^ 0x80808080u;
+                const int b0 = (h & 1) * 2;
+                const float f0 = __uint_as_float(__byte_perm(ub, 0x4B000000u, 0x7540 | b0)) - 8388736.f;
+                const float f1 = __uint_as_float(__byte_perm(ub, 0x4B000000u, 0x7540 | (b0 + 1))) - 8388736.f;
+                if constexpr (BF16) {
+                    __nv_bfloat162 d = __floats2bfloat162_rn(f0, f1);
+                    o[h] = *reinterpret_cast<uint32_t *>(&d);
+                } else {
+                    __half2 d = __floats2half2_rn(f0, f1);
+                    o[h] = *reinterpret_cast<uint32_t *>(&d);
+                }
+            }
+            const int n8 = part * 2 + jw;
+            const uint32_t da = dst + (n8 >> 3) * W_HALF + k * 128 + (((n8 & 7) ^ (k & 7)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(da), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
+        }
+    }
+}
+
+template <bool Q4, bool BF16, int MT, int NS, int NR>
+__global__ void __launch_bounds__(512, 1)
+wq_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w, const WqParams p) {
+    using L = WqSmem<Q4, MT, NS, NR>;
+    constexpr int TMEM_COLS = 4 * MT < 32 ? 32 : 4 * MT;   // accumulators [issuer][buffer]
+    constexpr uint32_t IDESC = instr_desc(1, BF16 ? 1 : 0, TILE_N, MT);
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *gen_base = smem_raw + (base - smem_u32(smem_raw));
+    auto w_stage = [&](int s) { return base + s * L::STAGE; };
+    auto w_tile = [&](int r, int h) { return base + L::RING_OFF + r * L::SLOT + h * W_TILE; };
+    auto x_tile = [&](int r, int h) { return base + L::RING_OFF + r * L::SLOT + 2 * W_TILE + h * (MT * 128); };
+    auto bar_sfull = [&](int s) { return base + L::BAR_OFF + 8 * s; };
+    auto bar_sempty = [&](int s) { return base + L::BAR_OFF + 8 * (NS + s); };
+    auto bar_ready = [&](int r) { return base + L::BAR_OFF + 8 * (2 * NS + r); };
+    auto bar_done = [&](int d) { return base + L::BAR_OFF + 8 * (2 * NS + NR + d); };
+    auto bar_acc_empty = [&](int issuer, int buf) { return base + L::BAR_OFF + 8 * (2 * NS + NR + ND + issuer * 2 + buf); };
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(gen_base + L::MISC_OFF);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(gen_base + L::MISC_OFF + 4);
+
+#ifdef WQ_PROFILE
+    const long long prof_start = clock64();
+    long long pc[5] = {0, 0, 0, 0, 0};
+#endif
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int P = gridDim.x, cta = blockIdx.x;
+    const long long q_begin = share_begin(cta, p.total_q, P), q_end = share_begin(cta + 1, p.total_q, P);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NS; ++s) { mbar_init(bar_sfull(s), 1); mbar_init(bar_sempty(s), 4); }
+        for (int r = 0; r < NR; ++r) mbar_init(bar_ready(r), 5);   // 4 converter warps + the activation TMA
+        for (int d = 0; d < ND; ++d) mbar_init(bar_done(d), 1);
+        for (int a = 0; a < 4; ++a) mbar_init(bar_acc_empty(a >> 1, a & 1), 4);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_proxy_async();
+    }
+    if (warp == 1) tmem_alloc(smem_u32((const void *)tmem_slot), TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    // Every role walks the same sequence: segments (tile, first quantum qo, len quanta) of this CTA's
+    // share, super-blocks inside a segment, numbered sb = 0,1,2,... over the whole share.
+    // "done(sb)" is phase (sb / ND) of barrier sb % ND.
+#define FOR_EACH_SEGMENT(...)                                                         \
+    for (long long q = q_begin; q < q_end;) {                                         \
+        const int tile = (int)(q / p.qpt), qo = (int)(q % p.qpt);                     \
+        const int len = (int)min((long long)(p.qpt - qo), q_end - q);                 \
+        const int nsb = len * p.sbq;                                                  \
+        (void)tile; (void)nsb;                                                        \
+        __VA_ARGS__                                                                   \
+        q += len;                                                                     \
+    }
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ packed-weight producer
+        if (lane == 0) {
+            int sb = 0;
+            bool ok = true;
+            FOR_EACH_SEGMENT({
+                const int n0 = (tile / p.m_tiles) * TILE_N;
+                for (int j = 0; j < nsb && ok; ++j, ++sb) {
+                    const int s = sb % NS;
+                    PROF_T0();
+                    if (sb >= NS && !mbar_wait(bar_sempty(s), ((sb / NS) - 1) & 1, abort_flag, 21)) { ok = false; break; }
+                    PROF_ADD(0);
+                    mbar_expect_tx(bar_sfull(s), L::STAGE);
+                    tma_load_2d(w_stage(s), &tm_w, bar_sfull(s), Q4 ? n0 / 2 : n0, (qo * p.sbq + j) * SBK);
+                }
+                if (!ok) break;
+            })
+        }
+    } else if (warp == 15) {
+        // ------------------------------------------------------------ activation producer
+        if (lane == 0) {
+            int sb = 0;
+            bool ok = true;
+            FOR_EACH_SEGMENT({
+                const int m0 = (tile % p.m_tiles) * MT;
+                for (int j = 0; j < nsb && ok; ++j, ++sb) {
+                    const int r = sb % NR;
+                    if (sb >= NR && !mbar_wait(bar_done((sb - NR) % ND), ((sb - NR) / ND) & 1, abort_flag, 22)) { ok = false; break; }
+                    mbar_expect_tx(bar_ready(r), L::X_BYTES);
+                    const int k = (qo * p.sbq + j) * SBK;
+                    tma_load_2d(x_tile(r, 0), &tm_x, bar_ready(r), k, m0);
+                    tma_load_2d(x_tile(r, 1), &tm_x, bar_ready(r), k + 64, m0);
+                }
+                if (!ok) break;
+            })
+        }
+    } else if (warp == 1 || warp == 14) {
+        // ------------------------------------------------------------ MMA issuers (even / odd super-blocks)
+        const int me = warp == 1 ? 0 : 1;
+        if (lane == 0) {
+            int sb = 0;
+            int uses = 0;   // accumulations this issuer has started; buffer = uses & 1
+            bool ok = true;
+            FOR_EACH_SEGMENT({
+                const int sb_per_fold = p.grouped ? p.sbq : nsb;
+                for (int j = 0; j < nsb && ok; ++j, ++sb) {
+                    if ((sb & 1) != me) continue;
+                    const int jf = j % sb_per_fold;          // position inside the fold
+                    // first super-block of this issuer in the fold: position 0, or 1 when the fold started on the other lane
+                    const bool first = jf == ((((sb - jf) & 1) == me) ? 0 : 1);
+                    if (first) {
+                        ++uses;
+                        const int u = uses - 1;
+                        if (u >= 2) {
+                            PROF_T0();
+                            if (!mbar_wait(bar_acc_empty(me, u & 1), ((u >> 1) - 1) & 1, abort_flag, 23)) { ok = false; break; }
+                            PROF_ADD(1);
+                            tc_fence_after();   // the epilogue's TMEM reads of this buffer are complete
+                        }
+                    }
+                    const int r = sb % NR, buf = (uses - 1) & 1;
+                    {
+                        PROF_T0();
+                        if (!mbar_wait(bar_ready(r), (sb / NR) & 1, abort_flag, 24)) { ok = false; break; }
+                        PROF_ADD(2);
+                    }
+                    PROF_T0();
+                    const uint32_t d = tmem_base + (me * 2 + buf) * MT;
+                    const uint32_t wa = w_tile(r, 0), xa = x_tile(r, 0);
+#pragma unroll
+                    for (int kk = 0; kk < 8; ++kk) {
+                        if (DBG(1)) continue;
+                        // 16 K rows per MMA: 2 KB further inside a 64-k weight tile, 32 B further inside a 64-k activation box
+                        const uint64_t a_desc = smem_desc(wa + (kk >> 2) * W_TILE + (kk & 3) * 2048, W_HALF, 1024);
+                        const uint64_t b_desc = smem_desc(xa + (kk >> 2) * (MT * 128) + (kk & 3) * 32, 16, 1024);
+                        tc_mma<false>(d, a_desc, b_desc, IDESC, (!first || kk > 0) ? 1u : 0u);
+                    }
+                    tc_commit(bar_done(sb % ND));
+                    PROF_ADD(3);
+                }
+                if (!ok) break;
+            })
+        }
+    } else if (warp < 6) {
+        // ------------------------------------------------------------ epilogue
+        const int qd = warp & 3, rr = qd * 32 + lane;
+        const int col = col_of_lane<Q4>(rr);
+        int sb = 0;
+        int uses[2] = {0, 0};   // mirrors of the issuers' accumulation counters
+        bool alive = true;
+        FOR_EACH_SEGMENT({
+            const int n = (tile / p.m_tiles) * TILE_N + col, m0 = (tile % p.m_tiles) * MT;
+            const bool n_ok = n < p.N;
+            const int folds = p.grouped ? len : 1;
+            const int sb_per_fold = p.grouped ? p.sbq : nsb;
+            constexpr int XR = (MT + 31) / 32;  // activation sums are shared by all lanes: lane l keeps rows l, l+32
+            // Global loads of a fold's scale, offset and activation sums are issued two folds ahead of
+            // their use, after an L2 prefetch of the segment's scale/offset rows.
+            // fetch() only ISSUES the loads: scale and offset stay as raw bits until the fold that uses
+            // them, so no instruction depends on a load that is still in flight.
+            auto fetch = [&](int f, uint32_t &sc, uint32_t &of, float (&xs)[XR]) {
+                const int g = p.grouped ? qo + f : 0;
+                sc = 0u; of = 0u;
+                if (n_ok) {
+                    const size_t idx = (size_t)g * p.N + n;
+                    if (p.sc_type == ET_F32) {
+                        sc = __ldg((const uint32_t *)p.scale + idx);
+                        if (p.offset) of = __ldg((const uint32_t *)p.offset + idx);
+                    } else {
+                        sc = __ldg((const uint16_t *)p.scale + idx);
+                        if (p.offset) of = __ldg((const uint16_t *)p.offset + idx);
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < XR; ++i) {
+                    xs[i] = 0.f;
+                    const int c = lane + 32 * i;
+                    if (p.offset && c < MT && m0 + c < p.M) {
+                        if (p.grouped) xs[i] = __ldg(p.xtab + (size_t)g * p.M + m0 + c);
+                        else xs[i] = __ldg(p.xtab + (size_t)((qo + len) * p.sbq) * p.M + m0 + c) -
+                                     __ldg(p.xtab + (size_t)(qo * p.sbq) * p.M + m0 + c);
+                    }
+                }
+            };
+            auto raw_to_float = [&](uint32_t raw) {
+                return p.sc_type == ET_F32 ? __uint_as_float(raw)
+                     : p.sc_type == ET_BF16 ? __uint_as_float(raw << 16)
+                                            : __half2float(__ushort_as_half((unsigned short)raw));
+            };
+            if (p.grouped) {
+                const int esz = p.sc_type == ET_F32 ? 4 : 2;
+                const size_t col0 = (size_t)(tile / p.m_tiles) * TILE_N;
+                for (int f = threadIdx.x - 64; f < folds; f += 128) {
+                    const char *a0 = (const char *)p.scale + ((size_t)(qo + f) * p.N + col0) * esz;
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(a0));
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(a0 + 128));
+                    if (p.offset) {
+                        const char *a1 = (const char *)p.offset + ((size_t)(qo + f) * p.N + col0) * esz;
+                        asm volatile("prefetch.global.L2 [%0];" ::"l"(a1));
+                        asm volatile("prefetch.global.L2 [%0];" ::"l"(a1 + 128));
+                    }
+                }
+            }
+            float tot[MT];
+#pragma unroll
+            for (int c = 0; c < MT; ++c) tot[c] = 0.f;
+            uint32_t scq[2], ofq[2];
+            float xsq[2][XR];
+            fetch(0, scq[0], ofq[0], xsq[0]);
+            if (folds > 1) fetch(1, scq[1], ofq[1], xsq[1]);
+            for (int f0 = 0; f0 < folds && alive; f0 += 2) {
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    const int f = f0 + u;
+                    if (f >= folds) break;
+                    const float sc = raw_to_float(scq[u]), of = raw_to_float(ofq[u]);
+                    float xs[XR];
+#pragma unroll
+                    for (int i = 0; i < XR; ++i) xs[i] = xsq[u][i];
+                    if (f + 2 < folds) fetch(f + 2, scq[u], ofq[u], xsq[u]);
+                    // the fold's last super-block, and the one before it when the other issuer took part
+                    const int sb_last = sb + sb_per_fold - 1;
+                    {
+                        PROF_T0();
+                        if (!mbar_wait(bar_done(sb_last % ND), (sb_last / ND) & 1, abort_flag, 25)) { alive = false; break; }
+                        if (sb_per_fold >= 2 &&
+                            !mbar_wait(bar_done((sb_last - 1) % ND), ((sb_last - 1) / ND) & 1, abort_flag, 26)) { alive = false; break; }
+                        PROF_ADD(0);
+                    }
+                    PROF_T0();
+                    tc_fence_after();
+                    // which issuers took part in this fold, and the buffer each of them used
+                    const int lanes_used = sb_per_fold >= 2 ? 2 : 1;
+                    const int i0 = lanes_used == 2 ? 0 : (sb_last & 1), i1 = 1;
+                    const int b0 = uses[i0] & 1, b1 = uses[1] & 1;
+#pragma unroll
+                    for (int c0 = 0; c0 < MT; c0 += 16) {
+                        uint32_t v[16], v2[16];
+                        const uint32_t lane_addr = tmem_base + ((uint32_t)(qd * 32) << 16);
+                        tmem_ld16(lane_addr + (i0 * 2 + b0) * MT + c0, v);
+                        if (lanes_used == 2) tmem_ld16(lane_addr + (i1 * 2 + b1) * MT + c0, v2);
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            float acc = __uint_as_float(v[j]);
+                            if (lanes_used == 2) acc += __uint_as_float(v2[j]);
+                            if (p.offset) acc -= of * __shfl_sync(0xffffffffu, xs[(c0 + j) / 32], (c0 + j) % 32);
+                            tot[c0 + j] = fmaf(sc, acc, tot[c0 + j]);
+                        }
+                    }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbar_arrive(bar_acc_empty(i0, b0));
+                        if (lanes_used == 2) mbar_arrive(bar_acc_empty(i1, b1));
+                    }
+                    ++uses[i0];
+                    if (lanes_used == 2) ++uses[i1];
+                    PROF_ADD(1);
+                    sb += sb_per_fold;
+                }
+            }
+            if (!alive) break;
+            if (len == p.qpt) {
+                // the whole tile is ours: finish it here
+                if (n_ok) {
+                    const float bv = p.bias ? load_as_float(p.bias, p.sc_type, n) : 0.f;
+#pragma unroll
+                    for (int c = 0; c < MT; ++c)
+                        if (m0 + c < p.M) store_from_float(p.out, p.out_type, (size_t)(m0 + c) * p.N + n, tot[c] + bv);
+                }
+            } else {
+                float *dst = p.slots + ((size_t)(tile + cta) * MT) * TILE_N + col;
+#pragma unroll
+                for (int c = 0; c < MT; ++c) dst[(size_t)c * TILE_N] = tot[c];
+            }
+        })
+    } else {
+        // ------------------------------------------------------------ converter teams (even / odd super-blocks)
+        const int team = warp < 10 ? 0 : 1;
+        const int t = (threadIdx.x - 192) & 127;       // 0..127 inside the team
+        const int row8 = t & 7;
+        constexpr int PARTS = Q4 ? 4 : 8;              // 16-byte chunks per staged row
+        constexpr int TASKS = Q4 ? 2 : 4;              // chunks per thread per 64-k tile
+        int sb = 0;
+        bool ok = true;
+        FOR_EACH_SEGMENT({
+            for (int j = 0; j < nsb && ok; ++j, ++sb) {
+                if ((sb & 1) != team) continue;
+                const int s = sb % NS, r = sb % NR;
+                {
+                    PROF_T0();
+                    if (!mbar_wait(bar_sfull(s), (sb / NS) & 1, abort_flag, 27)) { ok = false; break; }
+                    PROF_ADD(0);
+                }
+                {
+                    PROF_T0();
+                    if (sb >= NR && !mbar_wait(bar_done((sb - NR) % ND), ((sb - NR) / ND) & 1, abort_flag, 28)) { ok = false; break; }
+                    PROF_ADD(1);
+                }
+                PROF_T0();
+                const uint32_t src = w_stage(s);
+                if (!DBG(0)) {
+                    // all loads of the super-block first (independent), then the conversions
+                    uint32_t w[2 * TASKS][4];
+#pragma unroll
+                    for (int i = 0; i < 2 * TASKS; ++i) {
+                        const int h = i / TASKS, task = i % TASKS;
+                        const int uidx = (t >> 3) + 16 * task;
+                        const int rg = uidx / PARTS, part = uidx % PARTS;
+                        const int k = h * 64 + rg * 8 + row8;     // row inside the staged super-block
+                        const uint32_t sa = Q4 ? src + k * 64 + ((part ^ ((k >> 1) & 3)) << 4)     // 64-byte TMA swizzle
+                                               : src + k * 128 + ((part ^ (k & 7)) << 4);          // 128-byte TMA swizzle
+                        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                                     : "=r"(w[i][0]), "=r"(w[i][1]), "=r"(w[i][2]), "=r"(w[i][3]) : "r"(sa));
+                    }
+#pragma unroll
+                    for (int i = 0; i < 2 * TASKS; ++i) {
+                        const int h = i / TASKS, task = i % TASKS;
+                        const int uidx = (t >> 3) + 16 * task;
+                        const int rg = uidx / PARTS, part = uidx % PARTS;
+                        convert_chunk<Q4, BF16>(w[i], w_tile(r, h), rg * 8 + row8, part);
+                    }
+                }
+                PROF_ADD(2);
+                {
+                    PROF_T0();
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) { mbar_arrive(bar_sempty(s)); mbar_arrive(bar_ready(r)); }
+                    PROF_ADD(3);
+                }
+            }
+            if (!ok) break;
+        })
+    }
+#undef FOR_EACH_SEGMENT
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+#ifdef WQ_PROFILE
+    if (blockIdx.x == 0 && lane == 0) {
+        if (warp == 0) { g_prof[0] += pc[0]; g_prof[15] += (unsigned long long)(clock64() - prof_start); g_prof[16] += (unsigned long long)(q_end - q_begin) * p.sbq; }
+        if (warp == 1) for (int i = 1; i < 4; ++i) g_prof[i] += pc[i];
+        if (warp == 2) { g_prof[5] += pc[0]; g_prof[6] += pc[1]; }
+        if (warp == 6) for (int i = 0; i < 4; ++i) g_prof[7 + i] += pc[i];
+    }
+#endif
+}
+
+// Table of activation sums the epilogue needs (fp32).
+//   grouped:     out[g][m]  = sum of x[m][k] over scale group g
+//   per-channel: out[sb][m] = sum of x[m][k] over k < sb*128   (prefix sums, sb = 0..num_sb)
+// One block per row m; the row is scanned in chunks of `rows` elements.
+__global__ void wq_xtab_kernel(const void *x, int x_type, int M, int K, int rows, int entries, int prefix, float *out) {
+    const int m = blockIdx.x;
+    __shared__ float part[1024];
+    for (int e0 = 0; e0 < entries; e0 += 1024) {
+        // entry e covers k in [e*rows, (e+1)*rows); 8 threads per entry, all threads run every round
+        const int lim = min(entries, e0 + 1024);
+        for (int eb = e0; eb < lim; eb += blockDim.x >> 3) {
+            const int e = eb + (threadIdx.x >> 3);
+            float s = 0.f;
+            if (e < lim) {
+                const int k0 = e * rows, k1 = min(K, k0 + rows);
+                for (int k = k0 + (threadIdx.x & 7); k < k1; k += 8) s += load_as_float(x, x_type, (size_t)m * K + k);
+            }
+            s += __shfl_xor_sync(0xffffffffu, s, 4);
+            s += __shfl_xor_sync(0xffffffffu, s, 2);
+            s += __shfl_xor_sync(0xffffffffu, s, 1);
+            if (e < lim && (threadIdx.x & 7) == 0) part[e - e0] = s;
+        }
+        __syncthreads();
+        if (!prefix) {
+            for (int e = e0 + threadIdx.x; e < min(entries, e0 + 1024); e += blockDim.x) out[(size_t)e * M + m] = part[e - e0];
+        }
+        __syncthreads();
+        if (prefix && threadIdx.x == 0) {
+            float run = e0 == 0 ? 0.f : out[(size_t)e0 * M + m];
+            if (e0 == 0) out[m] = 0.f;
+            for (int e = e0; e < min(entries, e0 + 1024); ++e) { run += part[e - e0]; out[(size_t)(e + 1) * M + m] = run; }
+        }
+        __syncthreads();
+    }
+}
+
+// Sums the partial tiles of every output tile that was shared between CTAs, adds the bias, casts.
+template <int MT>
+__global__ void wq_finalize_kernel(WqParams p, int P) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)p.M * p.N) return;
+    const int n = (int)(i % p.N), m = (int)(i / p.N);
+    const int tile = (n / TILE_N) * p.m_tiles + m / MT;
+    const long long qa = (long long)tile * p.qpt;
+    const int c_first = share_owner(qa, p.total_q, P), c_last = share_owner(qa + p.qpt - 1, p.total_q, P);
+    if (c_first == c_last) return;  // written directly by its only owner
+    float v = 0.f;
+    for (int c = c_first; c <= c_last; ++c)
+        v += p.slots[((size_t)(tile + c) * MT + (m % MT)) * TILE_N + (n % TILE_N)];
+    if (p.bias) v += load_as_float(p.bias, p.sc_type, n);
+    store_from_float(p.out, p.out_type, i, v);
+}
+
+int sm_count() {
+    static int cached[64];
+    static std::once_flag once;
+    std::call_once(once, [] { for (int &c : cached) c = 0; });
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    dev &= 63;
+    if (!cached[dev]) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+struct WqPlan {
+    int mt, m_tiles, n_tiles, tiles, num_sb, sbq, qpt, grouped, P, entries;
+    long long total_q;
+    uint64_t xtab_bytes, slot_bytes;
+};
+
+WqPlan wq_make_plan(const MatmulArgs &p) {
+    WqPlan pl{};
+    pl.mt = p.M <= 16 ? 16 : (p.M <= 32 ? 32 : 64);
+    pl.m_tiles = (int)((p.M + pl.mt - 1) / pl.mt);
+    pl.n_tiles = (int)((p.N + TILE_N - 1) / TILE_N);
+    pl.tiles = pl.m_tiles * pl.n_tiles;
+    pl.num_sb = (int)((p.K + SBK - 1) / SBK);
+    pl.grouped = p.group < p.K ? 1 : 0;
+    pl.sbq = pl.grouped ? (int)(p.group / SBK) : 1;
+    pl.qpt = pl.num_sb / pl.sbq;
+    pl.total_q = (long long)pl.tiles * pl.qpt;
+    const int sms = sm_count();
+    pl.P = (int)(pl.total_q < sms ? pl.total_q : sms);
+    pl.entries = pl.grouped ? pl.qpt : pl.num_sb;
+    pl.xtab_bytes = p.offset ? align_up_u64((uint64_t)(pl.entries + 1) * p.M * sizeof(float), 256) : 0;
+    pl.slot_bytes = (uint64_t)(pl.tiles + pl.P) * pl.mt * TILE_N * sizeof(float);
+    return pl;
+}
+
+template <bool Q4, bool BF16, int MT, int NS, int NR>
+cudaError_t wq_launch_one(const CUtensorMap &tx, const CUtensorMap &tw, const WqParams &wp, int P, cudaStream_t s) {
+    using L = WqSmem<Q4, MT, NS, NR>;
+    static_assert(L::TOTAL <= 232448, "shared memory budget of one CTA");
+    static_assert(NR < ND && NS >= 2, "ring depths");
+    auto kern = wq_tc_kernel<Q4, BF16, MT, NS, NR>;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!attr_set[dev & 63]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+        if (e != cudaSuccess) return e;
+        attr_set[dev & 63] = true;
+    }
+    kern<<<P, 512, L::TOTAL, s>>>(tx, tw, wp);
+    count_launch();
+    return cudaGetLastError();
+}
+
+template <bool Q4, bool BF16>
+cudaError_t wq_dispatch(int mt, const CUtensorMap &tx, const CUtensorMap &tw, const WqParams &wp, int P, cudaStream_t s) {
+    // staging ring (packed weights in flight from HBM) x MMA ring (converted tiles + activations)
+    switch (mt) {
+        case 16: return wq_launch_one<Q4, BF16, 16, Q4 ? 6 : 4, Q4 ? 4 : 3>(tx, tw, wp, P, s);
+        case 32: return wq_launch_one<Q4, BF16, 32, Q4 ? 6 : 4, Q4 ? 4 : 3>(tx, tw, wp, P, s);
+        default: return wq_launch_one<Q4, BF16, 64, Q4 ? 6 : 4, 3>(tx, tw, wp, P, s);
+    }
+}
+
+}  // namespace
+
+bool wq_tc_supported(const MatmulArgs &p) {
+    if (p.epilogue != EPI_PLAIN || !p.scale || p.a_scale || p.b_scale) return false;
+    if (p.batch != 1 || p.b_transposed || p.accumulate || p.M < 1) return false;
+    if (p.a_type != ET_F16 && p.a_type != ET_BF16) return false;
+    if (p.b_type != ET_I4 && p.b_type != ET_I8) return false;
+    if (p.sc_type != p.a_type || p.out_type != p.a_type || (p.bias && p.bias_type != p.a_type)) return false;
+    if (p.K % 8 != 0 || p.K < SBK) return false;
+    if (p.b_type == ET_I4 ? (p.N % 32 != 0) : (p.N % 16 != 0)) return false;
+    if (p.group < p.K && (p.group % SBK != 0 || p.K % p.group != 0)) return false;
+    if (p.M > (1 << 20) || p.N > (1 << 24) || p.K > (1 << 24)) return false;
+    return true;
+}
+
+uint64_t wq_tc_workspace_bytes(const MatmulArgs &p) {
+    WqPlan pl = wq_make_plan(p);
+    return pl.xtab_bytes + pl.slot_bytes;
+}
+
+cudaError_t launch_wq_tc(const MatmulArgs &p, cudaStream_t s) {
+    const WqPlan pl = wq_make_plan(p);
+    if (p.workspace_bytes < pl.xtab_bytes + pl.slot_bytes || !p.workspace) return cudaErrorInvalidValue;
+    if ((reinterpret_cast<uintptr_t>(p.a) & 15) || (reinterpret_cast<uintptr_t>(p.b) & 15)) return cudaErrorMisalignedAddress;
+    const bool q4 = p.b_type == ET_I4, bf = p.a_type == ET_BF16;
+
+    CUtensorMap tx, tw;
+    bool ok = make_map(&tx, p.a, bf ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, p.K, p.M, p.K * 2, 64,
+                       pl.mt, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (q4) ok = ok && make_map(&tw, p.b, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.N / 2, p.K, p.N / 2, 64, SBK, CU_TENSOR_MAP_SWIZZLE_64B);
+    else ok = ok && make_map(&tw, p.b, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.N, p.K, p.N, 128, SBK, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (!ok) return cudaErrorInvalidValue;
+
+    char *ws = (char *)p.workspace;
+    WqParams wp{};
+    wp.out = p.out;
+    wp.xtab = p.offset ? (const float *)ws : nullptr;
+    wp.slots = (float *)(ws + pl.xtab_bytes);
+    wp.scale = p.scale; wp.offset = p.offset; wp.bias = p.bias;
+    wp.sc_type = p.sc_type; wp.out_type = p.out_type;
+    wp.M = (int)p.M; wp.N = (int)p.N; wp.K = (int)p.K;
+    wp.m_tiles = pl.m_tiles; wp.num_sb = pl.num_sb; wp.sbq = pl.sbq; wp.qpt = pl.qpt; wp.total_q = pl.total_q;
+    wp.grouped = pl.grouped;
+
+    cudaError_t e;
+    if (p.offset) {
+        wq_xtab_kernel<<<(unsigned)p.M, 256, 0, s>>>(p.a, p.a_type, wp.M, wp.K, pl.grouped ? (int)p.group : SBK, pl.entries,
+                                                     pl.grouped ? 0 : 1, (float *)ws);
+        count_launch();
+        if ((e = cudaGetLastError()) != cudaSuccess) return e;
+    }
+    if (q4) e = bf ? wq_dispatch<true, true>(pl.mt, tx, tw, wp, pl.P, s) : wq_dispatch<true, false>(pl.mt, tx, tw, wp, pl.P, s);
+    else e = bf ? wq_dispatch<false, true>(pl.mt, tx, tw, wp, pl.P, s) : wq_dispatch<false, false>(pl.mt, tx, tw, wp, pl.P, s);
+    if (e != cudaSuccess) return e;
+    // Tiles shared between CTAs exist unless every share boundary falls on a tile boundary.
+    if (pl.total_q % pl.P != 0 || (pl.total_q / pl.P) % pl.qpt != 0) {
+        const size_t mn = (size_t)p.M * p.N;
+        const unsigned blocks = (unsigned)((mn + 255) / 256);
+        switch (pl.mt) {
+            case 16: wq_finalize_kernel<16><<<blocks, 256, 0, s>>>(wp, pl.P); break;
+            case 32: wq_finalize_kernel<32><<<blocks, 256, 0, s>>>(wp, pl.P); break;
+            default: wq_finalize_kernel<64><<<blocks, 256, 0, s>>>(wp, pl.P); break;
+        }
+        count_launch();
+        e = cudaGetLastError();
+    }
+    return e;
+}
+
+#ifdef WQ_PROFILE
+extern "C" __attribute__((visibility("default"))) void wqProfileFlags(unsigned int f) { cudaMemcpyToSymbol(g_dbg_flags, &f, sizeof(f)); }
+extern "C" __attribute__((visibility("default"))) void wqProfileRead(unsigned long long *out, int reset) {
+    cudaMemcpyFromSymbol(out, g_prof, sizeof(unsigned long long) * 32);
+    if (reset) { unsigned long long z[32] = {}; cudaMemcpyToSymbol(g_prof, z, sizeof(z)); }
+}
+#endif
+
+unsigned int wq_tc_device_status() {
+    unsigned int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(v)) != cudaSuccess) return 0xFFFFFFFFu;
+    return v;
+}
+
+}  // namespace qmm
