@@ -98,7 +98,6 @@ void choose_path(aclOpExecutor *e, uint64_t *ws) {
     if (want == PATH_TC && tc_ok) e->path = PATH_TC;
     else if (want == PATH_GEMV && gemv_ok) e->path = PATH_GEMV;
     else if (want == PATH_GENERIC) e->path = PATH_GENERIC;
-    else if (gemv_ok && e->m <= 2) e->path = PATH_GEMV;
     else if (tc_ok) e->path = PATH_TC;
     else if (gemv_ok) e->path = PATH_GEMV;
     if (e->path == PATH_GEMV) {

@@ -1,6 +1,6 @@
 // Weight-only quantized matmul (W4A16 / W8A16) on tcgen05: persistent, stream-K, fused dequant.
 //
-// Per CTA (one per SM, 16 warps).  The unit of work is a "super-block" of 128 rows of K for one
+// Per CTA (one per SM, 20 warps).  The unit of work is a "super-block" of 128 rows of K for one
 // 128-column tile; even and odd super-blocks run on two independent lanes of the pipeline:
 //   warp 0        weight producer: TMA of the PACKED rows [128 k][128 n] (64 B or 128 B per row) into
 //                 a ring of staging slots -- this is what keeps tens of KB per SM in flight from HBM.
@@ -12,7 +12,8 @@
 //                 weights on the M side (128 columns n), activations on the N side (MT rows m), fp32
 //                 accumulators in TMEM, ONE tcgen05.commit per super-block (it releases the ring slot
 //                 and publishes the accumulator at once).
-//   warps 2-5     epilogue: per scale group, fold the finished accumulator(s) into fp32 registers with
+//   warps 2-5,    two epilogue sets (even / odd scale groups): fold the finished accumulator(s) into fp32 registers with
+//   warps 16-19
 //                 the reference's algebra  tot += s_g[n] * (sum x*q - off_g[n] * sum_g x)
 //                 (cuda/src/ops/matmul.cu:334-335), then write the tile or its partial sums.
 // Two issuers and two converter teams exist because the costs that matter at decode shapes are
@@ -45,7 +46,7 @@ __device__ unsigned long long g_prof[32];
 __device__ unsigned int g_dbg_flags;
 #define PROF_T0() const long long _t0 = clock64()
 #define PROF_ADD(i) do { pc[i] += clock64() - _t0; } while (0)
-#define DBG(bit) ((g_dbg_flags >> (bit)) & 1u)
+#define DBG(bit) ((dbg_flags >> (bit)) & 1u)
 #else
 #define DBG(bit) 0
 #define PROF_T0() do {} while (0)
@@ -74,9 +75,10 @@ struct WqSmem {
     static constexpr int SLOT = 2 * W_TILE + X_BYTES;        // MMA ring slot
     static constexpr int RING_OFF = NS * STAGE;
     static constexpr int BAR_OFF = RING_OFF + NR * SLOT;
-    static constexpr int NUM_BARS = 2 * NS + NR + ND + 4;
+    static constexpr int NUM_BARS = 2 * NS + NR + ND + 6;
     static constexpr int MISC_OFF = BAR_OFF + NUM_BARS * 8;
-    static constexpr int TOTAL = MISC_OFF + 16 + 1024;
+    static constexpr int MERGE_OFF = (MISC_OFF + 16 + 15) / 16 * 16;    // [MT][128] fp32: epilogue set 1 -> set 0
+    static constexpr int TOTAL = MERGE_OFF + (MT == 64 ? 0 : MT * TILE_N * 4) + 1024;
 };
 
 // Share of CTA c: quanta [c*T/P, (c+1)*T/P).
@@ -140,7 +142,7 @@ __device__ __forceinline__ void convert_chunk(const uint32_t (&w)[4], uint32_t d
 }
 
 template <bool Q4, bool BF16, int MT, int NS, int NR>
-__global__ void __launch_bounds__(512, 1)
+__global__ void __launch_bounds__(640, 1)
 wq_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w, const WqParams p) {
     using L = WqSmem<Q4, MT, NS, NR>;
     constexpr int TMEM_COLS = 4 * MT < 32 ? 32 : 4 * MT;   // accumulators [issuer][buffer]
@@ -157,12 +159,14 @@ wq_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
     auto bar_ready = [&](int r) { return base + L::BAR_OFF + 8 * (2 * NS + r); };
     auto bar_done = [&](int d) { return base + L::BAR_OFF + 8 * (2 * NS + NR + d); };
     auto bar_acc_empty = [&](int issuer, int buf) { return base + L::BAR_OFF + 8 * (2 * NS + NR + ND + issuer * 2 + buf); };
+    auto bar_merge = [&](int i) { return base + L::BAR_OFF + 8 * (2 * NS + NR + ND + 4 + i); };   // 0: full, 1: free
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(gen_base + L::MISC_OFF);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(gen_base + L::MISC_OFF + 4);
 
 #ifdef WQ_PROFILE
     const long long prof_start = clock64();
     long long pc[5] = {0, 0, 0, 0, 0};
+    const unsigned dbg_flags = g_dbg_flags;
 #endif
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int P = gridDim.x, cta = blockIdx.x;
@@ -172,7 +176,9 @@ wq_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
         for (int s = 0; s < NS; ++s) { mbar_init(bar_sfull(s), 1); mbar_init(bar_sempty(s), 4); }
         for (int r = 0; r < NR; ++r) mbar_init(bar_ready(r), 5);   // 4 converter warps + the activation TMA
         for (int d = 0; d < ND; ++d) mbar_init(bar_done(d), 1);
-        for (int a = 0; a < 4; ++a) mbar_init(bar_acc_empty(a >> 1, a & 1), 4);
+        for (int a = 0; a < 4; ++a) mbar_init(bar_acc_empty(a >> 1, a & 1), MT == 64 ? 8 : 4);
+        mbar_init(bar_merge(0), 4);
+        mbar_init(bar_merge(1), 4);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_proxy_async();
@@ -279,23 +285,37 @@ wq_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
                 if (!ok) break;
             })
         }
-    } else if (warp < 6) {
-        // ------------------------------------------------------------ epilogue
+    } else if (warp < 6 || warp >= 16) {
+        // ------------------------------------------------------------ epilogue (two sets of four warps)
+        // With one super-block per scale group, set 0 (warps 2-5) folds the groups of issuer 0 and set 1
+        // (warps 16-19) those of issuer 1, each into its own registers; at the end of a segment set 1
+        // hands its sums to set 0 through shared memory.  Folds that span both issuers (wider groups,
+        // per-channel scales) are done by set 0 alone.
+        const int eset = warp >= 16 ? 1 : 0;
+        const int et = (warp >= 16 ? (warp - 16) : (warp - 2)) * 32 + lane;   // 0..127 inside the set
         const int qd = warp & 3, rr = qd * 32 + lane;
         const int col = col_of_lane<Q4>(rr);
+        float *merge = reinterpret_cast<float *>(gen_base + L::MERGE_OFF);
         int sb = 0;
-        int uses[2] = {0, 0};   // mirrors of the issuers' accumulation counters
+        int uses0 = 0, uses1 = 0;   // mirrors of the issuers' accumulation counters
+        int merges = 0;             // hand-overs from set 1 to set 0 so far
         bool alive = true;
         FOR_EACH_SEGMENT({
             const int n = (tile / p.m_tiles) * TILE_N + col, m0 = (tile % p.m_tiles) * MT;
             const bool n_ok = n < p.N;
             const int folds = p.grouped ? len : 1;
             const int sb_per_fold = p.grouped ? p.sbq : nsb;
+            // MT = 64: the two sets split the 64 accumulator columns (32 registers each) and both take every
+            // fold; smaller tiles: the sets split the folds when every fold belongs to one issuer.
+            constexpr bool COLSPLIT = MT == 64;
+            constexpr int CT = COLSPLIT ? 32 : MT;               // accumulator columns per thread
+            const int cb = COLSPLIT ? eset * 32 : 0;             // first of them
+            const bool single = sb_per_fold == 1;                // every fold has one issuer
+            const bool split_sets = single && !COLSPLIT;         // folds alternate between the two sets
             constexpr int XR = (MT + 31) / 32;  // activation sums are shared by all lanes: lane l keeps rows l, l+32
-            // Global loads of a fold's scale, offset and activation sums are issued two folds ahead of
-            // their use, after an L2 prefetch of the segment's scale/offset rows.
-            // fetch() only ISSUES the loads: scale and offset stay as raw bits until the fold that uses
-            // them, so no instruction depends on a load that is still in flight.
+            // fetch() only ISSUES the loads of a fold's scale, offset and activation sums: scale and
+            // offset stay as raw bits until the fold that uses them, two own folds later, so no
+            // instruction depends on a load that is still in flight.
             auto fetch = [&](int f, uint32_t &sc, uint32_t &of, float (&xs)[XR]) {
                 const int g = p.grouped ? qo + f : 0;
                 sc = 0u; of = 0u;
@@ -325,10 +345,10 @@ wq_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
                      : p.sc_type == ET_BF16 ? __uint_as_float(raw << 16)
                                             : __half2float(__ushort_as_half((unsigned short)raw));
             };
-            if (p.grouped) {
+            if (p.grouped && eset == 0) {
                 const int esz = p.sc_type == ET_F32 ? 4 : 2;
                 const size_t col0 = (size_t)(tile / p.m_tiles) * TILE_N;
-                for (int f = threadIdx.x - 64; f < folds; f += 128) {
+                for (int f = et; f < folds; f += 128) {
                     const char *a0 = (const char *)p.scale + ((size_t)(qo + f) * p.N + col0) * esz;
                     asm volatile("prefetch.global.L2 [%0];" ::"l"(a0));
                     asm volatile("prefetch.global.L2 [%0];" ::"l"(a0 + 128));
@@ -339,25 +359,43 @@ wq_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
                     }
                 }
             }
-            float tot[MT];
+            float tot[CT];
 #pragma unroll
-            for (int c = 0; c < MT; ++c) tot[c] = 0.f;
+            for (int c = 0; c < CT; ++c) tot[c] = 0.f;
+            // own folds: every fold (set 0, shared folds) or every second one starting at f_first
+            const int f_step = split_sets ? 2 : 1;
+            const int f_first = split_sets ? ((sb & 1) == eset ? 0 : 1) : 0;
+            const bool active = COLSPLIT || split_sets || eset == 0;
             uint32_t scq[2], ofq[2];
             float xsq[2][XR];
-            fetch(0, scq[0], ofq[0], xsq[0]);
-            if (folds > 1) fetch(1, scq[1], ofq[1], xsq[1]);
-            for (int f0 = 0; f0 < folds && alive; f0 += 2) {
+            if (active) {
+                if (f_first < folds) fetch(f_first, scq[0], ofq[0], xsq[0]);
+                if (f_first + f_step < folds) fetch(f_first + f_step, scq[1], ofq[1], xsq[1]);
+            }
+            for (int f0 = f_first; active && f0 < folds && alive; f0 += 2 * f_step) {
 #pragma unroll
                 for (int u = 0; u < 2; ++u) {
-                    const int f = f0 + u;
+                    const int f = f0 + u * f_step;
                     if (f >= folds) break;
                     const float sc = raw_to_float(scq[u]), of = raw_to_float(ofq[u]);
                     float xs[XR];
 #pragma unroll
                     for (int i = 0; i < XR; ++i) xs[i] = xsq[u][i];
-                    if (f + 2 < folds) fetch(f + 2, scq[u], ofq[u], xsq[u]);
+                    { PROF_T0(); if (f + 2 * f_step < folds) fetch(f + 2 * f_step, scq[u], ofq[u], xsq[u]); PROF_ADD(2); }
                     // the fold's last super-block, and the one before it when the other issuer took part
-                    const int sb_last = sb + sb_per_fold - 1;
+                    const int sb_first = sb + f * sb_per_fold, sb_last = sb_first + sb_per_fold - 1;
+                    // accumulation counters of the two issuers at this fold: split sets -> one use per own fold
+                    const int done_folds = f;   // folds of this segment before this one
+                    int u0, u1;
+                    if (single) {
+                        // issuer i has taken the folds whose super-block has parity i
+                        const int before0 = (done_folds + ((sb & 1) == 0 ? 1 : 0)) >> 1;
+                        u0 = uses0 + before0;
+                        u1 = uses1 + (done_folds - before0);
+                    } else {
+                        u0 = uses0 + done_folds;
+                        u1 = uses1 + done_folds;
+                    }
                     {
                         PROF_T0();
                         if (!mbar_wait(bar_done(sb_last % ND), (sb_last / ND) & 1, abort_flag, 25)) { alive = false; break; }
@@ -367,21 +405,25 @@ wq_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
                     }
                     PROF_T0();
                     tc_fence_after();
-                    // which issuers took part in this fold, and the buffer each of them used
                     const int lanes_used = sb_per_fold >= 2 ? 2 : 1;
-                    const int i0 = lanes_used == 2 ? 0 : (sb_last & 1), i1 = 1;
-                    const int b0 = uses[i0] & 1, b1 = uses[1] & 1;
+                    const int i0 = lanes_used == 2 ? 0 : (sb_last & 1);
+                    const int b0 = (i0 == 0 ? u0 : u1) & 1, b1 = u1 & 1;
+                    const float xsel = COLSPLIT ? (eset ? xs[XR - 1] : xs[0]) : 0.f;
 #pragma unroll
-                    for (int c0 = 0; c0 < MT; c0 += 16) {
+                    for (int c0 = 0; c0 < CT; c0 += 16) {
                         uint32_t v[16], v2[16];
                         const uint32_t lane_addr = tmem_base + ((uint32_t)(qd * 32) << 16);
-                        tmem_ld16(lane_addr + (i0 * 2 + b0) * MT + c0, v);
-                        if (lanes_used == 2) tmem_ld16(lane_addr + (i1 * 2 + b1) * MT + c0, v2);
+                        tmem_ld16(lane_addr + (i0 * 2 + b0) * MT + cb + c0, v);
+                        if (lanes_used == 2) tmem_ld16(lane_addr + (2 + b1) * MT + cb + c0, v2);
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {
                             float acc = __uint_as_float(v[j]);
                             if (lanes_used == 2) acc += __uint_as_float(v2[j]);
-                            if (p.offset) acc -= of * __shfl_sync(0xffffffffu, xs[(c0 + j) / 32], (c0 + j) % 32);
+                            if (p.offset) {
+                                const float xv = COLSPLIT ? __shfl_sync(0xffffffffu, xsel, c0 + j)
+                                                          : __shfl_sync(0xffffffffu, xs[(c0 + j) / 32], (c0 + j) % 32);
+                                acc -= of * xv;
+                            }
                             tot[c0 + j] = fmaf(sc, acc, tot[c0 + j]);
                         }
                     }
@@ -389,27 +431,53 @@ wq_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
                     __syncwarp();
                     if (lane == 0) {
                         mbar_arrive(bar_acc_empty(i0, b0));
-                        if (lanes_used == 2) mbar_arrive(bar_acc_empty(i1, b1));
+                        if (lanes_used == 2) mbar_arrive(bar_acc_empty(1, b1));
                     }
-                    ++uses[i0];
-                    if (lanes_used == 2) ++uses[i1];
                     PROF_ADD(1);
-                    sb += sb_per_fold;
                 }
             }
             if (!alive) break;
-            if (len == p.qpt) {
-                // the whole tile is ours: finish it here
-                if (n_ok) {
-                    const float bv = p.bias ? load_as_float(p.bias, p.sc_type, n) : 0.f;
-#pragma unroll
-                    for (int c = 0; c < MT; ++c)
-                        if (m0 + c < p.M) store_from_float(p.out, p.out_type, (size_t)(m0 + c) * p.N + n, tot[c] + bv);
-                }
+            // counters and super-block index after the segment (both sets keep both in step)
+            if (single) {
+                const int took0 = (folds + ((sb & 1) == 0 ? 1 : 0)) >> 1;
+                uses0 += took0;
+                uses1 += folds - took0;
             } else {
-                float *dst = p.slots + ((size_t)(tile + cta) * MT) * TILE_N + col;
+                uses0 += folds;
+                uses1 += folds;
+            }
+            sb += folds * sb_per_fold;
+            if (split_sets) {
+                // set 1 hands its sums over through shared memory; set 0 adds them (bounded mbarrier waits)
+                if (eset == 1) {
+                    if (merges >= 1 && !mbar_wait(bar_merge(1), (merges - 1) & 1, abort_flag, 29)) break;
 #pragma unroll
-                for (int c = 0; c < MT; ++c) dst[(size_t)c * TILE_N] = tot[c];
+                    for (int c = 0; c < CT; ++c) merge[c * TILE_N + rr] = tot[c];
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_merge(0));
+                } else {
+                    if (!mbar_wait(bar_merge(0), merges & 1, abort_flag, 30)) break;
+#pragma unroll
+                    for (int c = 0; c < CT; ++c) tot[c] += merge[c * TILE_N + rr];
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_merge(1));
+                }
+                ++merges;
+            }
+            if (eset == 0 || COLSPLIT) {
+                if (len == p.qpt) {
+                    // the whole tile is ours: finish it here
+                    if (n_ok) {
+                        const float bv = p.bias ? load_as_float(p.bias, p.sc_type, n) : 0.f;
+#pragma unroll
+                        for (int c = 0; c < CT; ++c)
+                            if (m0 + cb + c < p.M) store_from_float(p.out, p.out_type, (size_t)(m0 + cb + c) * p.N + n, tot[c] + bv);
+                    }
+                } else {
+                    float *dst = p.slots + ((size_t)(tile + cta) * MT + cb) * TILE_N + col;
+#pragma unroll
+                    for (int c = 0; c < CT; ++c) dst[(size_t)c * TILE_N] = tot[c];
+                }
             }
         })
     } else {
@@ -483,7 +551,7 @@ wq_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
     if (blockIdx.x == 0 && lane == 0) {
         if (warp == 0) { g_prof[0] += pc[0]; g_prof[15] += (unsigned long long)(clock64() - prof_start); g_prof[16] += (unsigned long long)(q_end - q_begin) * p.sbq; }
         if (warp == 1) for (int i = 1; i < 4; ++i) g_prof[i] += pc[i];
-        if (warp == 2) { g_prof[5] += pc[0]; g_prof[6] += pc[1]; }
+        if (warp == 2) { g_prof[5] += pc[0]; g_prof[6] += pc[1]; g_prof[4] += pc[2]; }
         if (warp == 6) for (int i = 0; i < 4; ++i) g_prof[7 + i] += pc[i];
     }
 #endif
@@ -596,7 +664,7 @@ cudaError_t wq_launch_one(const CUtensorMap &tx, const CUtensorMap &tw, const Wq
         if (e != cudaSuccess) return e;
         attr_set[dev & 63] = true;
     }
-    kern<<<P, 512, L::TOTAL, s>>>(tx, tw, wp);
+    kern<<<P, 640, L::TOTAL, s>>>(tx, tw, wp);
     count_launch();
     return cudaGetLastError();
 }
@@ -606,7 +674,7 @@ cudaError_t wq_dispatch(int mt, const CUtensorMap &tx, const CUtensorMap &tw, co
     // staging ring (packed weights in flight from HBM) x MMA ring (converted tiles + activations)
     switch (mt) {
         case 16: return wq_launch_one<Q4, BF16, 16, Q4 ? 6 : 4, Q4 ? 4 : 3>(tx, tw, wp, P, s);
-        case 32: return wq_launch_one<Q4, BF16, 32, Q4 ? 6 : 4, Q4 ? 4 : 3>(tx, tw, wp, P, s);
+        case 32: return wq_launch_one<Q4, BF16, 32, Q4 ? 5 : 4, Q4 ? 4 : 3>(tx, tw, wp, P, s);
         default: return wq_launch_one<Q4, BF16, 64, Q4 ? 6 : 4, 3>(tx, tw, wp, P, s);
     }
 }
