@@ -2,17 +2,20 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--no-sweep]
 
-Workload (config.workload): W4A16 group-wise weight-only matmul, x bf16 [M=16, K=4096] @ int4
-[4096, 4096] with bf16 scales and offsets per 128 rows of K and a bf16 bias -- the decode-shaped,
-HBM-bound case of the benchmark configurations.  One step is one pass of the operator over a ring
-of R distinct weight sets whose total size exceeds twice the L2, so every call streams its weights
-from HBM.  The metric is weight GB/s: packed weight bytes streamed per second, summed over ranks.
+Workload (config.workload): the largest single-GPU configuration of the benchmark set -- the
+Llama-70B-shaped gate/up projection as a W4A16 group-wise weight-only matmul, x bf16 [M=1, K=8192] @
+int4 [8192, 28672] with bf16 scales per 128 rows of K (117 MB of packed weights per call, decode
+shape, HBM-bound).  The smaller W4A16 configuration (4096 x 4096, 8.4 MB) fits in L2 and its ideal
+time of 1.3 us is below a kernel launch, so it cannot show a memory roofline; it is reported in the
+sweep instead.  One step is one pass of the operator over a ring of R distinct weight sets whose
+total size exceeds twice the L2, so every call streams its weights from HBM.  The metric is weight
+GB/s: packed weight bytes streamed per second, summed over ranks.
 
-With N > 1 (launched by torch.distributed.run) every rank owns one column shard of that size of a
-[4096, 4096*N] layer and runs it independently: no data-path collective, weak scaling.
+With N > 1 (launched by torch.distributed.run) every rank owns one 28672-column shard of a
+[8192, 28672*N] layer and runs it independently: no data-path collective, weak scaling.
 
 --impl reference times the CPU restatement of the reference's algorithm (oracle/) on the host cores
-for the same operator.  Synthetic seeded inputs throughout.
+for the same operator, on a column slice of the weight.  Synthetic seeded inputs throughout.
 """
 import argparse
 import ctypes
@@ -29,11 +32,14 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 import __graft_entry__ as ge  # noqa: E402
 
-M, K, N, GROUP = 16, 4096, 4096, 128
-RING = 32  # 32 x 8.4 MB of packed weights = 268 MB > 2 x 126 MB of L2
+M, K, N, GROUP = 1, 8192, 28672, 128
+RING = 3  # 3 x 117 MB of packed weights = 352 MB > 2 x 126 MB of L2
 WEIGHT_BYTES = K * N // 2
-# Algorithmic bytes of one call: packed weights + scales + offsets + activations + output + bias.
-ALGO_BYTES = WEIGHT_BYTES + 2 * (K // GROUP) * N * 2 + M * K * 2 + M * N * 2 + N * 2
+# Algorithmic bytes of one call: packed weights + group scales + activations + output.
+ALGO_BYTES = WEIGHT_BYTES + (K // GROUP) * N * 2 + M * K * 2 + M * N * 2
+WORKLOAD = ("W4A16 group-128 weight-only matmul, Llama-70B gate/up shape: x bf16 [1,8192] @ int4 [8192,28672], "
+            "bf16 group scales, no offset, no bias")
+CPU_SLICE_N = 2048  # columns of the weight the CPU legs work on
 
 
 def peaks():
@@ -98,7 +104,7 @@ def make_ring(workloads, dev, rank, ring):
     """`ring` weight sets (distinct seeds) resident on the device, plus the shared activations."""
     sets = []
     for i in range(ring):
-        d = workloads.w4a16(M=M, K=K, N=N, group=GROUP, seed=1001 + 1000 * rank + i)
+        d = workloads.w4a16(M=M, K=K, N=N, group=GROUP, seed=1004 + 1000 * rank + i, with_offset=False, with_bias=False)
         sets.append({k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in d.items() if k != "w_vals"})
     return sets
 
@@ -113,7 +119,7 @@ class Runner:
         self.items = []
         for d in sets:
             self.items.append((pkg.AclTensor(d["x"]), pkg.AclTensor(d["w"], pkg.ACL_INT4, (K, N)), pkg.AclTensor(d["scale"]),
-                               pkg.AclTensor(d["offset"]), pkg.AclTensor(d["bias"]), d))
+                               None, None, d))
         self.ws = pkg.Workspace()
 
     def call(self, i, x_handle=None):
@@ -180,77 +186,114 @@ def timed(fn, steps, world, dev):
 
 
 def sweep(pkg, workloads, dev, pk):
-    """Other configurations, timed per call with CUDA events (not part of the headline value)."""
+    """The other benchmark configurations: each case is captured as one CUDA graph over a ring of
+    distinct weight sets (larger than L2 where memory allows) and timed with CUDA events."""
     rows = []
 
-    def time_calls(fn, flops, wbytes, name, reps=20, ring=1):
+    def run_case(name, calls, flops, wbytes, reps):
+        # calls: list of zero-argument functions, one per weight set of the ring
+        ws = pkg.Workspace()
+        for c in calls:
+            c(ws)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for c in calls:
+                c(ws)
         for _ in range(3):
-            fn(0)
+            g.replay()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for r in range(reps):
-            fn(r % ring)
+        for _ in range(reps):
+            g.replay()
         e1.record()
         torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1) / reps
-        rows.append({"case": name, "ms": round(ms, 5), "tflops": round(flops / ms / 1e9, 2),
-                     "weight_gbs": round(wbytes / ms / 1e6, 1)})
+        ms = e0.elapsed_time(e1) / (reps * len(calls))
+        rows.append({"case": name, "us": round(ms * 1e3, 2), "tflops": round(flops / ms / 1e9, 2),
+                     "weight_gbs": round(wbytes / ms / 1e6, 1), "ring": len(calls)})
+
+    def wq_calls(sets, int4, group, ex=True):
+        calls = []
+        for d in sets:
+            k, n = d["K"], d["N"]
+            out = torch.empty((d["M"], n), dtype=d["x"].dtype, device=dev)
+            args = [pkg.AclTensor(d["x"].to(dev)), pkg.AclTensor(d["w"].to(dev), pkg.ACL_INT4 if int4 else pkg.ACL_INT8, (k, n)),
+                    pkg.AclTensor(d["scale"].to(dev)), pkg.AclTensor(d["offset"].to(dev)) if d["offset"] is not None else None,
+                    pkg.AclTensor(d["bias"].to(dev)) if d["bias"] is not None else None, ctypes.c_int64(group), pkg.AclTensor(out)]
+            calls.append(lambda ws, a=args: pkg.call("aclnnWeightQuantBatchMatmulV2Ex", *a, workspace=ws, device=dev))
+        return calls
 
     try:
-        # config 0: W8A16 M=1 K=1024 N=3072 (3 MB: L2-resident and launch-bound; 64 distinct weight sets)
-        sets = [workloads.w8a16(seed=1000 + i) for i in range(64)]
-        ds = [{k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in d.items()} for d in sets]
-        time_calls(lambda i: pkg.weight_quant_matmul(ds[i]["x"], ds[i]["w"], ds[i]["scale"], name="aclnnWeightQuantBatchMatmulV2"),
-                   2 * 1024 * 3072, 1024 * 3072, "cfg0 W8A16 M=1 K=1024 N=3072", reps=128, ring=64)
-        del ds
-        # config 1 at M = 1 and 128 over the same ring idea (16 sets)
-        for m in (1, 128):
-            sets = [workloads.w4a16(M=m, seed=1001 + i) for i in range(16)]
-            ds = [{k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in d.items() if k != "w_vals"} for d in sets]
-            time_calls(lambda i: pkg.weight_quant_matmul(ds[i]["x"], ds[i]["w"], ds[i]["scale"], ds[i]["offset"], ds[i]["bias"],
-                                                         int4=True, group=GROUP),
-                       2 * m * K * N, WEIGHT_BYTES, f"cfg1 W4A16 g128 M={m} K=4096 N=4096", reps=64, ring=16)
-            del ds
-        # config 2: W8A8 M=2048 K=4096 N=14336
-        for m in (8, 2048):
-            d = workloads.w8a8(M=m)
-            dd = {k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in d.items()}
-            time_calls(lambda i: pkg.quant_matmul(dd["x"], dd["w"], dd["scale"], dd["pertoken"], dd["bias"]),
-                       2 * m * 4096 * 14336, 4096 * 14336, f"cfg2 W8A8 M={m} K=4096 N=14336", reps=10)
-            del dd
+        # config 0: W8A16 M=1 K=1024 N=3072 (3 MB per call: L2-resident and launch-bound)
+        sets = [workloads.w8a16(seed=1000 + i) for i in range(32)]
+        run_case("cfg0 W8A16 per-channel M=1 K=1024 N=3072 fp16", wq_calls(sets, False, 0), 2 * 1024 * 3072, 1024 * 3072, 20)
+        # config 1: W4A16 g128 K=4096 N=4096 with offset and bias, M = 1 / 16 / 128 (8.4 MB per call)
+        for m in (1, 16, 128):
+            sets = [workloads.w4a16(M=m, seed=1001 + i) for i in range(32)]
+            run_case(f"cfg1 W4A16 g128 M={m} K=4096 N=4096 bf16 +offset +bias", wq_calls(sets, True, 128),
+                     2 * m * 4096 * 4096, 4096 * 4096 // 2, 10)
+            del sets
+        # config 4: Llama-70B shapes, W4A16 g128, no offset
+        for which, k, n in (("gate/up", 8192, 28672), ("down", 28672, 8192)):
+            for m in ((32, 512) if which == "gate/up" else (32,)):
+                sets = [workloads.llama70b_shard(m, "gate_up" if which == "gate/up" else "down", seed=1004 + i) for i in range(3)]
+                run_case(f"cfg4 W4A16 g128 {which} M={m} K={k} N={n} bf16", wq_calls(sets, True, 128),
+                         2 * m * k * n, k * n // 2, 5)
+                del sets
+        # config 2: W8A8 K=4096 N=14336, per-token x per-channel scales, int32 bias, bf16 out
+        for m in (1, 8, 256, 2048, 4096):
+            calls = []
+            for i in range(5):
+                d = workloads.w8a8(M=m, seed=1002 + i)
+                out = torch.empty((m, 14336), dtype=torch.bfloat16, device=dev)
+                args = [pkg.AclTensor(d["x"].to(dev)), pkg.AclTensor(d["w"].to(dev)), pkg.AclTensor(d["scale"].to(dev)), None,
+                        pkg.AclTensor(d["pertoken"].to(dev)), pkg.AclTensor(d["bias"].to(dev)), pkg.AclTensor(out)]
+                calls.append(lambda ws, a=args: pkg.call("aclnnQuantMatmulV4Ex", *a, workspace=ws, device=dev))
+            run_case(f"cfg2 W8A8 M={m} K=4096 N=14336 bf16 out", calls, 2 * m * 4096 * 14336, 4096 * 14336, 5)
+            del calls
         # config 3: MXFP8 x MXFP4 4096 x 8192 x 8192
         d = workloads.mx()
         a, b, sa, sb = d["a"].reshape(-1).to(dev), d["b"].reshape(-1).to(dev), d["sa"].to(dev), d["sb"].to(dev)
-        time_calls(lambda i: pkg.mx_matmul(a, pkg.ACL_FLOAT8_E4M3FN, sa, b, pkg.ACL_FLOAT4_E2M1, sb, 4096, 8192, 8192),
-                   2 * 4096 * 8192 * 8192, 8192 * 8192 // 2, "cfg3 MXFP8xMXFP4 M=4096 K=8192 N=8192", reps=5)
+        out = torch.empty((4096, 8192), dtype=torch.bfloat16, device=dev)
+        args = [pkg.AclTensor(a, pkg.ACL_FLOAT8_E4M3FN, (4096, 8192)), pkg.AclTensor(sa, pkg.ACL_FLOAT8_E8M0, (4096, 256)),
+                pkg.AclTensor(b, pkg.ACL_FLOAT4_E2M1, (8192, 8192)), pkg.AclTensor(sb, pkg.ACL_FLOAT8_E8M0, (256, 8192)),
+                pkg.AclTensor(out)]
+        run_case("cfg3 MXFP8xMXFP4 M=4096 K=8192 N=8192 bf16 out",
+                 [lambda ws, a_=args: pkg.call("aclnnMatmulMxFp8", *a_, workspace=ws, device=dev)],
+                 2 * 4096 * 8192 * 8192, 8192 * 8192 // 2, 3)
     except Exception as e:  # a sweep failure must not lose the headline line
-        rows.append({"error": repr(e)[:200]})
+        rows.append({"error": repr(e)[:300]})
     for r in rows:
         if "tflops" in r:
-            r["frac_hbm"] = round(r["weight_gbs"] / pk["hbm_gbs"], 3)
-            r["frac_bf16_burst"] = round(r["tflops"] / pk["bf16_tflops"], 3)
+            r["frac_hbm_measured"] = round(r["weight_gbs"] / pk["hbm_gbs"], 3)
+            r["frac_bf16_measured_burst"] = round(r["tflops"] / pk["bf16_tflops"], 3)
     return rows
+
+
+def _cpu_problem():
+    """The CPU legs work on a column slice of one weight set of the device arm's ring."""
+    ge.load_package()
+    from cann_on_gpu_b200 import workloads
+    d = workloads.w4a16(M=M, K=K, N=CPU_SLICE_N, group=GROUP, seed=1004, with_offset=False, with_bias=False)
+    return (d["x"].float().numpy(), d["w"].numpy(), True, d["scale"].float().numpy(), None, None, M, K, CPU_SLICE_N, GROUP)
 
 
 def cpu_baseline(seconds=12.0):
     """The CPU restatement (BLAS-backed form) of the same operator on the host cores."""
     o = ge.load_oracle()
-    ge.load_package()
-    from cann_on_gpu_b200 import workloads
-    d = workloads.w4a16(M=M, K=K, N=N, group=GROUP, seed=1001)
-    args = (d["x"].float().numpy(), d["w"].numpy(), True, d["scale"].float().numpy(), d["offset"].float().numpy(),
-            d["bias"].float().numpy(), M, K, N, GROUP)
-    o.wqbmm_fast(*args)
+    args = _cpu_problem()
+    o.wqbmm_torch(*args)
     n, t0 = 0, time.perf_counter()
     while True:
-        o.wqbmm_fast(*args)
+        o.wqbmm_torch(*args)
         n += 1
         dt = time.perf_counter() - t0
         if dt >= seconds or n >= 200:
             break
-    return {"value": round(n * WEIGHT_BYTES / dt / 1e9, 4), "unit": "GB/s", "cores": os.cpu_count(), "kind": "port",
-            "sample": f"{n} passes of the numpy/BLAS restatement over one 4096x4096 int4 weight set at M=16 ({dt:.1f} s)"}
+    return {"value": round(n * K * CPU_SLICE_N // 2 / dt / 1e9, 4), "unit": "GB/s", "cores": os.cpu_count(), "kind": "port",
+            "sample": f"{n} passes of the PyTorch-CPU restatement (fp32 dequant + matmul, all cores) over a {K}x{CPU_SLICE_N} column slice of one weight set at M={M} "
+                      f"({dt:.1f} s)"}
 
 
 def reference_arm(args):
@@ -258,25 +301,21 @@ def reference_arm(args):
     if rank != 0:
         return
     o = ge.load_oracle()
-    ge.load_package()
-    from cann_on_gpu_b200 import workloads
-    d = workloads.w4a16(M=M, K=K, N=N, group=GROUP, seed=1001)
-    a = (d["x"].float().numpy(), d["w"].numpy(), True, d["scale"].float().numpy(), d["offset"].float().numpy(),
-         d["bias"].float().numpy(), M, K, N, GROUP)
+    a = _cpu_problem()
     for _ in range(max(1, args.warmup)):
-        o.wqbmm_fast(*a)
+        o.wqbmm_torch(*a)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        o.wqbmm_fast(*a)
+        o.wqbmm_torch(*a)
     dt = time.perf_counter() - t0
-    v = args.steps * WEIGHT_BYTES / dt / 1e9
-    sample = f"each step = 1 of the {RING} weight sets of the device arm's step (one 4096x4096 int4 matrix at M=16)"
+    v = args.steps * (K * CPU_SLICE_N // 2) / dt / 1e9
+    sample = (f"each step = one pass of the PyTorch-CPU restatement (fp32 dequant + matmul, all cores) over a {K}x{CPU_SLICE_N} column slice ({CPU_SLICE_N}/{N} of one of the "
+              f"{RING} weight sets of the device arm's step)")
     print(json.dumps({
         "impl": "reference", "metric": "w4a16_g128_weight_stream", "value": round(v, 4), "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt / args.steps * 1e3, 3), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "W4A16 group-128 weight-only matmul, x bf16 [16,4096] @ int4 [4096,4096], bf16 scale+offset+bias",
-                   "M": M, "K": K, "N": N, "group": GROUP},
+        "config": {"workload": WORKLOAD, "M": M, "K": K, "N": N, "group": GROUP},
         "cpu_baseline": {"value": round(v, 4), "unit": "GB/s", "cores": os.cpu_count(), "kind": "port", "sample": sample},
         "e2e": {"value": round(v, 4), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
 
@@ -352,8 +391,7 @@ def main():
             "metric": "w4a16_g128_weight_stream", "value": round(value, 2), "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 5), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "W4A16 group-128 weight-only matmul, x bf16 [16,4096] @ int4 [4096,4096], bf16 scale+offset+bias",
-                       "M": M, "K": K, "N": N, "group": GROUP, "calls_per_step": args.ring,
+            "config": {"workload": WORKLOAD, "M": M, "K": K, "N": N, "group": GROUP, "calls_per_step": args.ring,
                        "launch": "one CUDA graph per step (a pass over the ring), replayed",
                        "cache": f"ring of {args.ring} distinct weight sets ({args.ring * WEIGHT_BYTES >> 20} MiB) larger than 2x L2",
                        "parallelism": f"N-shard x{world}, no collective"},

@@ -112,3 +112,31 @@ def llama70b_shard(M, which, n_shards=1, shard=0, dtype=torch.bfloat16, seed=100
     d["x"] = torch.randn((M, K), generator=_gen(seed)).to(dtype)
     d["N_total"] = N
     return d
+
+
+def shard_columns(d, n_shards, shard):
+    """Column shard `shard` of `n_shards` of a weight-only problem: rank r owns
+    weight[:, r*N/g:(r+1)*N/g] with the matching scale / offset / bias slices as separate contiguous
+    tensors; activations are replicated.  Shard boundaries fall on even columns so a packed int4 byte
+    never straddles two ranks."""
+    K, N = d["K"], d["N"]
+    assert N % n_shards == 0 and (N // n_shards) % 2 == 0
+    ns = N // n_shards
+    lo, hi = shard * ns, (shard + 1) * ns
+    out = dict(d, N=ns)
+    if d["int4"]:
+        out["w"] = d["w"].reshape(K, N // 2)[:, lo // 2:hi // 2].contiguous().reshape(-1)
+        if "w_vals" in d:
+            out["w_vals"] = d["w_vals"][:, lo:hi].contiguous()
+    else:
+        out["w"] = d["w"][:, lo:hi].contiguous()
+    for k in ("scale", "offset", "bias"):
+        if d.get(k) is not None:
+            out[k] = d[k][..., lo:hi].contiguous()
+    return out
+
+
+def interleave_gathered(gathered, n_shards, M, N):
+    """An all-gather returns the shards rank-major, [g][M][N/g]; the [M,N] matrix is their interleave
+    along columns (identical only for M = 1)."""
+    return gathered.reshape(n_shards, M, N // n_shards).permute(1, 0, 2).reshape(M, N).contiguous()

@@ -270,3 +270,30 @@ def mx_dequant_fast(buf, kind, scales, rows, cols, scale_along_cols):
 
 def mx_matmul_fast(a, a_kind, sa, b, b_kind, sb, M, K, N):
     return mx_dequant_fast(a, a_kind, sa, M, K, True) @ mx_dequant_fast(b, b_kind, sb, K, N, False)
+
+
+# ------------------------------------------------------------------ PyTorch-CPU form (all host cores)
+def wqbmm_torch(x, w, is_int4, scale, offset, bias, M, K, N, group=0):
+    """The same weight-only matmul written with PyTorch CPU ops: dequantise in fp32, then torch.matmul
+    (the shape of the reference's torch oracles, tools/torch_common.py:20-40 -- which hold no
+    quant-matmul case of their own).  Multi-threaded; used as the timed CPU baseline."""
+    import torch
+    g = group if group > 0 else K
+    wt = torch.from_numpy(np.ascontiguousarray(w).view(np.uint8).reshape(-1))
+    if is_int4:
+        lo = (wt & 0xF).to(torch.int8)
+        hi = (wt >> 4).to(torch.int8)
+        v = torch.stack([lo, hi], dim=1).reshape(-1)[: K * N]
+        v = torch.where(v >= 8, v - 16, v)
+    else:
+        v = wt.view(torch.int8)[: K * N]
+    wf = v.reshape(K, N).to(torch.float32)
+    sc = torch.from_numpy(np.asarray(scale, dtype=np.float32)).reshape(-1, N)
+    rep = g if sc.shape[0] > 1 else K
+    if offset is not None:
+        wf = wf - torch.from_numpy(np.asarray(offset, dtype=np.float32)).reshape(-1, N).repeat_interleave(rep, dim=0)[:K]
+    wf = wf * sc.repeat_interleave(rep, dim=0)[:K]
+    out = torch.from_numpy(np.asarray(x, dtype=np.float32)).reshape(M, K) @ wf
+    if bias is not None:
+        out = out + torch.from_numpy(np.asarray(bias, dtype=np.float32)).reshape(1, N)
+    return out.numpy()

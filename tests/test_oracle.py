@@ -108,6 +108,8 @@ def test_wqbmm_matches_reference_test_formula(oracle, int4, G):
     assert np.allclose(got, want, rtol=1e-12, atol=1e-12)
     fast = oracle.wqbmm_fast(x, w, int4, sc, of, bias, M, K, N, group)
     assert np.allclose(fast, want, rtol=1e-10, atol=1e-10)
+    tor = oracle.wqbmm_torch(x, w, int4, sc, of, bias, M, K, N, group)
+    assert np.allclose(tor, want, rtol=1e-4, atol=1e-4)   # fp32 arithmetic
     # empty offset / bias
     got2 = oracle.wqbmm(x, w, int4, sc, None, None, M, K, N, group)
     fast2 = oracle.wqbmm_fast(x, w, int4, sc, None, None, M, K, N, group)
