@@ -40,6 +40,9 @@ ALGO_BYTES = WEIGHT_BYTES + (K // GROUP) * N * 2 + M * K * 2 + M * N * 2
 WORKLOAD = ("W4A16 group-128 weight-only matmul, Llama-70B gate/up shape: x bf16 [1,8192] @ int4 [8192,28672], "
             "bf16 group scales, no offset, no bias")
 CPU_SLICE_N = 2048  # columns of the weight the CPU legs work on
+# DRAM bytes (read + write) of one launch of the dominant kernel on this workload, from the ncu capture
+# summarised in profiles/wq_tc_kernel_w4a16_llama_gateup_m1.md.
+NCU_TRAFFIC_BYTES = 179_524_352
 
 
 def peaks():
@@ -358,6 +361,11 @@ def main():
     if rank == 0:
         sampler.start()
         time.sleep(0.3)
+    # bring the clocks back up after the pause (an idle GPU drops them within milliseconds)
+    t_spin = time.perf_counter()
+    while time.perf_counter() - t_spin < 0.2:
+        runner.replay()
+    torch.cuda.synchronize()
     ms = timed(runner.replay, args.steps, world, dev)
     launches = runner.launches_per_step * args.steps
     clocks = sampler.stop() if rank == 0 else None
@@ -397,7 +405,7 @@ def main():
                        "parallelism": f"N-shard x{world}, no collective"},
             "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                         "frac": round(achieved / pk["hbm_gbs"], 4), "traffic": None, "peak_source": pk["source"],
+                         "frac": round(achieved / pk["hbm_gbs"], 4), "traffic": NCU_TRAFFIC_BYTES, "peak_source": pk["source"],
                          "algorithmic_bytes_per_launch": ALGO_BYTES, "us_per_call": round(per_call_ms * 1e3, 3)},
             "tflops": round(world * calls * 2 * M * K * N / ms / 1e9, 3),
         }
