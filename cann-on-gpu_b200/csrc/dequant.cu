@@ -1,0 +1,182 @@
+// Expand-then-dense path: operands that the tensor core cannot read directly are first expanded to
+// bf16 / fp16 in the caller's workspace by HBM-bound streaming kernels, then multiplied by the dense
+// tcgen05 kernel (tc.cu).
+//
+//   * MX block-scaled matmuls: element * 2^(scale-127) is exact in bf16 for fp8 and fp4 elements, so
+//     expanding both operands and accumulating in fp32 gives the block-scaled product without any
+//     rounding of the operands.  (The reference's functional path does the same through fp16,
+//     cuda/src/ops/matmul.cu:153-189,454-483; its native path hands the job to cuBLASLt, :578-596.)
+//   * Weight-only matmuls with many rows (prefill): wf = (w - offset) * scale rounded once to the
+//     activation type, as the reference does (matmul.cu:733-747,790-795), but without its per-call
+//     transposes.  With few rows the fused stream-K kernel (wq_tc.cu) is used instead.
+#include "device_utils.cuh"
+
+namespace qmm {
+namespace {
+
+template <bool BF16> __device__ __forceinline__ uint32_t pack2(float a, float b) {
+    if constexpr (BF16) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<uint32_t *>(&v);
+    } else {
+        __half2 v = __floats2half2_rn(a, b);
+        return *reinterpret_cast<uint32_t *>(&v);
+    }
+}
+
+// Weight-only: out[k][n] = T((w[k][n] - off[g][n]) * scale[g][n]), g = k / group.  One thread expands
+// 16 consecutive columns of one row (8 B of int4 or 16 B of int8) and writes 32 B.
+template <bool Q4, bool BF16>
+__global__ void expand_wq_kernel(const uint8_t *w, const void *scale, const void *offset, int sc_type, uint16_t *out, int K, int N,
+                                 int group) {
+    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int per_row = N / 16;
+    if (t >= (int64_t)K * per_row) return;
+    const int k = (int)(t / per_row), n0 = (int)(t % per_row) * 16;
+    const int g = k / group;
+    float v[16];
+    if constexpr (Q4) {
+        const uint2 raw = __ldg(reinterpret_cast<const uint2 *>(w + ((size_t)k * N + n0) / 2));
+        const uint32_t words[2] = {raw.x, raw.y};
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const int nib = (words[i >> 3] >> (4 * (i & 7))) & 0xF;
+            v[i] = (float)(nib >= 8 ? nib - 16 : nib);
+        }
+    } else {
+        const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(w + (size_t)k * N + n0));
+        const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = (float)(int8_t)((words[i >> 2] >> (8 * (i & 3))) & 0xFF);
+    }
+    const size_t srow = (size_t)g * N + n0;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const float s = load_as_float(scale, sc_type, srow + i);
+        const float o = offset ? load_as_float(offset, sc_type, srow + i) : 0.f;
+        v[i] = (v[i] - o) * s;
+    }
+    uint4 o0, o1;
+    o0.x = pack2<BF16>(v[0], v[1]);   o0.y = pack2<BF16>(v[2], v[3]);   o0.z = pack2<BF16>(v[4], v[5]);   o0.w = pack2<BF16>(v[6], v[7]);
+    o1.x = pack2<BF16>(v[8], v[9]);   o1.y = pack2<BF16>(v[10], v[11]); o1.z = pack2<BF16>(v[12], v[13]); o1.w = pack2<BF16>(v[14], v[15]);
+    uint4 *dst = reinterpret_cast<uint4 *>(out + (size_t)k * N + n0);
+    dst[0] = o0;
+    dst[1] = o1;
+}
+
+// MX operand [rows][cols] -> bf16.  along_cols: one scale per (row, col / 32) (operand A, [M][K]);
+// otherwise one per (row / 32, col) (operand B, [K][N]).  One thread expands 16 consecutive columns.
+__global__ void expand_mx_kernel(const uint8_t *src, int elem_type, const uint8_t *scales, int along_cols, uint16_t *out, int rows,
+                                 int cols) {
+    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int per_row = cols / 16;
+    if (t >= (int64_t)rows * per_row) return;
+    const int r = (int)(t / per_row), c0 = (int)(t % per_row) * 16;
+    float v[16];
+    if (elem_type == ET_E2M1) {
+        const uint2 raw = __ldg(reinterpret_cast<const uint2 *>(src + ((size_t)r * cols + c0) / 2));
+        const uint32_t words[2] = {raw.x, raw.y};
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = e2m1_to_float((words[i >> 3] >> (4 * (i & 7))) & 0xF);
+    } else {
+        const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(src + (size_t)r * cols + c0));
+        const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const uint8_t b = (uint8_t)((words[i >> 2] >> (8 * (i & 3))) & 0xFF);
+            v[i] = elem_type == ET_E4M3 ? e4m3_to_float(b) : e5m2_to_float(b);
+        }
+    }
+    if (along_cols) {
+        const float s = e8m0_to_float(scales[(size_t)r * (cols / 32) + c0 / 32]);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] *= s;
+    } else {
+        const uint4 sraw = __ldg(reinterpret_cast<const uint4 *>(scales + (size_t)(r / 32) * cols + c0));
+        const uint32_t sw[4] = {sraw.x, sraw.y, sraw.z, sraw.w};
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] *= e8m0_to_float((sw[i >> 2] >> (8 * (i & 3))) & 0xFF);
+    }
+    uint4 o0, o1;
+    o0.x = pack2<true>(v[0], v[1]);   o0.y = pack2<true>(v[2], v[3]);   o0.z = pack2<true>(v[4], v[5]);   o0.w = pack2<true>(v[6], v[7]);
+    o1.x = pack2<true>(v[8], v[9]);   o1.y = pack2<true>(v[10], v[11]); o1.z = pack2<true>(v[12], v[13]); o1.w = pack2<true>(v[14], v[15]);
+    uint4 *dst = reinterpret_cast<uint4 *>(out + (size_t)r * cols + c0);
+    dst[0] = o0;
+    dst[1] = o1;
+}
+
+inline uint64_t up256(uint64_t x) { return (x + 255) / 256 * 256; }
+bool is_mx(const MatmulArgs &p) { return p.a_scale && p.b_scale; }
+
+// The dense problem that remains once the operands are expanded.
+MatmulArgs dense_args(const MatmulArgs &p, void *a16, void *b16) {
+    MatmulArgs d;
+    d.a = a16; d.b = b16; d.out = p.out;
+    d.a_type = d.b_type = is_mx(p) ? (int)ET_BF16 : p.a_type;
+    d.out_type = p.out_type;
+    d.bias = p.bias; d.bias_type = p.bias_type;
+    d.epilogue = EPI_PLAIN;
+    d.M = p.M; d.N = p.N; d.K = p.K; d.group = p.K;
+    return d;
+}
+
+}  // namespace
+
+bool expand_supported(const MatmulArgs &p) {
+    if (p.epilogue != EPI_PLAIN || p.batch != 1 || p.b_transposed || p.accumulate || p.M < 1) return false;
+    if (p.K % 32 != 0 || p.N % 16 != 0) return false;
+    auto aligned16 = [](const void *q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+    if (!aligned16(p.a) || !aligned16(p.b)) return false;
+    if (is_mx(p)) {
+        auto ok = [](int t) { return t == ET_E4M3 || t == ET_E5M2 || t == ET_E2M1; };
+        if (!ok(p.a_type) || !ok(p.b_type)) return false;
+        if (!aligned16(p.b_scale)) return false;
+    } else {
+        if (!p.scale) return false;
+        if (p.a_type != ET_F16 && p.a_type != ET_BF16) return false;
+        if (p.b_type != ET_I4 && p.b_type != ET_I8) return false;
+        if (p.sc_type != p.a_type || p.out_type != p.a_type || (p.bias && p.bias_type != p.a_type)) return false;
+        if (p.group < p.K && p.K % p.group != 0) return false;
+    }
+    return dense_tc_supported(dense_args(p, nullptr, nullptr));
+}
+
+uint64_t expand_workspace_bytes(const MatmulArgs &p) {
+    const uint64_t a_bytes = is_mx(p) ? up256((uint64_t)p.M * p.K * 2) : 0;
+    const uint64_t b_bytes = up256((uint64_t)p.K * p.N * 2);
+    return a_bytes + b_bytes + dense_tc_workspace_bytes(dense_args(p, nullptr, nullptr));
+}
+
+cudaError_t launch_expand(const MatmulArgs &p, cudaStream_t s) {
+    if (!p.workspace || p.workspace_bytes < expand_workspace_bytes(p)) return cudaErrorInvalidValue;
+    char *ws = (char *)p.workspace;
+    const uint64_t a_bytes = is_mx(p) ? up256((uint64_t)p.M * p.K * 2) : 0;
+    const uint64_t b_bytes = up256((uint64_t)p.K * p.N * 2);
+    uint16_t *a16 = (uint16_t *)ws, *b16 = (uint16_t *)(ws + a_bytes);
+    const int K = (int)p.K, N = (int)p.N, M = (int)p.M;
+    if (is_mx(p)) {
+        const int64_t ta = (int64_t)M * (K / 16), tb = (int64_t)K * (N / 16);
+        expand_mx_kernel<<<(unsigned)((ta + 255) / 256), 256, 0, s>>>((const uint8_t *)p.a, p.a_type, p.a_scale, 1, a16, M, K);
+        count_launch();
+        expand_mx_kernel<<<(unsigned)((tb + 255) / 256), 256, 0, s>>>((const uint8_t *)p.b, p.b_type, p.b_scale, 0, b16, K, N);
+        count_launch();
+    } else {
+        const int64_t tb = (int64_t)K * (N / 16);
+        const unsigned blocks = (unsigned)((tb + 255) / 256);
+        const bool q4 = p.b_type == ET_I4, bf = p.a_type == ET_BF16;
+        const uint8_t *w = (const uint8_t *)p.b;
+        if (q4 && bf) expand_wq_kernel<true, true><<<blocks, 256, 0, s>>>(w, p.scale, p.offset, p.sc_type, b16, K, N, (int)p.group);
+        else if (q4) expand_wq_kernel<true, false><<<blocks, 256, 0, s>>>(w, p.scale, p.offset, p.sc_type, b16, K, N, (int)p.group);
+        else if (bf) expand_wq_kernel<false, true><<<blocks, 256, 0, s>>>(w, p.scale, p.offset, p.sc_type, b16, K, N, (int)p.group);
+        else expand_wq_kernel<false, false><<<blocks, 256, 0, s>>>(w, p.scale, p.offset, p.sc_type, b16, K, N, (int)p.group);
+        count_launch();
+    }
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    MatmulArgs d = dense_args(p, is_mx(p) ? (void *)a16 : const_cast<void *>(p.a), b16);
+    d.workspace = ws + a_bytes + b_bytes;
+    d.workspace_bytes = p.workspace_bytes - a_bytes - b_bytes;
+    return launch_dense_tc(d, s);
+}
+
+}  // namespace qmm

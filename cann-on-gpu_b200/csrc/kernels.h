@@ -76,6 +76,14 @@ bool tc_supported(const MatmulArgs &p);
 void tc_plan(MatmulArgs &p);                 // fills split_k
 uint64_t tc_workspace_bytes(const MatmulArgs &p);
 cudaError_t launch_tc(const MatmulArgs &p, cudaStream_t s);
+// Dense tcgen05 kernel (tc.cu): W8A8, or 16-bit operands of one type.
+bool dense_tc_supported(const MatmulArgs &p);
+uint64_t dense_tc_workspace_bytes(const MatmulArgs &p);
+cudaError_t launch_dense_tc(const MatmulArgs &p, cudaStream_t s);
+// Expand-then-dense path (dequant.cu): MX matmuls and large-M weight-only matmuls.
+bool expand_supported(const MatmulArgs &p);
+uint64_t expand_workspace_bytes(const MatmulArgs &p);
+cudaError_t launch_expand(const MatmulArgs &p, cudaStream_t s);
 // Persistent stream-K tensor-core kernel for weight-only matmuls (wq_tc.cu).
 bool wq_tc_supported(const MatmulArgs &p);
 uint64_t wq_tc_workspace_bytes(const MatmulArgs &p);

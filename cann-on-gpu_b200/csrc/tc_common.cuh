@@ -140,7 +140,8 @@ inline EncodeFn encode_fn() {
 
 // 2-D row-major tensor map: `cols` contiguous elements per row, `rows` rows, row pitch in bytes.
 inline bool make_map(CUtensorMap *tm, const void *ptr, CUtensorMapDataType dt, uint64_t cols, uint64_t rows, uint64_t pitch_bytes,
-                     uint32_t box_cols, uint32_t box_rows, CUtensorMapSwizzle sw) {
+                     uint32_t box_cols, uint32_t box_rows, CUtensorMapSwizzle sw,
+                     CUtensorMapL2promotion promo = CU_TENSOR_MAP_L2_PROMOTION_L2_256B) {
     EncodeFn fn = encode_fn();
     if (!fn) return false;
     cuuint64_t dims[2] = {cols, rows};
@@ -148,7 +149,7 @@ inline bool make_map(CUtensorMap *tm, const void *ptr, CUtensorMapDataType dt, u
     cuuint32_t box[2] = {box_cols, box_rows};
     cuuint32_t estr[2] = {1, 1};
     return fn(tm, dt, 2, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
-              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+              promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 inline uint64_t align_up_u64(uint64_t x, uint64_t a) { return (x + a - 1) / a * a; }
