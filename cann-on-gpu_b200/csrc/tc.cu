@@ -337,7 +337,7 @@ cudaError_t dispatch_mt(int mt, const CUtensorMap &tx, const CUtensorMap &tw, co
 // the switch point.
 int wq_dense_threshold() {
     const char *e = getenv("B200_QMM_WQ_DENSE_M");
-    return e ? atoi(e) : 256;
+    return e ? atoi(e) : 128;
 }
 bool is_wq(const MatmulArgs &p) { return p.epilogue == EPI_PLAIN && p.scale && !p.a_scale && !p.b_scale; }
 bool is_mx(const MatmulArgs &p) { return p.epilogue == EPI_PLAIN && p.a_scale && p.b_scale; }

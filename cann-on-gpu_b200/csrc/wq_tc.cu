@@ -75,7 +75,7 @@ struct WqSmem {
     static constexpr int SLOT = 2 * W_TILE + X_BYTES;        // MMA ring slot
     static constexpr int RING_OFF = NS * STAGE;
     static constexpr int BAR_OFF = RING_OFF + NR * SLOT;
-    static constexpr int NUM_BARS = 2 * NS + NR + ND + 6;
+    static constexpr int NUM_BARS = 2 * NS + NR + ND + 10;
     static constexpr int MISC_OFF = BAR_OFF + NUM_BARS * 8;
     static constexpr int MERGE_OFF = (MISC_OFF + 16 + 15) / 16 * 16;    // [MT][128] fp32: epilogue set 1 -> set 0
     static constexpr int TOTAL = MERGE_OFF + (MT == 64 ? 0 : MT * TILE_N * 4) + 1024;
@@ -159,6 +159,7 @@ wq_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
     auto bar_ready = [&](int r) { return base + L::BAR_OFF + 8 * (2 * NS + r); };
     auto bar_done = [&](int d) { return base + L::BAR_OFF + 8 * (2 * NS + NR + d); };
     auto bar_acc_empty = [&](int issuer, int buf) { return base + L::BAR_OFF + 8 * (2 * NS + NR + ND + issuer * 2 + buf); };
+    auto bar_acc_full = [&](int issuer, int buf) { return base + L::BAR_OFF + 8 * (2 * NS + NR + ND + 6 + issuer * 2 + buf); };
     auto bar_merge = [&](int i) { return base + L::BAR_OFF + 8 * (2 * NS + NR + ND + 4 + i); };   // 0: full, 1: free
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(gen_base + L::MISC_OFF);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(gen_base + L::MISC_OFF + 4);
@@ -177,6 +178,7 @@ wq_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
         for (int r = 0; r < NR; ++r) mbar_init(bar_ready(r), 5);   // 4 converter warps + the activation TMA
         for (int d = 0; d < ND; ++d) mbar_init(bar_done(d), 1);
         for (int a = 0; a < 4; ++a) mbar_init(bar_acc_empty(a >> 1, a & 1), MT == 64 ? 8 : 4);
+        for (int a = 0; a < 4; ++a) mbar_init(bar_acc_full(a >> 1, a & 1), 1);
         mbar_init(bar_merge(0), 4);
         mbar_init(bar_merge(1), 4);
         *abort_flag = 0;
@@ -279,7 +281,10 @@ wq_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
                         const uint64_t b_desc = smem_desc(xa + (kk >> 2) * (MT * 128) + (kk & 3) * 32, 16, 1024);
                         tc_mma<false>(d, a_desc, b_desc, IDESC, (!first || kk > 0) ? 1u : 0u);
                     }
-                    tc_commit(bar_done(sb % ND));
+                    tc_commit(bar_done(sb % ND));                       // releases the ring slot
+                    // last super-block of this issuer in the fold: publish its accumulator
+                    const int last_own = (((sb - jf + sb_per_fold - 1) & 1) == me) ? sb_per_fold - 1 : sb_per_fold - 2;
+                    if (jf == last_own) tc_commit(bar_acc_full(me, buf));
                     PROF_ADD(3);
                 }
                 if (!ok) break;
@@ -398,9 +403,14 @@ wq_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
                     }
                     {
                         PROF_T0();
-                        if (!mbar_wait(bar_done(sb_last % ND), (sb_last / ND) & 1, abort_flag, 25)) { alive = false; break; }
-                        if (sb_per_fold >= 2 &&
-                            !mbar_wait(bar_done((sb_last - 1) % ND), ((sb_last - 1) / ND) & 1, abort_flag, 26)) { alive = false; break; }
+                        // every issuer that took part publishes its accumulator once, at its last
+                        // super-block of the fold (a barrier per issuer and buffer, so a waiter is never
+                        // more than one phase away from the phase it asks about)
+                        const int lanes_w = sb_per_fold >= 2 ? 2 : 1;
+                        const int iw = lanes_w == 2 ? 0 : (sb_last & 1);
+                        const int uw = iw == 0 ? u0 : u1;
+                        if (!mbar_wait(bar_acc_full(iw, uw & 1), (uw >> 1) & 1, abort_flag, 25)) { alive = false; break; }
+                        if (lanes_w == 2 && !mbar_wait(bar_acc_full(1, u1 & 1), (u1 >> 1) & 1, abort_flag, 26)) { alive = false; break; }
                         PROF_ADD(0);
                     }
                     PROF_T0();
@@ -654,7 +664,11 @@ template <bool Q4, bool BF16, int MT, int NS, int NR>
 cudaError_t wq_launch_one(const CUtensorMap &tx, const CUtensorMap &tw, const WqParams &wp, int P, cudaStream_t s) {
     using L = WqSmem<Q4, MT, NS, NR>;
     static_assert(L::TOTAL <= 232448, "shared memory budget of one CTA");
-    static_assert(NR < ND && NS >= 2, "ring depths");
+    // Both rings must have an even depth: super-blocks alternate between the two pipeline lanes, and an
+    // even depth makes every ring slot (and its mbarrier) the property of one lane.  A lane waits for its
+    // own slots in order, so it never asks a barrier about a phase beyond the one in progress -- a
+    // parity wait would answer "complete" for it at once.
+    static_assert(NR < ND && NS >= 2 && NS % 2 == 0 && NR % 2 == 0, "ring depths");
     auto kern = wq_tc_kernel<Q4, BF16, MT, NS, NR>;
     static bool attr_set[64] = {};
     int dev = 0;
@@ -673,9 +687,9 @@ template <bool Q4, bool BF16>
 cudaError_t wq_dispatch(int mt, const CUtensorMap &tx, const CUtensorMap &tw, const WqParams &wp, int P, cudaStream_t s) {
     // staging ring (packed weights in flight from HBM) x MMA ring (converted tiles + activations)
     switch (mt) {
-        case 16: return wq_launch_one<Q4, BF16, 16, Q4 ? 6 : 4, Q4 ? 4 : 3>(tx, tw, wp, P, s);
-        case 32: return wq_launch_one<Q4, BF16, 32, Q4 ? 5 : 4, Q4 ? 4 : 3>(tx, tw, wp, P, s);
-        default: return wq_launch_one<Q4, BF16, 64, Q4 ? 6 : 4, 3>(tx, tw, wp, P, s);
+        case 16: return wq_launch_one<Q4, BF16, 16, Q4 ? 6 : 4, 4>(tx, tw, wp, P, s);
+        case 32: return wq_launch_one<Q4, BF16, 32, Q4 ? 4 : 2, 4>(tx, tw, wp, P, s);
+        default: return wq_launch_one<Q4, BF16, 64, Q4 ? 4 : 2, 4>(tx, tw, wp, P, s);
     }
 }
 

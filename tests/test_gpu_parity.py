@@ -90,6 +90,21 @@ def test_config1_w4a16_full_size(pkg, oracle, workloads, dev, M):
     assert_close(to_np(run_wq(pkg, d2, dev)), ref_wq(oracle, d2), f"config1 no offset/bias M={M}")
 
 
+@pytest.mark.parametrize("int4", [True, False])
+@pytest.mark.parametrize("M", [1, 40])
+def test_wq_per_channel_long_k(pkg, oracle, workloads, dev, int4, M):
+    """Per-channel scales over a long K: one scale fold covers dozens of super-blocks of the streaming
+    kernel (shape of the Llama-70B projections the reference can run: fp16, [N] scales, offset)."""
+    K, N = (8192, 1536) if M > 1 else (8192, 28672)   # the second has more tiles than SMs: shares cut tiles anywhere
+    d = (workloads.w4a16(M=M, K=K, N=N, dtype=torch.float16, per_channel=True, with_bias=False, seed=31) if int4
+         else workloads.w8a16(M=M, K=K, N=N, dtype=torch.float16, with_offset=True, seed=31))
+    out = run_wq(pkg, d, dev, name="aclnnWeightQuantBatchMatmul")
+    assert_close(to_np(out), ref_wq(oracle, d), f"per-channel long K int4={int4} M={M}")
+    lib = pkg.load()
+    lib.aclnnB200DeviceStatus.restype = ctypes.c_uint32
+    assert lib.aclnnB200DeviceStatus() == 0
+
+
 def test_wq_fp32_and_ragged_shapes(pkg, oracle, workloads, dev):
     """fp32 activations (tests/test_quant_parity.cpp:405-413, tol 1e-4) and shapes off every tile size."""
     for (M, K, N) in [(5, 8, 6), (3, 40, 50), (17, 72, 34)]:
