@@ -188,10 +188,13 @@ def timed(fn, steps, world, dev):
     return max_over_ranks(ms, world, dev)
 
 
-def sweep(pkg, workloads, dev, pk):
+def sweep(pkg, workloads, dev, pk, only=None):
     """The other benchmark configurations: each case is captured as one CUDA graph over a ring of
     distinct weight sets (larger than L2 where memory allows) and timed with CUDA events."""
     rows = []
+
+    def wanted(name):
+        return only is None or only in name
 
     def run_case(name, calls, flops, wbytes, reps):
         # calls: list of zero-argument functions, one per weight set of the ring
@@ -229,23 +232,30 @@ def sweep(pkg, workloads, dev, pk):
 
     try:
         # config 0: W8A16 M=1 K=1024 N=3072 (3 MB per call: L2-resident and launch-bound)
-        sets = [workloads.w8a16(seed=1000 + i) for i in range(32)]
-        run_case("cfg0 W8A16 per-channel M=1 K=1024 N=3072 fp16", wq_calls(sets, False, 0), 2 * 1024 * 3072, 1024 * 3072, 20)
+        if wanted("cfg0 W8A16 per-channel M=1 K=1024 N=3072 fp16"):
+            sets = [workloads.w8a16(seed=1000 + i) for i in range(32)]
+            run_case("cfg0 W8A16 per-channel M=1 K=1024 N=3072 fp16", wq_calls(sets, False, 0), 2 * 1024 * 3072, 1024 * 3072, 20)
         # config 1: W4A16 g128 K=4096 N=4096 with offset and bias, M = 1 / 16 / 128 (8.4 MB per call)
         for m in (1, 16, 128):
+            name = f"cfg1 W4A16 g128 M={m} K=4096 N=4096 bf16 +offset +bias"
+            if not wanted(name):
+                continue
             sets = [workloads.w4a16(M=m, seed=1001 + i) for i in range(32)]
-            run_case(f"cfg1 W4A16 g128 M={m} K=4096 N=4096 bf16 +offset +bias", wq_calls(sets, True, 128),
-                     2 * m * 4096 * 4096, 4096 * 4096 // 2, 10)
+            run_case(name, wq_calls(sets, True, 128), 2 * m * 4096 * 4096, 4096 * 4096 // 2, 10)
             del sets
         # config 4: Llama-70B shapes, W4A16 g128, no offset
         for which, k, n in (("gate/up", 8192, 28672), ("down", 28672, 8192)):
-            for m in ((32, 512) if which == "gate/up" else (32,)):
+            for m in ((32, 512, 4096) if which == "gate/up" else (32,)):
+                name = f"cfg4 W4A16 g128 {which} M={m} K={k} N={n} bf16"
+                if not wanted(name):
+                    continue
                 sets = [workloads.llama70b_shard(m, "gate_up" if which == "gate/up" else "down", seed=1004 + i) for i in range(3)]
-                run_case(f"cfg4 W4A16 g128 {which} M={m} K={k} N={n} bf16", wq_calls(sets, True, 128),
-                         2 * m * k * n, k * n // 2, 5)
+                run_case(name, wq_calls(sets, True, 128), 2 * m * k * n, k * n // 2, 5 if m < 4096 else 3)
                 del sets
         # config 2: W8A8 K=4096 N=14336, per-token x per-channel scales, int32 bias, bf16 out
         for m in (1, 8, 256, 2048, 4096):
+            if not wanted(f"cfg2 W8A8 M={m} K=4096 N=14336 bf16 out"):
+                continue
             calls = []
             for i in range(5):
                 d = workloads.w8a8(M=m, seed=1002 + i)
@@ -256,6 +266,8 @@ def sweep(pkg, workloads, dev, pk):
             run_case(f"cfg2 W8A8 M={m} K=4096 N=14336 bf16 out", calls, 2 * m * 4096 * 14336, 4096 * 14336, 5)
             del calls
         # config 3: MXFP8 x MXFP4 4096 x 8192 x 8192
+        if not wanted("cfg3 MXFP8xMXFP4 M=4096 K=8192 N=8192 bf16 out"):
+            raise StopIteration
         d = workloads.mx()
         a, b, sa, sb = d["a"].reshape(-1).to(dev), d["b"].reshape(-1).to(dev), d["sa"].to(dev), d["sb"].to(dev)
         out = torch.empty((4096, 8192), dtype=torch.bfloat16, device=dev)
@@ -265,6 +277,8 @@ def sweep(pkg, workloads, dev, pk):
         run_case("cfg3 MXFP8xMXFP4 M=4096 K=8192 N=8192 bf16 out",
                  [lambda ws, a_=args: pkg.call("aclnnMatmulMxFp8", *a_, workspace=ws, device=dev)],
                  2 * 4096 * 8192 * 8192, 8192 * 8192 // 2, 3)
+    except StopIteration:
+        pass
     except Exception as e:  # a sweep failure must not lose the headline line
         rows.append({"error": repr(e)[:300]})
     for r in rows:
@@ -285,6 +299,7 @@ def _cpu_problem():
 def cpu_baseline(seconds=12.0):
     """The CPU restatement (BLAS-backed form) of the same operator on the host cores."""
     o = ge.load_oracle()
+    torch.set_num_threads(os.cpu_count() or 1)
     args = _cpu_problem()
     o.wqbmm_torch(*args)
     n, t0 = 0, time.perf_counter()
@@ -304,6 +319,7 @@ def reference_arm(args):
     if rank != 0:
         return
     o = ge.load_oracle()
+    torch.set_num_threads(os.cpu_count() or 1)   # torch.distributed.run pins OMP_NUM_THREADS to 1
     a = _cpu_problem()
     for _ in range(max(1, args.warmup)):
         o.wqbmm_torch(*a)
@@ -331,6 +347,7 @@ def main():
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--ring", type=int, default=RING)
     ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--sweep-only", default=None, help="run only the sweep cases whose name contains this text, and nothing else")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -347,6 +364,9 @@ def main():
     lib.aclnnB200KernelLaunchCount.restype = ctypes.c_uint64
     pk = peaks()
 
+    if args.sweep_only is not None:
+        print(json.dumps({"sweep": sweep(pkg, workloads, dev, pk, only=args.sweep_only)}))
+        return
     runner = Runner(pkg, make_ring(workloads, dev, rank, args.ring), dev)
     for _ in range(args.warmup):
         runner.step()
