@@ -188,6 +188,16 @@ tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUte
                     bf = load_as_float(p.bias, p.bias_type, n);
                 }
             }
+            // per-token scales of this set's rows: lane l keeps rows cb + l, cb + l + 32, ... and hands them
+            // out with shuffles, so the column loop issues no dependent global loads
+            constexpr int PR = (CH + 31) / 32;
+            float ptv[PR];
+#pragma unroll
+            for (int i = 0; i < PR; ++i) {
+                const int m = m0 + cb + lane + 32 * i;
+                ptv[i] = (p.pertoken && !p.partial && lane + 32 * i < CH && m < p.M) ? __ldg(p.pertoken + m) : 1.f;
+            }
+            const bool has_pt = p.pertoken != nullptr && !p.partial;
             if (!mbar_wait(bar_acc_full(a), (ui >> 1) & 1, abort_flag, 5)) break;
             tc_fence_after();
             if (active) {
@@ -195,11 +205,12 @@ tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUte
                 for (int c0 = cb; c0 < cb + CH; c0 += 16) {
                     uint32_t v[16];
                     tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + a * MT + c0, v);
-                    if (!n_ok) continue;
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
+                        const int cl = c0 - cb + j;
+                        const float pt = has_pt ? __shfl_sync(0xffffffffu, ptv[cl >> 5], cl & 31) : 1.f;
                         const int m = m0 + c0 + j;
-                        if (m >= p.M) continue;
+                        if (!n_ok || m >= p.M) continue;
                         const size_t o = (size_t)m * p.N + n;
                         if (p.partial) {
                             ((uint32_t *)p.partial)[(size_t)z * p.M * p.N + o] = v[j];   // raw fp32 or int32 bits
@@ -208,7 +219,7 @@ tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUte
                             if (p.epilogue == EPI_RAW_I32) ((int32_t *)p.out)[o] = acc;
                             else {
                                 float f = (float)(acc + bi) * sc;
-                                if (p.pertoken) f = f * p.pertoken[m];
+                                if (has_pt) f = f * pt;
                                 store_from_float(p.out, p.out_type, o, f);
                             }
                         } else {
