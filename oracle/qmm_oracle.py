@@ -230,8 +230,24 @@ def wq_dequant_fast(w, is_int4, scale, offset, K, N, group=0):
     return wf
 
 
-def wqbmm_fast(x, w, is_int4, scale, offset, bias, M, K, N, group=0):
+def wqbmm_fast(x, w, is_int4, scale, offset, bias, M, K, N, group=0, weight_round=None):
+    """weight_round = "bf16" | "f16": the reference's large-M form, which rounds each dequantised weight
+    (computed in fp32) once to the activation type before the GEMM (cuda/src/ops/matmul.cu:733-747,
+    790-795: deq_wq8 / deq_wq4 into a half buffer, then gemm_half)."""
     wf = wq_dequant_fast(w, is_int4, scale, offset, K, N, group)
+    if weight_round is not None:
+        g = group if group > 0 else K
+        wv = (int4_unpack(w, K * N) if is_int4 else np.ascontiguousarray(w).view(np.int8).reshape(-1)[: K * N])
+        w32 = wv.reshape(K, N).astype(np.float32)
+        sc = np.asarray(scale, dtype=np.float32).reshape(-1, N)
+        rep = g if sc.shape[0] > 1 else K
+        if offset is not None:
+            w32 = w32 - np.repeat(np.asarray(offset, dtype=np.float32).reshape(-1, N), rep, axis=0)[:K]
+        w32 = w32 * np.repeat(sc, rep, axis=0)[:K]
+        if weight_round == "bf16":
+            wf = bf16_bits_to_f32(f32_to_bf16_bits(w32)).astype(np.float64)
+        else:
+            wf = f16_bits_to_f32(f32_to_f16_bits(w32)).astype(np.float64)
     out = np.asarray(x, dtype=np.float64).reshape(M, K) @ wf
     if bias is not None:
         out = out + np.asarray(bias, dtype=np.float64).reshape(1, N)

@@ -105,6 +105,64 @@ def test_wq_per_channel_long_k(pkg, oracle, workloads, dev, int4, M):
     assert lib.aclnnB200DeviceStatus() == 0
 
 
+@pytest.mark.parametrize("shape", [(1, 1056, 160), (17, 200, 96), (70, 1160, 416), (300, 392, 224)])
+@pytest.mark.parametrize("int4", [True, False])
+def test_wq_tensor_core_tails(pkg, oracle, workloads, dev, shape, int4):
+    """Shapes that are not multiples of any tile: K tails are zero-filled by TMA, M and N tails are
+    masked in the epilogue.  Per-channel scales with offset and bias, through the tensor-core paths."""
+    M, K, N = shape
+    d = (workloads.w4a16(M=M, K=K, N=N, dtype=torch.bfloat16, per_channel=True, seed=41) if int4
+         else workloads.w8a16(M=M, K=K, N=N, dtype=torch.bfloat16, with_offset=True, seed=41))
+    if d["bias"] is None:
+        d["bias"] = (torch.randn(N, generator=torch.Generator().manual_seed(42)) * 0.02).to(torch.bfloat16)
+    with forced_path("tc"):
+        out = run_wq(pkg, d, dev)
+    assert_close(to_np(out), ref_wq(oracle, d), f"tails {shape} int4={int4}")
+
+
+@pytest.mark.parametrize("shape", [(1, 16, 16), (5, 48, 80), (100, 528, 400), (300, 1040, 272), (513, 144, 1040)])
+def test_w8a8_tensor_core_tails(pkg, oracle, workloads, dev, shape):
+    M, K, N = shape
+    d = workloads.w8a8(M=M, K=K, N=N, seed=43)
+    with forced_path("tc"):
+        acc = pkg.quant_matmul(d["x"].to(dev), d["w"].to(dev), None)
+        out = pkg.quant_matmul(d["x"].to(dev), d["w"].to(dev), d["scale"].to(dev), d["pertoken"].to(dev), d["bias"].to(dev),
+                               out_dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+    ref_acc, ref_out = ref_qmm(oracle, d, torch.bfloat16)
+    assert np.array_equal(acc.cpu().numpy(), ref_acc)
+    assert torch.equal(out.cpu(), ref_out)
+
+
+@pytest.mark.parametrize("shape", [(1, 32, 16), (33, 96, 48), (200, 544, 400)])
+@pytest.mark.parametrize("kinds", [(False, True), (True, False)])
+def test_mx_tensor_core_tails(pkg, oracle, workloads, dev, shape, kinds):
+    M, K, N = shape
+    d = workloads.mx(M=M, K=K, N=N, a_fp4=kinds[0], b_fp4=kinds[1], seed=44)
+    with forced_path("tc"):
+        out = run_mx(pkg, d, dev, torch.float32, "aclnnMatmulMxFp8")
+    assert_close(to_np(out), ref_mx(oracle, d), f"mx tails {shape} {kinds}")
+
+
+def test_large_m_weight_only_prefill(pkg, oracle, workloads, dev):
+    """M above the switch to the expand-then-dense path: weights are rounded once to the activation
+    type, as the reference's own large-M path does (cuda/src/ops/matmul.cu:733-747,790-795), and
+    multiplied by the dense kernel.  Checked at the usual bounds against that form of the reference,
+    and against the unrounded product with the mean bound widened to 4e-3 (bf16 weights carry 8
+    mantissa bits; their rounding adds to the output's own)."""
+    def ref_rounded(d, kind):
+        return oracle.wqbmm_fast(f32(d["x"]), d["w"].numpy(), d["int4"], f32(d["scale"]), f32(d["offset"]), f32(d["bias"]),
+                                 d["M"], d["K"], d["N"], d["group"], weight_round=kind)
+    d = workloads.w4a16(M=384, K=2048, N=1024, group=128, seed=45)
+    out = to_np(run_wq(pkg, d, dev))
+    assert_close(out, ref_rounded(d, "bf16"), "W4A16 g128 M=384 vs reference large-M form")
+    assert_close(out, ref_wq(oracle, d), "W4A16 g128 M=384 vs exact", mean_rel=4e-3)
+    d = workloads.w8a16(M=260, K=1024, N=512, dtype=torch.float16, with_offset=True, seed=46)
+    out = to_np(run_wq(pkg, d, dev, name="aclnnWeightQuantBatchMatmulV2"))
+    assert_close(out, ref_rounded(d, "f16"), "W8A16 M=260 vs reference large-M form")
+    assert_close(out, ref_wq(oracle, d), "W8A16 M=260 vs exact")
+
+
 def test_wq_fp32_and_ragged_shapes(pkg, oracle, workloads, dev):
     """fp32 activations (tests/test_quant_parity.cpp:405-413, tol 1e-4) and shapes off every tile size."""
     for (M, K, N) in [(5, 8, 6), (3, 40, 50), (17, 72, 34)]:
