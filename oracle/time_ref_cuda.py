@@ -2,10 +2,9 @@
 from the reference's sources for sm_100a) and this library on the same B200, on the closest form of
 each benchmark configuration that the reference accepts (fp16 activations, per-channel [N] scales,
 fp16 outputs, same-kind MX operands: cuda/src/ops/matmul.cu:761-767,802-807,437,491 of the
-reference).  Test infrastructure: prints one JSON line per case; the figures quoted in DESIGN.md
-and profiles/ come from here.
+reference).  Test infrastructure: prints one JSON line per case.
 
-    python oracle/time_ref_cuda.py > gpurun_out/ref_cuda_times.jsonl
+    python oracle/time_ref_cuda.py > ref_cuda_times.jsonl
 """
 import ctypes
 import json

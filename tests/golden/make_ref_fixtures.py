@@ -2,7 +2,7 @@
 by oracle/build_ref.sh from the reference's sources) on a B200 for the cases in cases.py.
 
 Run on a GPU box from the repository root:
-    python tests/golden/make_ref_fixtures.py gpurun_out/ref_b200_outputs.npz
+    python tests/golden/make_ref_fixtures.py <out.npz>    (then copy it to tests/golden/ref_b200_outputs.npz)
 The resulting file is committed as tests/golden/ref_b200_outputs.npz; the tests replay the same
 seeded inputs through the CPU checker (pinning it) and through this library's kernels.
 """
@@ -71,4 +71,4 @@ def main(out_path):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "gpurun_out/ref_b200_outputs.npz")
+    main(sys.argv[1] if len(sys.argv) > 1 else "ref_b200_outputs.npz")
