@@ -89,6 +89,11 @@ bool wq_tc_supported(const MatmulArgs &p);
 uint64_t wq_tc_workspace_bytes(const MatmulArgs &p);
 cudaError_t launch_wq_tc(const MatmulArgs &p, cudaStream_t s);
 unsigned int wq_tc_device_status();
+// Decode kernel for int4 weights at M <= 16 (wq_mma.cu): register dequant + mma.sync, stream-K.
+bool wq_mma_supported(const MatmulArgs &p);
+uint64_t wq_mma_workspace_bytes(const MatmulArgs &p);
+cudaError_t launch_wq_mma(const MatmulArgs &p, cudaStream_t s);
+unsigned int wq_mma_device_status();
 // 0, or the code of the first bounded wait that gave up on the current device (synchronises).
 unsigned int tc_device_status();
 

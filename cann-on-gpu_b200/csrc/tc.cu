@@ -356,6 +356,8 @@ bool use_stream_wq(const MatmulArgs &p) {
     return is_wq(p) && wq_tc_supported(p) && (p.M <= wq_dense_threshold() || !expand_supported(p));
 }
 bool use_expand(const MatmulArgs &p) { return (is_mx(p) || is_wq(p)) && !use_stream_wq(p) && expand_supported(p); }
+// Decode shapes of int4 weights: register-dequant kernel (wq_mma.cu).
+bool use_decode_wq(const MatmulArgs &p) { return use_stream_wq(p) && wq_mma_supported(p); }
 
 }  // namespace
 
@@ -427,12 +429,14 @@ bool tc_supported(const MatmulArgs &p) {
 void tc_plan(MatmulArgs &p) { p.split_k = (use_stream_wq(p) || use_expand(p)) ? 1 : make_plan(p).split; }
 
 uint64_t tc_workspace_bytes(const MatmulArgs &p) {
+    if (use_decode_wq(p)) return wq_mma_workspace_bytes(p);
     if (use_stream_wq(p)) return wq_tc_workspace_bytes(p);
     if (use_expand(p)) return expand_workspace_bytes(p);
     return dense_tc_workspace_bytes(p);
 }
 
 cudaError_t launch_tc(const MatmulArgs &p, cudaStream_t s) {
+    if (use_decode_wq(p)) return launch_wq_mma(p, s);
     if (use_stream_wq(p)) return launch_wq_tc(p, s);
     if (use_expand(p)) return launch_expand(p, s);
     return launch_dense_tc(p, s);
@@ -441,8 +445,8 @@ cudaError_t launch_tc(const MatmulArgs &p, cudaStream_t s) {
 unsigned int tc_device_status() {
     unsigned int v = 0;
     if (cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(v)) != cudaSuccess) return 0xFFFFFFFFu;
-    const unsigned int w = wq_tc_device_status();
-    return v ? v : w;
+    const unsigned int w = wq_tc_device_status(), d = wq_mma_device_status();
+    return v ? v : (w ? w : d);
 }
 
 }  // namespace qmm

@@ -1,0 +1,442 @@
+// W4A16 decode kernel (M <= 16): TMA-staged packed int4 weights, dequantised in registers, multiplied
+// on the warp-level tensor-core path (mma.sync m16n8k16), group scales folded in fp32, stream-K.
+//
+// Why not tcgen05 here: at decode shapes the matmul is a stream of weights from HBM, and feeding the
+// 5th-generation tensor core means writing every dequantised weight back to shared memory (2 B per
+// 4-bit weight) and having the MMA read it again -- shared-memory traffic that costs more than the HBM
+// stream itself.  Here a packed weight is read from shared memory once (0.5 B), expanded by one
+// lop3 per pair of weights, and goes to the tensor core from registers.
+//
+// Per CTA (one per SM, 18 warps):
+//   warp 0       producer: one TMA per super-block (128 K rows x 256 columns of packed int4 = 16 KB,
+//                128-byte swizzle) plus the activation rows of the same K range, into a ring of 8 slots.
+//   warps 1-16   four teams of four warps.  A team owns one quantum (= one scale group, or one
+//                super-block for per-channel scales) at a time; each of its warps covers 64 of the
+//                tile's 256 columns.  Per 16 K rows a lane reads four 32-bit words (rows 2t, 2t+1,
+//                2t+8, 2t+9 of its 8 columns -- bank-conflict free under the swizzle), interleaves row
+//                pairs with two byte-permutes and extracts each (k, k+1) nibble pair with one lop3
+//                into a bf16x2 / fp16x2 register holding the exact integers 136+q / 1032+q; these are
+//                the A fragments (weights^T) of mma.sync, the activations are the B fragments, and
+//                one more mma with an all-ones A accumulates the activation sums.  At the end of the
+//                group:   tot += s_g[n] * (acc - (136 + off_g[n]) * sum_g x)
+//                which is the reference's algebra (cuda/src/ops/matmul.cu:334-335) per group, in fp32.
+//   warp 17      reducer: when all teams have finished a tile (or this CTA's piece of it) it sums the
+//                teams' partial tiles from shared memory in a fixed order and writes the output
+//                (whole tile) or an fp32 slot (piece; summed by wq_mma_finalize_kernel).
+// Work split: the (tile, quantum) space is cut into gridDim.x equal contiguous shares (stream-K).
+//
+// Replaces the reference's k_wq_fused (cuda/src/ops/matmul.cu:337-352) for int4 weights.
+#include <mutex>
+
+#include "tc_common.cuh"
+
+namespace qmm {
+namespace {
+
+constexpr int MM_TILE_N = 256;      // output columns per tile
+constexpr int MM_SBK = 128;         // K rows per super-block
+constexpr int MM_W_BYTES = 16384;   // packed weights of one super-block: 128 rows x 128 B
+constexpr int MM_NS = 8;            // ring slots (a multiple of teams x super-blocks per quantum)
+constexpr int MM_TEAMS = 4;
+constexpr int MM_THREADS = 576;
+
+struct MmParams {
+    void *out;
+    float *slots;            // [tiles + P][M][256] fp32 partial tiles
+    const void *scale, *offset, *bias;
+    int sc_type, out_type;
+    int M, N, K;
+    int sbq;                 // super-blocks per quantum
+    int qpt;                 // quanta per tile
+    long long total_q;       // tiles * qpt
+    int grouped;
+};
+
+template <int MF>
+struct MmSmem {
+    static constexpr int XBOX = MF * 8 * 128;                 // one activation box: MF*8 rows x 64 k
+    static constexpr int SLOT = MM_W_BYTES + 2 * XBOX;        // multiple of 1024
+    static constexpr int PART_OFF = MM_NS * SLOT;
+    static constexpr int PART_BYTES = MM_TEAMS * MF * 8 * MM_TILE_N * 4;
+    static constexpr int BAR_OFF = PART_OFF + PART_BYTES;
+    static constexpr int NUM_BARS = 2 * MM_NS + 2;
+    static constexpr int MISC_OFF = BAR_OFF + NUM_BARS * 8;
+    static constexpr int TOTAL = MISC_OFF + 16 + 1024;        // + slack for the 1024-byte alignment
+};
+
+__host__ __device__ inline long long mm_share_begin(long long c, long long total_q, int P) { return c * total_q / P; }
+__host__ __device__ inline int mm_share_owner(long long q, long long total_q, int P) { return (int)(((q + 1) * P - 1) / total_q); }
+
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+
+template <bool BF16>
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    if constexpr (BF16) {
+        asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+            : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    } else {
+        asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+            : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    }
+}
+
+// Two nibbles (bits 0-3 and 16-19) -> two 16-bit floats holding the integers MAGIC + q, q the signed
+// 4-bit value: xor 8 turns the two's-complement nibble into q + 8 in the low mantissa bits of
+// 128.0 (bf16) or 1024.0 (fp16).
+template <bool BF16> __device__ __forceinline__ uint32_t dq_pair(uint32_t v) {
+    return (v & 0x000F000Fu) ^ (BF16 ? 0x43084308u : 0x64086408u);
+}
+template <bool BF16> __device__ __forceinline__ float half_bits_to_float(uint32_t h) {
+    if constexpr (BF16) return __uint_as_float(h << 16);
+    return __half2float(__ushort_as_half((unsigned short)h));
+}
+
+// Bounded wait that ignores the abort flag (used only to let copies in flight land before exit).
+__device__ __forceinline__ void mbar_drain(uint32_t bar, uint32_t parity) {
+    const unsigned long long t0 = global_ns();
+    while (!mbar_try_wait(bar, parity)) {
+        if (global_ns() - t0 > 2000000ull) return;
+    }
+}
+
+template <bool BF16, int MF>
+__global__ void __launch_bounds__(MM_THREADS, 1)
+wq_mma_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w, const MmParams p) {
+    using L = MmSmem<MF>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *gen_base = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t bars = base + L::BAR_OFF;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (MM_NS + s); };
+    const uint32_t seg_done = bars + 8u * (2 * MM_NS), seg_free = bars + 8u * (2 * MM_NS + 1);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(gen_base + L::MISC_OFF);
+    float *part = reinterpret_cast<float *>(gen_base + L::PART_OFF);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int P = gridDim.x, cta = blockIdx.x;
+    const long long qb = mm_share_begin(cta, p.total_q, P), qe = mm_share_begin(cta + 1, p.total_q, P);
+    const int nq = (int)(qe - qb);
+    const int tile_first = (int)(qb / p.qpt), tile_last = (int)((qe - 1) / p.qpt);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < MM_NS; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 4); }
+        mbar_init(seg_done, 16);
+        mbar_init(seg_free, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ producer
+        if (lane == 0) {
+            int i = 0;
+            bool ok = true;
+            for (int j = 0; j < nq && ok; ++j) {
+                const long long q = qb + j;
+                const int tile = (int)(q / p.qpt), qi = (int)(q % p.qpt);
+                for (int u = 0; u < p.sbq; ++u, ++i) {
+                    const int slot = i % MM_NS, k0 = (qi * p.sbq + u) * MM_SBK;
+                    if (i >= MM_NS && !mbar_wait(empty_bar(slot), ((i / MM_NS) - 1) & 1, abort_flag, 0x300u + slot)) { ok = false; break; }
+                    const uint32_t dst = base + slot * L::SLOT;
+                    mbar_expect_tx(full_bar(slot), L::SLOT);
+                    tma_load_2d(dst, &tm_w, full_bar(slot), tile * (MM_TILE_N / 2), k0);
+                    tma_load_2d(dst + MM_W_BYTES, &tm_x, full_bar(slot), k0, 0);
+                    tma_load_2d(dst + MM_W_BYTES + L::XBOX, &tm_x, full_bar(slot), k0 + 64, 0);
+                }
+            }
+            if (!ok) {   // let the copies already issued land before the CTA's shared memory goes away
+                for (int b = (i > MM_NS ? i - MM_NS : 0); b < i; ++b) mbar_drain(full_bar(b % MM_NS), (b / MM_NS) & 1);
+            }
+        }
+    } else if (warp <= 16) {
+        // ------------------------------------------------------------------ compute
+        const int cw = warp - 1, team = cw >> 2, wq = cw & 3;
+        const int g = lane >> 2, t = lane & 3;
+        // byte offsets inside a slot of the four weight words of step 0 (rows 2t, 2t+1, 2t+8, 2t+9)
+        uint32_t woff[4];
+        {
+            const int c16 = 2 * wq + (g >> 2), inb = 4 * (g & 3);
+            const int rows[4] = {2 * t, 2 * t + 1, 2 * t + 8, 2 * t + 9};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) woff[j] = 128 * rows[j] + (((c16 ^ (rows[j] & 7)) << 4)) + inb;
+        }
+        const uint32_t xrow = MM_W_BYTES + 128 * g + 4 * t;   // + ((chunk ^ g) << 4), + box, + 1024 for the second fragment
+        const uint32_t g16 = (uint32_t)g << 4;
+        constexpr uint32_t ONES = BF16 ? 0x3F803F80u : 0x3C003C00u;
+        constexpr float MAGIC = BF16 ? 136.f : 1032.f;
+        const int n_lane = 64 * wq + 8 * g;   // first of this lane's 8 columns inside the tile
+
+        float acc[MF][4][4], tot[MF][4][4], xs[MF][4];
+        bool ok = true;
+        int sg = 0;
+        for (int tile = tile_first; tile <= tile_last && ok; ++tile, ++sg) {
+            const long long t_lo = (long long)tile * p.qpt, t_hi = t_lo + p.qpt;
+            const int j_lo = (int)((t_lo > qb ? t_lo : qb) - qb), j_hi = (int)((t_hi < qe ? t_hi : qe) - qb);
+            const int n_glob = tile * MM_TILE_N + n_lane;
+            const bool n_ok = n_glob < p.N;
+            bool had = false;
+#pragma unroll
+            for (int f = 0; f < MF; ++f)
+#pragma unroll
+                for (int r = 0; r < 4; ++r)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) tot[f][r][e] = 0.f;
+            for (int j = j_lo + ((team - j_lo) & 3); j < j_hi && ok; j += MM_TEAMS) {
+                had = true;
+                const int qi = (int)((qb + j) % p.qpt);
+                // scale / offset rows of this group: 8 consecutive columns = 16 bytes per lane
+                uint4 sraw = make_uint4(0, 0, 0, 0), oraw = make_uint4(0, 0, 0, 0);
+                if (n_ok) {
+                    const size_t srow = (size_t)(p.grouped ? qi : 0) * p.N + n_glob;
+                    sraw = __ldg(reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(p.scale) + srow));
+                    if (p.offset) oraw = __ldg(reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(p.offset) + srow));
+                }
+#pragma unroll
+                for (int f = 0; f < MF; ++f) {
+#pragma unroll
+                    for (int r = 0; r < 4; ++r)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) acc[f][r][e] = 0.f;
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) xs[f][e] = 0.f;
+                }
+                for (int u = 0; u < p.sbq && ok; ++u) {
+                    const int i = j * p.sbq + u, slot = i % MM_NS;
+                    if (!mbar_wait(full_bar(slot), (i / MM_NS) & 1, abort_flag, 0x310u + slot)) { ok = false; break; }
+                    const uint32_t sb = base + slot * L::SLOT;
+#pragma unroll
+                    for (int st = 0; st < 8; ++st) {
+                        const uint32_t w0 = lds32(sb + woff[0] + st * 2048), w1 = lds32(sb + woff[1] + st * 2048);
+                        const uint32_t w2 = lds32(sb + woff[2] + st * 2048), w3 = lds32(sb + woff[3] + st * 2048);
+                        uint32_t b0[MF], b1[MF];
+                        {
+                            const uint32_t xa = sb + xrow + (st >> 2) * L::XBOX;
+                            const uint32_t c0 = ((uint32_t)(2 * (st & 3)) << 4) ^ g16, c1 = ((uint32_t)(2 * (st & 3) + 1) << 4) ^ g16;
+#pragma unroll
+                            for (int f = 0; f < MF; ++f) {
+                                b0[f] = lds32(xa + c0 + f * 1024);
+                                b1[f] = lds32(xa + c1 + f * 1024);
+                            }
+                        }
+                        // rows (k, k+1) side by side: low halves = nibbles 0-3, high halves = nibbles 4-7
+                        const uint32_t lo[2] = {__byte_perm(w0, w1, 0x5410), __byte_perm(w0, w1, 0x7632)};
+                        const uint32_t hi[2] = {__byte_perm(w2, w3, 0x5410), __byte_perm(w2, w3, 0x7632)};
+#pragma unroll
+                        for (int r = 0; r < 4; ++r) {
+                            const int sh = (r & 1) * 8;
+                            const uint32_t a0 = dq_pair<BF16>(lo[r >> 1] >> sh), a1 = dq_pair<BF16>(lo[r >> 1] >> (sh + 4));
+                            const uint32_t a2 = dq_pair<BF16>(hi[r >> 1] >> sh), a3 = dq_pair<BF16>(hi[r >> 1] >> (sh + 4));
+#pragma unroll
+                            for (int f = 0; f < MF; ++f) mma16816<BF16>(acc[f][r], a0, a1, a2, a3, b0[f], b1[f]);
+                        }
+#pragma unroll
+                        for (int f = 0; f < MF; ++f) mma16816<BF16>(xs[f], ONES, ONES, ONES, ONES, b0[f], b1[f]);
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(empty_bar(slot));
+                }
+                // fold the finished group
+                const uint32_t sw[4] = {sraw.x, sraw.y, sraw.z, sraw.w}, ow[4] = {oraw.x, oraw.y, oraw.z, oraw.w};
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const float sn = half_bits_to_float<BF16>(h ? sw[r] >> 16 : sw[r] & 0xFFFFu);
+                        const float cn = MAGIC + half_bits_to_float<BF16>(h ? ow[r] >> 16 : ow[r] & 0xFFFFu);
+#pragma unroll
+                        for (int f = 0; f < MF; ++f)
+#pragma unroll
+                            for (int e = 0; e < 2; ++e)
+                                tot[f][r][2 * h + e] = fmaf(sn, fmaf(-cn, xs[f][e], acc[f][r][2 * h + e]), tot[f][r][2 * h + e]);
+                    }
+                }
+            }
+            if (!ok) break;
+            // hand this team's partial tile to the reducer
+            if (sg >= 1 && !mbar_wait(seg_free, (sg - 1) & 1, abort_flag, 0x320u)) { ok = false; break; }
+            if (had) {
+#pragma unroll
+                for (int f = 0; f < MF; ++f)
+#pragma unroll
+                    for (int r = 0; r < 4; ++r)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int m = 8 * f + 2 * t + (e & 1), n = n_lane + 2 * r + (e >> 1);
+                            part[(team * (MF * 8) + m) * MM_TILE_N + n] = tot[f][r][e];
+                        }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(seg_done);
+        }
+    } else {
+        // ------------------------------------------------------------------ reducer
+        int sg = 0;
+        for (int tile = tile_first; tile <= tile_last; ++tile, ++sg) {
+            const long long t_lo = (long long)tile * p.qpt, t_hi = t_lo + p.qpt;
+            const int j_lo = (int)((t_lo > qb ? t_lo : qb) - qb), j_hi = (int)((t_hi < qe ? t_hi : qe) - qb);
+            const int cnt = j_hi - j_lo;
+            const bool whole = cnt == p.qpt;
+            if (!mbar_wait(seg_done, sg & 1, abort_flag, 0x330u)) break;
+            for (int m = 0; m < p.M; ++m) {
+                for (int n = lane; n < MM_TILE_N; n += 32) {
+                    const int n_glob = tile * MM_TILE_N + n;
+                    if (n_glob >= p.N) break;
+                    float v = 0.f;
+#pragma unroll
+                    for (int tm = 0; tm < MM_TEAMS; ++tm)
+                        if (cnt >= MM_TEAMS || ((tm - j_lo) & 3) < cnt) v += part[(tm * (MF * 8) + m) * MM_TILE_N + n];
+                    if (whole) {
+                        if (p.bias) v += load_as_float(p.bias, p.sc_type, n_glob);
+                        store_from_float(p.out, p.out_type, (size_t)m * p.N + n_glob, v);
+                    } else {
+                        p.slots[((size_t)(tile + cta) * p.M + m) * MM_TILE_N + n] = v;
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(seg_free);
+        }
+    }
+}
+
+// Sums the partial tiles of every output tile that was shared between CTAs, adds the bias, casts.
+__global__ void wq_mma_finalize_kernel(MmParams p, int P) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)p.M * p.N) return;
+    const int n = (int)(i % p.N), m = (int)(i / p.N);
+    const int tile = n / MM_TILE_N;
+    const long long qa = (long long)tile * p.qpt;
+    const int c_first = mm_share_owner(qa, p.total_q, P), c_last = mm_share_owner(qa + p.qpt - 1, p.total_q, P);
+    if (c_first == c_last) return;  // written directly by its only owner
+    float v = 0.f;
+    for (int c = c_first; c <= c_last; ++c) v += p.slots[((size_t)(tile + c) * p.M + m) * MM_TILE_N + (n % MM_TILE_N)];
+    if (p.bias) v += load_as_float(p.bias, p.sc_type, n);
+    store_from_float(p.out, p.out_type, i, v);
+}
+
+int mm_sm_count() {
+    static int cached[64];
+    static std::once_flag once;
+    std::call_once(once, [] { for (int &c : cached) c = 0; });
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    dev &= 63;
+    if (!cached[dev]) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+struct MmPlan {
+    int mf, tiles, sbq, qpt, grouped, P;
+    long long total_q;
+    uint64_t slot_bytes;
+};
+
+MmPlan mm_make_plan(const MatmulArgs &p) {
+    MmPlan pl{};
+    pl.mf = p.M <= 8 ? 1 : 2;
+    pl.tiles = (int)((p.N + MM_TILE_N - 1) / MM_TILE_N);
+    const int num_sb = (int)((p.K + MM_SBK - 1) / MM_SBK);
+    pl.grouped = p.group < p.K ? 1 : 0;
+    pl.sbq = pl.grouped ? (int)(p.group / MM_SBK) : 1;
+    pl.qpt = num_sb / pl.sbq;
+    pl.total_q = (long long)pl.tiles * pl.qpt;
+    const int sms = mm_sm_count();
+    pl.P = (int)(pl.total_q < sms ? pl.total_q : sms);
+    pl.slot_bytes = (uint64_t)(pl.tiles + pl.P) * p.M * MM_TILE_N * sizeof(float);
+    return pl;
+}
+
+template <bool BF16, int MF>
+cudaError_t mm_launch_one(const CUtensorMap &tx, const CUtensorMap &tw, const MmParams &mp, int P, cudaStream_t s) {
+    using L = MmSmem<MF>;
+    static_assert(L::TOTAL <= 232448, "shared memory budget of one CTA");
+    static_assert(L::SLOT % 1024 == 0, "slots keep the swizzle alignment");
+    auto kern = wq_mma_kernel<BF16, MF>;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!attr_set[dev & 63]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+        if (e != cudaSuccess) return e;
+        attr_set[dev & 63] = true;
+    }
+    kern<<<P, MM_THREADS, L::TOTAL, s>>>(tx, tw, mp);
+    count_launch();
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+bool wq_mma_supported(const MatmulArgs &p) {
+    if (p.epilogue != EPI_PLAIN || !p.scale || p.a_scale || p.b_scale) return false;
+    if (p.batch != 1 || p.b_transposed || p.accumulate || p.M < 1 || p.M > 16) return false;
+    if (p.a_type != ET_F16 && p.a_type != ET_BF16) return false;
+    if (p.b_type != ET_I4) return false;
+    if (p.sc_type != p.a_type || p.out_type != p.a_type || (p.bias && p.bias_type != p.a_type)) return false;
+    if (p.K % 8 != 0 || p.K < MM_SBK || p.N % 32 != 0) return false;
+    if (p.group < p.K) {
+        if (p.group % MM_SBK != 0 || p.K % p.group != 0) return false;
+        // a ring slot must belong to one team: ring depth = teams x super-blocks per quantum x integer
+        if (MM_NS % (MM_TEAMS * (int)(p.group / MM_SBK)) != 0) return false;
+    }
+    if (p.N > (1 << 24) || p.K > (1 << 24)) return false;
+    if (const char *e = getenv("B200_QMM_WQ_MMA")) {
+        if (atoi(e) == 0) return false;
+    }
+    return true;
+}
+
+uint64_t wq_mma_workspace_bytes(const MatmulArgs &p) { return mm_make_plan(p).slot_bytes; }
+
+cudaError_t launch_wq_mma(const MatmulArgs &p, cudaStream_t s) {
+    const MmPlan pl = mm_make_plan(p);
+    if (p.workspace_bytes < pl.slot_bytes || !p.workspace) return cudaErrorInvalidValue;
+    if ((reinterpret_cast<uintptr_t>(p.a) & 15) || (reinterpret_cast<uintptr_t>(p.b) & 15) ||
+        (reinterpret_cast<uintptr_t>(p.scale) & 15) || (reinterpret_cast<uintptr_t>(p.offset) & 15))
+        return cudaErrorMisalignedAddress;
+    const bool bf = p.a_type == ET_BF16;
+    CUtensorMap tx, tw;
+    bool ok = make_map(&tx, p.a, bf ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, p.K, p.M, p.K * 2, 64,
+                       pl.mf * 8, CU_TENSOR_MAP_SWIZZLE_128B);
+    ok = ok && make_map(&tw, p.b, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.N / 2, p.K, p.N / 2, 128, MM_SBK, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (!ok) return cudaErrorInvalidValue;
+
+    MmParams mp{};
+    mp.out = p.out;
+    mp.slots = (float *)p.workspace;
+    mp.scale = p.scale; mp.offset = p.offset; mp.bias = p.bias;
+    mp.sc_type = p.sc_type; mp.out_type = p.out_type;
+    mp.M = (int)p.M; mp.N = (int)p.N; mp.K = (int)p.K;
+    mp.sbq = pl.sbq; mp.qpt = pl.qpt; mp.total_q = pl.total_q; mp.grouped = pl.grouped;
+
+    cudaError_t e;
+    if (pl.mf == 1) e = bf ? mm_launch_one<true, 1>(tx, tw, mp, pl.P, s) : mm_launch_one<false, 1>(tx, tw, mp, pl.P, s);
+    else e = bf ? mm_launch_one<true, 2>(tx, tw, mp, pl.P, s) : mm_launch_one<false, 2>(tx, tw, mp, pl.P, s);
+    if (e != cudaSuccess) return e;
+    // Tiles shared between CTAs exist unless every share boundary falls on a tile boundary.
+    if (pl.total_q % pl.P != 0 || (pl.total_q / pl.P) % pl.qpt != 0) {
+        const size_t mn = (size_t)p.M * p.N;
+        wq_mma_finalize_kernel<<<(unsigned)((mn + 255) / 256), 256, 0, s>>>(mp, pl.P);
+        count_launch();
+        e = cudaGetLastError();
+    }
+    return e;
+}
+
+unsigned int wq_mma_device_status() {
+    unsigned int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(v)) != cudaSuccess) return 0xFFFFFFFFu;
+    return v;
+}
+
+}  // namespace qmm
