@@ -34,11 +34,8 @@ namespace qmm {
 namespace {
 
 constexpr int MM_TILE_N = 256;      // output columns per tile
-constexpr int MM_SBK = 128;         // K rows per super-block
+constexpr int MM_SBK = 128;         // K rows per super-block (the unit scale groups are counted in)
 constexpr int MM_W_BYTES = 16384;   // packed weights of one super-block: 128 rows x 128 B
-constexpr int MM_NS = 8;            // ring slots (a multiple of teams x super-blocks per quantum)
-constexpr int MM_TEAMS = 4;
-constexpr int MM_THREADS = 576;
 
 struct MmParams {
     void *out;
@@ -50,18 +47,17 @@ struct MmParams {
     int qpt;                 // quanta per tile
     long long total_q;       // tiles * qpt
     int grouped;
+    int ns;                  // ring slots (a multiple of the team count, see mm_ring_slots)
 };
 
+// Shared memory of one CTA: [ring: ns slots][partial tiles: teams x M rows x 256 fp32][barriers][flag].
 template <int MF>
 struct MmSmem {
     static constexpr int XBOX = MF * 8 * 128;                 // one activation box: MF*8 rows x 64 k
     static constexpr int SLOT = MM_W_BYTES + 2 * XBOX;        // multiple of 1024
-    static constexpr int PART_OFF = MM_NS * SLOT;
-    static constexpr int PART_BYTES = MM_TEAMS * MF * 8 * MM_TILE_N * 4;
-    static constexpr int BAR_OFF = PART_OFF + PART_BYTES;
-    static constexpr int NUM_BARS = 2 * MM_NS + 2;
-    static constexpr int MISC_OFF = BAR_OFF + NUM_BARS * 8;
-    static constexpr int TOTAL = MISC_OFF + 16 + 1024;        // + slack for the 1024-byte alignment
+    __host__ __device__ static int part_bytes(int teams, int M) { return teams * M * MM_TILE_N * 4; }
+    __host__ __device__ static int bar_off(int ns, int teams, int M) { return ns * SLOT + part_bytes(teams, M); }
+    __host__ __device__ static int total(int ns, int teams, int M) { return bar_off(ns, teams, M) + (2 * ns + 2) * 8 + 16 + 1024; }
 };
 
 __host__ __device__ inline long long mm_share_begin(long long c, long long total_q, int P) { return c * total_q / P; }
@@ -86,9 +82,17 @@ __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1
 
 // Two nibbles (bits 0-3 and 16-19) -> two 16-bit floats holding the integers MAGIC + q, q the signed
 // 4-bit value: xor 8 turns the two's-complement nibble into q + 8 in the low mantissa bits of
-// 128.0 (bf16) or 1024.0 (fp16).
-template <bool BF16> __device__ __forceinline__ uint32_t dq_pair(uint32_t v) {
-    return (v & 0x000F000Fu) ^ (BF16 ? 0x43084308u : 0x64086408u);
+// 128.0 (bf16) or 1024.0 (fp16).  One lop3, (v & mask) ^ magic, with both constants in registers.
+__device__ __forceinline__ uint32_t dq_pair(uint32_t v, uint32_t mask, uint32_t magic) {
+    uint32_t r;
+    asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(r) : "r"(v), "r"(mask), "r"(magic));
+    return r;
+}
+// 16-byte read-only load, issued where it is written (the compiler may not sink it to its use).
+__device__ __forceinline__ uint4 ldg16_now(const void *ptr) {
+    uint4 v;
+    asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(ptr));
+    return v;
 }
 template <bool BF16> __device__ __forceinline__ float half_bits_to_float(uint32_t h) {
     if constexpr (BF16) return __uint_as_float(h << 16);
@@ -103,19 +107,21 @@ __device__ __forceinline__ void mbar_drain(uint32_t bar, uint32_t parity) {
     }
 }
 
-template <bool BF16, int MF>
-__global__ void __launch_bounds__(MM_THREADS, 1)
+template <bool BF16, int MF, int MM_TEAMS>
+__global__ void __launch_bounds__((4 * MM_TEAMS + 2) * 32, 1)
 wq_mma_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w, const MmParams p) {
     using L = MmSmem<MF>;
+    const int MM_NS = p.ns;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *gen_base = smem_raw + (base - smem_u32(smem_raw));
-    const uint32_t bars = base + L::BAR_OFF;
+    const int bar_off = L::bar_off(MM_NS, MM_TEAMS, p.M);
+    const uint32_t bars = base + bar_off;
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (MM_NS + s); };
     const uint32_t seg_done = bars + 8u * (2 * MM_NS), seg_free = bars + 8u * (2 * MM_NS + 1);
-    volatile int *abort_flag = reinterpret_cast<volatile int *>(gen_base + L::MISC_OFF);
-    float *part = reinterpret_cast<float *>(gen_base + L::PART_OFF);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(gen_base + bar_off + (2 * MM_NS + 2) * 8);
+    float *part = reinterpret_cast<float *>(gen_base + MM_NS * L::SLOT);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int P = gridDim.x, cta = blockIdx.x;
@@ -125,7 +131,7 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < MM_NS; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 4); }
-        mbar_init(seg_done, 16);
+        mbar_init(seg_done, 4 * MM_TEAMS);
         mbar_init(seg_free, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -135,26 +141,27 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
     if (warp == 0) {
         // ------------------------------------------------------------------ producer
         if (lane == 0) {
-            int i = 0;
+            int i = 0, slot = 0, round = 0;
+            int tile = tile_first, qi = (int)(qb - (long long)tile_first * p.qpt);
             bool ok = true;
             for (int j = 0; j < nq && ok; ++j) {
-                const long long q = qb + j;
-                const int tile = (int)(q / p.qpt), qi = (int)(q % p.qpt);
                 for (int u = 0; u < p.sbq; ++u, ++i) {
-                    const int slot = i % MM_NS, k0 = (qi * p.sbq + u) * MM_SBK;
-                    if (i >= MM_NS && !mbar_wait(empty_bar(slot), ((i / MM_NS) - 1) & 1, abort_flag, 0x300u + slot)) { ok = false; break; }
+                    const int k0 = (qi * p.sbq + u) * MM_SBK;
+                    if (round > 0 && !mbar_wait(empty_bar(slot), (round - 1) & 1, abort_flag, 0x300u + slot)) { ok = false; break; }
                     const uint32_t dst = base + slot * L::SLOT;
                     mbar_expect_tx(full_bar(slot), L::SLOT);
                     tma_load_2d(dst, &tm_w, full_bar(slot), tile * (MM_TILE_N / 2), k0);
                     tma_load_2d(dst + MM_W_BYTES, &tm_x, full_bar(slot), k0, 0);
                     tma_load_2d(dst + MM_W_BYTES + L::XBOX, &tm_x, full_bar(slot), k0 + 64, 0);
+                    if (++slot == MM_NS) { slot = 0; ++round; }
                 }
+                if (++qi == p.qpt) { qi = 0; ++tile; }
             }
             if (!ok) {   // let the copies already issued land before the CTA's shared memory goes away
                 for (int b = (i > MM_NS ? i - MM_NS : 0); b < i; ++b) mbar_drain(full_bar(b % MM_NS), (b / MM_NS) & 1);
             }
         }
-    } else if (warp <= 16) {
+    } else if (warp <= 4 * MM_TEAMS) {
         // ------------------------------------------------------------------ compute
         const int cw = warp - 1, team = cw >> 2, wq = cw & 3;
         const int g = lane >> 2, t = lane & 3;
@@ -166,9 +173,12 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
 #pragma unroll
             for (int j = 0; j < 4; ++j) woff[j] = 128 * rows[j] + (((c16 ^ (rows[j] & 7)) << 4)) + inb;
         }
-        const uint32_t xrow = MM_W_BYTES + 128 * g + 4 * t;   // + ((chunk ^ g) << 4), + box, + 1024 for the second fragment
-        const uint32_t g16 = (uint32_t)g << 4;
+        // activation words: slot + xrow, with the 16-byte chunk index xor-ed in (the swizzle); + box,
+        // + 1024 for the second fragment
+        const uint32_t xrow = MM_W_BYTES + 128 * g + 16 * g + 4 * t;
         constexpr uint32_t ONES = BF16 ? 0x3F803F80u : 0x3C003C00u;
+        uint32_t dq_mask = 0x000F000Fu, dq_magic = BF16 ? 0x43084308u : 0x64086408u;
+        asm volatile("" : "+r"(dq_mask), "+r"(dq_magic));   // keep both constants in registers
         constexpr float MAGIC = BF16 ? 136.f : 1032.f;
         const int n_lane = 64 * wq + 8 * g;   // first of this lane's 8 columns inside the tile
 
@@ -187,16 +197,28 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
                 for (int r = 0; r < 4; ++r)
 #pragma unroll
                     for (int e = 0; e < 4; ++e) tot[f][r][e] = 0.f;
-            for (int j = j_lo + ((team - j_lo) & 3); j < j_hi && ok; j += MM_TEAMS) {
-                had = true;
-                const int qi = (int)((qb + j) % p.qpt);
-                // scale / offset rows of this group: 8 consecutive columns = 16 bytes per lane
-                uint4 sraw = make_uint4(0, 0, 0, 0), oraw = make_uint4(0, 0, 0, 0);
-                if (n_ok) {
-                    const size_t srow = (size_t)(p.grouped ? qi : 0) * p.N + n_glob;
-                    sraw = __ldg(reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(p.scale) + srow));
-                    if (p.offset) oraw = __ldg(reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(p.offset) + srow));
+            // scale / offset rows of a group: 8 consecutive columns = 16 bytes per lane, fetched one
+            // quantum ahead of their use
+            const uint16_t *sc_base = static_cast<const uint16_t *>(p.scale) + n_glob;
+            const uint16_t *of_base = p.offset ? static_cast<const uint16_t *>(p.offset) + n_glob : nullptr;
+            const int qi_seg = (int)(qb + j_lo - t_lo);   // quantum index inside the tile of local quantum j_lo
+            auto fetch_rows = [&](int jj, uint4 &sr, uint4 &orr) {
+                sr = make_uint4(0, 0, 0, 0);
+                orr = make_uint4(0, 0, 0, 0);
+                if (n_ok && jj < j_hi) {
+                    const size_t row = p.grouped ? (size_t)(qi_seg + jj - j_lo) * p.N : 0;
+                    sr = ldg16_now(sc_base + row);
+                    if (of_base) orr = ldg16_now(of_base + row);
                 }
+            };
+            const int j_first = j_lo + (team - j_lo % MM_TEAMS + MM_TEAMS) % MM_TEAMS;
+            uint4 sraw, oraw, snext, onext;
+            fetch_rows(j_first, snext, onext);
+            for (int j = j_first; j < j_hi && ok; j += MM_TEAMS) {
+                had = true;
+                sraw = snext;
+                oraw = onext;
+                fetch_rows(j + MM_TEAMS, snext, onext);
 #pragma unroll
                 for (int f = 0; f < MF; ++f) {
 #pragma unroll
@@ -207,21 +229,21 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
                     for (int e = 0; e < 4; ++e) xs[f][e] = 0.f;
                 }
                 for (int u = 0; u < p.sbq && ok; ++u) {
-                    const int i = j * p.sbq + u, slot = i % MM_NS;
-                    if (!mbar_wait(full_bar(slot), (i / MM_NS) & 1, abort_flag, 0x310u + slot)) { ok = false; break; }
-                    const uint32_t sb = base + slot * L::SLOT;
+                    const unsigned i = (unsigned)(j * p.sbq + u), round = i / (unsigned)MM_NS;
+                    const int slot = (int)(i - round * (unsigned)MM_NS);
+                    if (!mbar_wait(full_bar(slot), round & 1, abort_flag, 0x310u + slot)) { ok = false; break; }
+                    const uint32_t sb = base + slot * L::SLOT, xb = sb + xrow;
 #pragma unroll
                     for (int st = 0; st < 8; ++st) {
                         const uint32_t w0 = lds32(sb + woff[0] + st * 2048), w1 = lds32(sb + woff[1] + st * 2048);
                         const uint32_t w2 = lds32(sb + woff[2] + st * 2048), w3 = lds32(sb + woff[3] + st * 2048);
                         uint32_t b0[MF], b1[MF];
                         {
-                            const uint32_t xa = sb + xrow + (st >> 2) * L::XBOX;
-                            const uint32_t c0 = ((uint32_t)(2 * (st & 3)) << 4) ^ g16, c1 = ((uint32_t)(2 * (st & 3) + 1) << 4) ^ g16;
+                            const uint32_t xa0 = xb ^ ((uint32_t)(2 * (st & 3)) << 4), xa1 = xb ^ ((uint32_t)(2 * (st & 3) + 1) << 4);
 #pragma unroll
                             for (int f = 0; f < MF; ++f) {
-                                b0[f] = lds32(xa + c0 + f * 1024);
-                                b1[f] = lds32(xa + c1 + f * 1024);
+                                b0[f] = lds32(xa0 + (st >> 2) * L::XBOX + f * 1024);
+                                b1[f] = lds32(xa1 + (st >> 2) * L::XBOX + f * 1024);
                             }
                         }
                         // rows (k, k+1) side by side: low halves = nibbles 0-3, high halves = nibbles 4-7
@@ -230,8 +252,8 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
 #pragma unroll
                         for (int r = 0; r < 4; ++r) {
                             const int sh = (r & 1) * 8;
-                            const uint32_t a0 = dq_pair<BF16>(lo[r >> 1] >> sh), a1 = dq_pair<BF16>(lo[r >> 1] >> (sh + 4));
-                            const uint32_t a2 = dq_pair<BF16>(hi[r >> 1] >> sh), a3 = dq_pair<BF16>(hi[r >> 1] >> (sh + 4));
+                            const uint32_t a0 = dq_pair(lo[r >> 1] >> sh, dq_mask, dq_magic), a1 = dq_pair(lo[r >> 1] >> (sh + 4), dq_mask, dq_magic);
+                            const uint32_t a2 = dq_pair(hi[r >> 1] >> sh, dq_mask, dq_magic), a3 = dq_pair(hi[r >> 1] >> (sh + 4), dq_mask, dq_magic);
 #pragma unroll
                             for (int f = 0; f < MF; ++f) mma16816<BF16>(acc[f][r], a0, a1, a2, a3, b0[f], b1[f]);
                         }
@@ -268,7 +290,7 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
                             const int m = 8 * f + 2 * t + (e & 1), n = n_lane + 2 * r + (e >> 1);
-                            part[(team * (MF * 8) + m) * MM_TILE_N + n] = tot[f][r][e];
+                            if (m < p.M) part[(team * p.M + m) * MM_TILE_N + n] = tot[f][r][e];
                         }
             }
             __syncwarp();
@@ -283,19 +305,42 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
             const int cnt = j_hi - j_lo;
             const bool whole = cnt == p.qpt;
             if (!mbar_wait(seg_done, sg & 1, abort_flag, 0x330u)) break;
-            for (int m = 0; m < p.M; ++m) {
-                for (int n = lane; n < MM_TILE_N; n += 32) {
-                    const int n_glob = tile * MM_TILE_N + n;
-                    if (n_glob >= p.N) break;
-                    float v = 0.f;
+            // each lane owns 8 consecutive columns
+            const int n = 8 * lane, n_glob = tile * MM_TILE_N + n;
+            if (n_glob < p.N) {
+                for (int m = 0; m < p.M; ++m) {
+                    float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                    for (int tm = 0; tm < MM_TEAMS; ++tm)
-                        if (cnt >= MM_TEAMS || ((tm - j_lo) & 3) < cnt) v += part[(tm * (MF * 8) + m) * MM_TILE_N + n];
+                    for (int tm = 0; tm < MM_TEAMS; ++tm) {
+                        if (cnt >= MM_TEAMS || (tm - j_lo % MM_TEAMS + MM_TEAMS) % MM_TEAMS < cnt) {
+                            const float4 *src = reinterpret_cast<const float4 *>(part + (tm * p.M + m) * MM_TILE_N + n);
+                            const float4 a = src[0], b = src[1];
+                            v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w;
+                            v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
+                        }
+                    }
                     if (whole) {
-                        if (p.bias) v += load_as_float(p.bias, p.sc_type, n_glob);
-                        store_from_float(p.out, p.out_type, (size_t)m * p.N + n_glob, v);
+                        uint32_t o[4];
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            float lo = v[2 * c], hi = v[2 * c + 1];
+                            if (p.bias) {
+                                lo += load_as_float(p.bias, p.sc_type, n_glob + 2 * c);
+                                hi += load_as_float(p.bias, p.sc_type, n_glob + 2 * c + 1);
+                            }
+                            if constexpr (BF16) {
+                                __nv_bfloat162 t2 = __floats2bfloat162_rn(lo, hi);
+                                o[c] = *reinterpret_cast<uint32_t *>(&t2);
+                            } else {
+                                __half2 t2 = __floats2half2_rn(lo, hi);
+                                o[c] = *reinterpret_cast<uint32_t *>(&t2);
+                            }
+                        }
+                        *reinterpret_cast<uint4 *>(static_cast<uint16_t *>(p.out) + (size_t)m * p.N + n_glob) = make_uint4(o[0], o[1], o[2], o[3]);
                     } else {
-                        p.slots[((size_t)(tile + cta) * p.M + m) * MM_TILE_N + n] = v;
+                        float4 *dst = reinterpret_cast<float4 *>(p.slots + ((size_t)(tile + cta) * p.M + m) * MM_TILE_N + n);
+                        dst[0] = make_float4(v[0], v[1], v[2], v[3]);
+                        dst[1] = make_float4(v[4], v[5], v[6], v[7]);
                     }
                 }
             }
@@ -356,21 +401,39 @@ MmPlan mm_make_plan(const MatmulArgs &p) {
     return pl;
 }
 
+constexpr int MM_TEAMS_USED = 3;
+constexpr int MM_SMEM_LIMIT = 232448;
+
+// Ring depth: every slot must belong to one team (a team then meets the phases of a slot's barrier in
+// order), so the depth is c x teams, and with two super-blocks per quantum c must be even.  Three or
+// four slots per team hide the HBM round trip (one being read, the others in flight); take the
+// deepest ring that fits beside the partial tiles.
+template <int MF>
+int mm_ring_slots(int M, int sbq) {
+    for (int c = 4; c >= 2; --c) {
+        if (sbq == 2 && (c & 1)) continue;
+        if (MmSmem<MF>::total(c * MM_TEAMS_USED, MM_TEAMS_USED, M) <= MM_SMEM_LIMIT) return c * MM_TEAMS_USED;
+    }
+    return 0;
+}
+
 template <bool BF16, int MF>
-cudaError_t mm_launch_one(const CUtensorMap &tx, const CUtensorMap &tw, const MmParams &mp, int P, cudaStream_t s) {
+cudaError_t mm_launch_one(const CUtensorMap &tx, const CUtensorMap &tw, MmParams mp, int P, cudaStream_t s) {
     using L = MmSmem<MF>;
-    static_assert(L::TOTAL <= 232448, "shared memory budget of one CTA");
     static_assert(L::SLOT % 1024 == 0, "slots keep the swizzle alignment");
-    auto kern = wq_mma_kernel<BF16, MF>;
+    mp.ns = mm_ring_slots<MF>(mp.M, mp.sbq);
+    if (mp.ns == 0) return cudaErrorInvalidValue;
+    const int smem = L::total(mp.ns, MM_TEAMS_USED, mp.M);
+    auto kern = wq_mma_kernel<BF16, MF, MM_TEAMS_USED>;
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (!attr_set[dev & 63]) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, MM_SMEM_LIMIT);
         if (e != cudaSuccess) return e;
         attr_set[dev & 63] = true;
     }
-    kern<<<P, MM_THREADS, L::TOTAL, s>>>(tx, tw, mp);
+    kern<<<P, (4 * MM_TEAMS_USED + 2) * 32, smem, s>>>(tx, tw, mp);
     count_launch();
     return cudaGetLastError();
 }
@@ -386,8 +449,8 @@ bool wq_mma_supported(const MatmulArgs &p) {
     if (p.K % 8 != 0 || p.K < MM_SBK || p.N % 32 != 0) return false;
     if (p.group < p.K) {
         if (p.group % MM_SBK != 0 || p.K % p.group != 0) return false;
-        // a ring slot must belong to one team: ring depth = teams x super-blocks per quantum x integer
-        if (MM_NS % (MM_TEAMS * (int)(p.group / MM_SBK)) != 0) return false;
+        // a ring slot must belong to one team: the ring is two quanta per team deep
+        if (p.group / MM_SBK > 2) return false;
     }
     if (p.N > (1 << 24) || p.K > (1 << 24)) return false;
     if (const char *e = getenv("B200_QMM_WQ_MMA")) {
