@@ -178,7 +178,8 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
         const uint32_t xrow = MM_W_BYTES + 128 * g + 16 * g + 4 * t;
         constexpr uint32_t ONES = BF16 ? 0x3F803F80u : 0x3C003C00u;
         uint32_t dq_mask = 0x000F000Fu, dq_magic = BF16 ? 0x43084308u : 0x64086408u;
-        asm volatile("" : "+r"(dq_mask), "+r"(dq_magic));   // keep both constants in registers
+        uint32_t dq_mask2 = 0x00F000F0u, dq_magic2 = 0x64806480u;   // fp16 only: nibble at bits 4-7
+        asm volatile("" : "+r"(dq_mask), "+r"(dq_magic), "+r"(dq_mask2), "+r"(dq_magic2));   // keep the constants in registers
         constexpr float MAGIC = BF16 ? 136.f : 1032.f;
         const int n_lane = 64 * wq + 8 * g;   // first of this lane's 8 columns inside the tile
 
@@ -252,8 +253,22 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
 #pragma unroll
                         for (int r = 0; r < 4; ++r) {
                             const int sh = (r & 1) * 8;
-                            const uint32_t a0 = dq_pair(lo[r >> 1] >> sh, dq_mask, dq_magic), a1 = dq_pair(lo[r >> 1] >> (sh + 4), dq_mask, dq_magic);
-                            const uint32_t a2 = dq_pair(hi[r >> 1] >> sh, dq_mask, dq_magic), a3 = dq_pair(hi[r >> 1] >> (sh + 4), dq_mask, dq_magic);
+                            uint32_t a0, a1, a2, a3;
+                            if constexpr (BF16) {
+                                a0 = dq_pair(lo[r >> 1] >> sh, dq_mask, dq_magic);
+                                a1 = dq_pair(lo[r >> 1] >> (sh + 4), dq_mask, dq_magic);
+                                a2 = dq_pair(hi[r >> 1] >> sh, dq_mask, dq_magic);
+                                a3 = dq_pair(hi[r >> 1] >> (sh + 4), dq_mask, dq_magic);
+                            } else {
+                                // fp16 has room for a nibble at mantissa bits 4-7 too: the odd column of
+                                // each pair is taken in place as 1152 + 16 q (undone in the fold), which
+                                // saves its shift
+                                const uint32_t l = lo[r >> 1] >> sh, h = hi[r >> 1] >> sh;
+                                a0 = dq_pair(l, dq_mask, dq_magic);
+                                a1 = dq_pair(l, dq_mask2, dq_magic2);
+                                a2 = dq_pair(h, dq_mask, dq_magic);
+                                a3 = dq_pair(h, dq_mask2, dq_magic2);
+                            }
 #pragma unroll
                             for (int f = 0; f < MF; ++f) mma16816<BF16>(acc[f][r], a0, a1, a2, a3, b0[f], b1[f]);
                         }
@@ -269,8 +284,12 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
                 for (int r = 0; r < 4; ++r) {
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
-                        const float sn = half_bits_to_float<BF16>(h ? sw[r] >> 16 : sw[r] & 0xFFFFu);
-                        const float cn = MAGIC + half_bits_to_float<BF16>(h ? ow[r] >> 16 : ow[r] & 0xFFFFu);
+                        float sn = half_bits_to_float<BF16>(h ? sw[r] >> 16 : sw[r] & 0xFFFFu);
+                        float cn = MAGIC + half_bits_to_float<BF16>(h ? ow[r] >> 16 : ow[r] & 0xFFFFu);
+                        if (!BF16 && h) {   // odd columns were accumulated as 1152 + 16 q
+                            sn *= 0.0625f;
+                            cn = 1152.f + 16.f * (cn - MAGIC);
+                        }
 #pragma unroll
                         for (int f = 0; f < MF; ++f)
 #pragma unroll
@@ -469,9 +488,12 @@ cudaError_t launch_wq_mma(const MatmulArgs &p, cudaStream_t s) {
         return cudaErrorMisalignedAddress;
     const bool bf = p.a_type == ET_BF16;
     CUtensorMap tx, tw;
+    // No L2 promotion: every byte of the weight stream is used exactly once by exactly one CTA, and
+    // fetching wider L2 lines than asked for measurably slows the stream down.
     bool ok = make_map(&tx, p.a, bf ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, p.K, p.M, p.K * 2, 64,
-                       pl.mf * 8, CU_TENSOR_MAP_SWIZZLE_128B);
-    ok = ok && make_map(&tw, p.b, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.N / 2, p.K, p.N / 2, 128, MM_SBK, CU_TENSOR_MAP_SWIZZLE_128B);
+                       pl.mf * 8, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE);
+    ok = ok && make_map(&tw, p.b, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.N / 2, p.K, p.N / 2, 128, MM_SBK, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_NONE);
     if (!ok) return cudaErrorInvalidValue;
 
     MmParams mp{};
