@@ -7,10 +7,11 @@
 // stream itself.  Here a packed weight is read from shared memory once (0.5 B), expanded by one
 // lop3 per pair of weights, and goes to the tensor core from registers.
 //
-// Per CTA (one per SM, 18 warps):
+// Per CTA (one per SM, 14 warps):
 //   warp 0       producer: one TMA per super-block (128 K rows x 256 columns of packed int4 = 16 KB,
-//                128-byte swizzle) plus the activation rows of the same K range, into a ring of 8 slots.
-//   warps 1-16   four teams of four warps.  A team owns one quantum (= one scale group, or one
+//                128-byte swizzle, no L2 promotion) plus the activation rows of the same K range, into
+//                a ring of two to four slots per team (as many as fit beside the partial tiles).
+//   warps 1-12   three teams of four warps.  A team owns one quantum (= one scale group, or one
 //                super-block for per-channel scales) at a time; each of its warps covers 64 of the
 //                tile's 256 columns.  Per 16 K rows a lane reads four 32-bit words (rows 2t, 2t+1,
 //                2t+8, 2t+9 of its 8 columns -- bank-conflict free under the swizzle), interleaves row
@@ -20,10 +21,16 @@
 //                one more mma with an all-ones A accumulates the activation sums.  At the end of the
 //                group:   tot += s_g[n] * (acc - (136 + off_g[n]) * sum_g x)
 //                which is the reference's algebra (cuda/src/ops/matmul.cu:334-335) per group, in fp32.
-//   warp 17      reducer: when all teams have finished a tile (or this CTA's piece of it) it sums the
+//   warp 13      reducer: when all teams have finished a tile (or this CTA's piece of it) it sums the
 //                teams' partial tiles from shared memory in a fixed order and writes the output
 //                (whole tile) or an fp32 slot (piece; summed by wq_mma_finalize_kernel).
 // Work split: the (tile, quantum) space is cut into gridDim.x equal contiguous shares (stream-K).
+// Every ring slot belongs to one team, so a team meets the phases of a slot's barrier in order and a
+// parity wait can never be asked about a phase that is two ahead.
+//
+// What bounds it: the integer pipe (prmt, shift, lop3: one op per weight, issued at half rate) and the
+// issue slots run at 60-70 % while the weight stream is kept 128-192 KB deep per SM; a version that
+// skips the arithmetic streams the same bytes only 20 % faster.
 //
 // Replaces the reference's k_wq_fused (cuda/src/ops/matmul.cu:337-352) for int4 weights.
 #include <mutex>

@@ -32,6 +32,23 @@ class forced_path:
             os.environ["B200_QMM_PATH"] = self.prev
 
 
+class env_set:
+    """Set one environment knob of the library for the calls inside the block."""
+
+    def __init__(self, name, value):
+        self.name, self.value = name, value
+
+    def __enter__(self):
+        self.prev = os.environ.get(self.name)
+        os.environ[self.name] = self.value
+
+    def __exit__(self, *a):
+        if self.prev is None:
+            os.environ.pop(self.name, None)
+        else:
+            os.environ[self.name] = self.prev
+
+
 def run_wq(pkg, d, dev, name="aclnnWeightQuantBatchMatmulV2Ex"):
     out = pkg.weight_quant_matmul(d["x"].to(dev), d["w"].to(dev), d["scale"].to(dev), dev_or_none(d["offset"], dev),
                                   dev_or_none(d["bias"], dev), int4=d["int4"], group=d["group"], name=name)
@@ -142,6 +159,52 @@ def test_mx_tensor_core_tails(pkg, oracle, workloads, dev, shape, kinds):
     with forced_path("tc"):
         out = run_mx(pkg, d, dev, torch.float32, "aclnnMatmulMxFp8")
     assert_close(to_np(out), ref_mx(oracle, d), f"mx tails {shape} {kinds}")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M", [1, 2, 3, 5, 8, 9, 13, 16])
+def test_w4a16_decode_kernel_rows(pkg, oracle, workloads, dev, M, dtype):
+    """The decode kernel (register dequant + mma.sync, M <= 16): every row count on both sides of its
+    one- and two-fragment forms, with group scales, offsets and bias, over several tiles and K shares."""
+    d = workloads.w4a16(M=M, K=2048, N=1536, group=128, dtype=dtype, seed=5100 + M)
+    assert_close(to_np(run_wq(pkg, d, dev)), ref_wq(oracle, d), f"decode M={M} {dtype}")
+
+
+@pytest.mark.parametrize("case", [
+    dict(K=1024, N=512, group=256),                      # two super-blocks per scale group
+    dict(K=1024, N=512, group=128, with_offset=False),   # no offset: only the dequant constant is folded
+    dict(K=1024, N=512, group=128, with_bias=False),
+    dict(K=2176, N=800, per_channel=True),               # K and N off every tile size, per-channel scales
+    dict(K=136, N=32, per_channel=True),                 # smallest shape the tensor-core family takes
+    dict(K=8192, N=256, group=128),                      # one tile cut into many K shares
+    dict(K=128, N=8192, group=128),                      # one quantum per tile, more tiles than SMs
+])
+@pytest.mark.parametrize("M", [1, 7, 16])
+def test_w4a16_decode_kernel_shapes(pkg, oracle, workloads, dev, case, M):
+    d = workloads.w4a16(M=M, dtype=torch.bfloat16, seed=5200 + M, **case)
+    assert_close(to_np(run_wq(pkg, d, dev)), ref_wq(oracle, d), f"decode M={M} {case}")
+
+
+@pytest.mark.parametrize("M", [1, 16])
+def test_w4a16_decode_kernel_agrees_with_tcgen05_kernel(pkg, oracle, workloads, dev, M):
+    """The same call through the decode kernel and, with it switched off, through the stream-K
+    tcgen05 kernel that serves M > 16: both within the bounds of the oracle and of each other."""
+    d = workloads.w4a16(M=M, K=4096, N=1024, group=128, dtype=torch.bfloat16, seed=5300 + M)
+    ref = ref_wq(oracle, d)
+    a = to_np(run_wq(pkg, d, dev))
+    with env_set("B200_QMM_WQ_MMA", "0"):
+        b = to_np(run_wq(pkg, d, dev))
+    assert_close(a, ref, "decode kernel")
+    assert_close(b, ref, "tcgen05 stream-K kernel")
+    assert_close(a, b, "decode vs tcgen05")
+
+
+def test_w4a16_decode_kernel_repeatable(pkg, workloads, dev):
+    """Partial tiles are summed in a fixed order: two calls give identical bits."""
+    d = workloads.w4a16(M=4, K=4096, N=2048, group=128, dtype=torch.bfloat16, seed=5400)
+    a = run_wq(pkg, d, dev).clone()
+    b = run_wq(pkg, d, dev)
+    assert torch.equal(a, b)
 
 
 def test_large_m_weight_only_prefill(pkg, oracle, workloads, dev):
