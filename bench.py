@@ -41,8 +41,8 @@ WORKLOAD = ("W4A16 group-128 weight-only matmul, Llama-70B gate/up shape: x bf16
             "bf16 group scales, no offset, no bias")
 CPU_SLICE_N = 2048  # columns of the weight the CPU legs work on
 # DRAM bytes (read + write) of one launch of the dominant kernel on this workload, from the ncu capture
-# summarised in profiles/wq_tc_kernel_w4a16_llama_gateup_m1.md.
-NCU_TRAFFIC_BYTES = 179_524_352
+# summarised in profiles/wq_mma_kernel_w4a16_llama_gateup_m1.md.
+NCU_TRAFFIC_BYTES = 125_184_768
 
 
 def peaks():
