@@ -1,4 +1,4 @@
-// W4A16 decode kernel (M <= 16): TMA-staged packed int4 weights, dequantised in registers, multiplied
+// W4A16 / W8A16 decode kernel (M <= 16): TMA-staged packed weights, dequantised in registers, multiplied
 // on the warp-level tensor-core path (mma.sync m16n8k16), group scales folded in fp32, stream-K.
 //
 // Why not tcgen05 here: at decode shapes the matmul is a stream of weights from HBM, and feeding the
@@ -32,7 +32,10 @@
 // issue slots run at 60-70 % while the weight stream is kept 128-192 KB deep per SM; a version that
 // skips the arithmetic streams the same bytes only 20 % faster.
 //
-// Replaces the reference's k_wq_fused (cuda/src/ops/matmul.cu:337-352) for int4 weights.
+// int8 weights use the same path: a byte is lo + 16 * hi (unsigned low nibble, signed high nibble); the
+// two nibbles ride rows g and g+8 of one mma and are recombined in the fold (tile = 128 columns).
+//
+// Replaces the reference's k_wq_fused (cuda/src/ops/matmul.cu:337-352).
 #include <mutex>
 
 #include "tc_common.cuh"
@@ -46,7 +49,7 @@ constexpr int MM_W_BYTES = 16384;   // packed weights of one super-block: 128 ro
 
 struct MmParams {
     void *out;
-    float *slots;            // [tiles + P][M][256] fp32 partial tiles
+    float *slots;            // [tiles + P][M][tile_n] fp32 partial tiles
     const void *scale, *offset, *bias;
     int sc_type, out_type;
     int M, N, K;
@@ -55,6 +58,7 @@ struct MmParams {
     long long total_q;       // tiles * qpt
     int grouped;
     int ns;                  // ring slots (a multiple of the team count, see mm_ring_slots)
+    int tile_n;              // output columns per tile: 256 (int4) or 128 (int8: two nibbles per column)
 };
 
 // Shared memory of one CTA: [ring: ns slots][partial tiles: teams x M rows x 256 fp32][barriers][flag].
@@ -62,7 +66,7 @@ template <int MF>
 struct MmSmem {
     static constexpr int XBOX = MF * 8 * 128;                 // one activation box: MF*8 rows x 64 k
     static constexpr int SLOT = MM_W_BYTES + 2 * XBOX;        // multiple of 1024
-    __host__ __device__ static int part_bytes(int teams, int M) { return teams * M * MM_TILE_N * 4; }
+    __host__ __device__ static int part_bytes(int teams, int M) { return teams * M * MM_TILE_N * 4; }   // sized for the wider (int4) tile
     __host__ __device__ static int bar_off(int ns, int teams, int M) { return ns * SLOT + part_bytes(teams, M); }
     __host__ __device__ static int total(int ns, int teams, int M) { return bar_off(ns, teams, M) + (2 * ns + 2) * 8 + 16 + 1024; }
 };
@@ -106,6 +110,12 @@ template <bool BF16> __device__ __forceinline__ float half_bits_to_float(uint32_
     return __half2float(__ushort_as_half((unsigned short)h));
 }
 
+__device__ __forceinline__ uint2 ldg8_now(const void *ptr) {
+    uint2 v;
+    asm volatile("ld.global.nc.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(ptr));
+    return v;
+}
+
 // Bounded wait that ignores the abort flag (used only to let copies in flight land before exit).
 __device__ __forceinline__ void mbar_drain(uint32_t bar, uint32_t parity) {
     const unsigned long long t0 = global_ns();
@@ -114,10 +124,11 @@ __device__ __forceinline__ void mbar_drain(uint32_t bar, uint32_t parity) {
     }
 }
 
-template <bool BF16, int MF, int MM_TEAMS>
+template <bool Q8, bool BF16, int MF, int MM_TEAMS>
 __global__ void __launch_bounds__((4 * MM_TEAMS + 2) * 32, 1)
 wq_mma_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w, const MmParams p) {
     using L = MmSmem<MF>;
+    constexpr int TN = Q8 ? 128 : 256;   // output columns per tile (the tile is 256 nibble columns wide)
     const int MM_NS = p.ns;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -157,7 +168,7 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
                     if (round > 0 && !mbar_wait(empty_bar(slot), (round - 1) & 1, abort_flag, 0x300u + slot)) { ok = false; break; }
                     const uint32_t dst = base + slot * L::SLOT;
                     mbar_expect_tx(full_bar(slot), L::SLOT);
-                    tma_load_2d(dst, &tm_w, full_bar(slot), tile * (MM_TILE_N / 2), k0);
+                    tma_load_2d(dst, &tm_w, full_bar(slot), tile * 128, k0);
                     tma_load_2d(dst + MM_W_BYTES, &tm_x, full_bar(slot), k0, 0);
                     tma_load_2d(dst + MM_W_BYTES + L::XBOX, &tm_x, full_bar(slot), k0 + 64, 0);
                     if (++slot == MM_NS) { slot = 0; ++round; }
@@ -184,11 +195,15 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
         // + 1024 for the second fragment
         const uint32_t xrow = MM_W_BYTES + 128 * g + 16 * g + 4 * t;
         constexpr uint32_t ONES = BF16 ? 0x3F803F80u : 0x3C003C00u;
+        // int4: every nibble is a signed weight (xor 8 -> q + 8 above 128.0 / 1024.0).  int8: the byte
+        // is q = lo + 16 * hi with lo the unsigned low nibble (no xor) and hi the signed high nibble.
         uint32_t dq_mask = 0x000F000Fu, dq_magic = BF16 ? 0x43084308u : 0x64086408u;
+        uint32_t dq_magic_even = Q8 ? (BF16 ? 0x43004300u : 0x64006400u) : dq_magic;
         uint32_t dq_mask2 = 0x00F000F0u, dq_magic2 = 0x64806480u;   // fp16 only: nibble at bits 4-7
-        asm volatile("" : "+r"(dq_mask), "+r"(dq_magic), "+r"(dq_mask2), "+r"(dq_magic2));   // keep the constants in registers
+        asm volatile("" : "+r"(dq_mask), "+r"(dq_magic), "+r"(dq_magic_even), "+r"(dq_mask2), "+r"(dq_magic2));   // keep the constants in registers
         constexpr float MAGIC = BF16 ? 136.f : 1032.f;
-        const int n_lane = 64 * wq + 8 * g;   // first of this lane's 8 columns inside the tile
+        // first of this lane's columns inside the tile: 8 nibble columns = 8 (int4) or 4 (int8) outputs
+        const int n_lane = Q8 ? 32 * wq + 4 * g : 64 * wq + 8 * g;
 
         float acc[MF][4][4], tot[MF][4][4], xs[MF][4];
         bool ok = true;
@@ -196,7 +211,7 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
         for (int tile = tile_first; tile <= tile_last && ok; ++tile, ++sg) {
             const long long t_lo = (long long)tile * p.qpt, t_hi = t_lo + p.qpt;
             const int j_lo = (int)((t_lo > qb ? t_lo : qb) - qb), j_hi = (int)((t_hi < qe ? t_hi : qe) - qb);
-            const int n_glob = tile * MM_TILE_N + n_lane;
+            const int n_glob = tile * TN + n_lane;
             const bool n_ok = n_glob < p.N;
             bool had = false;
 #pragma unroll
@@ -215,8 +230,14 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
                 orr = make_uint4(0, 0, 0, 0);
                 if (n_ok && jj < j_hi) {
                     const size_t row = p.grouped ? (size_t)(qi_seg + jj - j_lo) * p.N : 0;
-                    sr = ldg16_now(sc_base + row);
-                    if (of_base) orr = ldg16_now(of_base + row);
+                    if constexpr (Q8) {
+                        const uint2 a = ldg8_now(sc_base + row);
+                        sr.x = a.x; sr.y = a.y;
+                        if (of_base) { const uint2 b = ldg8_now(of_base + row); orr.x = b.x; orr.y = b.y; }
+                    } else {
+                        sr = ldg16_now(sc_base + row);
+                        if (of_base) orr = ldg16_now(of_base + row);
+                    }
                 }
             };
             const int j_first = j_lo + (team - j_lo % MM_TEAMS + MM_TEAMS) % MM_TEAMS;
@@ -262,18 +283,18 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
                             const int sh = (r & 1) * 8;
                             uint32_t a0, a1, a2, a3;
                             if constexpr (BF16) {
-                                a0 = dq_pair(lo[r >> 1] >> sh, dq_mask, dq_magic);
+                                a0 = dq_pair(lo[r >> 1] >> sh, dq_mask, dq_magic_even);
                                 a1 = dq_pair(lo[r >> 1] >> (sh + 4), dq_mask, dq_magic);
-                                a2 = dq_pair(hi[r >> 1] >> sh, dq_mask, dq_magic);
+                                a2 = dq_pair(hi[r >> 1] >> sh, dq_mask, dq_magic_even);
                                 a3 = dq_pair(hi[r >> 1] >> (sh + 4), dq_mask, dq_magic);
                             } else {
                                 // fp16 has room for a nibble at mantissa bits 4-7 too: the odd column of
                                 // each pair is taken in place as 1152 + 16 q (undone in the fold), which
                                 // saves its shift
                                 const uint32_t l = lo[r >> 1] >> sh, h = hi[r >> 1] >> sh;
-                                a0 = dq_pair(l, dq_mask, dq_magic);
+                                a0 = dq_pair(l, dq_mask, dq_magic_even);
                                 a1 = dq_pair(l, dq_mask2, dq_magic2);
-                                a2 = dq_pair(h, dq_mask, dq_magic);
+                                a2 = dq_pair(h, dq_mask, dq_magic_even);
                                 a3 = dq_pair(h, dq_mask2, dq_magic2);
                             }
 #pragma unroll
@@ -287,6 +308,21 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
                 }
                 // fold the finished group
                 const uint32_t sw[4] = {sraw.x, sraw.y, sraw.z, sraw.w}, ow[4] = {oraw.x, oraw.y, oraw.z, oraw.w};
+                if constexpr (Q8) {
+                    // column r of this lane: rows g (low nibbles, MAGIC_LO + lo) and g+8 (high nibbles,
+                    // bf16: 136 + hi, to be taken 16 times; fp16: 1152 + 16 hi) of the same mma
+                    constexpr float HM = BF16 ? 16.f : 1.f, C = BF16 ? 128.f + 16.f * 136.f : 1024.f + 1152.f;
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+                        const float sn = half_bits_to_float<BF16>((r & 1) ? sw[r >> 1] >> 16 : sw[r >> 1] & 0xFFFFu);
+                        const float cn = C + half_bits_to_float<BF16>((r & 1) ? ow[r >> 1] >> 16 : ow[r >> 1] & 0xFFFFu);
+#pragma unroll
+                        for (int f = 0; f < MF; ++f)
+#pragma unroll
+                            for (int e = 0; e < 2; ++e)
+                                tot[f][r][e] = fmaf(sn, fmaf(-cn, xs[f][e], fmaf(HM, acc[f][r][2 + e], acc[f][r][e])), tot[f][r][e]);
+                    }
+                } else
 #pragma unroll
                 for (int r = 0; r < 4; ++r) {
 #pragma unroll
@@ -314,9 +350,9 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
 #pragma unroll
                     for (int r = 0; r < 4; ++r)
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const int m = 8 * f + 2 * t + (e & 1), n = n_lane + 2 * r + (e >> 1);
-                            if (m < p.M) part[(team * p.M + m) * MM_TILE_N + n] = tot[f][r][e];
+                        for (int e = 0; e < (Q8 ? 2 : 4); ++e) {
+                            const int m = 8 * f + 2 * t + (e & 1), n = Q8 ? n_lane + r : n_lane + 2 * r + (e >> 1);
+                            if (m < p.M) part[(team * p.M + m) * TN + n] = tot[f][r][e];
                         }
             }
             __syncwarp();
@@ -331,24 +367,29 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
             const int cnt = j_hi - j_lo;
             const bool whole = cnt == p.qpt;
             if (!mbar_wait(seg_done, sg & 1, abort_flag, 0x330u)) break;
-            // each lane owns 8 consecutive columns
-            const int n = 8 * lane, n_glob = tile * MM_TILE_N + n;
+            // each lane owns CPL consecutive columns
+            constexpr int CPL = TN / 32;
+            const int n = CPL * lane, n_glob = tile * TN + n;
             if (n_glob < p.N) {
                 for (int m = 0; m < p.M; ++m) {
-                    float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                    float v[CPL];
+#pragma unroll
+                    for (int c = 0; c < CPL; ++c) v[c] = 0.f;
 #pragma unroll
                     for (int tm = 0; tm < MM_TEAMS; ++tm) {
                         if (cnt >= MM_TEAMS || (tm - j_lo % MM_TEAMS + MM_TEAMS) % MM_TEAMS < cnt) {
-                            const float4 *src = reinterpret_cast<const float4 *>(part + (tm * p.M + m) * MM_TILE_N + n);
-                            const float4 a = src[0], b = src[1];
-                            v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w;
-                            v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
+                            const float4 *src = reinterpret_cast<const float4 *>(part + (tm * p.M + m) * TN + n);
+#pragma unroll
+                            for (int c = 0; c < CPL / 4; ++c) {
+                                const float4 a = src[c];
+                                v[4 * c] += a.x; v[4 * c + 1] += a.y; v[4 * c + 2] += a.z; v[4 * c + 3] += a.w;
+                            }
                         }
                     }
                     if (whole) {
-                        uint32_t o[4];
+                        uint32_t o[CPL / 2];
 #pragma unroll
-                        for (int c = 0; c < 4; ++c) {
+                        for (int c = 0; c < CPL / 2; ++c) {
                             float lo = v[2 * c], hi = v[2 * c + 1];
                             if (p.bias) {
                                 lo += load_as_float(p.bias, p.sc_type, n_glob + 2 * c);
@@ -362,11 +403,13 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
                                 o[c] = *reinterpret_cast<uint32_t *>(&t2);
                             }
                         }
-                        *reinterpret_cast<uint4 *>(static_cast<uint16_t *>(p.out) + (size_t)m * p.N + n_glob) = make_uint4(o[0], o[1], o[2], o[3]);
+                        uint16_t *dst = static_cast<uint16_t *>(p.out) + (size_t)m * p.N + n_glob;
+                        if constexpr (Q8) *reinterpret_cast<uint2 *>(dst) = make_uint2(o[0], o[1]);
+                        else *reinterpret_cast<uint4 *>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
                     } else {
-                        float4 *dst = reinterpret_cast<float4 *>(p.slots + ((size_t)(tile + cta) * p.M + m) * MM_TILE_N + n);
-                        dst[0] = make_float4(v[0], v[1], v[2], v[3]);
-                        dst[1] = make_float4(v[4], v[5], v[6], v[7]);
+                        float4 *dst = reinterpret_cast<float4 *>(p.slots + ((size_t)(tile + cta) * p.M + m) * TN + n);
+#pragma unroll
+                        for (int c = 0; c < CPL / 4; ++c) dst[c] = make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
                     }
                 }
             }
@@ -381,12 +424,12 @@ __global__ void wq_mma_finalize_kernel(MmParams p, int P) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (size_t)p.M * p.N) return;
     const int n = (int)(i % p.N), m = (int)(i / p.N);
-    const int tile = n / MM_TILE_N;
+    const int tile = n / p.tile_n;
     const long long qa = (long long)tile * p.qpt;
     const int c_first = mm_share_owner(qa, p.total_q, P), c_last = mm_share_owner(qa + p.qpt - 1, p.total_q, P);
     if (c_first == c_last) return;  // written directly by its only owner
     float v = 0.f;
-    for (int c = c_first; c <= c_last; ++c) v += p.slots[((size_t)(tile + c) * p.M + m) * MM_TILE_N + (n % MM_TILE_N)];
+    for (int c = c_first; c <= c_last; ++c) v += p.slots[((size_t)(tile + c) * p.M + m) * p.tile_n + (n % p.tile_n)];
     if (p.bias) v += load_as_float(p.bias, p.sc_type, n);
     store_from_float(p.out, p.out_type, i, v);
 }
@@ -415,7 +458,8 @@ struct MmPlan {
 MmPlan mm_make_plan(const MatmulArgs &p) {
     MmPlan pl{};
     pl.mf = p.M <= 8 ? 1 : 2;
-    pl.tiles = (int)((p.N + MM_TILE_N - 1) / MM_TILE_N);
+    const int tile_n = p.b_type == ET_I8 ? 128 : 256;
+    pl.tiles = (int)((p.N + tile_n - 1) / tile_n);
     const int num_sb = (int)((p.K + MM_SBK - 1) / MM_SBK);
     pl.grouped = p.group < p.K ? 1 : 0;
     pl.sbq = pl.grouped ? (int)(p.group / MM_SBK) : 1;
@@ -423,7 +467,7 @@ MmPlan mm_make_plan(const MatmulArgs &p) {
     pl.total_q = (long long)pl.tiles * pl.qpt;
     const int sms = mm_sm_count();
     pl.P = (int)(pl.total_q < sms ? pl.total_q : sms);
-    pl.slot_bytes = (uint64_t)(pl.tiles + pl.P) * p.M * MM_TILE_N * sizeof(float);
+    pl.slot_bytes = (uint64_t)(pl.tiles + pl.P) * p.M * tile_n * sizeof(float);
     return pl;
 }
 
@@ -443,14 +487,14 @@ int mm_ring_slots(int M, int sbq) {
     return 0;
 }
 
-template <bool BF16, int MF>
+template <bool Q8, bool BF16, int MF>
 cudaError_t mm_launch_one(const CUtensorMap &tx, const CUtensorMap &tw, MmParams mp, int P, cudaStream_t s) {
     using L = MmSmem<MF>;
     static_assert(L::SLOT % 1024 == 0, "slots keep the swizzle alignment");
     mp.ns = mm_ring_slots<MF>(mp.M, mp.sbq);
     if (mp.ns == 0) return cudaErrorInvalidValue;
     const int smem = L::total(mp.ns, MM_TEAMS_USED, mp.M);
-    auto kern = wq_mma_kernel<BF16, MF, MM_TEAMS_USED>;
+    auto kern = wq_mma_kernel<Q8, BF16, MF, MM_TEAMS_USED>;
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -470,9 +514,9 @@ bool wq_mma_supported(const MatmulArgs &p) {
     if (p.epilogue != EPI_PLAIN || !p.scale || p.a_scale || p.b_scale) return false;
     if (p.batch != 1 || p.b_transposed || p.accumulate || p.M < 1 || p.M > 16) return false;
     if (p.a_type != ET_F16 && p.a_type != ET_BF16) return false;
-    if (p.b_type != ET_I4) return false;
+    if (p.b_type != ET_I4 && p.b_type != ET_I8) return false;
     if (p.sc_type != p.a_type || p.out_type != p.a_type || (p.bias && p.bias_type != p.a_type)) return false;
-    if (p.K % 8 != 0 || p.K < MM_SBK || p.N % 32 != 0) return false;
+    if (p.K % 8 != 0 || p.K < MM_SBK || p.N % (p.b_type == ET_I4 ? 32 : 16) != 0) return false;
     if (p.group < p.K) {
         if (p.group % MM_SBK != 0 || p.K % p.group != 0) return false;
         // a ring slot must belong to one team: the ring is two quanta per team deep
@@ -499,7 +543,9 @@ cudaError_t launch_wq_mma(const MatmulArgs &p, cudaStream_t s) {
     // fetching wider L2 lines than asked for measurably slows the stream down.
     bool ok = make_map(&tx, p.a, bf ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, p.K, p.M, p.K * 2, 64,
                        pl.mf * 8, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE);
-    ok = ok && make_map(&tw, p.b, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.N / 2, p.K, p.N / 2, 128, MM_SBK, CU_TENSOR_MAP_SWIZZLE_128B,
+    const bool q8 = p.b_type == ET_I8;
+    const uint64_t row_bytes = q8 ? (uint64_t)p.N : (uint64_t)p.N / 2;
+    ok = ok && make_map(&tw, p.b, CU_TENSOR_MAP_DATA_TYPE_UINT8, row_bytes, p.K, row_bytes, 128, MM_SBK, CU_TENSOR_MAP_SWIZZLE_128B,
                         CU_TENSOR_MAP_L2_PROMOTION_NONE);
     if (!ok) return cudaErrorInvalidValue;
 
@@ -510,10 +556,16 @@ cudaError_t launch_wq_mma(const MatmulArgs &p, cudaStream_t s) {
     mp.sc_type = p.sc_type; mp.out_type = p.out_type;
     mp.M = (int)p.M; mp.N = (int)p.N; mp.K = (int)p.K;
     mp.sbq = pl.sbq; mp.qpt = pl.qpt; mp.total_q = pl.total_q; mp.grouped = pl.grouped;
+    mp.tile_n = q8 ? 128 : 256;
 
     cudaError_t e;
-    if (pl.mf == 1) e = bf ? mm_launch_one<true, 1>(tx, tw, mp, pl.P, s) : mm_launch_one<false, 1>(tx, tw, mp, pl.P, s);
-    else e = bf ? mm_launch_one<true, 2>(tx, tw, mp, pl.P, s) : mm_launch_one<false, 2>(tx, tw, mp, pl.P, s);
+    if (q8) {
+        if (pl.mf == 1) e = bf ? mm_launch_one<true, true, 1>(tx, tw, mp, pl.P, s) : mm_launch_one<true, false, 1>(tx, tw, mp, pl.P, s);
+        else e = bf ? mm_launch_one<true, true, 2>(tx, tw, mp, pl.P, s) : mm_launch_one<true, false, 2>(tx, tw, mp, pl.P, s);
+    } else {
+        if (pl.mf == 1) e = bf ? mm_launch_one<false, true, 1>(tx, tw, mp, pl.P, s) : mm_launch_one<false, false, 1>(tx, tw, mp, pl.P, s);
+        else e = bf ? mm_launch_one<false, true, 2>(tx, tw, mp, pl.P, s) : mm_launch_one<false, false, 2>(tx, tw, mp, pl.P, s);
+    }
     if (e != cudaSuccess) return e;
     // Tiles shared between CTAs exist unless every share boundary falls on a tile boundary.
     if (pl.total_q % pl.P != 0 || (pl.total_q / pl.P) % pl.qpt != 0) {

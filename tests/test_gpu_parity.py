@@ -207,6 +207,28 @@ def test_w4a16_decode_kernel_repeatable(pkg, workloads, dev):
     assert torch.equal(a, b)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M", [1, 4, 8, 11, 16])
+@pytest.mark.parametrize("shape", [(1024, 3072), (2176, 272), (4096, 1024)])
+def test_w8a16_decode_kernel(pkg, oracle, workloads, dev, M, dtype, shape):
+    """int8 weights through the decode kernel: each byte is split into an unsigned low and a signed
+    high nibble that share one mma and are recombined in the fold.  Includes the extreme values
+    -128 and 127, per-channel offsets and a group-wise case."""
+    K, N = shape
+    d = workloads.w8a16(M=M, K=K, N=N, dtype=dtype, with_offset=True, seed=5500 + M)
+    d["w"][0, :] = -128
+    d["w"][1, :] = 127
+    d["w"][2, ::2] = -1
+    assert_close(to_np(run_wq(pkg, d, dev)), ref_wq(oracle, d), f"W8A16 decode M={M} {shape} {dtype}")
+    if K % 256 == 0:
+        g = torch.Generator().manual_seed(5600 + M)
+        d["group"] = 256
+        d["scale"] = (torch.rand((K // 256, N), generator=g) * 0.015 + 0.005).to(dtype)
+        d["offset"] = (torch.rand((K // 256, N), generator=g) * 2 - 1).to(dtype)
+        d["bias"] = (torch.randn(N, generator=g) * 0.02).to(dtype)
+        assert_close(to_np(run_wq(pkg, d, dev)), ref_wq(oracle, d), f"W8A16 g256 decode M={M} {shape} {dtype}")
+
+
 def test_large_m_weight_only_prefill(pkg, oracle, workloads, dev):
     """M above the switch to the expand-then-dense path: weights are rounded once to the activation
     type, as the reference's own large-M path does (cuda/src/ops/matmul.cu:733-747,790-795), and
