@@ -37,6 +37,16 @@ def test_library_exports_every_declared_symbol(pkg):
     assert not missing, missing
 
 
+def test_c_client_library_loads(pkg):
+    """The plain C client of the ABI (the benchmark's end-to-end loop) links against the library
+    and exports its one entry point."""
+    path = os.path.join(os.path.dirname(pkg.LIB_PATH), "libqmm_client.so")
+    assert os.path.exists(path), "run __graft_entry__.build()"
+    ctypes.CDLL(pkg.LIB_PATH)
+    client = ctypes.CDLL(path)
+    assert hasattr(client, "qmmClientWeightQuantPass")
+
+
 def test_hccl_library_exports(pkg):
     if not os.path.exists(pkg.HCCL_PATH):
         pytest.skip("libhccl.so not built (nccl.h absent)")
