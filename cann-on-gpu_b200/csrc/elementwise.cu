@@ -68,6 +68,23 @@ static std::atomic<uint64_t> g_launches{0};
 void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
 uint64_t launch_count() { return g_launches.load(std::memory_order_relaxed); }
 
+// Quant parameter word: low 32 bits = the fp32 bits of the scale, high 32 bits = the offset rounded to
+// the nearest int32 (0 without an offset).  Reference: cuda/src/ops/quant.cu:572-576.
+__global__ void qparam_kernel(const float *scale, const float *offset, int64_t *out, int64_t n) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const uint32_t s = __float_as_uint(scale[i]);
+    const uint32_t o = offset ? (uint32_t)__float2int_rn(offset[i]) : 0u;
+    out[i] = (int64_t)(((uint64_t)o << 32) | (uint64_t)s);
+}
+
+cudaError_t launch_qparam(const float *scale, const float *offset, int64_t *out, int64_t n, cudaStream_t s) {
+    if (n <= 0) return cudaSuccess;
+    qparam_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(scale, offset, out, n);
+    count_launch();
+    return cudaGetLastError();
+}
+
 cudaError_t launch_fill_i64(int64_t *out, int64_t value, cudaStream_t s) {
     fill_i64_kernel<<<1, 1, 0, s>>>(out, value);
     count_launch();

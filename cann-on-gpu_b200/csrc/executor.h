@@ -13,6 +13,7 @@ enum PlanOp : int {
     PLAN_COPY,        // weight copy (identity pre-pack)
     PLAN_WEIGHT_SIZE, // element count of a weight shape
     PLAN_CAST,        // element-wise dtype cast
+    PLAN_QPARAM,      // fp32 scale (+ offset) -> packed int64 quant parameter
 };
 
 // Kernel families a plan can select.

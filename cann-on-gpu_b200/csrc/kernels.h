@@ -104,6 +104,7 @@ uint64_t launch_count();
 // Small element-wise helpers.
 cudaError_t launch_int4_pack(const int8_t *in, uint8_t *out, int64_t n_out, cudaStream_t s);
 cudaError_t launch_fill_i64(int64_t *out, int64_t value, cudaStream_t s);
+cudaError_t launch_qparam(const float *scale, const float *offset, int64_t *out, int64_t n, cudaStream_t s);
 cudaError_t launch_cast(const void *in, int in_type, void *out, int out_type, int64_t n, cudaStream_t s);
 
 }  // namespace qmm

@@ -269,6 +269,10 @@ aclnnStatus run_simple(aclOpExecutor *e, aclrtStream stream) {
             err = launch_cast(data_of(e->a), elem_type(e->a->dtype), const_cast<void *>(data_of(e->out)), elem_type(e->cast_to),
                               e->n, s);
             break;
+        case PLAN_QPARAM:
+            err = launch_qparam((const float *)data_of(e->a), e->b ? (const float *)data_of(e->b) : nullptr,
+                                (int64_t *)const_cast<void *>(data_of(e->out)), e->n, s);
+            break;
         default: err = cudaErrorInvalidValue;
     }
     delete e;
@@ -325,6 +329,37 @@ QMM_ALIAS(aclnnDualLevelQuantMatmulWeightNz, QmmOpts{})
 QMM_ALIAS(aclnnQuantBatchMatmulInplaceAdd, (QmmOpts{false, true, false}))
 QMM_ALIAS(aclnnTransposeQuantBatchMatMul, (QmmOpts{true, false, false}))
 QMM_ALIAS(aclnnBatchMatmulQuant, (QmmOpts{false, false, true}))
+
+// Grouped forms: like the reference (cuda/src/ops/matmul.cu:1195-1202,1402-1413) the group list is
+// accepted and not used -- one group spanning every row.
+#define QMM_GROUPED_ALIAS(NAME, OPTS)                                                                                \
+    aclnnStatus NAME##GetWorkspaceSize(const aclTensor *x, const aclTensor *weight, const aclTensor *scale,          \
+                                       const aclIntArray *groupList, aclTensor *out, uint64_t *ws, aclOpExecutor **ex) { \
+        (void)groupList;                                                                                             \
+        if (!scale) return ACLNN_ERR_PARAM_NULLPTR;                                                                  \
+        return qmm_plan(x, weight, scale, nullptr, nullptr, out, OPTS, ws, ex);                                      \
+    }                                                                                                                \
+    RUN_MATMUL(NAME)
+QMM_GROUPED_ALIAS(aclnnQuantGroupedMatmulDequant, QmmOpts{})
+QMM_GROUPED_ALIAS(aclnnQuantGroupedMatmulDequantWeightNZ, QmmOpts{})
+QMM_GROUPED_ALIAS(aclnnQuantGroupedMatmulInplaceAdd, (QmmOpts{false, true, false}))
+
+// Collective-signature names whose communicator the reference ignores (cuda/src/ops/matmul.cu:1294-1302):
+// the local W8A8 matmul.
+#define QMM_COMM_ALIAS(NAME)                                                                                         \
+    aclnnStatus NAME##GetWorkspaceSize(const aclTensor *x, const aclTensor *weight, const aclTensor *scale, void *comm, \
+                                       aclTensor *out, uint64_t *ws, aclOpExecutor **ex) {                           \
+        (void)comm;                                                                                                  \
+        if (!scale) return ACLNN_ERR_PARAM_NULLPTR;                                                                  \
+        return qmm_plan(x, weight, scale, nullptr, nullptr, out, QmmOpts{}, ws, ex);                                 \
+    }                                                                                                                \
+    RUN_MATMUL(NAME)
+QMM_COMM_ALIAS(aclnnAlltoAllQuantMatmul)
+QMM_COMM_ALIAS(aclnnQuantMatmulAlltoAll)
+QMM_COMM_ALIAS(aclnnAlltoAllvQuantGroupedMatMul)
+QMM_COMM_ALIAS(aclnnQuantGroupedMatMulAlltoAllv)
+QMM_COMM_ALIAS(aclnnQuantReduceScatter)
+QMM_COMM_ALIAS(aclnnQuantMatmulReduceSumWeightNz)
 
 aclnnStatus aclnnQuantMatmulV4ExGetWorkspaceSize(const aclTensor *x1, const aclTensor *x2, const aclTensor *scale,
         const aclTensor *offsetOptional, const aclTensor *pertokenScaleOptional, const aclTensor *biasOptional,
@@ -429,6 +464,26 @@ aclnnStatus aclnnCalculateMatmulWeightSizeV2GetWorkspaceSize(const aclIntArray *
     return weight_size_plan(weightShape, out, ws, ex);
 }
 RUN_SIMPLE(aclnnCalculateMatmulWeightSizeV2)
+
+// fp32 scale (+ optional fp32 offset) -> int64 quant parameter (cuda/src/ops/quant.cu:657-673).
+static aclnnStatus qparam_plan(const aclTensor *scale, const aclTensor *offset, aclTensor *out, uint64_t *ws, aclOpExecutor **ex) {
+    if (!scale || !out || !ws || !ex) return ACLNN_ERR_PARAM_NULLPTR;
+    if (!scale->data || !out->data || (offset && !offset->data)) return ACLNN_ERR_PARAM_NULLPTR;
+    if (scale->dtype != ACL_FLOAT || out->dtype != ACL_INT64 || (offset && offset->dtype != ACL_FLOAT)) return ACLNN_ERR_PARAM_INVALID;
+    if (scale->numel() != out->numel() || (offset && offset->numel() != out->numel())) return ACLNN_ERR_PARAM_INVALID;
+    if (!dense(scale) || !dense(out) || (offset && !dense(offset))) return ACLNN_ERR_PARAM_INVALID;
+    auto *e = new aclOpExecutor();
+    e->op = PLAN_QPARAM; e->a = scale; e->b = offset; e->out = out; e->n = out->numel();
+    *ws = 0; *ex = e;
+    return ACLNN_SUCCESS;
+}
+#define QPARAM_ALIAS(NAME)                                                                                           \
+    aclnnStatus NAME##GetWorkspaceSize(const aclTensor *scale, const aclTensor *offset, aclTensor *out, uint64_t *ws, \
+                                       aclOpExecutor **ex) { return qparam_plan(scale, offset, out, ws, ex); }       \
+    RUN_SIMPLE(NAME)
+QPARAM_ALIAS(aclnnTransQuantParam)
+QPARAM_ALIAS(aclnnTransQuantParamV2)
+QPARAM_ALIAS(aclnnTransQuantParamV3)
 
 aclnnStatus aclnnCastGetWorkspaceSize(const aclTensor *self, aclDataType dtype, aclTensor *out, uint64_t *ws, aclOpExecutor **ex) {
     if (!self || !out || !ws || !ex) return ACLNN_ERR_PARAM_NULLPTR;

@@ -90,6 +90,31 @@ B200_ACLNN_QMM(aclnnTransposeQuantBatchMatMul)
  * (cuda/src/ops/matmul.cu:1097-1149). */
 B200_ACLNN_QMM(aclnnBatchMatmulQuant)
 
+/* Grouped forms: the group list is accepted and ignored, as in the reference (one group over all
+ * rows) -- replaces aclnn_ops.h:2023-2036 (cuda/src/ops/matmul.cu:1195-1202,1402-1413).
+ * ...InplaceAdd: out += result. */
+#define B200_ACLNN_QMM_GROUPED(NAME) \
+    ACL_FUNC_VISIBILITY aclnnStatus NAME##GetWorkspaceSize(const aclTensor *x, const aclTensor *weight, \
+        const aclTensor *scale, const aclIntArray *groupList, aclTensor *out, uint64_t *workspaceSize, \
+        aclOpExecutor **executor); \
+    B200_ACLNN_RUN(NAME)
+B200_ACLNN_QMM_GROUPED(aclnnQuantGroupedMatmulDequant)
+B200_ACLNN_QMM_GROUPED(aclnnQuantGroupedMatmulDequantWeightNZ)
+B200_ACLNN_QMM_GROUPED(aclnnQuantGroupedMatmulInplaceAdd)
+
+/* Collective-signature names whose communicator the reference ignores: the local W8A8 matmul.
+ * comm is an HcclComm (void *).  Replaces aclnn_mc2.h:82-91 (cuda/src/ops/matmul.cu:1294-1302). */
+#define B200_ACLNN_QMM_COMM(NAME) \
+    ACL_FUNC_VISIBILITY aclnnStatus NAME##GetWorkspaceSize(const aclTensor *x, const aclTensor *weight, \
+        const aclTensor *scale, void *comm, aclTensor *out, uint64_t *workspaceSize, aclOpExecutor **executor); \
+    B200_ACLNN_RUN(NAME)
+B200_ACLNN_QMM_COMM(aclnnAlltoAllQuantMatmul)
+B200_ACLNN_QMM_COMM(aclnnQuantMatmulAlltoAll)
+B200_ACLNN_QMM_COMM(aclnnAlltoAllvQuantGroupedMatMul)
+B200_ACLNN_QMM_COMM(aclnnQuantGroupedMatMulAlltoAllv)
+B200_ACLNN_QMM_COMM(aclnnQuantReduceScatter)
+B200_ACLNN_QMM_COMM(aclnnQuantMatmulReduceSumWeightNz)
+
 /* Extended form: out = T( float(acc + bias[n]) * scale[n] * pertokenScale[m] ).
  * bias: ACL_INT32 [N] (added to the exact accumulator); pertokenScale: ACL_FLOAT [M];
  * offsetOptional is accepted for signature compatibility and must be null.
@@ -127,6 +152,16 @@ B200_ACLNN_RUN(aclnnConvertWeightToINT4Pack)
 ACL_FUNC_VISIBILITY aclnnStatus aclnnTransMatmulWeightGetWorkspaceSize(const aclTensor *weight, aclTensor *out,
     uint64_t *workspaceSize, aclOpExecutor **executor);
 B200_ACLNN_RUN(aclnnTransMatmulWeight)
+/* fp32 scale (+ optional fp32 offset) -> ACL_INT64 quant parameter: low 32 bits = bits of the scale,
+ * high 32 bits = offset rounded to the nearest int32.  Replaces aclnn_ops.h:1730-1735
+ * (cuda/src/ops/quant.cu:572-576,657-673). */
+#define B200_ACLNN_QPARAM(NAME) \
+    ACL_FUNC_VISIBILITY aclnnStatus NAME##GetWorkspaceSize(const aclTensor *scale, const aclTensor *offset, \
+        aclTensor *out, uint64_t *workspaceSize, aclOpExecutor **executor); \
+    B200_ACLNN_RUN(NAME)
+B200_ACLNN_QPARAM(aclnnTransQuantParam)
+B200_ACLNN_QPARAM(aclnnTransQuantParamV2)
+B200_ACLNN_QPARAM(aclnnTransQuantParamV3)
 ACL_FUNC_VISIBILITY aclnnStatus aclnnCalculateMatmulWeightSizeGetWorkspaceSize(const aclIntArray *weightShape, aclTensor *out,
     uint64_t *workspaceSize, aclOpExecutor **executor);
 B200_ACLNN_RUN(aclnnCalculateMatmulWeightSize)

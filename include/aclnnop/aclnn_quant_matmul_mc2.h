@@ -1,0 +1,38 @@
+/*
+ * aclnnop/aclnn_quant_matmul_mc2.h -- quantized matmuls followed by an all-reduce over the ranks of a
+ * communicator (K-split tensor parallelism: every rank multiplies its slice of K, the partial
+ * outputs are summed).  Exported by libhccl.so, which runs the local operator of libascendcl.so and
+ * then HcclAllReduce (NCCL over NVLink) on the caller's stream.  comm == NULL: local result only.
+ * Same names and argument order as the reference's include/aclnnop/aclnn_mc2.h:22-24,88-91
+ * (cuda/src/ops/mc2_ext.cu:67-87,185-195; cuda/src/ops/matmul.cu:1304-1319).
+ * Column sharding with no collective, not this, is the scaling path of the library.
+ */
+#ifndef B200_ACLNN_QUANT_MATMUL_MC2_H
+#define B200_ACLNN_QUANT_MATMUL_MC2_H
+
+#include "aclnnop/aclnn_quant_matmul.h"
+#include "hccl/hccl.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_ACLNN_QMM_ALLREDUCE(NAME) \
+    ACL_FUNC_VISIBILITY aclnnStatus NAME##GetWorkspaceSize(const aclTensor *x, const aclTensor *weight, \
+        const aclTensor *scale, HcclComm comm, aclTensor *out, uint64_t *workspaceSize, aclOpExecutor **executor); \
+    ACL_FUNC_VISIBILITY aclnnStatus NAME(void *workspace, uint64_t workspaceSize, aclOpExecutor *executor, aclrtStream stream);
+B200_ACLNN_QMM_ALLREDUCE(aclnnQuantMatmulAllReduce)
+B200_ACLNN_QMM_ALLREDUCE(aclnnQuantMatmulAllReduceV2)
+B200_ACLNN_QMM_ALLREDUCE(aclnnQuantMatmulAllReduceV3)
+B200_ACLNN_QMM_ALLREDUCE(aclnnQuantMatmulAllReduceV4)
+
+ACL_FUNC_VISIBILITY aclnnStatus aclnnWeightQuantMatmulAllReduceGetWorkspaceSize(const aclTensor *x, const aclTensor *weight,
+    const aclTensor *antiquantScale, const aclTensor *antiquantOffset, HcclComm comm, aclTensor *out,
+    uint64_t *workspaceSize, aclOpExecutor **executor);
+ACL_FUNC_VISIBILITY aclnnStatus aclnnWeightQuantMatmulAllReduce(void *workspace, uint64_t workspaceSize,
+    aclOpExecutor *executor, aclrtStream stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,100 @@
+"""One rank of the two-GPU checks (run by test_multi_gpu.py as `python multi_gpu_worker.py rank world dir`).
+
+Rank r uses GPU r.  The communicator is set up the way an HCCL program does it (tools/mc2_2node.cpp:24-31
+of the reference): rank 0 takes HcclGetRootInfo and hands the blob to the others -- here through a file --
+then every rank calls HcclCommInitRootInfo.  Checks:
+  1. column sharding: each rank multiplies its [K, N/g] shard, HcclAllGather returns [g][M][N/g], the
+     interleave is the [M, N] result of the whole problem;
+  2. K-split all-reduce forms: aclnnWeightQuantMatmulAllReduce and aclnnQuantMatmulAllReduce sum the
+     ranks' partial products.
+"""
+import ctypes
+import os
+import sys
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+import __graft_entry__ as ge  # noqa: E402
+from util import assert_close, f32, to_np  # noqa: E402
+
+
+def main():
+    rank, world, tmp = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3]
+    dev = torch.device(f"cuda:{rank}")
+    torch.cuda.set_device(dev)
+    pkg = ge.load_package()
+    oracle = ge.load_oracle()
+    from cann_on_gpu_b200 import workloads
+    hccl_path = os.path.join(os.path.dirname(pkg.LIB_PATH), "libhccl.so")
+    pkg.load()
+    hccl = pkg.load(hccl_path)
+
+    info = ctypes.create_string_buffer(4108)
+    blob = os.path.join(tmp, "root_info.bin")
+    if rank == 0:
+        assert hccl.HcclGetRootInfo(info) == 0
+        with open(blob + ".tmp", "wb") as f:
+            f.write(info.raw)
+        os.rename(blob + ".tmp", blob)
+    else:
+        t0 = time.time()
+        while not os.path.exists(blob):
+            assert time.time() - t0 < 60, "rank 0 never published the root info"
+            time.sleep(0.05)
+        info.raw = open(blob, "rb").read()
+    comm = ctypes.c_void_p()
+    assert hccl.HcclCommInitRootInfo(ctypes.c_uint32(world), info, ctypes.c_uint32(rank), ctypes.byref(comm)) == 0
+    stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+
+    # 1. column shards + all-gather
+    M = 4
+    full = workloads.w4a16(M=M, K=1024, N=1024 * world, group=128, dtype=torch.bfloat16, seed=77)
+    mine = workloads.shard_columns(full, world, rank)
+    out_r = pkg.weight_quant_matmul(mine["x"].to(dev), mine["w"].to(dev), mine["scale"].to(dev), mine["offset"].to(dev),
+                                    mine["bias"].to(dev), int4=True, group=128)
+    gathered = torch.empty((world, M, mine["N"]), dtype=torch.bfloat16, device=dev)
+    HCCL_BF16 = 11   # HCCL_DATA_TYPE_BFP16 (include/hccl/hccl_types.h)
+    assert hccl.HcclAllGather(ctypes.c_void_p(out_r.data_ptr()), ctypes.c_void_p(gathered.data_ptr()),
+                              ctypes.c_uint64(out_r.numel()), ctypes.c_int(HCCL_BF16), comm, stream) == 0
+    torch.cuda.synchronize()
+    whole = workloads.interleave_gathered(gathered, world, M, full["N"])
+    ref = oracle.wqbmm_fast(f32(full["x"]), full["w"].numpy(), True, f32(full["scale"]), f32(full["offset"]), f32(full["bias"]),
+                            M, full["K"], full["N"], 128)
+    assert_close(to_np(whole), ref, f"rank {rank}: gathered column shards")
+
+    # 2. K-split all-reduce forms (reference signatures: fp16, per-channel)
+    d = workloads.w8a16(M=8, K=512 * world, N=256, dtype=torch.float16, with_offset=True, seed=78)
+    ks = slice(rank * 512, (rank + 1) * 512)
+    x_r, w_r = d["x"][:, ks].contiguous().to(dev), d["w"][ks, :].contiguous().to(dev)
+    out = torch.empty((8, 256), dtype=torch.float16, device=dev)
+    with pkg.use_library(hccl_path):
+        pkg.call("aclnnWeightQuantMatmulAllReduce", pkg.AclTensor(x_r), pkg.AclTensor(w_r), pkg.AclTensor(d["scale"].to(dev)),
+                 pkg.AclTensor(d["offset"].to(dev)), comm, pkg.AclTensor(out))
+    torch.cuda.synchronize()
+    ref = oracle.wqbmm_fast(f32(d["x"]), d["w"].numpy(), False, f32(d["scale"]), f32(d["offset"]), None, 8, d["K"], 256, 0)
+    assert_close(to_np(out), ref, f"rank {rank}: aclnnWeightQuantMatmulAllReduce")
+
+    q = workloads.w8a8(M=16, K=256 * world, N=128, seed=79, with_pertoken=False, with_bias=False, scale_dtype=torch.float16)
+    ks = slice(rank * 256, (rank + 1) * 256)
+    qx, qw = q["x"][:, ks].contiguous().to(dev), q["w"][ks, :].contiguous().to(dev)
+    out = torch.empty((16, 128), dtype=torch.float16, device=dev)
+    with pkg.use_library(hccl_path):
+        pkg.call("aclnnQuantMatmulAllReduce", pkg.AclTensor(qx), pkg.AclTensor(qw), pkg.AclTensor(q["scale"].to(dev)), comm,
+                 pkg.AclTensor(out))
+    torch.cuda.synchronize()
+    acc = oracle.qmm_acc_fast(q["x"].numpy(), q["w"].numpy(), 16, q["K"], 128)
+    ref = oracle.qmm_epilogue_fast(acc, f32(q["scale"])).astype(np.float64)
+    assert_close(to_np(out), ref, f"rank {rank}: aclnnQuantMatmulAllReduce")
+
+    assert hccl.HcclCommDestroy(comm) == 0
+    with open(os.path.join(tmp, f"ok.{rank}"), "w") as f:
+        f.write("ok")
+
+
+if __name__ == "__main__":
+    main()

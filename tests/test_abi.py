@@ -14,7 +14,7 @@ def declared_symbols():
     names = set()
     qm = open(os.path.join(INC, "aclnnop", "aclnn_quant_matmul.h")).read()
     body = qm.split('extern "C"', 1)[1]
-    for m in re.finditer(r"^B200_ACLNN_(?:WQBMM|QMM|MX)\((\w+)\)", body, re.M):
+    for m in re.finditer(r"^B200_ACLNN_(?:WQBMM|QMM|MX|QMM_GROUPED|QMM_COMM|QPARAM)\((\w+)\)", body, re.M):
         names.update({m.group(1), m.group(1) + "GetWorkspaceSize"})
     for m in re.finditer(r"^B200_ACLNN_RUN\((\w+)\)", body, re.M):
         names.add(m.group(1))
@@ -80,6 +80,22 @@ def phase1(pkg, name, *args):
     if st == 0:
         lib.aclDestroyAclOpExecutor(ex)
     return st, ws.value
+
+
+def test_hccl_library_exports_allreduce_matmuls(pkg):
+    path = os.path.join(os.path.dirname(pkg.LIB_PATH), "libhccl.so")
+    if not os.path.exists(path):
+        pytest.skip("libhccl.so not built (nccl.h absent)")
+    ctypes.CDLL(pkg.LIB_PATH)
+    try:
+        lib = ctypes.CDLL(path)
+    except OSError as e:
+        pytest.skip(f"libhccl.so not loadable here: {e}")
+    hdr = open(os.path.join(INC, "aclnnop", "aclnn_quant_matmul_mc2.h")).read()
+    names = set(re.findall(r"^B200_ACLNN_QMM_ALLREDUCE\((\w+)\)", hdr, re.M)) | {"aclnnWeightQuantMatmulAllReduce"}
+    assert len(names) == 5
+    for n in names:
+        assert hasattr(lib, n) and hasattr(lib, n + "GetWorkspaceSize"), n
 
 
 def test_wqbmm_phase1_validation(pkg):

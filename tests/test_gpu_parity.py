@@ -473,6 +473,80 @@ def test_against_reference_backend_outputs(pkg, oracle, workloads, dev):
         assert_close(to_np(out), ref[name].astype(np.float64), name)
 
 
+def test_grouped_and_collective_signature_forwards(pkg, oracle, workloads, dev):
+    """Names that the reference forwards to the W8A8 matmul: the grouped forms (group list ignored,
+    cuda/src/ops/matmul.cu:1195-1202,1402-1413) and the collective-signature forms that ignore
+    their communicator (matmul.cu:1294-1302).  Same bits as aclnnQuantMatmul."""
+    d = workloads.w8a8(M=40, K=256, N=96, seed=21, with_pertoken=False, with_bias=False, scale_dtype=torch.float16)
+    _, want = ref_qmm(oracle, d, torch.float16)
+    x, w, sc = d["x"].to(dev), d["w"].to(dev), d["scale"].to(dev)
+    arr = (ctypes.c_int64 * 1)(40)
+    lib = pkg.load()
+    glist = ctypes.c_void_p(lib.aclCreateIntArray(arr, 1))
+    for name in ("aclnnQuantGroupedMatmulDequant", "aclnnQuantGroupedMatmulDequantWeightNZ"):
+        out = torch.empty((40, 96), dtype=torch.float16, device=dev)
+        pkg.call(name, pkg.AclTensor(x), pkg.AclTensor(w), pkg.AclTensor(sc), glist, pkg.AclTensor(out))
+        torch.cuda.synchronize()
+        assert torch.equal(out.cpu(), want), name
+    acc0 = torch.full((40, 96), 0.25, dtype=torch.float16)
+    out = acc0.clone().to(dev)
+    pkg.call("aclnnQuantGroupedMatmulInplaceAdd", pkg.AclTensor(x), pkg.AclTensor(w), pkg.AclTensor(sc), glist, pkg.AclTensor(out))
+    torch.cuda.synchronize()
+    assert torch.equal(out.cpu(), (acc0.float() + want.float()).to(torch.float16))
+    lib.aclDestroyIntArray(glist)
+    for name in ("aclnnAlltoAllQuantMatmul", "aclnnQuantMatmulAlltoAll", "aclnnAlltoAllvQuantGroupedMatMul",
+                 "aclnnQuantGroupedMatMulAlltoAllv", "aclnnQuantReduceScatter", "aclnnQuantMatmulReduceSumWeightNz"):
+        out = torch.empty((40, 96), dtype=torch.float16, device=dev)
+        pkg.call(name, pkg.AclTensor(x), pkg.AclTensor(w), pkg.AclTensor(sc), ctypes.c_void_p(None), pkg.AclTensor(out))
+        torch.cuda.synchronize()
+        assert torch.equal(out.cpu(), want), name
+
+
+def test_trans_quant_param_known_answers(pkg, dev):
+    """fp32 scale (+ offset) -> int64 word: low half the scale's bits, high half the offset rounded
+    to the nearest int32 (cuda/src/ops/quant.cu:572-576)."""
+    scale = torch.tensor([1.0, 0.5, 3.25e-3, 1e10], dtype=torch.float32)
+    offset = torch.tensor([0.0, -1.4, 2.5, 7.6], dtype=torch.float32)
+    bits = scale.view(torch.int32).to(torch.int64) & 0xFFFFFFFF
+    for name in ("aclnnTransQuantParam", "aclnnTransQuantParamV2", "aclnnTransQuantParamV3"):
+        out = torch.zeros(4, dtype=torch.int64, device=dev)
+        pkg.call(name, pkg.AclTensor(scale.to(dev)), pkg.AclTensor(offset.to(dev)), pkg.AclTensor(out))
+        torch.cuda.synchronize()
+        hi = torch.tensor([0, -1, 2, 8], dtype=torch.int64)   # round half to even: 2.5 -> 2
+        assert torch.equal(out.cpu(), ((hi & 0xFFFFFFFF) << 32) | bits), name
+        out = torch.zeros(4, dtype=torch.int64, device=dev)
+        pkg.call(name, pkg.AclTensor(scale.to(dev)), None, pkg.AclTensor(out))
+        torch.cuda.synchronize()
+        assert torch.equal(out.cpu(), bits), name
+    bad = torch.zeros(4, dtype=torch.int32, device=dev)
+    assert pkg.call("aclnnTransQuantParam", pkg.AclTensor(scale.to(dev)), None, pkg.AclTensor(bad), return_status=True) == 161002
+
+
+def test_allreduce_matmuls_without_communicator(pkg, oracle, workloads, dev):
+    """The all-reduce forms with comm == NULL give the local result (the reference's one-rank case,
+    cuda/src/ops/matmul.cu:1304-1319); they live in libhccl.so and run the operators of libascendcl.so."""
+    hccl = os.path.join(os.path.dirname(pkg.LIB_PATH), "libhccl.so")
+    if not os.path.exists(hccl):
+        pytest.skip("libhccl.so not built")
+    d = workloads.w8a8(M=24, K=128, N=64, seed=22, with_pertoken=False, with_bias=False, scale_dtype=torch.float16)
+    _, want = ref_qmm(oracle, d, torch.float16)
+    x, w, sc = pkg.AclTensor(d["x"].to(dev)), pkg.AclTensor(d["w"].to(dev)), pkg.AclTensor(d["scale"].to(dev))
+    dw = workloads.w8a16(M=4, K=256, N=128, dtype=torch.float16, with_offset=True, seed=23)
+    wx, ww = pkg.AclTensor(dw["x"].to(dev)), pkg.AclTensor(dw["w"].to(dev))
+    ws_, wo = pkg.AclTensor(dw["scale"].to(dev)), pkg.AclTensor(dw["offset"].to(dev))
+    with pkg.use_library(hccl):
+        for name in ("aclnnQuantMatmulAllReduce", "aclnnQuantMatmulAllReduceV2", "aclnnQuantMatmulAllReduceV3",
+                     "aclnnQuantMatmulAllReduceV4"):
+            out = torch.empty((24, 64), dtype=torch.float16, device=dev)
+            pkg.call(name, x, w, sc, ctypes.c_void_p(None), pkg.AclTensor(out))
+            torch.cuda.synchronize()
+            assert torch.equal(out.cpu(), want), name
+        out = torch.empty((4, 128), dtype=torch.float16, device=dev)
+        pkg.call("aclnnWeightQuantMatmulAllReduce", wx, ww, ws_, wo, ctypes.c_void_p(None), pkg.AclTensor(out))
+        torch.cuda.synchronize()
+    assert_close(to_np(out), ref_wq(oracle, dw), "aclnnWeightQuantMatmulAllReduce, one rank")
+
+
 def test_zz_no_bounded_wait_gave_up(pkg, dev):
     """Every spin inside the tensor-core kernels is bounded and records a code when it gives up;
     after the whole suite the device status word must still be 0."""
