@@ -37,6 +37,7 @@
 //
 // Replaces the reference's k_wq_fused (cuda/src/ops/matmul.cu:337-352).
 #include <mutex>
+#include <type_traits>
 
 #include "tc_common.cuh"
 
@@ -88,6 +89,18 @@ __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1
     } else {
         asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
             : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    }
+}
+
+// The same with a zero C operand: the first step of a group needs no cleared accumulators.
+template <bool BF16>
+__device__ __forceinline__ void mma16816_first(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    if constexpr (BF16) {
+        asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %10, %10, %10};"
+            : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
+    } else {
+        asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %10, %10, %10};"
+            : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
     }
 }
 
@@ -208,6 +221,9 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
         float acc[MF][4][4], tot[MF][4][4], xs[MF][4];
         bool ok = true;
         int sg = 0;
+        // This team's stages are i = j * sbq + u for its quanta j = team, team + TEAMS, ...; their ring
+        // slot and pass number are kept incrementally.
+        int slot = team * p.sbq, round = 0;
         for (int tile = tile_first; tile <= tile_last && ok; ++tile, ++sg) {
             const long long t_lo = (long long)tile * p.qpt, t_hi = t_lo + p.qpt;
             const int j_lo = (int)((t_lo > qb ? t_lo : qb) - qb), j_hi = (int)((t_hi < qe ? t_hi : qe) - qb);
@@ -248,18 +264,8 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
                 sraw = snext;
                 oraw = onext;
                 fetch_rows(j + MM_TEAMS, snext, onext);
-#pragma unroll
-                for (int f = 0; f < MF; ++f) {
-#pragma unroll
-                    for (int r = 0; r < 4; ++r)
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) acc[f][r][e] = 0.f;
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) xs[f][e] = 0.f;
-                }
                 for (int u = 0; u < p.sbq && ok; ++u) {
-                    const unsigned i = (unsigned)(j * p.sbq + u), round = i / (unsigned)MM_NS;
-                    const int slot = (int)(i - round * (unsigned)MM_NS);
+                    const bool first_sb = u == 0;
                     if (!mbar_wait(full_bar(slot), round & 1, abort_flag, 0x310u + slot)) { ok = false; break; }
                     const uint32_t sb = base + slot * L::SLOT, xb = sb + xrow;
 #pragma unroll
@@ -298,48 +304,69 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
                                 a3 = dq_pair(h, dq_mask2, dq_magic2);
                             }
 #pragma unroll
-                            for (int f = 0; f < MF; ++f) mma16816<BF16>(acc[f][r], a0, a1, a2, a3, b0[f], b1[f]);
+                            for (int f = 0; f < MF; ++f) {
+                                if (st == 0 && first_sb) mma16816_first<BF16>(acc[f][r], a0, a1, a2, a3, b0[f], b1[f]);
+                                else mma16816<BF16>(acc[f][r], a0, a1, a2, a3, b0[f], b1[f]);
+                            }
                         }
 #pragma unroll
-                        for (int f = 0; f < MF; ++f) mma16816<BF16>(xs[f], ONES, ONES, ONES, ONES, b0[f], b1[f]);
+                        for (int f = 0; f < MF; ++f) {
+                            if (st == 0 && first_sb) mma16816_first<BF16>(xs[f], ONES, ONES, ONES, ONES, b0[f], b1[f]);
+                            else mma16816<BF16>(xs[f], ONES, ONES, ONES, ONES, b0[f], b1[f]);
+                        }
                     }
                     __syncwarp();
                     if (lane == 0) mbar_arrive(empty_bar(slot));
+                    if (++slot == MM_NS) { slot = 0; ++round; }
                 }
-                // fold the finished group
+                // skip the other teams' stages of this round robin
+                slot += (MM_TEAMS - 1) * p.sbq;
+                while (slot >= MM_NS) { slot -= MM_NS; ++round; }
+                // fold the finished group (one uniform branch on the presence of offsets, so that the
+                // common offset-free form carries no conversions or selects for them)
                 const uint32_t sw[4] = {sraw.x, sraw.y, sraw.z, sraw.w}, ow[4] = {oraw.x, oraw.y, oraw.z, oraw.w};
-                if constexpr (Q8) {
-                    // column r of this lane: rows g (low nibbles, MAGIC_LO + lo) and g+8 (high nibbles,
-                    // bf16: 136 + hi, to be taken 16 times; fp16: 1152 + 16 hi) of the same mma
-                    constexpr float HM = BF16 ? 16.f : 1.f, C = BF16 ? 128.f + 16.f * 136.f : 1024.f + 1152.f;
+                auto fold = [&](auto has_off) {
+                    constexpr bool OFF = decltype(has_off)::value;
+                    if constexpr (Q8) {
+                        // column r of this lane: rows g (low nibbles, MAGIC_LO + lo) and g+8 (high nibbles,
+                        // bf16: 136 + hi, to be taken 16 times; fp16: 1152 + 16 hi) of the same mma
+                        constexpr float HM = BF16 ? 16.f : 1.f, C = BF16 ? 128.f + 16.f * 136.f : 1024.f + 1152.f;
 #pragma unroll
-                    for (int r = 0; r < 4; ++r) {
-                        const float sn = half_bits_to_float<BF16>((r & 1) ? sw[r >> 1] >> 16 : sw[r >> 1] & 0xFFFFu);
-                        const float cn = C + half_bits_to_float<BF16>((r & 1) ? ow[r >> 1] >> 16 : ow[r >> 1] & 0xFFFFu);
+                        for (int r = 0; r < 4; ++r) {
+                            const float sn = half_bits_to_float<BF16>((r & 1) ? sw[r >> 1] >> 16 : sw[r >> 1] & 0xFFFFu);
+                            float cn = C;
+                            if constexpr (OFF) cn += half_bits_to_float<BF16>((r & 1) ? ow[r >> 1] >> 16 : ow[r >> 1] & 0xFFFFu);
 #pragma unroll
-                        for (int f = 0; f < MF; ++f)
+                            for (int f = 0; f < MF; ++f)
 #pragma unroll
-                            for (int e = 0; e < 2; ++e)
-                                tot[f][r][e] = fmaf(sn, fmaf(-cn, xs[f][e], fmaf(HM, acc[f][r][2 + e], acc[f][r][e])), tot[f][r][e]);
-                    }
-                } else
-#pragma unroll
-                for (int r = 0; r < 4; ++r) {
-#pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        float sn = half_bits_to_float<BF16>(h ? sw[r] >> 16 : sw[r] & 0xFFFFu);
-                        float cn = MAGIC + half_bits_to_float<BF16>(h ? ow[r] >> 16 : ow[r] & 0xFFFFu);
-                        if (!BF16 && h) {   // odd columns were accumulated as 1152 + 16 q
-                            sn *= 0.0625f;
-                            cn = 1152.f + 16.f * (cn - MAGIC);
+                                for (int e = 0; e < 2; ++e)
+                                    tot[f][r][e] = fmaf(sn, fmaf(-cn, xs[f][e], fmaf(HM, acc[f][r][2 + e], acc[f][r][e])), tot[f][r][e]);
                         }
+                    } else {
 #pragma unroll
-                        for (int f = 0; f < MF; ++f)
+                        for (int r = 0; r < 4; ++r) {
 #pragma unroll
-                            for (int e = 0; e < 2; ++e)
-                                tot[f][r][2 * h + e] = fmaf(sn, fmaf(-cn, xs[f][e], acc[f][r][2 * h + e]), tot[f][r][2 * h + e]);
+                            for (int h = 0; h < 2; ++h) {
+                                float sn = half_bits_to_float<BF16>(h ? sw[r] >> 16 : sw[r] & 0xFFFFu);
+                                // odd columns of the fp16 form were accumulated as 1152 + 16 q
+                                const bool scaled = !BF16 && h;
+                                float cn = scaled ? 1152.f : MAGIC;
+                                if constexpr (OFF) {
+                                    const float off = half_bits_to_float<BF16>(h ? ow[r] >> 16 : ow[r] & 0xFFFFu);
+                                    cn += scaled ? 16.f * off : off;
+                                }
+                                if (scaled) sn *= 0.0625f;
+#pragma unroll
+                                for (int f = 0; f < MF; ++f)
+#pragma unroll
+                                    for (int e = 0; e < 2; ++e)
+                                        tot[f][r][2 * h + e] = fmaf(sn, fmaf(-cn, xs[f][e], acc[f][r][2 * h + e]), tot[f][r][2 * h + e]);
+                            }
+                        }
                     }
-                }
+                };
+                if (of_base) fold(std::true_type{});
+                else fold(std::false_type{});
             }
             if (!ok) break;
             // hand this team's partial tile to the reducer
