@@ -236,34 +236,34 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
                 for (int r = 0; r < 4; ++r)
 #pragma unroll
                     for (int e = 0; e < 4; ++e) tot[f][r][e] = 0.f;
-            // scale / offset rows of a group: 8 consecutive columns = 16 bytes per lane, fetched one
-            // quantum ahead of their use
-            const uint16_t *sc_base = static_cast<const uint16_t *>(p.scale) + n_glob;
-            const uint16_t *of_base = p.offset ? static_cast<const uint16_t *>(p.offset) + n_glob : nullptr;
+            // scale / offset rows of a group: 8 consecutive columns = 16 bytes per lane (8 bytes for int8
+            // weights), fetched one quantum ahead of their use.  Lanes beyond N read column 0 (unused).
+            const int n_safe = n_ok ? n_glob : 0;
             const int qi_seg = (int)(qb + j_lo - t_lo);   // quantum index inside the tile of local quantum j_lo
-            auto fetch_rows = [&](int jj, uint4 &sr, uint4 &orr) {
-                sr = make_uint4(0, 0, 0, 0);
-                orr = make_uint4(0, 0, 0, 0);
-                if (n_ok && jj < j_hi) {
-                    const size_t row = p.grouped ? (size_t)(qi_seg + jj - j_lo) * p.N : 0;
-                    if constexpr (Q8) {
-                        const uint2 a = ldg8_now(sc_base + row);
-                        sr.x = a.x; sr.y = a.y;
-                        if (of_base) { const uint2 b = ldg8_now(of_base + row); orr.x = b.x; orr.y = b.y; }
-                    } else {
-                        sr = ldg16_now(sc_base + row);
-                        if (of_base) orr = ldg16_now(of_base + row);
-                    }
+            const int j_first = j_lo + (team - j_lo % MM_TEAMS + MM_TEAMS) % MM_TEAMS;
+            const size_t row_step = p.grouped ? (size_t)MM_TEAMS * p.N : 0;
+            const uint16_t *sc_ptr = static_cast<const uint16_t *>(p.scale) + n_safe +
+                                     (p.grouped ? (size_t)(qi_seg + j_first - j_lo) * p.N : 0);
+            const uint16_t *of_base = p.offset ? static_cast<const uint16_t *>(p.offset) : nullptr;
+            const ptrdiff_t of_delta = of_base ? reinterpret_cast<const uint16_t *>(p.offset) - reinterpret_cast<const uint16_t *>(p.scale) : 0;
+            auto fetch_rows = [&](const uint16_t *sp, uint4 &sr, uint4 &orr) {
+                if constexpr (Q8) {
+                    const uint2 a = ldg8_now(sp);
+                    sr.x = a.x; sr.y = a.y;
+                    if (of_base) { const uint2 b = ldg8_now(sp + of_delta); orr.x = b.x; orr.y = b.y; }
+                } else {
+                    sr = ldg16_now(sp);
+                    if (of_base) orr = ldg16_now(sp + of_delta);
                 }
             };
-            const int j_first = j_lo + (team - j_lo % MM_TEAMS + MM_TEAMS) % MM_TEAMS;
-            uint4 sraw, oraw, snext, onext;
-            fetch_rows(j_first, snext, onext);
+            uint4 sraw = make_uint4(0, 0, 0, 0), oraw = sraw, snext = sraw, onext = sraw;
+            if (j_first < j_hi) fetch_rows(sc_ptr, snext, onext);
             for (int j = j_first; j < j_hi && ok; j += MM_TEAMS) {
                 had = true;
                 sraw = snext;
                 oraw = onext;
-                fetch_rows(j + MM_TEAMS, snext, onext);
+                if (j + MM_TEAMS < j_hi) sc_ptr += row_step;   // the last quantum fetches its own row again
+                fetch_rows(sc_ptr, snext, onext);
                 for (int u = 0; u < p.sbq && ok; ++u) {
                     const bool first_sb = u == 0;
                     if (!mbar_wait(full_bar(slot), round & 1, abort_flag, 0x310u + slot)) { ok = false; break; }
