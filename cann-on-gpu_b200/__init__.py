@@ -204,6 +204,15 @@ def mx_matmul(a, a_kind, sa, b, b_kind, sb, M, K, N, out_dtype=None, name="aclnn
     return out
 
 
+def dynamic_quant(x, name="aclnnDynamicQuant", **kw):
+    """x [..., D] f32/f16/bf16 -> (int8 [..., D], fp32 per-row scales [...])."""
+    import torch
+    q = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+    scale = torch.empty(x.shape[:-1] if x.dim() > 1 else (1,), dtype=torch.float32, device=x.device)
+    call(name, AclTensor(x), AclTensor(q), AclTensor(scale), **kw)
+    return q, scale
+
+
 def cast(src, src_kind, dst_kind, n, **kw):
     """aclnnCast over flat buffers; returns the destination buffer (uint8 for fp8/fp4 kinds)."""
     import torch

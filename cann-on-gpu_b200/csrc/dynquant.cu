@@ -1,0 +1,119 @@
+// Per-token dynamic int8 quantiser, the step in front of the W8A8 matmul: for every row of x
+//   scale = max|x| / 127 (1 for an all-zero row),  q = clamp(rint(x * (1 / scale)), -128, 127)
+// written as int8 plus the fp32 scale per row (which the matmul takes as pertokenScale).
+// Same arithmetic, in the same order, as the reference (cuda/src/ops/quant.cu:37-49): the quotient
+// is formed as x * (1.f / scale) in fp32 and rounded half-to-even, so results are bit-identical.
+//
+// HBM-bound: the reference reads x twice (maximum, then quantise); here a row of up to 16384 elements
+// stays in registers between the two phases, so x is read once: algorithmic bytes per row
+// D * (sizeof(x) + 1) + 4.  One CTA per row, 16-byte loads and 8/16-byte stores.
+#include "device_utils.cuh"
+
+namespace qmm {
+namespace {
+
+constexpr int DQ_THREADS = 256;
+constexpr int DQ_VEC = 8;   // elements per 16-byte load of a 16-bit type
+
+__device__ __forceinline__ int8_t quant_i8(float v) {
+    const int q = (int)rintf(v);
+    return (int8_t)(q < -128 ? -128 : (q > 127 ? 127 : q));
+}
+
+__device__ __forceinline__ float block_max(float v, float *sh) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float m = 0.f;
+#pragma unroll
+    for (int w = 0; w < DQ_THREADS / 32; ++w) m = fmaxf(m, sh[w]);
+    return m;
+}
+
+// 16-bit inputs, D % 8 == 0, D <= DQ_THREADS * 8 * CHUNKS: the row lives in registers.
+template <bool BF16, int CHUNKS>
+__global__ void __launch_bounds__(DQ_THREADS) dynquant_row_kernel(const uint16_t *x, int8_t *q, float *scale_out, int64_t D) {
+    __shared__ float sh[DQ_THREADS / 32];
+    const int64_t base = (int64_t)blockIdx.x * D;
+    uint4 v[CHUNKS];
+    float amax = 0.f;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+        const int64_t d = ((int64_t)c * DQ_THREADS + threadIdx.x) * DQ_VEC;
+        v[c] = make_uint4(0, 0, 0, 0);
+        if (d < D) v[c] = __ldg(reinterpret_cast<const uint4 *>(x + base + d));
+        const uint32_t w[4] = {v[c].x, v[c].y, v[c].z, v[c].w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float lo, hi;
+            if constexpr (BF16) { lo = __uint_as_float(w[i] << 16); hi = __uint_as_float(w[i] & 0xFFFF0000u); }
+            else { lo = __half2float(__ushort_as_half((unsigned short)(w[i] & 0xFFFFu))); hi = __half2float(__ushort_as_half((unsigned short)(w[i] >> 16))); }
+            amax = fmaxf(amax, fmaxf(fabsf(lo), fabsf(hi)));
+        }
+    }
+    const float m = block_max(amax, sh);
+    const float scale = m == 0.f ? 1.f : m / 127.f;
+    if (threadIdx.x == 0) scale_out[blockIdx.x] = scale;
+    const float inv = 1.f / scale;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+        const int64_t d = ((int64_t)c * DQ_THREADS + threadIdx.x) * DQ_VEC;
+        if (d >= D) continue;
+        const uint32_t w[4] = {v[c].x, v[c].y, v[c].z, v[c].w};
+        uint32_t o[2] = {0, 0};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float lo, hi;
+            if constexpr (BF16) { lo = __uint_as_float(w[i] << 16); hi = __uint_as_float(w[i] & 0xFFFF0000u); }
+            else { lo = __half2float(__ushort_as_half((unsigned short)(w[i] & 0xFFFFu))); hi = __half2float(__ushort_as_half((unsigned short)(w[i] >> 16))); }
+            const uint32_t b0 = (uint8_t)quant_i8(lo * inv), b1 = (uint8_t)quant_i8(hi * inv);
+            o[i >> 1] |= (b0 | (b1 << 8)) << (16 * (i & 1));
+        }
+        *reinterpret_cast<uint2 *>(q + base + d) = make_uint2(o[0], o[1]);
+    }
+}
+
+// Any type, any D: two passes over the row (the second one hits L2).
+__global__ void __launch_bounds__(DQ_THREADS) dynquant_generic_kernel(const void *x, int x_type, int8_t *q, float *scale_out, int64_t D) {
+    __shared__ float sh[DQ_THREADS / 32];
+    const int64_t base = (int64_t)blockIdx.x * D;
+    float amax = 0.f;
+    for (int64_t d = threadIdx.x; d < D; d += DQ_THREADS) amax = fmaxf(amax, fabsf(load_as_float(x, x_type, base + d)));
+    const float m = block_max(amax, sh);
+    const float scale = m == 0.f ? 1.f : m / 127.f;
+    if (threadIdx.x == 0) scale_out[blockIdx.x] = scale;
+    const float inv = 1.f / scale;
+    for (int64_t d = threadIdx.x; d < D; d += DQ_THREADS) q[base + d] = quant_i8(load_as_float(x, x_type, base + d) * inv);
+}
+
+}  // namespace
+
+cudaError_t launch_dynamic_quant(const void *x, int x_type, int8_t *q, float *scale_out, int64_t rows, int64_t D, cudaStream_t s) {
+    if (rows <= 0 || D <= 0) return cudaSuccess;
+    if (rows > 0x7fffffffLL) return cudaErrorInvalidValue;
+    const bool vec = (x_type == ET_BF16 || x_type == ET_F16) && D % DQ_VEC == 0 &&
+                     (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(q) & 7) == 0;
+    const unsigned g = (unsigned)rows;
+    const uint16_t *x16 = static_cast<const uint16_t *>(x);
+    const int64_t per = (int64_t)DQ_THREADS * DQ_VEC;
+    if (vec && D <= per * 1) {
+        if (x_type == ET_BF16) dynquant_row_kernel<true, 1><<<g, DQ_THREADS, 0, s>>>(x16, q, scale_out, D);
+        else dynquant_row_kernel<false, 1><<<g, DQ_THREADS, 0, s>>>(x16, q, scale_out, D);
+    } else if (vec && D <= per * 2) {
+        if (x_type == ET_BF16) dynquant_row_kernel<true, 2><<<g, DQ_THREADS, 0, s>>>(x16, q, scale_out, D);
+        else dynquant_row_kernel<false, 2><<<g, DQ_THREADS, 0, s>>>(x16, q, scale_out, D);
+    } else if (vec && D <= per * 4) {
+        if (x_type == ET_BF16) dynquant_row_kernel<true, 4><<<g, DQ_THREADS, 0, s>>>(x16, q, scale_out, D);
+        else dynquant_row_kernel<false, 4><<<g, DQ_THREADS, 0, s>>>(x16, q, scale_out, D);
+    } else if (vec && D <= per * 8) {
+        if (x_type == ET_BF16) dynquant_row_kernel<true, 8><<<g, DQ_THREADS, 0, s>>>(x16, q, scale_out, D);
+        else dynquant_row_kernel<false, 8><<<g, DQ_THREADS, 0, s>>>(x16, q, scale_out, D);
+    } else {
+        dynquant_generic_kernel<<<g, DQ_THREADS, 0, s>>>(x, x_type, q, scale_out, D);
+    }
+    count_launch();
+    return cudaGetLastError();
+}
+
+}  // namespace qmm

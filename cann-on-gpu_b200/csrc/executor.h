@@ -14,6 +14,7 @@ enum PlanOp : int {
     PLAN_WEIGHT_SIZE, // element count of a weight shape
     PLAN_CAST,        // element-wise dtype cast
     PLAN_QPARAM,      // fp32 scale (+ offset) -> packed int64 quant parameter
+    PLAN_DYNQUANT,    // per-token dynamic int8 quantiser
 };
 
 // Kernel families a plan can select.
@@ -35,6 +36,7 @@ struct aclOpExecutor {
     const aclTensor *bias = nullptr;
     const aclTensor *pertoken = nullptr;
     aclTensor *out = nullptr;
+    aclTensor *out2 = nullptr;            // second output (per-token scales of the dynamic quantiser)
     int64_t batch = 1, m = 0, n = 0, k = 0;
     int64_t group = 0;          // rows of K per antiquant scale row (K for per-channel)
     bool b_transposed = false;  // weight stored [N,K]

@@ -269,6 +269,10 @@ aclnnStatus run_simple(aclOpExecutor *e, aclrtStream stream) {
             err = launch_cast(data_of(e->a), elem_type(e->a->dtype), const_cast<void *>(data_of(e->out)), elem_type(e->cast_to),
                               e->n, s);
             break;
+        case PLAN_DYNQUANT:
+            err = launch_dynamic_quant(data_of(e->a), elem_type(e->a->dtype), (int8_t *)const_cast<void *>(data_of(e->out)),
+                                       (float *)const_cast<void *>(data_of(e->out2)), e->m, e->k, s);
+            break;
         case PLAN_QPARAM:
             err = launch_qparam((const float *)data_of(e->a), e->b ? (const float *)data_of(e->b) : nullptr,
                                 (int64_t *)const_cast<void *>(data_of(e->out)), e->n, s);
@@ -464,6 +468,32 @@ aclnnStatus aclnnCalculateMatmulWeightSizeV2GetWorkspaceSize(const aclIntArray *
     return weight_size_plan(weightShape, out, ws, ex);
 }
 RUN_SIMPLE(aclnnCalculateMatmulWeightSizeV2)
+
+// Per-token dynamic int8 quantiser: x [..., D] -> int8 of the same shape + fp32 scale per row
+// (cuda/src/ops/quant.cu:99-111; V2-V4 are the reference's version aliases).
+static aclnnStatus dynquant_plan(const aclTensor *x, aclTensor *out, aclTensor *scaleOut, uint64_t *ws, aclOpExecutor **ex) {
+    if (!x || !out || !scaleOut || !ws || !ex) return ACLNN_ERR_PARAM_NULLPTR;
+    if (x->viewDims.empty()) return ACLNN_ERR_PARAM_INVALID;
+    if (x->numel() > 0 && (!x->data || !out->data || !scaleOut->data)) return ACLNN_ERR_PARAM_NULLPTR;
+    if (out->dtype != ACL_INT8 || scaleOut->dtype != ACL_FLOAT || x->viewDims != out->viewDims) return ACLNN_ERR_PARAM_INVALID;
+    if (x->dtype != ACL_FLOAT && x->dtype != ACL_FLOAT16 && x->dtype != ACL_BF16) return ACLNN_ERR_PARAM_INVALID;
+    if (!dense(x) || !dense(out) || !dense(scaleOut)) return ACLNN_ERR_PARAM_INVALID;
+    const int64_t D = x->viewDims.back();
+    const int64_t rows = D > 0 ? x->numel() / D : 0;
+    if (scaleOut->numel() != rows) return ACLNN_ERR_PARAM_INVALID;
+    auto *e = new aclOpExecutor();
+    e->op = PLAN_DYNQUANT; e->a = x; e->out = out; e->out2 = scaleOut; e->m = rows; e->k = D;
+    *ws = 0; *ex = e;
+    return ACLNN_SUCCESS;
+}
+#define DYNQUANT_ALIAS(NAME)                                                                                         \
+    aclnnStatus NAME##GetWorkspaceSize(const aclTensor *x, aclTensor *out, aclTensor *scaleOut, uint64_t *ws,        \
+                                       aclOpExecutor **ex) { return dynquant_plan(x, out, scaleOut, ws, ex); }      \
+    RUN_SIMPLE(NAME)
+DYNQUANT_ALIAS(aclnnDynamicQuant)
+DYNQUANT_ALIAS(aclnnDynamicQuantV2)
+DYNQUANT_ALIAS(aclnnDynamicQuantV3)
+DYNQUANT_ALIAS(aclnnDynamicQuantV4)
 
 // fp32 scale (+ optional fp32 offset) -> int64 quant parameter (cuda/src/ops/quant.cu:657-673).
 static aclnnStatus qparam_plan(const aclTensor *scale, const aclTensor *offset, aclTensor *out, uint64_t *ws, aclOpExecutor **ex) {

@@ -385,13 +385,19 @@ cudaError_t launch_dense_tc(const MatmulArgs &p, cudaStream_t s) {
 
     CUtensorMap tx, tw;
     bool ok;
+    // With one row tile every weight byte is read once by one CTA: asking L2 for wider lines than the
+    // box needs only slows the stream (measured on the decode kernel).  With several row tiles the
+    // CTAs that share a weight tile run together and the wider fetch is kept.
+    static const int promo_knob = [] { const char *e = getenv("B200_QMM_DENSE_W_PROMO"); return e ? atoi(e) : -1; }();
+    CUtensorMapL2promotion w_promo = pl.m_tiles == 1 ? CU_TENSOR_MAP_L2_PROMOTION_NONE : CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
+    if (promo_knob >= 0) w_promo = promo_knob == 0 ? CU_TENSOR_MAP_L2_PROMOTION_NONE : CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
     if (pl.mode == D_I8) {
         ok = make_map(&tx, p.a, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.K, p.M, p.K, 128, pl.mt, CU_TENSOR_MAP_SWIZZLE_128B) &&
-             make_map(&tw, p.b, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.N, p.K, p.N, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+             make_map(&tw, p.b, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.N, p.K, p.N, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B, w_promo);
     } else {
         const CUtensorMapDataType dt = pl.mode == D_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
         ok = make_map(&tx, p.a, dt, p.K, p.M, p.K * 2, 64, pl.mt, CU_TENSOR_MAP_SWIZZLE_128B) &&
-             make_map(&tw, p.b, dt, p.N, p.K, p.N * 2, 64, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+             make_map(&tw, p.b, dt, p.N, p.K, p.N * 2, 64, 64, CU_TENSOR_MAP_SWIZZLE_128B, w_promo);
     }
     if (!ok) return cudaErrorInvalidValue;
 

@@ -152,6 +152,19 @@ B200_ACLNN_RUN(aclnnConvertWeightToINT4Pack)
 ACL_FUNC_VISIBILITY aclnnStatus aclnnTransMatmulWeightGetWorkspaceSize(const aclTensor *weight, aclTensor *out,
     uint64_t *workspaceSize, aclOpExecutor **executor);
 B200_ACLNN_RUN(aclnnTransMatmulWeight)
+/* Per-token dynamic int8 quantiser, the producer of x1 and pertokenScale for the W8A8 matmul:
+ * per row of x [..., D] (ACL_FLOAT, ACL_FLOAT16 or ACL_BF16): scaleOut = max|x| / 127 (1 for a zero row,
+ * ACL_FLOAT, one per row), out = clamp(rint(x * (1 / scaleOut)), -128, 127) as ACL_INT8.
+ * Replaces aclnn_ops.h:1076-1095 (cuda/src/ops/quant.cu:37-49,99-111). */
+#define B200_ACLNN_DYNQUANT(NAME) \
+    ACL_FUNC_VISIBILITY aclnnStatus NAME##GetWorkspaceSize(const aclTensor *x, aclTensor *out, aclTensor *scaleOut, \
+        uint64_t *workspaceSize, aclOpExecutor **executor); \
+    B200_ACLNN_RUN(NAME)
+B200_ACLNN_DYNQUANT(aclnnDynamicQuant)
+B200_ACLNN_DYNQUANT(aclnnDynamicQuantV2)
+B200_ACLNN_DYNQUANT(aclnnDynamicQuantV3)
+B200_ACLNN_DYNQUANT(aclnnDynamicQuantV4)
+
 /* fp32 scale (+ optional fp32 offset) -> ACL_INT64 quant parameter: low 32 bits = bits of the scale,
  * high 32 bits = offset rounded to the nearest int32.  Replaces aclnn_ops.h:1730-1735
  * (cuda/src/ops/quant.cu:572-576,657-673). */

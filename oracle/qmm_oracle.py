@@ -288,6 +288,19 @@ def mx_matmul_fast(a, a_kind, sa, b, b_kind, sb, M, K, N):
     return mx_dequant_fast(a, a_kind, sa, M, K, True) @ mx_dequant_fast(b, b_kind, sb, K, N, False)
 
 
+def dynamic_quant(x):
+    """Per-token dynamic int8 quantiser, restating cuda/src/ops/quant.cu:37-49 of the reference in fp32:
+    scale = max|x| / 127 per row (1 for an all-zero row), q = clamp(rint(x * (1 / scale)), -128, 127)
+    with the quotient formed as x * (1.f / scale) and rint rounding half to even.
+    x: float array [..., D] (already widened to fp32 exactly).  Returns (int8 [..., D], float32 [...])."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    amax = np.abs(x).max(axis=-1) if x.shape[-1] else np.zeros(x.shape[:-1], np.float32)
+    scale = np.where(amax == 0, np.float32(1), amax / np.float32(127)).astype(np.float32)
+    inv = (np.float32(1) / scale).astype(np.float32)
+    q = np.rint((x * inv[..., None]).astype(np.float32))
+    return np.clip(q, -128, 127).astype(np.int8), scale
+
+
 # ------------------------------------------------------------------ PyTorch-CPU form (all host cores)
 def wqbmm_torch(x, w, is_int4, scale, offset, bias, M, K, N, group=0):
     """The same weight-only matmul written with PyTorch CPU ops: dequantise in fp32, then torch.matmul

@@ -547,6 +547,39 @@ def test_allreduce_matmuls_without_communicator(pkg, oracle, workloads, dev):
     assert_close(to_np(out), ref_wq(oracle, dw), "aclnnWeightQuantMatmulAllReduce, one rank")
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(1, 1024), (8, 4096), (300, 8192), (5, 100), (3, 7, 520), (2, 16384), (2, 20000)])
+def test_dynamic_quant_bit_exact(pkg, oracle, dev, shape, dtype):
+    """Per-token int8 quantiser (cuda/src/ops/quant.cu:37-49,99-111): int8 codes and fp32 scales are
+    bit-identical to the oracle for every input type, row length (register-resident, vectorised and
+    generic forms) and for all-zero rows; all four names."""
+    g = torch.Generator().manual_seed(6000 + shape[-1])
+    x = (torch.randn(shape, generator=g) * 3).to(dtype)
+    x.view(-1, shape[-1])[0, :] = 0
+    want_q, want_s = oracle.dynamic_quant(x.float().numpy())
+    for name in ("aclnnDynamicQuant", "aclnnDynamicQuantV2", "aclnnDynamicQuantV3", "aclnnDynamicQuantV4"):
+        q, sc = pkg.dynamic_quant(x.to(dev), name=name)
+        torch.cuda.synchronize()
+        assert np.array_equal(sc.cpu().numpy().reshape(want_s.shape), want_s), name
+        assert np.array_equal(q.cpu().numpy(), want_q), name
+
+
+def test_dynamic_quant_feeds_the_w8a8_matmul(pkg, oracle, workloads, dev):
+    """The chain a W8A8 layer runs: quantise the activations per token, then aclnnQuantMatmulV4 with
+    the scales as pertokenScale.  Accumulators and output bit-exact against the oracle's chain."""
+    g = torch.Generator().manual_seed(6100)
+    M, K, N = 48, 1024, 256
+    x = torch.randn((M, K), generator=g).to(torch.bfloat16)
+    d = workloads.w8a8(M=M, K=K, N=N, seed=6101, with_pertoken=False)
+    q, sc = pkg.dynamic_quant(x.to(dev))
+    out = pkg.quant_matmul(q, d["w"].to(dev), d["scale"].to(dev), sc, d["bias"].to(dev), out_dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+    want_q, want_s = oracle.dynamic_quant(x.float().numpy())
+    acc = oracle.qmm_acc_fast(want_q, d["w"].numpy(), M, K, N)
+    want = torch.from_numpy(oracle.qmm_epilogue_fast(acc, f32(d["scale"]), want_s, d["bias"].numpy())).to(torch.bfloat16)
+    assert torch.equal(out.cpu(), want)
+
+
 def test_zz_no_bounded_wait_gave_up(pkg, dev):
     """Every spin inside the tensor-core kernels is bounded and records a code when it gives up;
     after the whole suite the device status word must still be 0."""

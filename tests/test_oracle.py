@@ -208,3 +208,21 @@ def test_reference_backend_outputs_pin_the_oracle(oracle, workloads):
     x = cases.cast_input().numpy()
     assert np.array_equal(ref["cast_e2m1"], oracle.pack_nibbles(oracle.e2m1_encode_fast(x)))
     assert np.array_equal(ref["cast_e4m3"], oracle.e4m3_encode_fast(x * 64))
+
+
+def test_dynamic_quant_oracle_matches_the_reference_tests_formula(oracle):
+    """The reference's own check of DynamicQuant (tests/test_fp8.cpp:391-399) recomputes
+    scale = amax / 127 and q = lrint(x / scale) on the host and demands zero mismatches on
+    rand()*4-2 inputs; the oracle (which forms the quotient as x * (1/scale), like the reference's
+    kernel) must agree with that formula on such data up to ties of the two roundings."""
+    rng = np.random.default_rng(7)
+    x = (rng.random((64, 512), dtype=np.float32) * 4 - 2).astype(np.float32)
+    x[3] = 0
+    q, sc = oracle.dynamic_quant(x)
+    amax = np.abs(x).max(axis=1)
+    want_sc = np.where(amax == 0, 1.0, amax / np.float32(127)).astype(np.float32)
+    assert np.array_equal(sc, want_sc)
+    want_q = np.clip(np.rint(x / want_sc[:, None]), -128, 127).astype(np.int8)
+    assert (q != want_q).mean() < 1e-4 and np.abs(q.astype(int) - want_q.astype(int)).max() <= 1
+    assert np.abs(q).max() == 127 and (q[3] == 0).all() and sc[3] == 1
+    assert np.abs(q * sc[:, None] - x).max() <= sc.max() * 0.5 + 1e-6
