@@ -42,7 +42,7 @@ WORKLOAD = ("W4A16 group-128 weight-only matmul, Llama-70B gate/up shape: x bf16
 CPU_SLICE_N = 2048  # columns of the weight the CPU legs work on
 # DRAM bytes (read + write) of one launch of the dominant kernel on this workload, from the ncu capture
 # summarised in profiles/wq_mma_kernel_w4a16_llama_gateup_m1.md.
-NCU_TRAFFIC_BYTES = 125_184_768
+NCU_TRAFFIC_BYTES = 124_836_608
 
 
 def peaks():
@@ -264,6 +264,21 @@ def sweep(pkg, workloads, dev, pk, only=None):
                         pkg.AclTensor(d["pertoken"].to(dev)), pkg.AclTensor(d["bias"].to(dev)), pkg.AclTensor(out)]
                 calls.append(lambda ws, a=args: pkg.call("aclnnQuantMatmulV4Ex", *a, workspace=ws, device=dev))
             run_case(f"cfg2 W8A8 M={m} K=4096 N=14336 bf16 out", calls, 2 * m * 4096 * 14336, 4096 * 14336, 5)
+            del calls
+        # the activation quantiser in front of config 2 (HBM-bound: "weight_gbs" here is all bytes moved,
+        # rows * D * (2 + 1) + rows * 4, per second)
+        for m in (2048, 4096):
+            name = f"DynamicQuant per-token bf16 [{m},4096] -> int8 (feeds cfg2)"
+            if not wanted(name):
+                continue
+            calls = []
+            for i in range(12):   # 12 x (32 MB in + 16 MB out) > 2 x L2
+                x = torch.randn((m, 4096), generator=torch.Generator().manual_seed(3000 + i)).to(torch.bfloat16).to(dev)
+                q = torch.empty((m, 4096), dtype=torch.int8, device=dev)
+                sc = torch.empty((m,), dtype=torch.float32, device=dev)
+                args = [pkg.AclTensor(x), pkg.AclTensor(q), pkg.AclTensor(sc)]
+                calls.append(lambda ws, a=args: pkg.call("aclnnDynamicQuant", *a, workspace=ws, device=dev))
+            run_case(name, calls, 0, m * 4096 * 3 + m * 4, 10)
             del calls
         # config 3: MXFP8 x MXFP4 4096 x 8192 x 8192
         if not wanted("cfg3 MXFP8xMXFP4 M=4096 K=8192 N=8192 bf16 out"):

@@ -561,8 +561,11 @@ uint64_t wq_mma_workspace_bytes(const MatmulArgs &p) { return mm_make_plan(p).sl
 cudaError_t launch_wq_mma(const MatmulArgs &p, cudaStream_t s) {
     const MmPlan pl = mm_make_plan(p);
     if (p.workspace_bytes < pl.slot_bytes || !p.workspace) return cudaErrorInvalidValue;
+    // TMA sources, the 16-byte scale / offset loads, the 16-byte output stores and the float4 partial
+    // tiles all need 16-byte aligned bases (every row pitch already is a multiple of 16 bytes).
     if ((reinterpret_cast<uintptr_t>(p.a) & 15) || (reinterpret_cast<uintptr_t>(p.b) & 15) ||
-        (reinterpret_cast<uintptr_t>(p.scale) & 15) || (reinterpret_cast<uintptr_t>(p.offset) & 15))
+        (reinterpret_cast<uintptr_t>(p.scale) & 15) || (reinterpret_cast<uintptr_t>(p.offset) & 15) ||
+        (reinterpret_cast<uintptr_t>(p.out) & 15) || (reinterpret_cast<uintptr_t>(p.workspace) & 15))
         return cudaErrorMisalignedAddress;
     const bool bf = p.a_type == ET_BF16;
     CUtensorMap tx, tw;
