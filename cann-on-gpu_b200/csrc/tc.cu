@@ -300,10 +300,28 @@ TcPlan make_plan(const MatmulArgs &p) {
     pl.m_tiles = (int)((p.M + pl.mt - 1) / pl.mt);
     pl.tiles = n_tiles * pl.m_tiles;
     const int sms = dev_info().sms > 0 ? dev_info().sms : 148;
-    // Split K while there are fewer tiles than about two per SM, keeping at least 4 K blocks per unit.
+    // Split K only where it pays.  A unit pulls kb * bk * (mt + 128) operand bytes into its SM at about
+    // 45 GB/s (what one SM gets when all of them stream), units run in rounds of one per SM, and a
+    // split adds the fp32 partial tiles (written, then read by the finalize kernel) plus that kernel's
+    // launch.  Take the split with the smallest estimate, keeping at least 4 K blocks per unit.
+    // (Measured on W8A8 4096 x 14336: M = 1 takes 14.0 us unsplit and 18.4 us split in 3; M = 256 takes
+    // 34 us unsplit and 59 us split in 3.)  B200_QMM_DENSE_SPLIT=<n> overrides for A/B runs.
     int split = 1;
-    if (pl.tiles < 2 * sms) split = (2 * sms + pl.tiles - 1) / pl.tiles;
-    if (split > pl.num_kb / 4) split = pl.num_kb / 4;
+    {
+        const double elem = pl.mode == D_I8 ? 1.0 : 2.0;
+        double best = 1e30;
+        const int max_split = pl.num_kb / 4 > 1 ? pl.num_kb / 4 : 1;
+        for (int sct = 1; sct <= max_split && sct <= 32; ++sct) {
+            const int kbps = (pl.num_kb + sct - 1) / sct, eff = (pl.num_kb + kbps - 1) / kbps;
+            const long long units = (long long)pl.tiles * eff;
+            const double rounds = (double)((units + sms - 1) / sms);
+            double t = rounds * kbps * pl.bk * (pl.mt + TILE_N) * elem / 45e9;
+            if (eff > 1) t += 2.0 * eff * (double)p.M * (double)p.N * 4.0 / 3e12 + 3e-6;   // partial tiles move at about 3 TB/s
+            if (t < best * 0.97) { best = t; split = eff; }   // a later split must win by a margin
+        }
+    }
+    if (const char *e = getenv("B200_QMM_DENSE_SPLIT")) { const int v = atoi(e); if (v >= 1) split = v; }
+    if (split > pl.num_kb) split = pl.num_kb;
     if (split < 1) split = 1;
     pl.kb_per_split = (pl.num_kb + split - 1) / split;
     pl.split = (pl.num_kb + pl.kb_per_split - 1) / pl.kb_per_split;
@@ -388,9 +406,7 @@ cudaError_t launch_dense_tc(const MatmulArgs &p, cudaStream_t s) {
     // With one row tile every weight byte is read once by one CTA: asking L2 for wider lines than the
     // box needs only slows the stream (measured on the decode kernel).  With several row tiles the
     // CTAs that share a weight tile run together and the wider fetch is kept.
-    static const int promo_knob = [] { const char *e = getenv("B200_QMM_DENSE_W_PROMO"); return e ? atoi(e) : -1; }();
-    CUtensorMapL2promotion w_promo = pl.m_tiles == 1 ? CU_TENSOR_MAP_L2_PROMOTION_NONE : CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
-    if (promo_knob >= 0) w_promo = promo_knob == 0 ? CU_TENSOR_MAP_L2_PROMOTION_NONE : CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
+    const CUtensorMapL2promotion w_promo = pl.m_tiles == 1 ? CU_TENSOR_MAP_L2_PROMOTION_NONE : CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
     if (pl.mode == D_I8) {
         ok = make_map(&tx, p.a, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.K, p.M, p.K, 128, pl.mt, CU_TENSOR_MAP_SWIZZLE_128B) &&
              make_map(&tw, p.b, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.N, p.K, p.N, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B, w_promo);

@@ -722,13 +722,7 @@ cudaError_t launch_wq_tc(const MatmulArgs &p, cudaStream_t s) {
     CUtensorMap tx, tw;
     bool ok = make_map(&tx, p.a, bf ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, p.K, p.M, p.K * 2, 64,
                        pl.mt, CU_TENSOR_MAP_SWIZZLE_128B);
-    // L2 promotion of the weight stream: B200_QMM_W_L2PROMO = 0 (none), 1 (64 B), 2 (128 B), 3 (256 B)
-    CUtensorMapL2promotion promo = CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
-    if (const char *e = getenv("B200_QMM_W_L2PROMO")) {
-        const int v = atoi(e);
-        promo = v == 0 ? CU_TENSOR_MAP_L2_PROMOTION_NONE : v == 1 ? CU_TENSOR_MAP_L2_PROMOTION_L2_64B
-              : v == 2 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B : CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
-    }
+    const CUtensorMapL2promotion promo = CU_TENSOR_MAP_L2_PROMOTION_L2_256B;   // none / 128 B measured the same here
     if (q4) ok = ok && make_map(&tw, p.b, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.N / 2, p.K, p.N / 2, 64, SBK, CU_TENSOR_MAP_SWIZZLE_64B, promo);
     else ok = ok && make_map(&tw, p.b, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.N, p.K, p.N, 128, SBK, CU_TENSOR_MAP_SWIZZLE_128B, promo);
     if (!ok) return cudaErrorInvalidValue;
