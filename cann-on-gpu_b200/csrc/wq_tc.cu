@@ -95,14 +95,18 @@ template <bool Q4, bool BF16>
 __device__ __forceinline__ void convert_chunk(const uint32_t (&w)[4], uint32_t dst, int k, int part) {
     if constexpr (Q4) {
         // (nibble ^ 8) | magic == (x & 0x000F000F) ^ MAGIC_X: value + 8 + 128 (bf16) or + 1024 (fp16), exact
-        constexpr uint32_t MAGIC_X = BF16 ? 0x43084308u : 0x64086408u;
         constexpr uint32_t BIAS = BF16 ? 0x43084308u : 0x64086408u;  // 136.0 | 1032.0
+        // mask and magic live in registers so that (v & mask) ^ magic is ONE lop3 (with two
+        // immediates the compiler emits two)
+        uint32_t mask = 0x000F000Fu, magic = BIAS;
+        asm volatile("" : "+r"(mask), "+r"(magic));
 #pragma unroll
         for (int jw = 0; jw < 4; ++jw) {
             uint32_t o[4];
 #pragma unroll
             for (int h = 0; h < 4; ++h) {
-                const uint32_t pair = ((w[jw] >> (4 * h)) & 0x000F000Fu) ^ MAGIC_X;
+                uint32_t pair;
+                asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(pair) : "r"(w[jw] >> (4 * h)), "r"(mask), "r"(magic));
                 if constexpr (BF16) {
                     __nv_bfloat162 d = __hsub2(*reinterpret_cast<const __nv_bfloat162 *>(&pair),
                                                *reinterpret_cast<const __nv_bfloat162 *>(&BIAS));
