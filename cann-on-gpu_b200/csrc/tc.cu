@@ -17,8 +17,11 @@
 //     alternate between units, so the epilogue of one unit overlaps the MMAs of the next.
 //     Warp 0 = TMA producer, warp 1 = MMA issuer (+TMEM owner), warps 2-9 = epilogue (two sets of four
 //     warps, each set takes half of the accumulator columns).
-//   * Split-K (K slices as separate units) fills the SMs at decode shapes; partial sums go to the
-//     caller's workspace and tc_finalize_kernel reduces them and applies the epilogue.
+//   * Whole rounds of one tile per SM run unsplit; only the tiles left over after them (all tiles
+//     when there are fewer tiles than SMs) may be cut into K slices, so that the last round is
+//     short instead of mostly idle.  Their raw accumulators go to the caller's workspace, one
+//     [MT][128] tile per slice, and tc_finalize_kernel sums them and applies the epilogue.  Whether
+//     to cut, and how finely, is decided by a small cost model (make_plan).
 //   * Every wait is bounded (about a second) and records a code in a device status word.
 #include <cstring>
 #include <mutex>
@@ -42,7 +45,7 @@ constexpr int W_TILE_BYTES = 16384;  // weight tile per stage: 128 n x 128 k int
 
 struct TcParams {
     void *out;
-    void *partial;            // [split][M][N] fp32 or int32 raw accumulators, or null
+    void *partial;            // [split][tail tile][MT][128] fp32 or int32 raw accumulators of the split tiles, or null
     const void *scale;        // W8A8: [N]
     const void *bias;
     const float *pertoken;
@@ -50,8 +53,12 @@ struct TcParams {
     int M, N, K;
     int m_tiles, tiles;       // tiles are numbered n_tile * m_tiles + m_tile
     int num_kb;               // K blocks in total
-    int kb_per_split;         // K blocks per unit
-    int units;                // tiles * split
+    int full_units;           // the first full_units tiles run unsplit, one unit each (a multiple of the grid)
+    int tail_tiles;           // the remaining tiles ...
+    int split;                // ... are cut into `split` K slices each, so the last round is short
+    int kb_per_split;         // K blocks per slice of a tail tile
+    int units;                // full_units + tail_tiles * split
+    int mt;                   // rows per tile (for the finalize kernel)
 };
 
 template <int MT, int STAGES>
@@ -103,13 +110,22 @@ tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUte
 
     // unit u -> (K slice z, tile); tiles of one K slice are consecutive and m-tiles of one weight tile
     // are adjacent, so CTAs running side by side share weight tiles in L2.
+    // z < 0: the unit is a whole tile and runs the epilogue itself; z >= 0: K slice z of tail tile
+    // (tile - full_units), whose raw accumulators go to the workspace.
     auto unit_geom = [&](int u, int &n0, int &m0, int &kb0, int &nkb, int &z) {
-        z = u / p.tiles;
-        const int tile = u % p.tiles;
+        int tile;
+        if (u < p.full_units) {
+            tile = u; z = -1; kb0 = 0; nkb = p.num_kb;
+        } else {
+            const int v = u - p.full_units;
+            tile = p.full_units + v % p.tail_tiles;
+            z = v / p.tail_tiles;
+            kb0 = z * p.kb_per_split;
+            nkb = min(p.num_kb, kb0 + p.kb_per_split) - kb0;
+            if (p.split == 1) z = -1;
+        }
         n0 = (tile / p.m_tiles) * TILE_N;
         m0 = (tile % p.m_tiles) * MT;
-        kb0 = z * p.kb_per_split;
-        nkb = min(p.num_kb, kb0 + p.kb_per_split) - kb0;
     };
 
     if (warp == 0) {
@@ -178,9 +194,15 @@ tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUte
             const int a = ui & 1;
             const int n = n0 + r;
             const bool n_ok = n < p.N;
+            const bool to_partial = z >= 0;
+            uint32_t *part_tile = nullptr;   // this unit's [MT][128] raw tile in the workspace
+            if (to_partial) {
+                const int tail_idx = (u - p.full_units) % p.tail_tiles;
+                part_tile = (uint32_t *)p.partial + ((size_t)z * p.tail_tiles + tail_idx) * (MT * TILE_N);
+            }
             float sc = 0.f, bf = 0.f;
             int bi = 0;
-            if (n_ok && !p.partial) {
+            if (n_ok && !to_partial) {
                 if (p.epilogue == EPI_DEQ_I32) {
                     sc = load_as_float(p.scale, p.sc_type, n);
                     if (p.bias) bi = ((const int32_t *)p.bias)[n];
@@ -195,12 +217,21 @@ tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUte
 #pragma unroll
             for (int i = 0; i < PR; ++i) {
                 const int m = m0 + cb + lane + 32 * i;
-                ptv[i] = (p.pertoken && !p.partial && lane + 32 * i < CH && m < p.M) ? __ldg(p.pertoken + m) : 1.f;
+                ptv[i] = (p.pertoken && lane + 32 * i < CH && m < p.M) ? __ldg(p.pertoken + m) : 1.f;
             }
-            const bool has_pt = p.pertoken != nullptr && !p.partial;
+            const bool has_pt = p.pertoken != nullptr;
             if (!mbar_wait(bar_acc_full(a), (ui >> 1) & 1, abort_flag, 5)) break;
             tc_fence_after();
-            if (active) {
+            if (active && to_partial) {
+                // K slice of a tail tile: raw fp32 / int32 bits of the whole tile go to the workspace
+#pragma unroll 1
+                for (int c0 = cb; c0 < cb + CH; c0 += 16) {
+                    uint32_t v[16];
+                    tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + a * MT + c0, v);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) part_tile[(c0 + j) * TILE_N + r] = v[j];
+                }
+            } else if (active) {
 #pragma unroll 1
                 for (int c0 = cb; c0 < cb + CH; c0 += 16) {
                     uint32_t v[16];
@@ -212,9 +243,7 @@ tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUte
                         const int m = m0 + c0 + j;
                         if (!n_ok || m >= p.M) continue;
                         const size_t o = (size_t)m * p.N + n;
-                        if (p.partial) {
-                            ((uint32_t *)p.partial)[(size_t)z * p.M * p.N + o] = v[j];   // raw fp32 or int32 bits
-                        } else if constexpr (INT8) {
+                        if constexpr (INT8) {
                             const int acc = (int)v[j];
                             if (p.epilogue == EPI_RAW_I32) ((int32_t *)p.out)[o] = acc;
                             else {
@@ -244,19 +273,23 @@ tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUte
 }
 
 // Split-K reduction + epilogue: out = epi(sum_z partial[z]).
-__global__ void tc_finalize_kernel(TcParams p, int split) {
-    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x, mn = (size_t)p.M * p.N;
-    if (i >= mn) return;
-    const int n = (int)(i % p.N), m = (int)(i / p.N);
+__global__ void tc_finalize_kernel(TcParams p) {
+    const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x, per_tile = (size_t)p.mt * TILE_N;
+    if (e >= per_tile * p.tail_tiles) return;
+    const int t = (int)(e / per_tile), ml = (int)((e / TILE_N) % p.mt), nl = (int)(e % TILE_N);
+    const int tile = p.full_units + t;
+    const int n = (tile / p.m_tiles) * TILE_N + nl, m = (tile % p.m_tiles) * p.mt + ml;
+    if (n >= p.N || m >= p.M) return;
+    const size_t i = (size_t)m * p.N + n, stride = per_tile * p.tail_tiles, off = e;
     if (p.epilogue == EPI_PLAIN) {
         float v = 0.f;
-        for (int z = 0; z < split; ++z) v += ((const float *)p.partial)[z * mn + i];
+        for (int z = 0; z < p.split; ++z) v += ((const float *)p.partial)[z * stride + off];
         if (p.bias) v += load_as_float(p.bias, p.bias_type, n);
         store_from_float(p.out, p.out_type, i, v);
         return;
     }
     int acc = 0;
-    for (int z = 0; z < split; ++z) acc += ((const int32_t *)p.partial)[z * mn + i];
+    for (int z = 0; z < p.split; ++z) acc += ((const int32_t *)p.partial)[z * stride + off];
     if (p.epilogue == EPI_RAW_I32) { ((int32_t *)p.out)[i] = acc; return; }
     if (p.bias) acc += ((const int32_t *)p.bias)[n];
     float f = (float)acc * load_as_float(p.scale, p.sc_type, n);
@@ -285,7 +318,7 @@ DevInfo &dev_info() {
 }
 
 struct TcPlan {
-    int mode, mt, bk, split, num_kb, kb_per_split, m_tiles, tiles, units, P;
+    int mode, mt, bk, split, num_kb, kb_per_split, m_tiles, tiles, units, P, full_units, tail_tiles;
     uint64_t partial_bytes;
 };
 
@@ -300,34 +333,38 @@ TcPlan make_plan(const MatmulArgs &p) {
     pl.m_tiles = (int)((p.M + pl.mt - 1) / pl.mt);
     pl.tiles = n_tiles * pl.m_tiles;
     const int sms = dev_info().sms > 0 ? dev_info().sms : 148;
-    // Split K only where it pays.  A unit pulls kb * bk * (mt + 128) operand bytes into its SM at about
-    // 45 GB/s (what one SM gets when all of them stream), units run in rounds of one per SM, and a
-    // split adds the fp32 partial tiles (written, then read by the finalize kernel) plus that kernel's
-    // launch.  Take the split with the smallest estimate, keeping at least 4 K blocks per unit.
-    // (Measured on W8A8 4096 x 14336: M = 1 takes 14.0 us unsplit and 18.4 us split in 3; M = 256 takes
-    // 34 us unsplit and 59 us split in 3.)  B200_QMM_DENSE_SPLIT=<n> overrides for A/B runs.
+    // Whole rounds of one tile per SM run unsplit.  The tiles left over (all of them when there are
+    // fewer tiles than SMs) are cut along K so that the last round is short instead of leaving most
+    // SMs idle -- but only where that pays.  A unit pulls kb * bk * (mt + 128) operand bytes into its SM
+    // at about 45 GB/s (what one SM gets when all of them stream), units run in rounds of one per SM, and
+    // a split adds the raw partial tiles (written, then read by the finalize kernel, at about 3 TB/s)
+    // plus that kernel's launch.  Take the split with the smallest estimate, keeping at least 4 K
+    // blocks per unit.  (Measured on W8A8 4096 x 14336: M = 1 takes 14.0 us unsplit and 18.4 us split in
+    // 3; M = 256 takes 34 us unsplit and 59 us split in 3.)  B200_QMM_DENSE_SPLIT=<n> overrides.
+    pl.full_units = (pl.tiles / sms) * sms;
+    pl.tail_tiles = pl.tiles - pl.full_units;
     int split = 1;
-    {
+    if (pl.tail_tiles > 0) {
         const double elem = pl.mode == D_I8 ? 1.0 : 2.0;
         double best = 1e30;
         const int max_split = pl.num_kb / 4 > 1 ? pl.num_kb / 4 : 1;
-        for (int sct = 1; sct <= max_split && sct <= 32; ++sct) {
+        for (int sct = 1; sct <= max_split && sct <= 64; ++sct) {
             const int kbps = (pl.num_kb + sct - 1) / sct, eff = (pl.num_kb + kbps - 1) / kbps;
-            const long long units = (long long)pl.tiles * eff;
+            const long long units = (long long)pl.tail_tiles * eff;
             const double rounds = (double)((units + sms - 1) / sms);
             double t = rounds * kbps * pl.bk * (pl.mt + TILE_N) * elem / 45e9;
-            if (eff > 1) t += 2.0 * eff * (double)p.M * (double)p.N * 4.0 / 3e12 + 3e-6;   // partial tiles move at about 3 TB/s
+            if (eff > 1) t += 2.0 * eff * (double)pl.tail_tiles * pl.mt * TILE_N * 4.0 / 3e12 + 3e-6;
             if (t < best * 0.97) { best = t; split = eff; }   // a later split must win by a margin
         }
+        if (const char *e = getenv("B200_QMM_DENSE_SPLIT")) { const int v = atoi(e); if (v >= 1) split = v; }
+        if (split > pl.num_kb) split = pl.num_kb;
+        if (split < 1) split = 1;
     }
-    if (const char *e = getenv("B200_QMM_DENSE_SPLIT")) { const int v = atoi(e); if (v >= 1) split = v; }
-    if (split > pl.num_kb) split = pl.num_kb;
-    if (split < 1) split = 1;
     pl.kb_per_split = (pl.num_kb + split - 1) / split;
     pl.split = (pl.num_kb + pl.kb_per_split - 1) / pl.kb_per_split;
-    pl.units = pl.tiles * pl.split;
+    pl.units = pl.full_units + pl.tail_tiles * pl.split;
     pl.P = pl.units < sms ? pl.units : sms;
-    pl.partial_bytes = pl.split > 1 ? (uint64_t)pl.split * p.M * p.N * 4 : 0;
+    pl.partial_bytes = pl.split > 1 ? (uint64_t)pl.split * pl.tail_tiles * pl.mt * TILE_N * 4 : 0;
     return pl;
 }
 
@@ -424,6 +461,7 @@ cudaError_t launch_dense_tc(const MatmulArgs &p, cudaStream_t s) {
     tp.sc_type = p.sc_type; tp.bias_type = p.bias_type; tp.out_type = p.out_type; tp.epilogue = p.epilogue;
     tp.M = (int)p.M; tp.N = (int)p.N; tp.K = (int)p.K;
     tp.m_tiles = pl.m_tiles; tp.tiles = pl.tiles; tp.num_kb = pl.num_kb; tp.kb_per_split = pl.kb_per_split; tp.units = pl.units;
+    tp.full_units = pl.full_units; tp.tail_tiles = pl.tail_tiles; tp.split = pl.split; tp.mt = pl.mt;
 
     cudaError_t e;
     switch (pl.mode) {
@@ -433,8 +471,8 @@ cudaError_t launch_dense_tc(const MatmulArgs &p, cudaStream_t s) {
     }
     if (e != cudaSuccess) return e;
     if (pl.split > 1) {
-        const size_t mn = (size_t)p.M * p.N;
-        tc_finalize_kernel<<<(unsigned)((mn + 255) / 256), 256, 0, s>>>(tp, pl.split);
+        const size_t elems = (size_t)pl.tail_tiles * pl.mt * TILE_N;
+        tc_finalize_kernel<<<(unsigned)((elems + 255) / 256), 256, 0, s>>>(tp);
         count_launch();
         e = cudaGetLastError();
     }
