@@ -1,9 +1,15 @@
 /* A plain C client of the AscendCL ABI, the way an Ascend-API program drives the weight-only
  * quantized matmul with host data (the reference's test harness does the same steps,
  * tests/harness.h:62-70): copy the activations to the device, phase 1 (workspace size + executor),
- * phase 2 (enqueue), copy the result back, and synchronise the stream once per pass.  It touches
- * the library only through its exported C symbols; the benchmark's end-to-end leg calls it so that
- * the timed region holds what a compiled client pays, not the overhead of a Python loop. */
+ * phase 2 (enqueue), copy the result back.  It touches the library only through its exported C
+ * symbols; the benchmark's end-to-end leg calls it so that the timed region holds what a compiled
+ * client pays, not the overhead of a Python loop.
+ *
+ * The pass is software-pipelined over three streams the way a serving loop does it: the copy-in of
+ * call i+1 and the copy-out of call i-1 run beside the matmul of call i (two activation buffers,
+ * two output buffers, events between the streams).  Every call still pays its own host-to-device
+ * copy, both phases of the operator and its device-to-host copy, and the pass ends with everything
+ * synchronised. */
 #include <stddef.h>
 #include <stdint.h>
 
@@ -12,28 +18,59 @@
 
 #define QMM_CLIENT_API __attribute__((visibility("default")))
 
-/* One pass over n argument sets that share the activation buffer dev_x / tensor x and the output
- * tensor out.  host_x[i] is copied to dev_x before call i, the output is copied to host_out after
- * it.  Returns 0, or the first status that was not success.  The workspace must hold
- * workspace_bytes; a call that asks for more returns 161002 from here. */
-QMM_CLIENT_API int qmmClientWeightQuantPass(int n, const void *const *host_x, size_t x_bytes, void *dev_x, const aclTensor *x,
-                                            const aclTensor *const *weight, const aclTensor *const *scale,
-                                            const aclTensor *const *offset, const aclTensor *const *bias, int64_t group,
-                                            aclTensor *out, const void *dev_out, void *host_out, size_t out_bytes,
-                                            void *workspace, uint64_t workspace_bytes, aclrtStream stream) {
+static aclrtStream g_in, g_out;          /* copy streams, created on first use */
+static aclrtEvent g_ev_in[2], g_ev_comp[2], g_ev_out[2];
+static int g_ready;
+
+static int client_setup(void) {
+    if (g_ready) return 0;
+    if (aclrtCreateStream(&g_in) != ACL_SUCCESS || aclrtCreateStream(&g_out) != ACL_SUCCESS) return 1;
+    for (int b = 0; b < 2; ++b) {
+        if (aclrtCreateEvent(&g_ev_in[b]) != ACL_SUCCESS || aclrtCreateEvent(&g_ev_comp[b]) != ACL_SUCCESS ||
+            aclrtCreateEvent(&g_ev_out[b]) != ACL_SUCCESS) return 1;
+    }
+    g_ready = 1;
+    return 0;
+}
+
+/* One pass over n argument sets.  dev_x[b] / x[b] and dev_out[b] / out[b] (b = 0, 1) are the two
+ * activation and output buffers with their tensors; call i uses buffer i % 2.  host_x[i] is copied
+ * in before call i, the output is copied to host_out after it.  Returns 0, or the first status
+ * that was not success.  The workspace must hold workspace_bytes; a call that asks for more returns
+ * 161002 from here.  Not re-entrant (one set of streams and events per process). */
+QMM_CLIENT_API int qmmClientWeightQuantPass(int n, const void *const *host_x, size_t x_bytes, void *const *dev_x,
+                                            const aclTensor *const *x, const aclTensor *const *weight,
+                                            const aclTensor *const *scale, const aclTensor *const *offset,
+                                            const aclTensor *const *bias, int64_t group, aclTensor *const *out,
+                                            const void *const *dev_out, void *host_out, size_t out_bytes, void *workspace,
+                                            uint64_t workspace_bytes, aclrtStream stream) {
+    if (client_setup()) return 361001;
     for (int i = 0; i < n; ++i) {
-        aclError e = aclrtMemcpyAsync(dev_x, x_bytes, host_x[i], x_bytes, ACL_MEMCPY_HOST_TO_DEVICE, stream);
-        if (e != ACL_SUCCESS) return (int)e;
+        const int b = i & 1;
+        aclError e;
+        /* copy-in stream: the buffer is free once call i-2 has run */
+        if (i >= 2 && (e = aclrtStreamWaitEvent(g_in, g_ev_comp[b])) != ACL_SUCCESS) return (int)e;
+        if ((e = aclrtMemcpyAsync(dev_x[b], x_bytes, host_x[i], x_bytes, ACL_MEMCPY_HOST_TO_DEVICE, g_in)) != ACL_SUCCESS) return (int)e;
+        if ((e = aclrtRecordEvent(g_ev_in[b], g_in)) != ACL_SUCCESS) return (int)e;
+        /* compute stream: needs the activations, and the output buffer drained by call i-2's copy-out */
+        if ((e = aclrtStreamWaitEvent(stream, g_ev_in[b])) != ACL_SUCCESS) return (int)e;
+        if (i >= 2 && (e = aclrtStreamWaitEvent(stream, g_ev_out[b])) != ACL_SUCCESS) return (int)e;
         uint64_t need = 0;
         aclOpExecutor *ex = NULL;
-        aclnnStatus st = aclnnWeightQuantBatchMatmulV2ExGetWorkspaceSize(x, weight[i], scale[i], offset ? offset[i] : NULL,
-                                                                         bias ? bias[i] : NULL, group, out, &need, &ex);
+        aclnnStatus st = aclnnWeightQuantBatchMatmulV2ExGetWorkspaceSize(x[b], weight[i], scale[i], offset ? offset[i] : NULL,
+                                                                         bias ? bias[i] : NULL, group, out[b], &need, &ex);
         if (st != 0) return (int)st;
         if (need > workspace_bytes) return 161002;
         st = aclnnWeightQuantBatchMatmulV2Ex(workspace, workspace_bytes, ex, stream);
         if (st != 0) return (int)st;
-        e = aclrtMemcpyAsync(host_out, out_bytes, dev_out, out_bytes, ACL_MEMCPY_DEVICE_TO_HOST, stream);
-        if (e != ACL_SUCCESS) return (int)e;
+        if ((e = aclrtRecordEvent(g_ev_comp[b], stream)) != ACL_SUCCESS) return (int)e;
+        /* copy-out stream */
+        if ((e = aclrtStreamWaitEvent(g_out, g_ev_comp[b])) != ACL_SUCCESS) return (int)e;
+        if ((e = aclrtMemcpyAsync(host_out, out_bytes, dev_out[b], out_bytes, ACL_MEMCPY_DEVICE_TO_HOST, g_out)) != ACL_SUCCESS) return (int)e;
+        if ((e = aclrtRecordEvent(g_ev_out[b], g_out)) != ACL_SUCCESS) return (int)e;
     }
-    return (int)aclrtSynchronizeStream(stream);
+    aclError e = aclrtSynchronizeStream(g_out);
+    if (e == ACL_SUCCESS) e = aclrtSynchronizeStream(stream);
+    if (e == ACL_SUCCESS) e = aclrtSynchronizeStream(g_in);
+    return (int)e;
 }

@@ -126,6 +126,9 @@ aclError aclrtDestroyEvent(aclrtEvent event) { return acl_from_cuda(cudaEventDes
 aclError aclrtRecordEvent(aclrtEvent event, aclrtStream stream) {
     return acl_from_cuda(cudaEventRecord((cudaEvent_t)event, (cudaStream_t)stream));
 }
+aclError aclrtStreamWaitEvent(aclrtStream stream, aclrtEvent event) {
+    return acl_from_cuda(cudaStreamWaitEvent((cudaStream_t)stream, (cudaEvent_t)event, 0));
+}
 aclError aclrtSynchronizeEvent(aclrtEvent event) { return acl_from_cuda(cudaEventSynchronize((cudaEvent_t)event)); }
 aclError aclrtEventElapsedTime(float *ms, aclrtEvent startEvent, aclrtEvent endEvent) {
     if (!ms) return ACLNN_ERR_PARAM_NULLPTR;

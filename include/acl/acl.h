@@ -95,6 +95,8 @@ ACL_FUNC_VISIBILITY aclError aclrtSynchronizeDevice(void);
 ACL_FUNC_VISIBILITY aclError aclrtCreateEvent(aclrtEvent *event);
 ACL_FUNC_VISIBILITY aclError aclrtDestroyEvent(aclrtEvent event);
 ACL_FUNC_VISIBILITY aclError aclrtRecordEvent(aclrtEvent event, aclrtStream stream);
+/* reference: cuda/src/runtime.cu:221. */
+ACL_FUNC_VISIBILITY aclError aclrtStreamWaitEvent(aclrtStream stream, aclrtEvent event);
 ACL_FUNC_VISIBILITY aclError aclrtSynchronizeEvent(aclrtEvent event);
 ACL_FUNC_VISIBILITY aclError aclrtEventElapsedTime(float *ms, aclrtEvent startEvent, aclrtEvent endEvent);
 

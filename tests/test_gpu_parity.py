@@ -580,6 +580,42 @@ def test_dynamic_quant_feeds_the_w8a8_matmul(pkg, oracle, workloads, dev):
     assert torch.equal(out.cpu(), want)
 
 
+def test_c_client_pipelined_pass(pkg, oracle, workloads, dev):
+    """The compiled C client the benchmark's end-to-end leg uses (csrc/acl_client.c): copy-in, both phases
+    and copy-out per call, overlapped over three streams with two activation and two output buffers.
+    After a pass of n calls the host buffer holds call n-1's result: every n from 1 to 5 must give the
+    bits of the plain call on that set."""
+    path = os.path.join(os.path.dirname(pkg.LIB_PATH), "libqmm_client.so")
+    client = ctypes.CDLL(path)
+    client.qmmClientWeightQuantPass.restype = ctypes.c_int
+    M, K, N, G = 2, 1024, 768, 128
+    sets = [workloads.w4a16(M=M, K=K, N=N, group=G, seed=7000 + i, with_offset=False, with_bias=False) for i in range(5)]
+    VP = ctypes.c_void_p
+    hx = [d["x"].pin_memory() for d in sets]
+    hout = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
+    dxs = [torch.empty((M, K), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    douts = [torch.empty((M, N), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    tdx, tdo = [pkg.AclTensor(t) for t in dxs], [pkg.AclTensor(t) for t in douts]
+    w = [d["w"].to(dev) for d in sets]
+    sc = [d["scale"].to(dev) for d in sets]
+    tw = [pkg.AclTensor(t, pkg.ACL_INT4, (K, N)) for t in w]
+    ts = [pkg.AclTensor(t) for t in sc]
+    ws = torch.empty(64 << 20, dtype=torch.uint8, device=dev)
+    stream = VP(torch.cuda.current_stream(dev).cuda_stream)
+    want = [pkg.weight_quant_matmul(d["x"].to(dev), w[i], sc[i], int4=True, group=G).cpu() for i, d in enumerate(sets)]
+    torch.cuda.synchronize()
+    for n in range(1, 6):
+        hout.zero_()
+        st = client.qmmClientWeightQuantPass(
+            ctypes.c_int(n), (VP * n)(*[VP(h.data_ptr()) for h in hx[:n]]), ctypes.c_size_t(M * K * 2),
+            (VP * 2)(*[VP(t.data_ptr()) for t in dxs]), (VP * 2)(*[VP(t.h) for t in tdx]),
+            (VP * n)(*[VP(t.h) for t in tw[:n]]), (VP * n)(*[VP(t.h) for t in ts[:n]]), None, None, ctypes.c_int64(G),
+            (VP * 2)(*[VP(t.h) for t in tdo]), (VP * 2)(*[VP(t.data_ptr()) for t in douts]), VP(hout.data_ptr()),
+            ctypes.c_size_t(M * N * 2), VP(ws.data_ptr()), ctypes.c_uint64(ws.numel()), stream)
+        assert st == 0
+        assert torch.equal(hout, want[n - 1]), n
+
+
 def test_zz_no_bounded_wait_gave_up(pkg, dev):
     """Every spin inside the tensor-core kernels is bounded and records a code when it gives up;
     after the whole suite the device status word must still be 0."""
