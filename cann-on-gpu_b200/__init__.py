@@ -213,6 +213,15 @@ def dynamic_quant(x, name="aclnnDynamicQuant", **kw):
     return q, scale
 
 
+def dynamic_mx_quant(x, block, name="aclnnDynamicMxQuant", **kw):
+    """x (numel a multiple of block) f32/f16/bf16 -> (int8 of x's shape, fp32 power-of-two scale per block)."""
+    import torch
+    q = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+    scale = torch.empty((x.numel() // block,), dtype=torch.float32, device=x.device)
+    call(name, AclTensor(x), ctypes.c_int64(block), AclTensor(q), AclTensor(scale), **kw)
+    return q, scale
+
+
 def cast(src, src_kind, dst_kind, n, **kw):
     """aclnnCast over flat buffers; returns the destination buffer (uint8 for fp8/fp4 kinds)."""
     import torch

@@ -1,4 +1,6 @@
-// Per-token dynamic int8 quantiser, the step in front of the W8A8 matmul: for every row of x
+// Dynamic int8 quantisers of activations.
+//
+// Per-token, the step in front of the W8A8 matmul: for every row of x
 //   scale = max|x| / 127 (1 for an all-zero row),  q = clamp(rint(x * (1 / scale)), -128, 127)
 // written as int8 plus the fp32 scale per row (which the matmul takes as pertokenScale).
 // Same arithmetic, in the same order, as the reference (cuda/src/ops/quant.cu:37-49): the quotient
@@ -87,7 +89,73 @@ __global__ void __launch_bounds__(DQ_THREADS) dynquant_generic_kernel(const void
     for (int64_t d = threadIdx.x; d < D; d += DQ_THREADS) q[base + d] = quant_i8(load_as_float(x, x_type, base + d) * inv);
 }
 
+// ---- block-wise power-of-two scales ("MX-style" int8): per block of `blk` consecutive elements
+//   scale = 2^ceil(log2(max|x| / 127)) (1 for an all-zero block),  q = clamp(rint(x * (1 / scale)))
+// with the reference's expression exp2f(ceilf(log2f(m / 127.f))) evaluated by the same device functions
+// (cuda/src/ops/quant.cu:380-389), so scales and codes are bit-identical to it.
+__device__ __forceinline__ float mx_block_scale(float m) { return m > 0.f ? exp2f(ceilf(log2f(m / 127.f))) : 1.f; }
+
+// 16-bit inputs, blk = 8 * LPB with LPB (lanes per block) in {4, 8, 16, 32}: a lane holds 8 elements
+// (one 16-byte load), a block's maximum is LPB-lane butterfly, 8-byte stores of the codes.
+template <bool BF16, int LPB>
+__global__ void __launch_bounds__(256) mxquant_vec_kernel(const uint16_t *x, int8_t *q, float *scale_out, int64_t n) {
+    const int64_t i0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    const bool in = i0 < n;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (in) v = __ldg(reinterpret_cast<const uint4 *>(x + i0));
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    float f[8], amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        if constexpr (BF16) { f[2 * i] = __uint_as_float(w[i] << 16); f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u); }
+        else { f[2 * i] = __half2float(__ushort_as_half((unsigned short)(w[i] & 0xFFFFu))); f[2 * i + 1] = __half2float(__ushort_as_half((unsigned short)(w[i] >> 16))); }
+        amax = fmaxf(amax, fmaxf(fabsf(f[2 * i]), fabsf(f[2 * i + 1])));
+    }
+#pragma unroll
+    for (int o = LPB / 2; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float sc = mx_block_scale(amax);
+    if (in && (threadIdx.x & (LPB - 1)) == 0) scale_out[i0 / (8 * LPB)] = sc;
+    const float inv = 1.f / sc;
+    uint32_t o[2] = {0, 0};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i >> 2] |= (uint32_t)(uint8_t)quant_i8(f[i] * inv) << (8 * (i & 3));
+    if (in) *reinterpret_cast<uint2 *>(q + i0) = make_uint2(o[0], o[1]);
+}
+
+// Any type, any block size: one CTA per block.
+__global__ void __launch_bounds__(DQ_THREADS) mxquant_generic_kernel(const void *x, int x_type, int8_t *q, float *scale_out, int64_t blk) {
+    __shared__ float sh[DQ_THREADS / 32];
+    const int64_t base = (int64_t)blockIdx.x * blk;
+    float amax = 0.f;
+    for (int64_t d = threadIdx.x; d < blk; d += DQ_THREADS) amax = fmaxf(amax, fabsf(load_as_float(x, x_type, base + d)));
+    const float sc = mx_block_scale(block_max(amax, sh));
+    if (threadIdx.x == 0) scale_out[blockIdx.x] = sc;
+    const float inv = 1.f / sc;
+    for (int64_t d = threadIdx.x; d < blk; d += DQ_THREADS) q[base + d] = quant_i8(load_as_float(x, x_type, base + d) * inv);
+}
+
 }  // namespace
+
+cudaError_t launch_dynamic_mx_quant(const void *x, int x_type, int8_t *q, float *scale_out, int64_t nblocks, int64_t blk, cudaStream_t s) {
+    if (nblocks <= 0 || blk <= 0) return cudaSuccess;
+    const int64_t n = nblocks * blk;
+    const bool vec = (x_type == ET_BF16 || x_type == ET_F16) && (blk == 32 || blk == 64 || blk == 128 || blk == 256) &&
+                     (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(q) & 7) == 0;
+    if (vec) {
+        const unsigned g = (unsigned)((n / 8 + 255) / 256);
+        const uint16_t *x16 = static_cast<const uint16_t *>(x);
+        const bool bf = x_type == ET_BF16;
+#define MXQ(LPB) do { if (bf) mxquant_vec_kernel<true, LPB><<<g, 256, 0, s>>>(x16, q, scale_out, n); \
+                      else mxquant_vec_kernel<false, LPB><<<g, 256, 0, s>>>(x16, q, scale_out, n); } while (0)
+        switch (blk) { case 32: MXQ(4); break; case 64: MXQ(8); break; case 128: MXQ(16); break; default: MXQ(32); break; }
+#undef MXQ
+    } else {
+        if (nblocks > 0x7fffffffLL) return cudaErrorInvalidValue;
+        mxquant_generic_kernel<<<(unsigned)nblocks, DQ_THREADS, 0, s>>>(x, x_type, q, scale_out, blk);
+    }
+    count_launch();
+    return cudaGetLastError();
+}
 
 cudaError_t launch_dynamic_quant(const void *x, int x_type, int8_t *q, float *scale_out, int64_t rows, int64_t D, cudaStream_t s) {
     if (rows <= 0 || D <= 0) return cudaSuccess;

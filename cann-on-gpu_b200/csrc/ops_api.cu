@@ -273,6 +273,10 @@ aclnnStatus run_simple(aclOpExecutor *e, aclrtStream stream) {
             err = launch_dynamic_quant(data_of(e->a), elem_type(e->a->dtype), (int8_t *)const_cast<void *>(data_of(e->out)),
                                        (float *)const_cast<void *>(data_of(e->out2)), e->m, e->k, s);
             break;
+        case PLAN_MXQUANT:
+            err = launch_dynamic_mx_quant(data_of(e->a), elem_type(e->a->dtype), (int8_t *)const_cast<void *>(data_of(e->out)),
+                                          (float *)const_cast<void *>(data_of(e->out2)), e->m, e->k, s);
+            break;
         case PLAN_QPARAM:
             err = launch_qparam((const float *)data_of(e->a), e->b ? (const float *)data_of(e->b) : nullptr,
                                 (int64_t *)const_cast<void *>(data_of(e->out)), e->n, s);
@@ -494,6 +498,28 @@ DYNQUANT_ALIAS(aclnnDynamicQuant)
 DYNQUANT_ALIAS(aclnnDynamicQuantV2)
 DYNQUANT_ALIAS(aclnnDynamicQuantV3)
 DYNQUANT_ALIAS(aclnnDynamicQuantV4)
+
+// Block-wise int8 quantiser with power-of-two scales (cuda/src/ops/quant.cu:380-389,496-514).
+static aclnnStatus mxquant_plan(const aclTensor *x, int64_t blockSize, aclTensor *out, aclTensor *scaleOut, uint64_t *ws,
+                                aclOpExecutor **ex) {
+    if (!x || !out || !scaleOut || !ws || !ex) return ACLNN_ERR_PARAM_NULLPTR;
+    if (blockSize <= 0) return ACLNN_ERR_PARAM_INVALID;
+    if (x->numel() > 0 && (!x->data || !out->data || !scaleOut->data)) return ACLNN_ERR_PARAM_NULLPTR;
+    if (out->dtype != ACL_INT8 || scaleOut->dtype != ACL_FLOAT || x->viewDims != out->viewDims) return ACLNN_ERR_PARAM_INVALID;
+    if (x->dtype != ACL_FLOAT && x->dtype != ACL_FLOAT16 && x->dtype != ACL_BF16) return ACLNN_ERR_PARAM_INVALID;
+    if (x->numel() % blockSize != 0 || scaleOut->numel() != x->numel() / blockSize) return ACLNN_ERR_PARAM_INVALID;
+    if (!dense(x) || !dense(out) || !dense(scaleOut)) return ACLNN_ERR_PARAM_INVALID;
+    auto *e = new aclOpExecutor();
+    e->op = PLAN_MXQUANT; e->a = x; e->out = out; e->out2 = scaleOut; e->m = x->numel() / blockSize; e->k = blockSize;
+    *ws = 0; *ex = e;
+    return ACLNN_SUCCESS;
+}
+#define MXQUANT_ALIAS(NAME)                                                                                          \
+    aclnnStatus NAME##GetWorkspaceSize(const aclTensor *x, int64_t blockSize, aclTensor *out, aclTensor *scaleOut,   \
+                                       uint64_t *ws, aclOpExecutor **ex) { return mxquant_plan(x, blockSize, out, scaleOut, ws, ex); } \
+    RUN_SIMPLE(NAME)
+MXQUANT_ALIAS(aclnnDynamicMxQuant)
+MXQUANT_ALIAS(aclnnDynamicMxQuantV2)
 
 // fp32 scale (+ optional fp32 offset) -> int64 quant parameter (cuda/src/ops/quant.cu:657-673).
 static aclnnStatus qparam_plan(const aclTensor *scale, const aclTensor *offset, aclTensor *out, uint64_t *ws, aclOpExecutor **ex) {

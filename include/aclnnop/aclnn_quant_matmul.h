@@ -165,6 +165,17 @@ B200_ACLNN_DYNQUANT(aclnnDynamicQuantV2)
 B200_ACLNN_DYNQUANT(aclnnDynamicQuantV3)
 B200_ACLNN_DYNQUANT(aclnnDynamicQuantV4)
 
+/* Block-wise dynamic int8 quantiser with power-of-two scales: per block of blockSize consecutive elements
+ * scaleOut = 2^ceil(log2(max|x| / 127)) (1 for a zero block; ACL_FLOAT, one per block),
+ * out = clamp(rint(x * (1 / scaleOut)), -128, 127) as ACL_INT8.
+ * Replaces aclnn_ops.h:1481-1484 (cuda/src/ops/quant.cu:380-389,496-514). */
+#define B200_ACLNN_MXQUANT(NAME) \
+    ACL_FUNC_VISIBILITY aclnnStatus NAME##GetWorkspaceSize(const aclTensor *x, int64_t blockSize, aclTensor *out, \
+        aclTensor *scaleOut, uint64_t *workspaceSize, aclOpExecutor **executor); \
+    B200_ACLNN_RUN(NAME)
+B200_ACLNN_MXQUANT(aclnnDynamicMxQuant)
+B200_ACLNN_MXQUANT(aclnnDynamicMxQuantV2)
+
 /* fp32 scale (+ optional fp32 offset) -> ACL_INT64 quant parameter: low 32 bits = bits of the scale,
  * high 32 bits = offset rounded to the nearest int32.  Replaces aclnn_ops.h:1730-1735
  * (cuda/src/ops/quant.cu:572-576,657-673). */

@@ -301,6 +301,21 @@ def dynamic_quant(x):
     return np.clip(q, -128, 127).astype(np.int8), scale
 
 
+def dynamic_mx_quant(x, block):
+    """Block-wise int8 quantiser with power-of-two scales, restating cuda/src/ops/quant.cu:380-389 in fp32:
+    per block of `block` consecutive elements scale = 2^ceil(log2(max|x| / 127)) (1 for a zero block),
+    q = clamp(rint(x * (1 / scale)), -128, 127).  Returns (int8 of x's shape, float32 [numel / block])."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    b = x.reshape(-1, block)
+    amax = np.abs(b).max(axis=1)
+    with np.errstate(divide="ignore"):
+        e = np.ceil(np.log2((amax / np.float32(127)).astype(np.float32)).astype(np.float32))
+    scale = np.where(amax > 0, np.exp2(e).astype(np.float32), np.float32(1)).astype(np.float32)
+    inv = (np.float32(1) / scale).astype(np.float32)
+    q = np.clip(np.rint((b * inv[:, None]).astype(np.float32)), -128, 127).astype(np.int8)
+    return q.reshape(x.shape), scale
+
+
 # ------------------------------------------------------------------ PyTorch-CPU form (all host cores)
 def wqbmm_torch(x, w, is_int4, scale, offset, bias, M, K, N, group=0):
     """The same weight-only matmul written with PyTorch CPU ops: dequantise in fp32, then torch.matmul

@@ -564,6 +564,28 @@ def test_dynamic_quant_bit_exact(pkg, oracle, dev, shape, dtype):
         assert np.array_equal(q.cpu().numpy(), want_q), name
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("case", [((64, 4096), 32), ((7, 512), 64), ((3, 1024), 128), ((2, 2048), 256), ((5, 96), 48), ((4, 1000), 1000)])
+def test_dynamic_mx_quant_bit_exact(pkg, oracle, dev, case, dtype):
+    """Block-wise int8 quantiser with power-of-two scales (cuda/src/ops/quant.cu:380-389,496-514): codes and
+    scales identical to the oracle for the vectorised block sizes, odd block sizes, zero blocks and blocks
+    whose maximum is an exact power of two times 127; both names."""
+    shape, block = case
+    g = torch.Generator().manual_seed(6200 + block)
+    x = (torch.randn(shape, generator=g) * 2).to(dtype)
+    flat = x.view(-1, block)
+    flat[0, :] = 0
+    flat[1, :] = 0.25
+    flat[1, 0] = 127.0 * 0.5      # max / 127 = 2^-1 exactly
+    want_q, want_s = oracle.dynamic_mx_quant(x.float().numpy(), block)
+    for name in ("aclnnDynamicMxQuant", "aclnnDynamicMxQuantV2"):
+        q, sc = pkg.dynamic_mx_quant(x.to(dev), block, name=name)
+        torch.cuda.synchronize()
+        assert np.array_equal(sc.cpu().numpy(), want_s), name
+        assert np.array_equal(q.cpu().numpy(), want_q), name
+    assert want_s[0] == 1 and want_s[1] == 0.5
+
+
 def test_dynamic_quant_feeds_the_w8a8_matmul(pkg, oracle, workloads, dev):
     """The chain a W8A8 layer runs: quantise the activations per token, then aclnnQuantMatmulV4 with
     the scales as pertokenScale.  Accumulators and output bit-exact against the oracle's chain."""
