@@ -64,6 +64,56 @@ __global__ void expand_wq_kernel(const uint8_t *w, const void *scale, const void
     dst[1] = o1;
 }
 
+// The same expansion written for bandwidth: a lane owns 8 consecutive columns (one 32-bit word of
+// int4, or 8 bytes of int8) and walks 4 rows of a 32-row chunk, so the 8 scales and 8 offsets of the
+// chunk's group are loaded once (two 16-byte loads) and every output is one 16-byte store; integers
+// become floats through the 2^23 mantissa trick instead of conversions.  Same fp32 expression per
+// element as above, so the same bits.  Needs 16-bit scales of the output type, N % 8 == 0 and a
+// group size that is a multiple of 32 (or per-channel scales).
+template <bool Q4, bool BF16>
+__global__ void __launch_bounds__(256) expand_wq_fast_kernel(const uint8_t *w, const uint16_t *scale, const uint16_t *offset,
+                                                             uint16_t *out, int K, int N, int group) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int n0 = (blockIdx.x * 32 + lane) * 8;
+    const int k0 = blockIdx.y * 32;
+    if (n0 >= N) return;
+    const int g = k0 / group;
+    const uint4 sraw = __ldg(reinterpret_cast<const uint4 *>(scale + (size_t)g * N + n0));
+    uint4 oraw = make_uint4(0, 0, 0, 0);
+    if (offset) oraw = __ldg(reinterpret_cast<const uint4 *>(offset + (size_t)g * N + n0));
+    const uint32_t sw[4] = {sraw.x, sraw.y, sraw.z, sraw.w}, ow[4] = {oraw.x, oraw.y, oraw.z, oraw.w};
+    float sc[8], of[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const uint32_t sb = (i & 1) ? sw[i >> 1] >> 16 : sw[i >> 1] & 0xFFFFu, ob = (i & 1) ? ow[i >> 1] >> 16 : ow[i >> 1] & 0xFFFFu;
+        if constexpr (BF16) { sc[i] = __uint_as_float(sb << 16); of[i] = __uint_as_float(ob << 16); }
+        else { sc[i] = __half2float(__ushort_as_half((unsigned short)sb)); of[i] = __half2float(__ushort_as_half((unsigned short)ob)); }
+    }
+#pragma unroll
+    for (int rr = 0; rr < 4; ++rr) {
+        const int k = k0 + wid + 8 * rr;
+        if (k >= K) break;
+        float v[8];
+        if constexpr (Q4) {
+            const uint32_t word = __ldg(reinterpret_cast<const uint32_t *>(w + ((size_t)k * N + n0) / 2));
+#pragma unroll
+            for (int i = 0; i < 8; ++i)   // two's-complement nibble -> q + 8 in the mantissa of 2^23
+                v[i] = __uint_as_float(0x4B000000u | (((word >> (4 * i)) & 0xFu) ^ 8u)) - 8388616.f;
+        } else {
+            const uint2 raw = __ldg(reinterpret_cast<const uint2 *>(w + (size_t)k * N + n0));
+            const uint32_t words[2] = {raw.x, raw.y};
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                v[i] = __uint_as_float(0x4B000000u | (((words[i >> 2] >> (8 * (i & 3))) & 0xFFu) ^ 0x80u)) - 8388736.f;
+        }
+        uint4 o;
+        uint32_t *op = reinterpret_cast<uint32_t *>(&o);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) op[i] = pack2<BF16>((v[2 * i] - of[2 * i]) * sc[2 * i], (v[2 * i + 1] - of[2 * i + 1]) * sc[2 * i + 1]);
+        *reinterpret_cast<uint4 *>(out + (size_t)k * N + n0) = o;
+    }
+}
+
 // MX operand [rows][cols] -> bf16.  along_cols: one scale per (row, col / 32) (operand A, [M][K]);
 // otherwise one per (row / 32, col) (operand B, [K][N]).  One thread expands 16 consecutive columns.
 __global__ void expand_mx_kernel(const uint8_t *src, int elem_type, const uint8_t *scales, int along_cols, uint16_t *out, int rows,
@@ -165,7 +215,18 @@ cudaError_t launch_expand(const MatmulArgs &p, cudaStream_t s) {
         const unsigned blocks = (unsigned)((tb + 255) / 256);
         const bool q4 = p.b_type == ET_I4, bf = p.a_type == ET_BF16;
         const uint8_t *w = (const uint8_t *)p.b;
-        if (q4 && bf) expand_wq_kernel<true, true><<<blocks, 256, 0, s>>>(w, p.scale, p.offset, p.sc_type, b16, K, N, (int)p.group);
+        const bool fast = p.sc_type == p.a_type && N % 8 == 0 && (p.group >= p.K || p.group % 32 == 0) &&
+                          (reinterpret_cast<uintptr_t>(p.scale) & 15) == 0 && (reinterpret_cast<uintptr_t>(p.offset) & 15) == 0 &&
+                          (reinterpret_cast<uintptr_t>(p.b) & 7) == 0 && (K + 31) / 32 <= 65535;
+        if (fast) {
+            const dim3 grid((unsigned)((N + 255) / 256), (unsigned)((K + 31) / 32));
+            const uint16_t *sc16 = (const uint16_t *)p.scale, *of16 = (const uint16_t *)p.offset;
+            const int grp = p.group >= p.K ? (K + 31) / 32 * 32 : (int)p.group;   // per-channel: one group over all rows
+            if (q4 && bf) expand_wq_fast_kernel<true, true><<<grid, 256, 0, s>>>(w, sc16, of16, b16, K, N, grp);
+            else if (q4) expand_wq_fast_kernel<true, false><<<grid, 256, 0, s>>>(w, sc16, of16, b16, K, N, grp);
+            else if (bf) expand_wq_fast_kernel<false, true><<<grid, 256, 0, s>>>(w, sc16, of16, b16, K, N, grp);
+            else expand_wq_fast_kernel<false, false><<<grid, 256, 0, s>>>(w, sc16, of16, b16, K, N, grp);
+        } else if (q4 && bf) expand_wq_kernel<true, true><<<blocks, 256, 0, s>>>(w, p.scale, p.offset, p.sc_type, b16, K, N, (int)p.group);
         else if (q4) expand_wq_kernel<true, false><<<blocks, 256, 0, s>>>(w, p.scale, p.offset, p.sc_type, b16, K, N, (int)p.group);
         else if (bf) expand_wq_kernel<false, true><<<blocks, 256, 0, s>>>(w, p.scale, p.offset, p.sc_type, b16, K, N, (int)p.group);
         else expand_wq_kernel<false, false><<<blocks, 256, 0, s>>>(w, p.scale, p.offset, p.sc_type, b16, K, N, (int)p.group);
