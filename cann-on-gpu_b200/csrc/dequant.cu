@@ -155,6 +155,73 @@ __global__ void expand_mx_kernel(const uint8_t *src, int elem_type, const uint8_
     dst[1] = o1;
 }
 
+// The same written for bandwidth, like expand_wq_fast_kernel: a lane owns 8 consecutive columns and
+// walks 4 rows of a 32-row chunk; operand B loads its 8 scale bytes once per chunk, operand A one
+// scale byte per row; one 16-byte store per row.  ELEM: 0 = e2m1 (two per byte), 1 = e4m3, 2 = e5m2.
+template <int ELEM, bool ALONG_COLS>
+__global__ void __launch_bounds__(256) expand_mx_fast_kernel(const uint8_t *src, const uint8_t *scales, uint16_t *out, int rows,
+                                                             int cols) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int c0 = (blockIdx.x * 32 + lane) * 8;
+    const int r0 = blockIdx.y * 32;
+    if (c0 >= cols) return;
+    float sc[8];
+    if constexpr (!ALONG_COLS) {
+        const uint2 sraw = __ldg(reinterpret_cast<const uint2 *>(scales + (size_t)(r0 / 32) * cols + c0));
+        const uint32_t sw[2] = {sraw.x, sraw.y};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sc[i] = e8m0_to_float((sw[i >> 2] >> (8 * (i & 3))) & 0xFFu);
+    }
+#pragma unroll
+    for (int rr = 0; rr < 4; ++rr) {
+        const int r = r0 + wid + 8 * rr;
+        if (r >= rows) break;
+        float v[8];
+        if constexpr (ELEM == 0) {
+            const uint32_t word = __ldg(reinterpret_cast<const uint32_t *>(src + ((size_t)r * cols + c0) / 2));
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = e2m1_to_float((word >> (4 * i)) & 0xFu);
+        } else {
+            const uint2 raw = __ldg(reinterpret_cast<const uint2 *>(src + (size_t)r * cols + c0));
+            const uint32_t words[2] = {raw.x, raw.y};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {   // two fp8 at a time through the hardware conversion
+                const __nv_fp8x2_storage_t pair = (__nv_fp8x2_storage_t)((words[i >> 1] >> (16 * (i & 1))) & 0xFFFFu);
+                const __half2 h2 = __half2(__nv_cvt_fp8x2_to_halfraw2(pair, ELEM == 1 ? __NV_E4M3 : __NV_E5M2));
+                const float2 f2 = __half22float2(h2);
+                v[2 * i] = f2.x;
+                v[2 * i + 1] = f2.y;
+            }
+        }
+        if constexpr (ALONG_COLS) {
+            const float s1 = e8m0_to_float(__ldg(scales + (size_t)r * (cols / 32) + c0 / 32));
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] *= s1;
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] *= sc[i];
+        }
+        uint4 o;
+        uint32_t *op = reinterpret_cast<uint32_t *>(&o);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) op[i] = pack2<true>(v[2 * i], v[2 * i + 1]);
+        *reinterpret_cast<uint4 *>(out + (size_t)r * cols + c0) = o;
+    }
+}
+
+template <bool ALONG_COLS>
+bool launch_expand_mx_fast(const uint8_t *src, int elem_type, const uint8_t *scales, uint16_t *out, int rows, int cols, cudaStream_t s) {
+    if (cols % 32 != 0 || (reinterpret_cast<uintptr_t>(src) & 7) || (reinterpret_cast<uintptr_t>(scales) & 7) || (rows + 31) / 32 > 65535)
+        return false;
+    if (!ALONG_COLS && rows % 32 != 0) return false;
+    const dim3 grid((unsigned)((cols + 255) / 256), (unsigned)((rows + 31) / 32));
+    if (elem_type == ET_E2M1) expand_mx_fast_kernel<0, ALONG_COLS><<<grid, 256, 0, s>>>(src, scales, out, rows, cols);
+    else if (elem_type == ET_E4M3) expand_mx_fast_kernel<1, ALONG_COLS><<<grid, 256, 0, s>>>(src, scales, out, rows, cols);
+    else if (elem_type == ET_E5M2) expand_mx_fast_kernel<2, ALONG_COLS><<<grid, 256, 0, s>>>(src, scales, out, rows, cols);
+    else return false;
+    return true;
+}
+
 inline uint64_t up256(uint64_t x) { return (x + 255) / 256 * 256; }
 bool is_mx(const MatmulArgs &p) { return p.a_scale && p.b_scale; }
 
@@ -206,9 +273,11 @@ cudaError_t launch_expand(const MatmulArgs &p, cudaStream_t s) {
     const int K = (int)p.K, N = (int)p.N, M = (int)p.M;
     if (is_mx(p)) {
         const int64_t ta = (int64_t)M * (K / 16), tb = (int64_t)K * (N / 16);
-        expand_mx_kernel<<<(unsigned)((ta + 255) / 256), 256, 0, s>>>((const uint8_t *)p.a, p.a_type, p.a_scale, 1, a16, M, K);
+        if (!launch_expand_mx_fast<true>((const uint8_t *)p.a, p.a_type, (const uint8_t *)p.a_scale, a16, M, K, s))
+            expand_mx_kernel<<<(unsigned)((ta + 255) / 256), 256, 0, s>>>((const uint8_t *)p.a, p.a_type, p.a_scale, 1, a16, M, K);
         count_launch();
-        expand_mx_kernel<<<(unsigned)((tb + 255) / 256), 256, 0, s>>>((const uint8_t *)p.b, p.b_type, p.b_scale, 0, b16, K, N);
+        if (!launch_expand_mx_fast<false>((const uint8_t *)p.b, p.b_type, (const uint8_t *)p.b_scale, b16, K, N, s))
+            expand_mx_kernel<<<(unsigned)((tb + 255) / 256), 256, 0, s>>>((const uint8_t *)p.b, p.b_type, p.b_scale, 0, b16, K, N);
         count_launch();
     } else {
         const int64_t tb = (int64_t)K * (N / 16);
