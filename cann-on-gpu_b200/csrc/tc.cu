@@ -58,7 +58,7 @@ struct TcParams {
     int split;                // ... are cut into `split` K slices each, so the last round is short
     int kb_per_split;         // K blocks per slice of a tail tile
     int units;                // full_units + tail_tiles * split
-    int mt;                   // rows per tile (for the finalize kernel)
+    int mt, tn;               // rows and columns per tile (for the finalize kernel)
 };
 
 template <int MT, int STAGES>
@@ -272,13 +272,278 @@ tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUte
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Row-tile variant for many rows (M > 128): the ACTIVATION tile (128 rows m) sits on the MMA's M side
+// and the WEIGHT tile (256 columns n, still MN-major straight from the caller's [K,N]) on its N side,
+// so TMEM lane = output row and a thread holds consecutive output columns: the epilogue packs them
+// and writes 16 bytes per store instead of one 2-byte store per element.  With short K (W8A8,
+// K = 4096) the column-per-lane epilogue above takes longer than the unit's MMAs and sets the pace
+// (measured: 17-21 us per 256 x 128 tile against 14 us of MMAs); this one does not.
+// Same warp roles, unit list, K-split tail and bounded waits as tc_kernel.
+constexpr int RT_M = 128, RT_N = 256;
+
+template <int STAGES>
+struct RSmem {
+    static constexpr int X_BYTES = RT_M * 128;
+    static constexpr int W_BYTES = RT_N * 128;
+    static constexpr int STAGE_BYTES = X_BYTES + W_BYTES;
+    static constexpr int BAR_OFF = STAGES * STAGE_BYTES;
+    static constexpr int NUM_BARS = 2 * STAGES + 4;
+    static constexpr int MISC_OFF = BAR_OFF + NUM_BARS * 8;
+    static constexpr int COL_OFF = MISC_OFF + 16;           // scale[256] then bias[256] of the current tile
+    static constexpr int TOTAL = COL_OFF + 2 * RT_N * 4 + 1024;
+};
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
+enum ROut : int { RO_BF16 = 0, RO_F16, RO_F32, RO_RAW };
+
+// One row's 128 accumulator columns [cb, cb + 128) of a tile -> out[m][n0 + cb ...], 8 columns per
+// step.  sc_s / bi_s hold the tile's per-column scale and bias (float bits in bi_s for the 16-bit modes).
+template <bool INT8, int OUT>
+__device__ __forceinline__ void rt_store_row(uint32_t taddr, const TcParams &p, const float *sc_s, const int32_t *bi_s, int cb, int n0,
+                                             int m, bool m_ok, float pt) {
+    constexpr int ESZ = (OUT == RO_BF16 || OUT == RO_F16) ? 2 : 4;
+    uint8_t *orow = (uint8_t *)p.out + ((size_t)m * p.N + n0 + cb) * ESZ;
+#pragma unroll 1
+    for (int c0 = 0; c0 < 128; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld32(taddr + c0, v);
+        if (!m_ok) continue;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            const int c = c0 + 8 * g;
+            if (n0 + cb + c >= p.N) break;   // N is a multiple of 8 on this path
+            const float4 s0 = *reinterpret_cast<const float4 *>(sc_s + cb + c), s1 = *reinterpret_cast<const float4 *>(sc_s + cb + c + 4);
+            const int4 b0 = *reinterpret_cast<const int4 *>(bi_s + cb + c), b1 = *reinterpret_cast<const int4 *>(bi_s + cb + c + 4);
+            const float sc[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+            const int bi[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+            if constexpr (OUT == RO_RAW) {
+                uint4 *o = reinterpret_cast<uint4 *>(orow + (size_t)c * 4);
+                o[0] = make_uint4(v[8 * g], v[8 * g + 1], v[8 * g + 2], v[8 * g + 3]);
+                o[1] = make_uint4(v[8 * g + 4], v[8 * g + 5], v[8 * g + 6], v[8 * g + 7]);
+            } else {
+                float f[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    if constexpr (INT8) f[j] = ((float)((int)v[8 * g + j] + bi[j]) * sc[j]) * pt;   // pt is 1 without per-token scales
+                    else f[j] = __uint_as_float(v[8 * g + j]) + __int_as_float(bi[j]);
+                }
+                if constexpr (OUT == RO_F32) {
+                    float4 *o = reinterpret_cast<float4 *>(orow + (size_t)c * 4);
+                    o[0] = make_float4(f[0], f[1], f[2], f[3]);
+                    o[1] = make_float4(f[4], f[5], f[6], f[7]);
+                } else {
+                    uint4 o;
+                    if constexpr (OUT == RO_BF16) {
+                        __nv_bfloat162 h0 = __floats2bfloat162_rn(f[0], f[1]), h1 = __floats2bfloat162_rn(f[2], f[3]),
+                                       h2 = __floats2bfloat162_rn(f[4], f[5]), h3 = __floats2bfloat162_rn(f[6], f[7]);
+                        o = make_uint4(*reinterpret_cast<uint32_t *>(&h0), *reinterpret_cast<uint32_t *>(&h1),
+                                       *reinterpret_cast<uint32_t *>(&h2), *reinterpret_cast<uint32_t *>(&h3));
+                    } else {
+                        __half2 h0 = __floats2half2_rn(f[0], f[1]), h1 = __floats2half2_rn(f[2], f[3]), h2 = __floats2half2_rn(f[4], f[5]),
+                                h3 = __floats2half2_rn(f[6], f[7]);
+                        o = make_uint4(*reinterpret_cast<uint32_t *>(&h0), *reinterpret_cast<uint32_t *>(&h1),
+                                       *reinterpret_cast<uint32_t *>(&h2), *reinterpret_cast<uint32_t *>(&h3));
+                    }
+                    *reinterpret_cast<uint4 *>(orow + (size_t)c * 2) = o;
+                }
+            }
+        }
+    }
+}
+
+template <int MODE, int STAGES>
+__global__ void __launch_bounds__(320, 1)
+tc_rowtile_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w, const TcParams p) {
+    using T = DTraits<MODE>;
+    using L = RSmem<STAGES>;
+    constexpr bool INT8 = (MODE == D_I8);
+    constexpr int TMEM_COLS = 2 * RT_N;
+    constexpr int KSTEPS = T::BK / T::UMMA_K;
+    constexpr int W_BOXES = INT8 ? 2 : 4;              // 128-byte-wide column blocks of the weight tile
+    constexpr int W_BOX_COLS = INT8 ? 128 : 64;
+    // A = activations, K-major; B = weights, MN-major; M = 128, N = 256
+    constexpr uint32_t IDESC = (INT8 ? instr_desc(2, 1, RT_M, RT_N) : instr_desc(1, MODE == D_BF16 ? 1 : 0, RT_M, RT_N)) ^ (1u << 15) ^ (1u << 16);
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *gen_base = smem_raw + (base - smem_u32(smem_raw));
+    auto x_tile = [&](int s) { return base + s * L::STAGE_BYTES; };
+    auto w_tile = [&](int s) { return base + s * L::STAGE_BYTES + L::X_BYTES; };
+    auto bar_full = [&](int s) { return base + L::BAR_OFF + 8 * s; };
+    auto bar_empty = [&](int s) { return base + L::BAR_OFF + 8 * (STAGES + s); };
+    auto bar_acc_full = [&](int a) { return base + L::BAR_OFF + 8 * (2 * STAGES + a); };
+    auto bar_acc_empty = [&](int a) { return base + L::BAR_OFF + 8 * (2 * STAGES + 2 + a); };
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(gen_base + L::MISC_OFF);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(gen_base + L::MISC_OFF + 4);
+    float *sc_s = reinterpret_cast<float *>(gen_base + L::COL_OFF);
+    int32_t *bi_s = reinterpret_cast<int32_t *>(sc_s + RT_N);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(bar_acc_full(a), 1); mbar_init(bar_acc_empty(a), 8); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_proxy_async();
+    }
+    if (warp == 1) tmem_alloc(smem_u32((const void *)tmem_slot), TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    // Same unit list as tc_kernel; a tile is 128 rows x 256 columns here.
+    auto unit_geom = [&](int u, int &n0, int &m0, int &kb0, int &nkb, int &z) {
+        int tile;
+        if (u < p.full_units) {
+            tile = u; z = -1; kb0 = 0; nkb = p.num_kb;
+        } else {
+            const int v = u - p.full_units;
+            tile = p.full_units + v % p.tail_tiles;
+            z = v / p.tail_tiles;
+            kb0 = z * p.kb_per_split;
+            nkb = min(p.num_kb, kb0 + p.kb_per_split) - kb0;
+            if (p.split == 1) z = -1;
+        }
+        n0 = (tile / p.m_tiles) * RT_N;
+        m0 = (tile % p.m_tiles) * RT_M;
+    };
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int it = 0;
+            bool ok = true;
+            for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
+                int n0, m0, kb0, nkb, z;
+                unit_geom(u, n0, m0, kb0, nkb, z);
+                for (int i = 0; i < nkb; ++i, ++it) {
+                    const int s = it % STAGES;
+                    if (it >= STAGES && !mbar_wait(bar_empty(s), ((it / STAGES) - 1) & 1, abort_flag, 1)) { ok = false; break; }
+                    mbar_expect_tx(bar_full(s), L::STAGE_BYTES);
+                    const int k = (kb0 + i) * T::BK;
+                    tma_load_2d(x_tile(s), &tm_x, bar_full(s), k, m0);
+#pragma unroll
+                    for (int j = 0; j < W_BOXES; ++j) tma_load_2d(w_tile(s) + j * T::W_LBO, &tm_w, bar_full(s), n0 + j * W_BOX_COLS, k);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            int it = 0, ui = 0;
+            bool ok = true;
+            for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x, ++ui) {
+                int n0, m0, kb0, nkb, z;
+                unit_geom(u, n0, m0, kb0, nkb, z);
+                const int a = ui & 1;
+                if (ui >= 2) {
+                    if (!mbar_wait(bar_acc_empty(a), ((ui >> 1) - 1) & 1, abort_flag, 2)) { ok = false; break; }
+                    tc_fence_after();
+                }
+                const uint32_t d = tmem_base + a * RT_N;
+                for (int i = 0; i < nkb; ++i, ++it) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(bar_full(s), (it / STAGES) & 1, abort_flag, 3)) { ok = false; break; }
+#pragma unroll
+                    for (int kk = 0; kk < KSTEPS; ++kk) {
+                        const uint64_t a_desc = smem_desc(x_tile(s) + kk * 32, 16, 1024);
+                        const uint64_t b_desc = smem_desc(w_tile(s) + kk * T::W_KSTEP, T::W_LBO, 1024);
+                        tc_mma<INT8>(d, a_desc, b_desc, IDESC, (i > 0 || kk > 0) ? 1u : 0u);
+                    }
+                    tc_commit(bar_empty(s));
+                }
+                if (ok) tc_commit(bar_acc_full(a));
+            }
+        }
+    } else {
+        // epilogue: warp's TMEM lane quarter = 32 rows; the two sets of four warps take 128 columns each
+        const int te = threadIdx.x - 64;
+        const int eset = (warp - 2) >> 2, q = warp & 3;
+        const int row = q * 32 + lane, cb = eset * 128;
+        int ui = 0;
+        for (int u = blockIdx.x; u < p.units; u += gridDim.x, ++ui) {
+            int n0, m0, kb0, nkb, z;
+            unit_geom(u, n0, m0, kb0, nkb, z);
+            const int a = ui & 1;
+            const bool to_partial = z >= 0;
+            const int m = m0 + row;
+            const bool m_ok = m < p.M;
+            epi_bar_sync();   // every warp is done with the previous tile's scale and bias
+            {
+                const int n = n0 + te;
+                float sc = 0.f;
+                int bi = 0;
+                if (n < p.N && !to_partial) {
+                    if (p.epilogue == EPI_DEQ_I32) {
+                        sc = load_as_float(p.scale, p.sc_type, n);
+                        if (p.bias) bi = ((const int32_t *)p.bias)[n];
+                    } else if (p.epilogue == EPI_PLAIN && p.bias) {
+                        bi = __float_as_int(load_as_float(p.bias, p.bias_type, n));
+                    }
+                }
+                sc_s[te] = sc;
+                bi_s[te] = bi;
+            }
+            const float pt = (p.pertoken && m_ok && !to_partial) ? __ldg(p.pertoken + m) : 1.f;
+            epi_bar_sync();
+            if (!mbar_wait(bar_acc_full(a), (ui >> 1) & 1, abort_flag, 5)) break;
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + a * RT_N + cb;
+            if (to_partial) {
+                // K slice of a tail tile: the raw [128][256] accumulators go to the workspace
+                const int tail_idx = (u - p.full_units) % p.tail_tiles;
+                uint32_t *prow = (uint32_t *)p.partial + ((size_t)z * p.tail_tiles + tail_idx) * (RT_M * RT_N) + (size_t)row * RT_N + cb;
+#pragma unroll 1
+                for (int c0 = 0; c0 < 128; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(taddr + c0, v);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        reinterpret_cast<uint4 *>(prow + c0)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                }
+            } else if (p.epilogue == EPI_RAW_I32) {
+                rt_store_row<INT8, RO_RAW>(taddr, p, sc_s, bi_s, cb, n0, m, m_ok, pt);
+            } else if (p.out_type == ET_BF16) {
+                rt_store_row<INT8, RO_BF16>(taddr, p, sc_s, bi_s, cb, n0, m, m_ok, pt);
+            } else if (p.out_type == ET_F16) {
+                rt_store_row<INT8, RO_F16>(taddr, p, sc_s, bi_s, cb, n0, m, m_ok, pt);
+            } else {
+                rt_store_row<INT8, RO_F32>(taddr, p, sc_s, bi_s, cb, n0, m, m_ok, pt);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_acc_empty(a));
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
 // Split-K reduction + epilogue: out = epi(sum_z partial[z]).
 __global__ void tc_finalize_kernel(TcParams p) {
-    const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x, per_tile = (size_t)p.mt * TILE_N;
+    const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x, per_tile = (size_t)p.mt * p.tn;
     if (e >= per_tile * p.tail_tiles) return;
-    const int t = (int)(e / per_tile), ml = (int)((e / TILE_N) % p.mt), nl = (int)(e % TILE_N);
+    const int t = (int)(e / per_tile), ml = (int)((e / p.tn) % p.mt), nl = (int)(e % p.tn);
     const int tile = p.full_units + t;
-    const int n = (tile / p.m_tiles) * TILE_N + nl, m = (tile % p.m_tiles) * p.mt + ml;
+    const int n = (tile / p.m_tiles) * p.tn + nl, m = (tile % p.m_tiles) * p.mt + ml;
     if (n >= p.N || m >= p.M) return;
     const size_t i = (size_t)m * p.N + n, stride = per_tile * p.tail_tiles, off = e;
     if (p.epilogue == EPI_PLAIN) {
@@ -318,7 +583,8 @@ DevInfo &dev_info() {
 }
 
 struct TcPlan {
-    int mode, mt, bk, split, num_kb, kb_per_split, m_tiles, tiles, units, P, full_units, tail_tiles;
+    int mode, mt, tn, bk, split, num_kb, kb_per_split, m_tiles, tiles, units, P, full_units, tail_tiles;
+    bool rowtile;
     uint64_t partial_bytes;
 };
 
@@ -328,8 +594,20 @@ TcPlan make_plan(const MatmulArgs &p) {
     pl.bk = pl.mode == D_I8 ? 128 : 64;
     pl.mt = 16;
     while (pl.mt < p.M && pl.mt < 256) pl.mt *= 2;
+    pl.tn = TILE_N;
+    // Many rows: 128-row x 256-column tiles with the rows on the accumulator lanes (tc_rowtile_kernel),
+    // where the output type and alignment allow its 16-byte stores.  B200_QMM_DENSE_ROWTILE=0 keeps the
+    // column-per-lane kernel.
+    pl.rowtile = false;
+    if (p.M > 128 && p.N % 8 == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0) {
+        const bool out_ok = p.epilogue == EPI_RAW_I32 ? p.out_type == ET_I32
+                                                      : (p.out_type == ET_BF16 || p.out_type == ET_F16 || p.out_type == ET_F32);
+        const char *e = getenv("B200_QMM_DENSE_ROWTILE");
+        pl.rowtile = out_ok && !(e && atoi(e) == 0);
+    }
+    if (pl.rowtile) { pl.mt = RT_M; pl.tn = RT_N; }
     pl.num_kb = (int)((p.K + pl.bk - 1) / pl.bk);
-    const int n_tiles = (int)((p.N + TILE_N - 1) / TILE_N);
+    const int n_tiles = (int)((p.N + pl.tn - 1) / pl.tn);
     pl.m_tiles = (int)((p.M + pl.mt - 1) / pl.mt);
     pl.tiles = n_tiles * pl.m_tiles;
     const int sms = dev_info().sms > 0 ? dev_info().sms : 148;
@@ -352,8 +630,8 @@ TcPlan make_plan(const MatmulArgs &p) {
             const int kbps = (pl.num_kb + sct - 1) / sct, eff = (pl.num_kb + kbps - 1) / kbps;
             const long long units = (long long)pl.tail_tiles * eff;
             const double rounds = (double)((units + sms - 1) / sms);
-            double t = rounds * kbps * pl.bk * (pl.mt + TILE_N) * elem / 45e9;
-            if (eff > 1) t += 2.0 * eff * (double)pl.tail_tiles * pl.mt * TILE_N * 4.0 / 3e12 + 3e-6;
+            double t = rounds * kbps * pl.bk * (pl.mt + pl.tn) * elem / 45e9;
+            if (eff > 1) t += 2.0 * eff * (double)pl.tail_tiles * pl.mt * pl.tn * 4.0 / 3e12 + 3e-6;
             if (t < best * 0.97) { best = t; split = eff; }   // a later split must win by a margin
         }
         if (const char *e = getenv("B200_QMM_DENSE_SPLIT")) { const int v = atoi(e); if (v >= 1) split = v; }
@@ -364,7 +642,7 @@ TcPlan make_plan(const MatmulArgs &p) {
     pl.split = (pl.num_kb + pl.kb_per_split - 1) / pl.kb_per_split;
     pl.units = pl.full_units + pl.tail_tiles * pl.split;
     pl.P = pl.units < sms ? pl.units : sms;
-    pl.partial_bytes = pl.split > 1 ? (uint64_t)pl.split * pl.tail_tiles * pl.mt * TILE_N * 4 : 0;
+    pl.partial_bytes = pl.split > 1 ? (uint64_t)pl.split * pl.tail_tiles * pl.mt * pl.tn * 4 : 0;
     return pl;
 }
 
@@ -373,6 +651,24 @@ cudaError_t launch_one(const CUtensorMap &tx, const CUtensorMap &tw, const TcPar
     using L = DSmem<MT, STAGES>;
     static_assert(L::TOTAL <= 232448, "shared memory budget of one CTA");
     auto kern = tc_kernel<MODE, MT, STAGES>;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!attr_set[dev & 63]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+        if (e != cudaSuccess) return e;
+        attr_set[dev & 63] = true;
+    }
+    kern<<<P, 320, L::TOTAL, s>>>(tx, tw, tp);
+    count_launch();
+    return cudaGetLastError();
+}
+
+template <int MODE>
+cudaError_t launch_rowtile(const CUtensorMap &tx, const CUtensorMap &tw, const TcParams &tp, int P, cudaStream_t s) {
+    using L = RSmem<4>;
+    static_assert(L::TOTAL <= 232448, "shared memory budget of one CTA");
+    auto kern = tc_rowtile_kernel<MODE, 4>;
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -461,9 +757,16 @@ cudaError_t launch_dense_tc(const MatmulArgs &p, cudaStream_t s) {
     tp.sc_type = p.sc_type; tp.bias_type = p.bias_type; tp.out_type = p.out_type; tp.epilogue = p.epilogue;
     tp.M = (int)p.M; tp.N = (int)p.N; tp.K = (int)p.K;
     tp.m_tiles = pl.m_tiles; tp.tiles = pl.tiles; tp.num_kb = pl.num_kb; tp.kb_per_split = pl.kb_per_split; tp.units = pl.units;
-    tp.full_units = pl.full_units; tp.tail_tiles = pl.tail_tiles; tp.split = pl.split; tp.mt = pl.mt;
+    tp.full_units = pl.full_units; tp.tail_tiles = pl.tail_tiles; tp.split = pl.split; tp.mt = pl.mt; tp.tn = pl.tn;
 
     cudaError_t e;
+    if (pl.rowtile) {
+        switch (pl.mode) {
+            case D_I8: e = launch_rowtile<D_I8>(tx, tw, tp, pl.P, s); break;
+            case D_BF16: e = launch_rowtile<D_BF16>(tx, tw, tp, pl.P, s); break;
+            default: e = launch_rowtile<D_F16>(tx, tw, tp, pl.P, s); break;
+        }
+    } else
     switch (pl.mode) {
         case D_I8: e = dispatch_mt<D_I8>(pl.mt, tx, tw, tp, pl.P, s); break;
         case D_BF16: e = dispatch_mt<D_BF16>(pl.mt, tx, tw, tp, pl.P, s); break;
@@ -471,7 +774,7 @@ cudaError_t launch_dense_tc(const MatmulArgs &p, cudaStream_t s) {
     }
     if (e != cudaSuccess) return e;
     if (pl.split > 1) {
-        const size_t elems = (size_t)pl.tail_tiles * pl.mt * TILE_N;
+        const size_t elems = (size_t)pl.tail_tiles * pl.mt * pl.tn;
         tc_finalize_kernel<<<(unsigned)((elems + 255) / 256), 256, 0, s>>>(tp);
         count_launch();
         e = cudaGetLastError();
