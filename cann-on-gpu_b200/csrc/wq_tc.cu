@@ -66,6 +66,9 @@ struct WqParams {
     int qpt;                 // quanta per tile
     long long total_q;       // tiles * qpt
     int grouped;
+    // pre-scaled mode (converters apply scale and offset; the pipeline then runs as if per-channel with scale 1)
+    const void *cv_scale, *cv_offset;   // [K/group][N] of the activation type
+    int cv_gsb;                         // super-blocks per scale group
 };
 
 template <bool Q4, int MT, int NS, int NR>
@@ -145,7 +148,7 @@ __device__ __forceinline__ void convert_chunk(const uint32_t (&w)[4], uint32_t d
     }
 }
 
-template <bool Q4, bool BF16, int MT, int NS, int NR>
+template <bool Q4, bool BF16, int MT, int NS, int NR, bool PRE>
 __global__ void __launch_bounds__(640, 1)
 wq_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w, const WqParams p) {
     using L = WqSmem<Q4, MT, NS, NR>;
@@ -328,7 +331,7 @@ wq_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
             auto fetch = [&](int f, uint32_t &sc, uint32_t &of, float (&xs)[XR]) {
                 const int g = p.grouped ? qo + f : 0;
                 sc = 0u; of = 0u;
-                if (n_ok) {
+                if (n_ok && !PRE) {
                     const size_t idx = (size_t)g * p.N + n;
                     if (p.sc_type == ET_F32) {
                         sc = __ldg((const uint32_t *)p.scale + idx);
@@ -386,7 +389,7 @@ wq_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
                 for (int u = 0; u < 2; ++u) {
                     const int f = f0 + u * f_step;
                     if (f >= folds) break;
-                    const float sc = raw_to_float(scq[u]), of = raw_to_float(ofq[u]);
+                    const float sc = PRE ? 1.f : raw_to_float(scq[u]), of = PRE ? 0.f : raw_to_float(ofq[u]);
                     float xs[XR];
 #pragma unroll
                     for (int i = 0; i < XR; ++i) xs[i] = xsq[u][i];
@@ -503,10 +506,80 @@ wq_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
         constexpr int TASKS = Q4 ? 2 : 4;              // chunks per thread per 64-k tile
         int sb = 0;
         bool ok = true;
+        // pre-scaled mode: a thread owns one word of 8 columns (cw) and rows rsub + 8 i of every super-block
+        const int cw = t & 15, rsub = t >> 4;
+        uint32_t s2[4] = {0u, 0u, 0u, 0u}, c2[4] = {0u, 0u, 0u, 0u};   // (scale, -offset*scale) for column pairs (h, h+4)
+        int cur_g = -1, cur_tile = -1, nx_g = -1, nx_tile = -1;
+        uint4 nx_s = make_uint4(0u, 0u, 0u, 0u), nx_o = make_uint4(0u, 0u, 0u, 0u);
+        // 8 scales and 8 offsets (raw 16-bit floats) of this thread's columns in group g of a tile; the
+        // loads are issued here and now (volatile), their results are first touched an own super-block later
+        auto cv_fetch = [&](int tl, int g, uint4 &sraw, uint4 &oraw) {
+            if (DBG(2)) g = 0;
+            const int n = (tl / p.m_tiles) * TILE_N + cw * 8;
+            sraw = make_uint4(0u, 0u, 0u, 0u); oraw = make_uint4(0u, 0u, 0u, 0u);
+            if (n < p.N) {
+                const uint16_t *sp = (const uint16_t *)p.cv_scale + (size_t)g * p.N + n;
+                asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(sraw.x), "=r"(sraw.y), "=r"(sraw.z), "=r"(sraw.w) : "l"(sp));
+                if (p.cv_offset) {
+                    const uint16_t *op = (const uint16_t *)p.cv_offset + (size_t)g * p.N + n;
+                    asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(oraw.x), "=r"(oraw.y), "=r"(oraw.z), "=r"(oraw.w) : "l"(op));
+                }
+            }
+        };
         FOR_EACH_SEGMENT({
+            if constexpr (PRE) {
+                // pull the segment's scale rows into L2 well ahead of the register fetches
+                if (team == 0) {
+                    const size_t col0 = (size_t)(tile / p.m_tiles) * TILE_N;
+                    const int g_first = qo / p.cv_gsb, g_last = (qo + nsb - 1) / p.cv_gsb;
+                    for (int g = g_first + t; g <= g_last; g += 128) {
+                        const char *a0 = (const char *)p.cv_scale + ((size_t)g * p.N + col0) * 2;
+                        asm volatile("prefetch.global.L2 [%0];" ::"l"(a0));
+                        asm volatile("prefetch.global.L2 [%0];" ::"l"(a0 + 128));
+                        if (p.cv_offset) {
+                            const char *a1 = (const char *)p.cv_offset + ((size_t)g * p.N + col0) * 2;
+                            asm volatile("prefetch.global.L2 [%0];" ::"l"(a1));
+                            asm volatile("prefetch.global.L2 [%0];" ::"l"(a1 + 128));
+                        }
+                    }
+                }
+            }
             for (int j = 0; j < nsb && ok; ++j, ++sb) {
                 if ((sb & 1) != team) continue;
                 const int s = sb % NS, r = sb % NR;
+                if constexpr (PRE) {
+                    // Scale and offset of this super-block's group: fetched one own super-block ahead
+                    // (they stream from HBM once, so a load issued at the point of use would expose its
+                    // whole latency), straight from memory only at the start of a share.
+                    const int g = (qo + j) / p.cv_gsb;   // one super-block per quantum in this mode
+                    if (g != cur_g || tile != cur_tile) {
+                        uint4 sraw, oraw;
+                        if (g == nx_g && tile == nx_tile) { sraw = nx_s; oraw = nx_o; }
+                        else cv_fetch(tile, g, sraw, oraw);
+                        cur_g = g; cur_tile = tile;
+                        s2[0] = __byte_perm(sraw.x, sraw.z, 0x5410); s2[1] = __byte_perm(sraw.x, sraw.z, 0x7632);
+                        s2[2] = __byte_perm(sraw.y, sraw.w, 0x5410); s2[3] = __byte_perm(sraw.y, sraw.w, 0x7632);
+                        const uint32_t o2[4] = {__byte_perm(oraw.x, oraw.z, 0x5410), __byte_perm(oraw.x, oraw.z, 0x7632),
+                                                __byte_perm(oraw.y, oraw.w, 0x5410), __byte_perm(oraw.y, oraw.w, 0x7632)};
+#pragma unroll
+                        for (int h = 0; h < 4; ++h) {
+                            // -(offset * scale), rounded once (the product of two 16-bit floats is exact in fp32)
+                            if constexpr (BF16) {
+                                __nv_bfloat162 m2 = __hmul2(*reinterpret_cast<const __nv_bfloat162 *>(&o2[h]), *reinterpret_cast<const __nv_bfloat162 *>(&s2[h]));
+                                c2[h] = *reinterpret_cast<uint32_t *>(&m2) ^ 0x80008000u;
+                            } else {
+                                __half2 m2 = __hmul2(*reinterpret_cast<const __half2 *>(&o2[h]), *reinterpret_cast<const __half2 *>(&s2[h]));
+                                c2[h] = *reinterpret_cast<uint32_t *>(&m2) ^ 0x80008000u;
+                            }
+                        }
+                    }
+                    // this team's next super-block is two further on in the share
+                    const long long nq = q + j + 2;
+                    if (nq < q_end) {
+                        const int nqi = (int)nq, nt = nqi / p.qpt, ng = (nqi - nt * p.qpt) / p.cv_gsb;   // total_q fits 31 bits in this mode
+                        if (nt != cur_tile || ng != cur_g) { nx_tile = nt; nx_g = ng; cv_fetch(nt, ng, nx_s, nx_o); }
+                    }
+                }
                 {
                     PROF_T0();
                     if (!mbar_wait(bar_sfull(s), (sb / NS) & 1, abort_flag, 27)) { ok = false; break; }
@@ -519,7 +592,40 @@ wq_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
                 }
                 PROF_T0();
                 const uint32_t src = w_stage(s);
-                if (!DBG(0)) {
+                if constexpr (PRE) {
+                    // 16 words (one per row) first, then (q - 8 + 8 - ...) -> exact integer -> q*scale - offset*scale
+                    constexpr uint32_t BIAS = BF16 ? 0x43084308u : 0x64086408u;
+                    uint32_t mask = 0x000F000Fu, magic = BIAS;
+                    asm volatile("" : "+r"(mask), "+r"(magic));
+                    uint32_t wv[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const int k = rsub + 8 * i;
+                        const uint32_t sa = src + k * 64 + ((((cw >> 2) ^ ((k >> 1) & 3)) << 4) | ((cw & 3) << 2));
+                        asm volatile("ld.shared.b32 %0, [%1];" : "=r"(wv[i]) : "r"(sa));
+                    }
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const int k = rsub + 8 * i, hh = k >> 6, kk = k & 63;
+                        uint32_t o[4];
+#pragma unroll
+                        for (int h = 0; h < 4; ++h) {
+                            uint32_t pair;
+                            asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(pair) : "r"(wv[i] >> (4 * h)), "r"(mask), "r"(magic));
+                            if constexpr (BF16) {
+                                __nv_bfloat162 d = __hsub2(*reinterpret_cast<const __nv_bfloat162 *>(&pair), *reinterpret_cast<const __nv_bfloat162 *>(&BIAS));
+                                d = __hfma2(d, *reinterpret_cast<const __nv_bfloat162 *>(&s2[h]), *reinterpret_cast<const __nv_bfloat162 *>(&c2[h]));
+                                o[h] = *reinterpret_cast<uint32_t *>(&d);
+                            } else {
+                                __half2 d = __hsub2(*reinterpret_cast<const __half2 *>(&pair), *reinterpret_cast<const __half2 *>(&BIAS));
+                                d = __hfma2(d, *reinterpret_cast<const __half2 *>(&s2[h]), *reinterpret_cast<const __half2 *>(&c2[h]));
+                                o[h] = *reinterpret_cast<uint32_t *>(&d);
+                            }
+                        }
+                        const uint32_t da = w_tile(r, hh) + (cw >> 3) * W_HALF + kk * 128 + ((((cw & 7) ^ (kk & 7))) << 4);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(da), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
+                    }
+                } else if (!DBG(0)) {
                     // all loads of the super-block first (independent), then the conversions
                     uint32_t w[2 * TASKS][4];
 #pragma unroll
@@ -641,6 +747,8 @@ int sm_count() {
 
 struct WqPlan {
     int mt, m_tiles, n_tiles, tiles, num_sb, sbq, qpt, grouped, P, entries;
+    bool pre;                // converters apply scale and offset (group-wise int4, more than 16 rows)
+    int cv_gsb;
     long long total_q;
     uint64_t xtab_bytes, slot_bytes;
 };
@@ -653,18 +761,33 @@ WqPlan wq_make_plan(const MatmulArgs &p) {
     pl.tiles = pl.m_tiles * pl.n_tiles;
     pl.num_sb = (int)((p.K + SBK - 1) / SBK);
     pl.grouped = p.group < p.K ? 1 : 0;
+    // Group-wise scales with more than 16 rows: folding every 128-row group in the epilogue costs
+    // MT x 128 accumulator reads per group and sets the pace (measured on 8192 x 28672: 127 us at M = 64
+    // against 91 us pre-scaled; at M = 32 the fold still keeps up: 84 against 86 us).  There the converters multiply the scale in and subtract offset*scale (the weight
+    // is then rounded to the activation type, as in the reference's path for M > 16,
+    // cuda/src/ops/matmul.cu:734-747,790-795), the accumulator runs over the whole K range of a share and
+    // the epilogue reads it once.  B200_QMM_WQ_PRESCALE=0 keeps the exact per-group fold.
+    pl.pre = false;
+    if (pl.grouped && p.b_type == ET_I4 && p.M > 32 && (reinterpret_cast<uintptr_t>(p.scale) & 15) == 0 &&
+        (!p.offset || (reinterpret_cast<uintptr_t>(p.offset) & 15) == 0)) {
+        const char *e = getenv("B200_QMM_WQ_PRESCALE");
+        pl.pre = !(e && atoi(e) == 0);
+    }
+    pl.cv_gsb = pl.grouped ? (int)(p.group / SBK) : 1;
+    if (pl.pre && (long long)pl.tiles * pl.num_sb >= (1ll << 31)) pl.pre = false;
+    if (pl.pre) pl.grouped = 0;
     pl.sbq = pl.grouped ? (int)(p.group / SBK) : 1;
     pl.qpt = pl.num_sb / pl.sbq;
     pl.total_q = (long long)pl.tiles * pl.qpt;
     const int sms = sm_count();
     pl.P = (int)(pl.total_q < sms ? pl.total_q : sms);
     pl.entries = pl.grouped ? pl.qpt : pl.num_sb;
-    pl.xtab_bytes = p.offset ? align_up_u64((uint64_t)(pl.entries + 1) * p.M * sizeof(float), 256) : 0;
+    pl.xtab_bytes = (p.offset && !pl.pre) ? align_up_u64((uint64_t)(pl.entries + 1) * p.M * sizeof(float), 256) : 0;
     pl.slot_bytes = (uint64_t)(pl.tiles + pl.P) * pl.mt * TILE_N * sizeof(float);
     return pl;
 }
 
-template <bool Q4, bool BF16, int MT, int NS, int NR>
+template <bool Q4, bool BF16, int MT, int NS, int NR, bool PRE = false>
 cudaError_t wq_launch_one(const CUtensorMap &tx, const CUtensorMap &tw, const WqParams &wp, int P, cudaStream_t s) {
     using L = WqSmem<Q4, MT, NS, NR>;
     static_assert(L::TOTAL <= 232448, "shared memory budget of one CTA");
@@ -673,7 +796,7 @@ cudaError_t wq_launch_one(const CUtensorMap &tx, const CUtensorMap &tw, const Wq
     // own slots in order, so it never asks a barrier about a phase beyond the one in progress -- a
     // parity wait would answer "complete" for it at once.
     static_assert(NR < ND && NS >= 2 && NS % 2 == 0 && NR % 2 == 0, "ring depths");
-    auto kern = wq_tc_kernel<Q4, BF16, MT, NS, NR>;
+    auto kern = wq_tc_kernel<Q4, BF16, MT, NS, NR, PRE>;
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -685,6 +808,12 @@ cudaError_t wq_launch_one(const CUtensorMap &tx, const CUtensorMap &tw, const Wq
     kern<<<P, 640, L::TOTAL, s>>>(tx, tw, wp);
     count_launch();
     return cudaGetLastError();
+}
+
+template <bool BF16>
+cudaError_t wq_dispatch_pre(int mt, const CUtensorMap &tx, const CUtensorMap &tw, const WqParams &wp, int P, cudaStream_t s) {
+    (void)mt;   // more than 32 rows: 64-row tiles
+    return wq_launch_one<true, BF16, 64, 4, 4, true>(tx, tw, wp, P, s);
 }
 
 template <bool Q4, bool BF16>
@@ -734,22 +863,24 @@ cudaError_t launch_wq_tc(const MatmulArgs &p, cudaStream_t s) {
     char *ws = (char *)p.workspace;
     WqParams wp{};
     wp.out = p.out;
-    wp.xtab = p.offset ? (const float *)ws : nullptr;
+    wp.xtab = (p.offset && !pl.pre) ? (const float *)ws : nullptr;
     wp.slots = (float *)(ws + pl.xtab_bytes);
-    wp.scale = p.scale; wp.offset = p.offset; wp.bias = p.bias;
+    wp.scale = p.scale; wp.offset = pl.pre ? nullptr : p.offset; wp.bias = p.bias;
+    wp.cv_scale = p.scale; wp.cv_offset = p.offset; wp.cv_gsb = pl.cv_gsb;
     wp.sc_type = p.sc_type; wp.out_type = p.out_type;
     wp.M = (int)p.M; wp.N = (int)p.N; wp.K = (int)p.K;
     wp.m_tiles = pl.m_tiles; wp.num_sb = pl.num_sb; wp.sbq = pl.sbq; wp.qpt = pl.qpt; wp.total_q = pl.total_q;
     wp.grouped = pl.grouped;
 
     cudaError_t e;
-    if (p.offset) {
+    if (p.offset && !pl.pre) {
         wq_xtab_kernel<<<(unsigned)p.M, 256, 0, s>>>(p.a, p.a_type, wp.M, wp.K, pl.grouped ? (int)p.group : SBK, pl.entries,
                                                      pl.grouped ? 0 : 1, (float *)ws);
         count_launch();
         if ((e = cudaGetLastError()) != cudaSuccess) return e;
     }
-    if (q4) e = bf ? wq_dispatch<true, true>(pl.mt, tx, tw, wp, pl.P, s) : wq_dispatch<true, false>(pl.mt, tx, tw, wp, pl.P, s);
+    if (pl.pre) e = bf ? wq_dispatch_pre<true>(pl.mt, tx, tw, wp, pl.P, s) : wq_dispatch_pre<false>(pl.mt, tx, tw, wp, pl.P, s);
+    else if (q4) e = bf ? wq_dispatch<true, true>(pl.mt, tx, tw, wp, pl.P, s) : wq_dispatch<true, false>(pl.mt, tx, tw, wp, pl.P, s);
     else e = bf ? wq_dispatch<false, true>(pl.mt, tx, tw, wp, pl.P, s) : wq_dispatch<false, false>(pl.mt, tx, tw, wp, pl.P, s);
     if (e != cudaSuccess) return e;
     // Tiles shared between CTAs exist unless every share boundary falls on a tile boundary.
