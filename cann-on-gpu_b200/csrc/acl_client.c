@@ -9,7 +9,8 @@
  * call i+1 and the copy-out of call i-1 run beside the matmul of call i (two activation buffers,
  * two output buffers, events between the streams).  Every call still pays its own host-to-device
  * copy, both phases of the operator and its device-to-host copy, and the pass ends with everything
- * synchronised. */
+ * synchronised.  The pass can also be captured once into a model and replayed, which removes the
+ * per-call host work and the gaps between dependent launches on different streams. */
 #include <stddef.h>
 #include <stdint.h>
 
@@ -19,7 +20,7 @@
 #define QMM_CLIENT_API __attribute__((visibility("default")))
 
 static aclrtStream g_in, g_out;          /* copy streams, created on first use */
-static aclrtEvent g_ev_in[2], g_ev_comp[2], g_ev_out[2];
+static aclrtEvent g_ev_in[2], g_ev_comp[2], g_ev_out[2], g_ev_fork, g_ev_join;
 static int g_ready;
 
 static int client_setup(void) {
@@ -29,25 +30,27 @@ static int client_setup(void) {
         if (aclrtCreateEvent(&g_ev_in[b]) != ACL_SUCCESS || aclrtCreateEvent(&g_ev_comp[b]) != ACL_SUCCESS ||
             aclrtCreateEvent(&g_ev_out[b]) != ACL_SUCCESS) return 1;
     }
+    if (aclrtCreateEvent(&g_ev_fork) != ACL_SUCCESS || aclrtCreateEvent(&g_ev_join) != ACL_SUCCESS) return 1;
     g_ready = 1;
     return 0;
 }
 
-/* One pass over n argument sets.  dev_x[b] / x[b] and dev_out[b] / out[b] (b = 0, 1) are the two
- * activation and output buffers with their tensors; call i uses buffer i % 2.  host_x[i] is copied
- * in before call i, the output is copied to host_out after it.  Returns 0, or the first status
- * that was not success.  The workspace must hold workspace_bytes; a call that asks for more returns
- * 161002 from here.  Not re-entrant (one set of streams and events per process). */
-QMM_CLIENT_API int qmmClientWeightQuantPass(int n, const void *const *host_x, size_t x_bytes, void *const *dev_x,
-                                            const aclTensor *const *x, const aclTensor *const *weight,
-                                            const aclTensor *const *scale, const aclTensor *const *offset,
-                                            const aclTensor *const *bias, int64_t group, aclTensor *const *out,
-                                            const void *const *dev_out, void *host_out, size_t out_bytes, void *workspace,
-                                            uint64_t workspace_bytes, aclrtStream stream) {
-    if (client_setup()) return 361001;
+/* Enqueues one pass over n argument sets (no synchronisation).  With `forked` set the copy-in stream
+ * first waits for an event recorded on `stream` and both copy streams are joined back into `stream`
+ * at the end, which is what stream capture needs (every captured stream must fork from and rejoin the
+ * capturing one). */
+static int enqueue_pass(int n, const void *const *host_x, size_t x_bytes, void *const *dev_x, const aclTensor *const *x,
+                        const aclTensor *const *weight, const aclTensor *const *scale, const aclTensor *const *offset,
+                        const aclTensor *const *bias, int64_t group, aclTensor *const *out, const void *const *dev_out,
+                        void *host_out, size_t out_bytes, void *workspace, uint64_t workspace_bytes, aclrtStream stream,
+                        int forked) {
+    aclError e;
+    if (forked) {
+        if ((e = aclrtRecordEvent(g_ev_fork, stream)) != ACL_SUCCESS) return (int)e;
+        if ((e = aclrtStreamWaitEvent(g_in, g_ev_fork)) != ACL_SUCCESS) return (int)e;
+    }
     for (int i = 0; i < n; ++i) {
         const int b = i & 1;
-        aclError e;
         /* copy-in stream: the buffer is free once call i-2 has run */
         if (i >= 2 && (e = aclrtStreamWaitEvent(g_in, g_ev_comp[b])) != ACL_SUCCESS) return (int)e;
         if ((e = aclrtMemcpyAsync(dev_x[b], x_bytes, host_x[i], x_bytes, ACL_MEMCPY_HOST_TO_DEVICE, g_in)) != ACL_SUCCESS) return (int)e;
@@ -69,8 +72,67 @@ QMM_CLIENT_API int qmmClientWeightQuantPass(int n, const void *const *host_x, si
         if ((e = aclrtMemcpyAsync(host_out, out_bytes, dev_out[b], out_bytes, ACL_MEMCPY_DEVICE_TO_HOST, g_out)) != ACL_SUCCESS) return (int)e;
         if ((e = aclrtRecordEvent(g_ev_out[b], g_out)) != ACL_SUCCESS) return (int)e;
     }
+    if (forked) {
+        if ((e = aclrtRecordEvent(g_ev_join, g_in)) != ACL_SUCCESS) return (int)e;
+        if ((e = aclrtStreamWaitEvent(stream, g_ev_join)) != ACL_SUCCESS) return (int)e;
+        if (n > 0 && (e = aclrtStreamWaitEvent(stream, g_ev_out[(n - 1) & 1])) != ACL_SUCCESS) return (int)e;
+        if (n > 1 && (e = aclrtStreamWaitEvent(stream, g_ev_out[n & 1])) != ACL_SUCCESS) return (int)e;
+    }
+    return 0;
+}
+
+/* One pass over n argument sets.  dev_x[b] / x[b] and dev_out[b] / out[b] (b = 0, 1) are the two
+ * activation and output buffers with their tensors; call i uses buffer i % 2.  host_x[i] is copied
+ * in before call i, the output is copied to host_out after it.  Returns 0, or the first status
+ * that was not success.  The workspace must hold workspace_bytes; a call that asks for more returns
+ * 161002 from here.  Not re-entrant (one set of streams and events per process). */
+QMM_CLIENT_API int qmmClientWeightQuantPass(int n, const void *const *host_x, size_t x_bytes, void *const *dev_x,
+                                            const aclTensor *const *x, const aclTensor *const *weight,
+                                            const aclTensor *const *scale, const aclTensor *const *offset,
+                                            const aclTensor *const *bias, int64_t group, aclTensor *const *out,
+                                            const void *const *dev_out, void *host_out, size_t out_bytes, void *workspace,
+                                            uint64_t workspace_bytes, aclrtStream stream) {
+    if (client_setup()) return 361001;
+    const int st = enqueue_pass(n, host_x, x_bytes, dev_x, x, weight, scale, offset, bias, group, out, dev_out, host_out, out_bytes,
+                                workspace, workspace_bytes, stream, 0);
+    if (st != 0) return st;
     aclError e = aclrtSynchronizeStream(g_out);
     if (e == ACL_SUCCESS) e = aclrtSynchronizeStream(stream);
     if (e == ACL_SUCCESS) e = aclrtSynchronizeStream(g_in);
+    return (int)e;
+}
+
+/* The same pass captured once into a model (aclmdlRICaptureBegin / End, the way the reference's
+ * tests/test_graph.cpp captures a decode step): phase 1 of every call runs here, on the host, at
+ * capture time; a replay re-issues the copies from the same host buffers, the kernels and the copies
+ * back.  Run the pass directly once before capturing (first launches set kernel attributes).  The
+ * host buffers, device buffers, tensors' data and the workspace must stay valid while the model is
+ * used.  On failure the capture is ended and its model dropped. */
+QMM_CLIENT_API int qmmClientWeightQuantCapture(int n, const void *const *host_x, size_t x_bytes, void *const *dev_x,
+                                               const aclTensor *const *x, const aclTensor *const *weight,
+                                               const aclTensor *const *scale, const aclTensor *const *offset,
+                                               const aclTensor *const *bias, int64_t group, aclTensor *const *out,
+                                               const void *const *dev_out, void *host_out, size_t out_bytes, void *workspace,
+                                               uint64_t workspace_bytes, aclrtStream stream, aclmdlRI *model) {
+    if (!model) return 161001;
+    *model = NULL;
+    if (client_setup()) return 361001;
+    aclError e = aclmdlRICaptureBegin(stream, ACL_MODEL_RI_CAPTURE_MODE_RELAXED);
+    if (e != ACL_SUCCESS) return (int)e;
+    const int st = enqueue_pass(n, host_x, x_bytes, dev_x, x, weight, scale, offset, bias, group, out, dev_out, host_out, out_bytes,
+                                workspace, workspace_bytes, stream, 1);
+    e = aclmdlRICaptureEnd(stream, model);
+    if (st != 0) {
+        if (e == ACL_SUCCESS) aclmdlRIDestroy(*model);
+        *model = NULL;
+        return st;
+    }
+    return (int)e;
+}
+
+/* Replays a captured pass on `stream` and waits for it. */
+QMM_CLIENT_API int qmmClientReplay(aclmdlRI model, aclrtStream stream) {
+    aclError e = aclmdlRIExecuteAsync(model, stream);
+    if (e == ACL_SUCCESS) e = aclrtSynchronizeStream(stream);
     return (int)e;
 }

@@ -1,6 +1,7 @@
 // aclrt* runtime subset over the CUDA runtime: what a standalone client of the quantized-matmul
 // operators needs (device, stream, event, memory).  Mirrors the call contract of the reference's
 // cuda/src/runtime.cu:45-134.
+#include <new>
 #include <map>
 #include <mutex>
 #include <unordered_map>
@@ -133,6 +134,61 @@ aclError aclrtSynchronizeEvent(aclrtEvent event) { return acl_from_cuda(cudaEven
 aclError aclrtEventElapsedTime(float *ms, aclrtEvent startEvent, aclrtEvent endEvent) {
     if (!ms) return ACLNN_ERR_PARAM_NULLPTR;
     return acl_from_cuda(cudaEventElapsedTime(ms, (cudaEvent_t)startEvent, (cudaEvent_t)endEvent));
+}
+
+// ---- stream capture and replay (reference: cuda/src/runtime.cu:138-189) ---------------------------
+// A model is a captured CUDA graph with its executable instance.
+namespace {
+struct CapturedModel {
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    ~CapturedModel() {
+        if (exec) cudaGraphExecDestroy(exec);
+        if (graph) cudaGraphDestroy(graph);
+    }
+};
+}  // namespace
+
+aclError aclmdlRICaptureBegin(aclrtStream stream, aclmdlRICaptureMode mode) {
+    const cudaStreamCaptureMode m = mode == ACL_MODEL_RI_CAPTURE_MODE_THREAD_LOCAL ? cudaStreamCaptureModeThreadLocal
+                                  : mode == ACL_MODEL_RI_CAPTURE_MODE_RELAXED    ? cudaStreamCaptureModeRelaxed
+                                                                                 : cudaStreamCaptureModeGlobal;
+    return acl_from_cuda(cudaStreamBeginCapture((cudaStream_t)stream, m));
+}
+aclError aclmdlRICaptureGetInfo(aclrtStream stream, aclmdlRICaptureStatus *status, aclmdlRI *modelRI) {
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    const cudaError_t e = cudaStreamIsCapturing((cudaStream_t)stream, &cs);
+    if (status) {
+        *status = cs == cudaStreamCaptureStatusActive        ? ACL_MODEL_RI_CAPTURE_STATUS_ACTIVE
+                : cs == cudaStreamCaptureStatusInvalidated   ? ACL_MODEL_RI_CAPTURE_STATUS_INVALIDATED
+                                                             : ACL_MODEL_RI_CAPTURE_STATUS_NONE;
+    }
+    if (modelRI) *modelRI = nullptr;   // a model exists only after aclmdlRICaptureEnd
+    return acl_from_cuda(e);
+}
+aclError aclmdlRICaptureEnd(aclrtStream stream, aclmdlRI *modelRI) {
+    if (!modelRI) return ACLNN_ERR_PARAM_NULLPTR;
+    *modelRI = nullptr;
+    CapturedModel *m = new (std::nothrow) CapturedModel();
+    if (!m) return ACLNN_ERR_RUNTIME_ERROR;
+    cudaError_t e = cudaStreamEndCapture((cudaStream_t)stream, &m->graph);
+    if (e == cudaSuccess) e = cudaGraphInstantiate(&m->exec, m->graph, 0);
+    if (e != cudaSuccess) { delete m; return acl_from_cuda(e); }
+    *modelRI = m;
+    return ACL_SUCCESS;
+}
+aclError aclmdlRIExecuteAsync(aclmdlRI modelRI, aclrtStream stream) {
+    if (!modelRI) return ACLNN_ERR_PARAM_NULLPTR;
+    return acl_from_cuda(cudaGraphLaunch(static_cast<CapturedModel *>(modelRI)->exec, (cudaStream_t)stream));
+}
+aclError aclmdlRIExecute(aclmdlRI modelRI, int32_t /*timeout*/) {
+    if (!modelRI) return ACLNN_ERR_PARAM_NULLPTR;
+    const cudaError_t e = cudaGraphLaunch(static_cast<CapturedModel *>(modelRI)->exec, nullptr);
+    return acl_from_cuda(e == cudaSuccess ? cudaStreamSynchronize(nullptr) : e);
+}
+aclError aclmdlRIDestroy(aclmdlRI modelRI) {
+    delete static_cast<CapturedModel *>(modelRI);
+    return ACL_SUCCESS;
 }
 
 aclError aclrtMalloc(void **devPtr, size_t size, aclrtMemMallocPolicy) {

@@ -100,6 +100,28 @@ ACL_FUNC_VISIBILITY aclError aclrtStreamWaitEvent(aclrtStream stream, aclrtEvent
 ACL_FUNC_VISIBILITY aclError aclrtSynchronizeEvent(aclrtEvent event);
 ACL_FUNC_VISIBILITY aclError aclrtEventElapsedTime(float *ms, aclrtEvent startEvent, aclrtEvent endEvent);
 
+/* Stream capture and replay (reference: cuda/src/runtime.cu:138-189; used as in tests/test_graph.cpp:
+ * warm up, capture a sequence of two-phase operator calls that reuse a caller-owned workspace, then
+ * replay the model).  Phase 1 runs on the host at capture time only; phase 2 of every operator of
+ * this library enqueues without allocating or synchronising, so it can be captured. */
+typedef void *aclmdlRI;
+typedef enum {
+    ACL_MODEL_RI_CAPTURE_MODE_GLOBAL = 0,
+    ACL_MODEL_RI_CAPTURE_MODE_THREAD_LOCAL = 1,
+    ACL_MODEL_RI_CAPTURE_MODE_RELAXED = 2
+} aclmdlRICaptureMode;
+typedef enum {
+    ACL_MODEL_RI_CAPTURE_STATUS_NONE = 0,
+    ACL_MODEL_RI_CAPTURE_STATUS_ACTIVE = 1,
+    ACL_MODEL_RI_CAPTURE_STATUS_INVALIDATED = 2
+} aclmdlRICaptureStatus;
+ACL_FUNC_VISIBILITY aclError aclmdlRICaptureBegin(aclrtStream stream, aclmdlRICaptureMode mode);
+ACL_FUNC_VISIBILITY aclError aclmdlRICaptureGetInfo(aclrtStream stream, aclmdlRICaptureStatus *status, aclmdlRI *modelRI);
+ACL_FUNC_VISIBILITY aclError aclmdlRICaptureEnd(aclrtStream stream, aclmdlRI *modelRI);
+ACL_FUNC_VISIBILITY aclError aclmdlRIExecuteAsync(aclmdlRI modelRI, aclrtStream stream);
+ACL_FUNC_VISIBILITY aclError aclmdlRIExecute(aclmdlRI modelRI, int32_t timeout);
+ACL_FUNC_VISIBILITY aclError aclmdlRIDestroy(aclmdlRI modelRI);
+
 /* Device / pinned-host memory (reference: cuda/src/runtime.cu:103-134). */
 ACL_FUNC_VISIBILITY aclError aclrtMalloc(void **devPtr, size_t size, aclrtMemMallocPolicy policy);
 ACL_FUNC_VISIBILITY aclError aclrtFree(void *devPtr);

@@ -660,7 +660,8 @@ def test_c_client_pipelined_pass(pkg, oracle, workloads, dev):
     tw = [pkg.AclTensor(t, pkg.ACL_INT4, (K, N)) for t in w]
     ts = [pkg.AclTensor(t) for t in sc]
     ws = torch.empty(64 << 20, dtype=torch.uint8, device=dev)
-    stream = VP(torch.cuda.current_stream(dev).cuda_stream)
+    own_stream = torch.cuda.Stream(dev)   # the legacy default stream cannot be captured
+    stream = VP(own_stream.cuda_stream)
     want = [pkg.weight_quant_matmul(d["x"].to(dev), w[i], sc[i], int4=True, group=G).cpu() for i, d in enumerate(sets)]
     torch.cuda.synchronize()
     for n in range(1, 6):
@@ -673,6 +674,74 @@ def test_c_client_pipelined_pass(pkg, oracle, workloads, dev):
             ctypes.c_size_t(M * N * 2), VP(ws.data_ptr()), ctypes.c_uint64(ws.numel()), stream)
         assert st == 0
         assert torch.equal(hout, want[n - 1]), n
+    # the same pass captured into a model and replayed: new activations in the same host buffers must
+    # come through (the copies are part of the model), three replays give the same bits
+    client.qmmClientWeightQuantCapture.restype = ctypes.c_int
+    client.qmmClientReplay.restype = ctypes.c_int
+    for n in (1, 2, 5):
+        model = VP()
+        st = client.qmmClientWeightQuantCapture(
+            ctypes.c_int(n), (VP * n)(*[VP(h.data_ptr()) for h in hx[:n]]), ctypes.c_size_t(M * K * 2),
+            (VP * 2)(*[VP(t.data_ptr()) for t in dxs]), (VP * 2)(*[VP(t.h) for t in tdx]),
+            (VP * n)(*[VP(t.h) for t in tw[:n]]), (VP * n)(*[VP(t.h) for t in ts[:n]]), None, None, ctypes.c_int64(G),
+            (VP * 2)(*[VP(t.h) for t in tdo]), (VP * 2)(*[VP(t.data_ptr()) for t in douts]), VP(hout.data_ptr()),
+            ctypes.c_size_t(M * N * 2), VP(ws.data_ptr()), ctypes.c_uint64(ws.numel()), stream, ctypes.byref(model))
+        assert st == 0 and model.value
+        for rep in range(3):
+            hout.zero_()
+            assert client.qmmClientReplay(model, stream) == 0
+            assert torch.equal(hout, want[n - 1]), (n, rep)
+        saved = hx[n - 1].clone()
+        hx[n - 1].copy_(sets[(n + 1) % 5]["x"])   # other activations, same buffer
+        want2 = pkg.weight_quant_matmul(hx[n - 1].to(dev), w[n - 1], sc[n - 1], int4=True, group=G).cpu()
+        torch.cuda.synchronize()
+        assert client.qmmClientReplay(model, stream) == 0
+        assert torch.equal(hout, want2), n
+        hx[n - 1].copy_(saved)
+        assert pkg.load().aclmdlRIDestroy(model) == 0
+
+
+def test_capture_replay_of_the_two_phase_call(pkg, oracle, workloads, dev):
+    """aclmdlRICaptureBegin / End / ExecuteAsync around quantized matmuls, used like the reference's
+    tests/test_graph.cpp:30-78: warm up, capture calls that share a caller-owned workspace (phase 1 runs
+    at capture time only), destroy the tensors, replay three times; every replay equals the direct call.
+    Covers the decode kernel (two launches), the W8A8 dense kernel and the capture status query."""
+    lib = pkg.load()
+    VP = ctypes.c_void_p
+    own_stream = torch.cuda.Stream(dev)   # the legacy default stream cannot be captured
+    stream = VP(own_stream.cuda_stream)
+    d = workloads.w4a16(M=4, K=1024, N=512, group=128, seed=7300)
+    q = workloads.w8a8(M=200, K=512, N=256, seed=7301)
+    dd = {k: v.to(dev) for k, v in d.items() if isinstance(v, torch.Tensor)}
+    qd = {k: v.to(dev) for k, v in q.items() if isinstance(v, torch.Tensor)}
+    out_wq = torch.empty((4, 512), dtype=torch.bfloat16, device=dev)
+    out_q = torch.empty((200, 256), dtype=torch.bfloat16, device=dev)
+
+    def both():   # device tensors only, no allocation, no synchronisation: legal inside a capture
+        pkg.weight_quant_matmul(dd["x"], dd["w"], dd["scale"], dd.get("offset"), dd.get("bias"), int4=True, group=128, out=out_wq,
+                                stream=own_stream.cuda_stream)
+        pkg.quant_matmul(qd["x"], qd["w"], qd["scale"], qd["pertoken"], qd["bias"], out=out_q, stream=own_stream.cuda_stream)
+
+    both()   # warm-up: sizes the shared workspace, sets kernel attributes
+    torch.cuda.synchronize()
+    direct_wq, direct_q = out_wq.clone(), out_q.clone()
+    assert_close(to_np(direct_wq), ref_wq(oracle, d), "captured W4A16 case, direct")
+    status = ctypes.c_int(-1)
+    assert lib.aclmdlRICaptureGetInfo(stream, ctypes.byref(status), None) == 0 and status.value == 0
+    assert lib.aclmdlRICaptureBegin(stream, ctypes.c_int(2)) == 0
+    assert lib.aclmdlRICaptureGetInfo(stream, ctypes.byref(status), None) == 0 and status.value == 1
+    both()
+    model = VP()
+    assert lib.aclmdlRICaptureEnd(stream, ctypes.byref(model)) == 0 and model.value
+    assert lib.aclmdlRICaptureEnd(stream, None) == 161001
+    for _ in range(3):
+        out_wq.zero_(); out_q.zero_()
+        torch.cuda.synchronize()   # the zeroing ran on another stream
+        assert lib.aclmdlRIExecuteAsync(model, stream) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(out_wq, direct_wq) and torch.equal(out_q, direct_q)
+    assert lib.aclmdlRIExecuteAsync(None, stream) == 161001
+    assert lib.aclmdlRIDestroy(model) == 0
 
 
 def test_zz_no_bounded_wait_gave_up(pkg, dev):
