@@ -280,6 +280,21 @@ def sweep(pkg, workloads, dev, pk, only=None):
                 calls.append(lambda ws, a=args: pkg.call("aclnnDynamicQuant", *a, workspace=ws, device=dev))
             run_case(name, calls, 0, m * 4096 * 3 + m * 4, 10)
             del calls
+        # SwiGLU + per-token quantiser between a gate/up projection [m, 2 x 14336] and a W8A8 down projection
+        # (bytes moved: rows * (2 D * 2 + D) + rows * 4)
+        for m in (2048,):
+            name = f"SwiGluQuant bf16 [{m},28672] -> int8 [{m},14336]"
+            if not wanted(name):
+                continue
+            calls = []
+            for i in range(3):   # 3 x (117 MB in + 29 MB out) > 2 x L2
+                x = torch.randn((m, 28672), generator=torch.Generator().manual_seed(3100 + i)).to(torch.bfloat16).to(dev)
+                q = torch.empty((m, 14336), dtype=torch.int8, device=dev)
+                sc = torch.empty((m,), dtype=torch.float32, device=dev)
+                args = [pkg.AclTensor(x), pkg.AclTensor(q), pkg.AclTensor(sc)]
+                calls.append(lambda ws, a=args: pkg.call("aclnnSwiGluQuant", *a, workspace=ws, device=dev))
+            run_case(name, calls, 0, m * 14336 * 5 + m * 4, 10)
+            del calls
         # config 3: MXFP8 x MXFP4 4096 x 8192 x 8192
         if not wanted("cfg3 MXFP8xMXFP4 M=4096 K=8192 N=8192 bf16 out"):
             raise StopIteration

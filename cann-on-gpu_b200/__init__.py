@@ -213,6 +213,16 @@ def dynamic_quant(x, name="aclnnDynamicQuant", **kw):
     return q, scale
 
 
+
+def swiglu_quant(x, name="aclnnSwiGluQuant", **kw):
+    """x [..., 2D] f32/f16/bf16 -> (int8 [..., D] of silu(x[..., :D]) * x[..., D:], fp32 per-row scales [...])."""
+    import torch
+    D = x.shape[-1] // 2
+    q = torch.empty(tuple(x.shape[:-1]) + (D,), dtype=torch.int8, device=x.device)
+    scale = torch.empty(x.shape[:-1] if x.dim() > 1 else (1,), dtype=torch.float32, device=x.device)
+    call(name, AclTensor(x), AclTensor(q), AclTensor(scale), **kw)
+    return q, scale
+
 def dynamic_mx_quant(x, block, name="aclnnDynamicMxQuant", **kw):
     """x (numel a multiple of block) f32/f16/bf16 -> (int8 of x's shape, fp32 power-of-two scale per block)."""
     import torch

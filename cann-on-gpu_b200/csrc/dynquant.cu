@@ -1,4 +1,4 @@
-// Dynamic int8 quantisers of activations.
+// Dynamic int8 quantisers of activations (per token, block-wise, and SwiGLU fused with per token).
 //
 // Per-token, the step in front of the W8A8 matmul: for every row of x
 //   scale = max|x| / 127 (1 for an all-zero row),  q = clamp(rint(x * (1 / scale)), -128, 127)
@@ -20,6 +20,18 @@ constexpr int DQ_VEC = 8;   // elements per 16-byte load of a 16-bit type
 __device__ __forceinline__ int8_t quant_i8(float v) {
     const int q = (int)rintf(v);
     return (int8_t)(q < -128 ? -128 : (q > 127 ? 127 : q));
+}
+
+template <int THREADS>
+__device__ __forceinline__ float block_max_t(float v, float *sh) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float m = 0.f;
+#pragma unroll
+    for (int w = 0; w < THREADS / 32; ++w) m = fmaxf(m, sh[w]);
+    return m;
 }
 
 __device__ __forceinline__ float block_max(float v, float *sh) {
@@ -134,7 +146,104 @@ __global__ void __launch_bounds__(DQ_THREADS) mxquant_generic_kernel(const void 
     for (int64_t d = threadIdx.x; d < blk; d += DQ_THREADS) q[base + d] = quant_i8(load_as_float(x, x_type, base + d) * inv);
 }
 
+// ---- SwiGLU fused with the per-token quantiser: the step between the gate/up projection and a W8A8
+// down projection.  Row layout [a (D) | b (D)]; g = a / (1 + exp(-a)) * b in fp32, evaluated with the
+// reference's expression (cuda/src/ops/glu_ext.cu:89-103); scale = max|g| / 127 (1 for an all-zero
+// row), q = clamp(rint(g * (1 / scale)), -127, 127).  The reference computes g twice (maximum, then
+// quantise); here a row of up to 16384 outputs keeps g in registers: one read of 2 D inputs, one
+// write of D codes.
+__device__ __forceinline__ float swiglu_of(float a, float b) { return a / (1.f + expf(-a)) * b; }
+__device__ __forceinline__ int8_t quant_i8_sym(float v) {
+    const int q = __float2int_rn(v);
+    return (int8_t)(q < -127 ? -127 : (q > 127 ? 127 : q));
+}
+template <bool BF16> __device__ __forceinline__ void unpack8(const uint4 &v, float (&f)[8]) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        if constexpr (BF16) { f[2 * i] = __uint_as_float(w[i] << 16); f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u); }
+        else { f[2 * i] = __half2float(__ushort_as_half((unsigned short)(w[i] & 0xFFFFu))); f[2 * i + 1] = __half2float(__ushort_as_half((unsigned short)(w[i] >> 16))); }
+    }
+}
+
+// 16-bit inputs, D % 8 == 0, D <= THREADS * 8 * CHUNKS.  Long rows use 512 threads with at most four
+// chunks each: the arithmetic per element (expf, an IEEE division) needs the occupancy more than the
+// per-token quantiser does.
+template <bool BF16, int CHUNKS, int THREADS>
+__global__ void __launch_bounds__(THREADS) swigluquant_row_kernel(const uint16_t *x, int8_t *q, float *scale_out, int64_t D) {
+    __shared__ float sh[THREADS / 32];
+    const int64_t ib = (int64_t)blockIdx.x * 2 * D, ob = (int64_t)blockIdx.x * D;
+    float g[CHUNKS][8];
+    float amax = 0.f;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+        const int64_t d = ((int64_t)c * THREADS + threadIdx.x) * DQ_VEC;
+        uint4 va = make_uint4(0, 0, 0, 0), vb = make_uint4(0, 0, 0, 0);
+        if (d < D) {
+            va = __ldg(reinterpret_cast<const uint4 *>(x + ib + d));
+            vb = __ldg(reinterpret_cast<const uint4 *>(x + ib + D + d));
+        }
+        float fa[8], fb[8];
+        unpack8<BF16>(va, fa);
+        unpack8<BF16>(vb, fb);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            g[c][i] = swiglu_of(fa[i], fb[i]);      // 0 beyond the row: silu(0) * 0
+            amax = fmaxf(amax, fabsf(g[c][i]));
+        }
+    }
+    const float m = block_max_t<THREADS>(amax, sh);
+    const float scale = m > 0.f ? m / 127.f : 1.f;
+    if (threadIdx.x == 0) scale_out[blockIdx.x] = scale;
+    const float inv = 1.f / scale;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+        const int64_t d = ((int64_t)c * THREADS + threadIdx.x) * DQ_VEC;
+        if (d >= D) continue;
+        uint32_t o[2] = {0, 0};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i >> 2] |= (uint32_t)(uint8_t)quant_i8_sym(g[c][i] * inv) << (8 * (i & 3));
+        *reinterpret_cast<uint2 *>(q + ob + d) = make_uint2(o[0], o[1]);
+    }
+}
+
+// Any type, any D: g is evaluated twice, the second read of the row hits L2.
+__global__ void __launch_bounds__(DQ_THREADS) swigluquant_generic_kernel(const void *x, int x_type, int8_t *q, float *scale_out, int64_t D) {
+    __shared__ float sh[DQ_THREADS / 32];
+    const int64_t ib = (int64_t)blockIdx.x * 2 * D, ob = (int64_t)blockIdx.x * D;
+    float amax = 0.f;
+    for (int64_t d = threadIdx.x; d < D; d += DQ_THREADS)
+        amax = fmaxf(amax, fabsf(swiglu_of(load_as_float(x, x_type, ib + d), load_as_float(x, x_type, ib + D + d))));
+    const float m = block_max(amax, sh);
+    const float scale = m > 0.f ? m / 127.f : 1.f;
+    if (threadIdx.x == 0) scale_out[blockIdx.x] = scale;
+    const float inv = 1.f / scale;
+    for (int64_t d = threadIdx.x; d < D; d += DQ_THREADS)
+        q[ob + d] = quant_i8_sym(swiglu_of(load_as_float(x, x_type, ib + d), load_as_float(x, x_type, ib + D + d)) * inv);
+}
+
 }  // namespace
+
+cudaError_t launch_swiglu_quant(const void *x, int x_type, int8_t *q, float *scale_out, int64_t rows, int64_t D, cudaStream_t s) {
+    if (rows <= 0 || D <= 0) return cudaSuccess;
+    if (rows > 0x7fffffffLL) return cudaErrorInvalidValue;
+    const bool vec = (x_type == ET_BF16 || x_type == ET_F16) && D % DQ_VEC == 0 && D <= (int64_t)512 * DQ_VEC * 4 &&
+                     (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(q) & 7) == 0;
+    const unsigned g = (unsigned)rows;
+    const uint16_t *x16 = static_cast<const uint16_t *>(x);
+    const int64_t per = (int64_t)DQ_THREADS * DQ_VEC;
+    const bool bf = x_type == ET_BF16;
+#define SGQ(C, T) do { if (bf) swigluquant_row_kernel<true, C, T><<<g, T, 0, s>>>(x16, q, scale_out, D); \
+                       else swigluquant_row_kernel<false, C, T><<<g, T, 0, s>>>(x16, q, scale_out, D); } while (0)
+    if (!vec) swigluquant_generic_kernel<<<g, DQ_THREADS, 0, s>>>(x, x_type, q, scale_out, D);
+    else if (D <= per) SGQ(1, 256);
+    else if (D <= per * 2) SGQ(2, 256);
+    else if (D <= per * 4) SGQ(2, 512);
+    else SGQ(4, 512);
+#undef SGQ
+    count_launch();
+    return cudaGetLastError();
+}
 
 cudaError_t launch_dynamic_mx_quant(const void *x, int x_type, int8_t *q, float *scale_out, int64_t nblocks, int64_t blk, cudaStream_t s) {
     if (nblocks <= 0 || blk <= 0) return cudaSuccess;

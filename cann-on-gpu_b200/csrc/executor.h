@@ -15,6 +15,7 @@ enum PlanOp : int {
     PLAN_CAST,        // element-wise dtype cast
     PLAN_QPARAM,      // fp32 scale (+ offset) -> packed int64 quant parameter
     PLAN_DYNQUANT,    // per-token dynamic int8 quantiser
+    PLAN_SWIGLUQUANT, // SwiGLU fused with the per-token quantiser
     PLAN_MXQUANT,     // block-wise power-of-two-scale int8 quantiser
 };
 

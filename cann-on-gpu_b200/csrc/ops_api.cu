@@ -273,6 +273,10 @@ aclnnStatus run_simple(aclOpExecutor *e, aclrtStream stream) {
             err = launch_dynamic_quant(data_of(e->a), elem_type(e->a->dtype), (int8_t *)const_cast<void *>(data_of(e->out)),
                                        (float *)const_cast<void *>(data_of(e->out2)), e->m, e->k, s);
             break;
+        case PLAN_SWIGLUQUANT:
+            err = launch_swiglu_quant(data_of(e->a), elem_type(e->a->dtype), (int8_t *)const_cast<void *>(data_of(e->out)),
+                                      (float *)const_cast<void *>(data_of(e->out2)), e->m, e->k, s);
+            break;
         case PLAN_MXQUANT:
             err = launch_dynamic_mx_quant(data_of(e->a), elem_type(e->a->dtype), (int8_t *)const_cast<void *>(data_of(e->out)),
                                           (float *)const_cast<void *>(data_of(e->out2)), e->m, e->k, s);
@@ -498,6 +502,33 @@ DYNQUANT_ALIAS(aclnnDynamicQuant)
 DYNQUANT_ALIAS(aclnnDynamicQuantV2)
 DYNQUANT_ALIAS(aclnnDynamicQuantV3)
 DYNQUANT_ALIAS(aclnnDynamicQuantV4)
+
+// SwiGLU fused with the per-token quantiser: x [..., 2 D] -> int8 [..., D] + fp32 scale per row
+// (cuda/src/ops/glu_ext.cu:118-141; V2 is the reference's alias).
+static aclnnStatus swigluquant_plan(const aclTensor *x, aclTensor *out, aclTensor *scaleOut, uint64_t *ws, aclOpExecutor **ex) {
+    if (!x || !out || !scaleOut || !ws || !ex) return ACLNN_ERR_PARAM_NULLPTR;
+    if (x->viewDims.empty() || out->viewDims.size() != x->viewDims.size()) return ACLNN_ERR_PARAM_INVALID;
+    if (x->numel() > 0 && (!x->data || !out->data || !scaleOut->data)) return ACLNN_ERR_PARAM_NULLPTR;
+    if (out->dtype != ACL_INT8 || scaleOut->dtype != ACL_FLOAT) return ACLNN_ERR_PARAM_INVALID;
+    if (x->dtype != ACL_FLOAT && x->dtype != ACL_FLOAT16 && x->dtype != ACL_BF16) return ACLNN_ERR_PARAM_INVALID;
+    const int64_t D = out->viewDims.back();
+    if (x->viewDims.back() != 2 * D) return ACLNN_ERR_PARAM_INVALID;
+    for (size_t i = 0; i + 1 < x->viewDims.size(); ++i)
+        if (x->viewDims[i] != out->viewDims[i]) return ACLNN_ERR_PARAM_INVALID;
+    if (!dense(x) || !dense(out) || !dense(scaleOut)) return ACLNN_ERR_PARAM_INVALID;
+    const int64_t rows = D > 0 ? out->numel() / D : 0;
+    if (scaleOut->numel() != rows) return ACLNN_ERR_PARAM_INVALID;
+    auto *e = new aclOpExecutor();
+    e->op = PLAN_SWIGLUQUANT; e->a = x; e->out = out; e->out2 = scaleOut; e->m = rows; e->k = D;
+    *ws = 0; *ex = e;
+    return ACLNN_SUCCESS;
+}
+#define SWIGLUQUANT_ALIAS(NAME)                                                                                      \
+    aclnnStatus NAME##GetWorkspaceSize(const aclTensor *x, aclTensor *out, aclTensor *scaleOut, uint64_t *ws,        \
+                                       aclOpExecutor **ex) { return swigluquant_plan(x, out, scaleOut, ws, ex); }   \
+    RUN_SIMPLE(NAME)
+SWIGLUQUANT_ALIAS(aclnnSwiGluQuant)
+SWIGLUQUANT_ALIAS(aclnnSwiGluQuantV2)
 
 // Block-wise int8 quantiser with power-of-two scales (cuda/src/ops/quant.cu:380-389,496-514).
 static aclnnStatus mxquant_plan(const aclTensor *x, int64_t blockSize, aclTensor *out, aclTensor *scaleOut, uint64_t *ws,

@@ -165,6 +165,14 @@ B200_ACLNN_DYNQUANT(aclnnDynamicQuantV2)
 B200_ACLNN_DYNQUANT(aclnnDynamicQuantV3)
 B200_ACLNN_DYNQUANT(aclnnDynamicQuantV4)
 
+/* SwiGLU fused with the per-token quantiser, the step between a gate/up projection and a W8A8 down
+ * projection: x [..., 2 D] (ACL_FLOAT, ACL_FLOAT16 or ACL_BF16) holds a = x[..., :D] and b = x[..., D:];
+ * g = a / (1 + exp(-a)) * b in fp32; scaleOut = max|g| / 127 (1 for a zero row; ACL_FLOAT, one per row),
+ * out [..., D] = clamp(rint(g * (1 / scaleOut)), -127, 127) as ACL_INT8.
+ * Replaces aclnn_ops.h:1275-1278 (cuda/src/ops/glu_ext.cu:89-103,118-141). */
+B200_ACLNN_DYNQUANT(aclnnSwiGluQuant)
+B200_ACLNN_DYNQUANT(aclnnSwiGluQuantV2)
+
 /* Block-wise dynamic int8 quantiser with power-of-two scales: per block of blockSize consecutive elements
  * scaleOut = 2^ceil(log2(max|x| / 127)) (1 for a zero block; ACL_FLOAT, one per block),
  * out = clamp(rint(x * (1 / scaleOut)), -128, 127) as ACL_INT8.

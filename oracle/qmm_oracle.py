@@ -301,6 +301,24 @@ def dynamic_quant(x):
     return np.clip(q, -128, 127).astype(np.int8), scale
 
 
+def swiglu_quant(x):
+    """SwiGLU fused with the per-token int8 quantiser, restating cuda/src/ops/glu_ext.cu:89-103 in fp32:
+    x [..., 2D] = [a | b]; g = a / (1 + exp(-a)) * b; scale = max|g| / 127 per row (1 for a zero row);
+    q = clamp(rint(g * (1 / scale)), -127, 127).  exp here is numpy's float32 exp, the device uses
+    CUDA's expf (both within a couple of ulp of the true value), so a code may differ by one where
+    g / scale falls next to a rounding boundary.  Returns (int8 [..., D], float32 [...])."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    D = x.shape[-1] // 2
+    a, b = x[..., :D], x[..., D:]
+    with np.errstate(over="ignore"):
+        g = ((a / (np.float32(1) + np.exp(-a, dtype=np.float32))).astype(np.float32) * b).astype(np.float32)
+    amax = np.abs(g).max(axis=-1) if D else np.zeros(x.shape[:-1], np.float32)
+    scale = np.where(amax > 0, amax / np.float32(127), np.float32(1)).astype(np.float32)
+    inv = (np.float32(1) / scale).astype(np.float32)
+    q = np.rint((g * inv[..., None]).astype(np.float32))
+    return np.clip(q, -127, 127).astype(np.int8), scale
+
+
 def dynamic_mx_quant(x, block):
     """Block-wise int8 quantiser with power-of-two scales, restating cuda/src/ops/quant.cu:380-389 in fp32:
     per block of `block` consecutive elements scale = 2^ceil(log2(max|x| / 127)) (1 for a zero block),

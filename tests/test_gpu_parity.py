@@ -623,6 +623,46 @@ def test_dynamic_mx_quant_bit_exact(pkg, oracle, dev, case, dtype):
     assert want_s[0] == 1 and want_s[1] == 0.5
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(8, 32), (5, 200), (64, 4096), (3, 2, 8192), (4, 28672), (2, 40000)])
+def test_swiglu_quant(pkg, oracle, dev, shape, dtype):
+    """SwiGLU fused with the per-token quantiser (cuda/src/ops/glu_ext.cu:89-141), both names, the
+    register-resident and the generic form, a zero row.  Scales agree to fp32 rounding of expf; codes are
+    equal except where g / scale sits on a rounding boundary (at most 1 apart, under 1 in 1000), and the
+    reference's own dequantisation check (tests/test_norm.cpp:152-161) holds."""
+    g = torch.Generator().manual_seed(6400 + shape[-1])
+    x = (torch.rand(shape, generator=g) * 4 - 2).to(dtype)
+    x.view(-1, shape[-1])[0, :] = 0
+    want_q, want_s = oracle.swiglu_quant(x.float().numpy())
+    D = shape[-1] // 2
+    a, b = x.double()[..., :D].numpy(), x.double()[..., D:].numpy()
+    gd = a / (1.0 + np.exp(-a)) * b
+    for name in ("aclnnSwiGluQuant", "aclnnSwiGluQuantV2"):
+        q, sc = pkg.swiglu_quant(x.to(dev), name=name)
+        torch.cuda.synchronize()
+        q, sc = q.cpu().numpy(), sc.cpu().numpy().reshape(want_s.shape)
+        assert np.allclose(sc, want_s, rtol=2e-6, atol=0), name
+        diff = np.abs(q.astype(int) - want_q.astype(int))
+        assert diff.max() <= 1 and (diff != 0).mean() < 1e-3, (name, diff.max(), (diff != 0).mean())
+        assert np.abs(q * sc[..., None].astype(np.float64) - gd).max() / np.abs(gd).max() <= 1e-2, name
+        assert (q.reshape(-1, D)[0] == 0).all() and sc.reshape(-1)[0] == 1
+
+
+def test_swiglu_quant_feeds_the_w8a8_matmul(pkg, oracle, workloads, dev):
+    """gate/up output -> SwiGluQuant -> aclnnQuantMatmulV4 with the scales as pertokenScale: the matmul's
+    result is bit-exact for the codes and scales the quantiser produced."""
+    g = torch.Generator().manual_seed(6500)
+    M, K, N = 40, 1024, 256
+    x = torch.randn((M, 2 * K), generator=g).to(torch.bfloat16)
+    d = workloads.w8a8(M=M, K=K, N=N, seed=6501, with_pertoken=False)
+    q, sc = pkg.swiglu_quant(x.to(dev))
+    out = pkg.quant_matmul(q, d["w"].to(dev), d["scale"].to(dev), sc, d["bias"].to(dev), out_dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+    acc = oracle.qmm_acc_fast(q.cpu().numpy(), d["w"].numpy(), M, K, N)
+    want = torch.from_numpy(oracle.qmm_epilogue_fast(acc, f32(d["scale"]), sc.cpu().numpy(), d["bias"].numpy())).to(torch.bfloat16)
+    assert torch.equal(out.cpu(), want)
+
+
 def test_dynamic_quant_feeds_the_w8a8_matmul(pkg, oracle, workloads, dev):
     """The chain a W8A8 layer runs: quantise the activations per token, then aclnnQuantMatmulV4 with
     the scales as pertokenScale.  Accumulators and output bit-exact against the oracle's chain."""

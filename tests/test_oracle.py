@@ -226,3 +226,19 @@ def test_dynamic_quant_oracle_matches_the_reference_tests_formula(oracle):
     assert (q != want_q).mean() < 1e-4 and np.abs(q.astype(int) - want_q.astype(int)).max() <= 1
     assert np.abs(q).max() == 127 and (q[3] == 0).all() and sc[3] == 1
     assert np.abs(q * sc[:, None] - x).max() <= sc.max() * 0.5 + 1e-6
+
+
+def test_swiglu_quant_oracle_matches_the_reference_tests_check(oracle):
+    """The reference checks SwiGluQuant by dequantising (tests/test_norm.cpp:152-161): with
+    g = a / (1 + exp(-a)) * b in double, max|q * scale - g| / max|g| <= 1e-2 on inputs in [-2, 2].
+    The oracle must pass that check, give scale = max|g| / 127, codes within +-127, and 1 for a zero row."""
+    rng = np.random.default_rng(11)
+    x = (rng.random((8, 32), dtype=np.float32) * 4 - 2).astype(np.float32)
+    x[5] = 0
+    q, sc = oracle.swiglu_quant(x)
+    a, b = x[:, :16].astype(np.float64), x[:, 16:].astype(np.float64)
+    g = a / (1.0 + np.exp(-a)) * b
+    assert q.shape == (8, 16) and sc.shape == (8,)
+    assert np.abs(q * sc[:, None].astype(np.float64) - g).max() / np.abs(g).max() <= 1e-2
+    assert np.allclose(sc[np.arange(8) != 5], np.abs(g).max(axis=1)[np.arange(8) != 5] / 127, rtol=1e-6)
+    assert sc[5] == 1 and (q[5] == 0).all() and np.abs(q).max() == 127 and q.min() >= -127
