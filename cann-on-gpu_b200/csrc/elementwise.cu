@@ -85,6 +85,43 @@ cudaError_t launch_qparam(const float *scale, const float *offset, int64_t *out,
     return cudaGetLastError();
 }
 
+// Residual add + RMS norm, the tail of the all-reduce matmuls (cuda/src/ops/norm_ext.cu:123-139):
+// v = x + residual in fp32; residual_sum = T(v); y = T(float(residual_sum) * rsqrt(mean(v^2) + eps) * gamma).
+// One CTA per row.  The second pass reads residual_sum back, like the reference, so residual_sum may
+// alias residual and y may alias x.
+__global__ void __launch_bounds__(256) add_rmsnorm_kernel(const void *x, const void *res, const void *gamma, int type, int gamma_type,
+                                                          void *ysum, void *y, int64_t D, float eps) {
+    __shared__ float sh[8];
+    const int64_t base = (int64_t)blockIdx.x * D;
+    float ss = 0.f;
+    for (int64_t d = threadIdx.x; d < D; d += 256) {
+        const float v = load_as_float(x, type, base + d) + load_as_float(res, type, base + d);
+        store_from_float(ysum, type, base + d, v);
+        ss += v * v;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) tot += sh[w];
+    const float inv = rsqrtf(tot / (float)D + eps);
+    for (int64_t d = threadIdx.x; d < D; d += 256) {
+        const float g = gamma ? load_as_float(gamma, gamma_type, d) : 1.f;
+        store_from_float(y, type, base + d, load_as_float(ysum, type, base + d) * inv * g);
+    }
+}
+
+cudaError_t launch_add_rmsnorm(const void *x, const void *res, const void *gamma, int type, int gamma_type, void *ysum, void *y,
+                               int64_t rows, int64_t D, float eps, cudaStream_t s) {
+    if (rows <= 0 || D <= 0) return cudaSuccess;
+    if (rows > 0x7fffffffLL) return cudaErrorInvalidValue;
+    add_rmsnorm_kernel<<<(unsigned)rows, 256, 0, s>>>(x, res, gamma, type, gamma_type, ysum, y, D, eps);
+    count_launch();
+    return cudaGetLastError();
+}
+
 cudaError_t launch_fill_i64(int64_t *out, int64_t value, cudaStream_t s) {
     fill_i64_kernel<<<1, 1, 0, s>>>(out, value);
     count_launch();

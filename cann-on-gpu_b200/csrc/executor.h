@@ -17,6 +17,7 @@ enum PlanOp : int {
     PLAN_DYNQUANT,    // per-token dynamic int8 quantiser
     PLAN_SWIGLUQUANT, // SwiGLU fused with the per-token quantiser
     PLAN_MXQUANT,     // block-wise power-of-two-scale int8 quantiser
+    PLAN_ADDRMSNORM,  // residual add + RMS norm (tail of the all-reduce matmuls)
 };
 
 // Kernel families a plan can select.
@@ -46,5 +47,6 @@ struct aclOpExecutor {
     int split_k = 1;
     uint64_t ws_bytes = 0;
     aclDataType cast_to = ACL_DT_UNDEFINED;
+    double eps = 0.0;            // PLAN_ADDRMSNORM
     std::vector<int64_t> shape;  // PLAN_WEIGHT_SIZE
 };

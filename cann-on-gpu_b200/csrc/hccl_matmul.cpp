@@ -77,9 +77,102 @@ aclnnStatus run(void *ws, uint64_t wsz, aclOpExecutor *e, aclrtStream s) {
     return st;
 }
 
+// ---- W8A8 matmul -> all-reduce -> residual add + RMS norm (cuda/src/ops/matmul.cu:1222-1233,1344-1370).
+// The matmul's partial output lives at the start of the caller's workspace (the reference allocates it
+// with cudaMallocAsync inside phase 2); the norm is not linear, so the sum over ranks happens on that
+// partial before it.
+constexpr uint64_t NORM_MAGIC = 0x423230304e524d53ull;
+
+struct NormExecutor {
+    uint64_t magic = NORM_MAGIC;
+    const aclTensor *x = nullptr, *weight = nullptr, *scale = nullptr, *residual = nullptr, *gamma = nullptr;
+    aclTensor *y = nullptr, *residual_sum = nullptr;
+    double eps = 0.0;
+    HcclComm comm = nullptr;
+    uint64_t tmp_bytes = 0;
+};
+
+// A tensor of y's shape and type over `data`.
+aclTensor *like(const aclTensor *y, void *data, uint64_t *count, aclDataType *dt) {
+    int64_t *dims = nullptr;
+    uint64_t nd = 0;
+    if (aclGetViewShape(y, &dims, &nd) != ACLNN_SUCCESS || aclGetDataType(y, dt) != ACLNN_SUCCESS) return nullptr;
+    *count = 1;
+    for (uint64_t i = 0; i < nd; ++i) *count *= (uint64_t)dims[i];
+    return aclCreateTensor(dims, nd, *dt, nullptr, 0, ACL_FORMAT_ND, dims, nd, data);
+}
+
+aclnnStatus norm_plan(const aclTensor *x, const aclTensor *weight, const aclTensor *scale, const aclTensor *residual,
+                      const aclTensor *gamma, double eps, HcclComm comm, aclTensor *y, aclTensor *residual_sum, uint64_t *ws,
+                      aclOpExecutor **ex) {
+    if (!x || !weight || !scale || !residual || !y || !residual_sum || !ws || !ex) return ACLNN_ERR_PARAM_NULLPTR;
+    void *ydata = nullptr;
+    if (aclGetRawTensorAddr(y, &ydata) != ACLNN_SUCCESS || !ydata) return ACLNN_ERR_PARAM_NULLPTR;
+    uint64_t count = 0;
+    aclDataType dt = ACL_DT_UNDEFINED;
+    aclTensor *probe = like(y, ydata, &count, &dt);   // same shape and type as the partial output
+    if (!probe) return ACLNN_ERR_PARAM_INVALID;
+    HcclDataType ht;
+    aclnnStatus st = hccl_type(dt, &ht) ? ACLNN_SUCCESS : ACLNN_ERR_PARAM_INVALID;
+    uint64_t inner_ws = 0, norm_ws = 0;
+    aclOpExecutor *inner = nullptr;
+    if (st == ACLNN_SUCCESS) st = aclnnQuantMatmulGetWorkspaceSize(x, weight, scale, probe, &inner_ws, &inner);
+    if (st == ACLNN_SUCCESS) {
+        aclDestroyAclOpExecutor(inner);
+        st = aclnnAddRmsNormGetWorkspaceSize(probe, residual, gamma, eps, y, residual_sum, &norm_ws, &inner);
+        if (st == ACLNN_SUCCESS) aclDestroyAclOpExecutor(inner);
+    }
+    aclDestroyTensor(probe);
+    if (st != ACLNN_SUCCESS) return st;
+    auto *n = new NormExecutor();
+    n->x = x; n->weight = weight; n->scale = scale; n->residual = residual; n->gamma = gamma; n->y = y; n->residual_sum = residual_sum;
+    n->eps = eps; n->comm = comm;
+    n->tmp_bytes = (count * (dt == ACL_FLOAT ? 4 : 2) + 255) / 256 * 256;
+    *ws = n->tmp_bytes + inner_ws;
+    *ex = reinterpret_cast<aclOpExecutor *>(n);
+    return ACLNN_SUCCESS;
+}
+
+aclnnStatus norm_run(void *ws, uint64_t wsz, aclOpExecutor *e, aclrtStream s) {
+    auto *np = reinterpret_cast<NormExecutor *>(e);
+    if (!np || np->magic != NORM_MAGIC) return ACLNN_ERR_PARAM_INVALID;
+    const NormExecutor n = *np;
+    np->magic = 0;
+    delete np;
+    if (!ws || wsz < n.tmp_bytes) return ACLNN_ERR_PARAM_INVALID;
+    uint64_t count = 0;
+    aclDataType dt = ACL_DT_UNDEFINED;
+    aclTensor *tmp = like(n.y, ws, &count, &dt);
+    if (!tmp) return ACLNN_ERR_PARAM_INVALID;
+    uint64_t need = 0;
+    aclOpExecutor *inner = nullptr;
+    aclnnStatus st = aclnnQuantMatmulGetWorkspaceSize(n.x, n.weight, n.scale, tmp, &need, &inner);
+    if (st == ACLNN_SUCCESS) {
+        if (need > wsz - n.tmp_bytes) { aclDestroyAclOpExecutor(inner); st = ACLNN_ERR_PARAM_INVALID; }
+        else st = aclnnQuantMatmul(static_cast<char *>(ws) + n.tmp_bytes, wsz - n.tmp_bytes, inner, s);
+    }
+    HcclDataType ht;
+    if (st == ACLNN_SUCCESS && n.comm && count > 0) {
+        if (!hccl_type(dt, &ht) || HcclAllReduce(ws, ws, count, ht, HCCL_REDUCE_SUM, n.comm, s) != HCCL_SUCCESS) st = ACLNN_ERR_RUNTIME_ERROR;
+    }
+    if (st == ACLNN_SUCCESS) {
+        st = aclnnAddRmsNormGetWorkspaceSize(tmp, n.residual, n.gamma, n.eps, n.y, n.residual_sum, &need, &inner);
+        if (st == ACLNN_SUCCESS) st = aclnnAddRmsNorm(nullptr, 0, inner, s);
+    }
+    aclDestroyTensor(tmp);
+    return st;
+}
+
 }  // namespace
 
 extern "C" {
+
+aclnnStatus aclnnQuantMatmulAllReduceAddRmsNormGetWorkspaceSize(const aclTensor *x, const aclTensor *weight, const aclTensor *scale,
+        const aclTensor *residual, const aclTensor *gamma, double eps, HcclComm comm, aclTensor *y, aclTensor *residualSum,
+        uint64_t *ws, aclOpExecutor **ex) {
+    return norm_plan(x, weight, scale, residual, gamma, eps, comm, y, residualSum, ws, ex);
+}
+aclnnStatus aclnnQuantMatmulAllReduceAddRmsNorm(void *ws, uint64_t wsz, aclOpExecutor *e, aclrtStream s) { return norm_run(ws, wsz, e, s); }
 
 #define QMM_ALLREDUCE(NAME)                                                                                          \
     aclnnStatus NAME##GetWorkspaceSize(const aclTensor *x, const aclTensor *weight, const aclTensor *scale, HcclComm comm, \

@@ -104,6 +104,9 @@ uint64_t launch_count();
 // Small element-wise helpers.
 cudaError_t launch_int4_pack(const int8_t *in, uint8_t *out, int64_t n_out, cudaStream_t s);
 cudaError_t launch_fill_i64(int64_t *out, int64_t value, cudaStream_t s);
+// residual add + RMS norm over rows of D elements (x, residual, outputs of one 16/32-bit float type).
+cudaError_t launch_add_rmsnorm(const void *x, const void *res, const void *gamma, int type, int gamma_type, void *ysum, void *y,
+                               int64_t rows, int64_t D, float eps, cudaStream_t s);
 cudaError_t launch_qparam(const float *scale, const float *offset, int64_t *out, int64_t n, cudaStream_t s);
 // Per-token dynamic int8 quantiser (dynquant.cu).
 cudaError_t launch_dynamic_quant(const void *x, int x_type, int8_t *q, float *scale_out, int64_t rows, int64_t D, cudaStream_t s);

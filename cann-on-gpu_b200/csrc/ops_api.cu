@@ -281,6 +281,11 @@ aclnnStatus run_simple(aclOpExecutor *e, aclrtStream stream) {
             err = launch_dynamic_mx_quant(data_of(e->a), elem_type(e->a->dtype), (int8_t *)const_cast<void *>(data_of(e->out)),
                                           (float *)const_cast<void *>(data_of(e->out2)), e->m, e->k, s);
             break;
+        case PLAN_ADDRMSNORM:
+            err = launch_add_rmsnorm(data_of(e->a), data_of(e->b), e->scale ? data_of(e->scale) : nullptr, elem_type(e->a->dtype),
+                                     e->scale ? elem_type(e->scale->dtype) : ET_NONE, const_cast<void *>(data_of(e->out2)),
+                                     const_cast<void *>(data_of(e->out)), e->m, e->k, (float)e->eps, s);
+            break;
         case PLAN_QPARAM:
             err = launch_qparam((const float *)data_of(e->a), e->b ? (const float *)data_of(e->b) : nullptr,
                                 (int64_t *)const_cast<void *>(data_of(e->out)), e->n, s);
@@ -502,6 +507,31 @@ DYNQUANT_ALIAS(aclnnDynamicQuant)
 DYNQUANT_ALIAS(aclnnDynamicQuantV2)
 DYNQUANT_ALIAS(aclnnDynamicQuantV3)
 DYNQUANT_ALIAS(aclnnDynamicQuantV4)
+
+// Residual add + RMS norm (cuda/src/ops/norm_ext.cu:233-247): y = rmsnorm(x + residual) * gamma,
+// residualSum = x + residual.  Needed here as the tail of the all-reduce matmuls.
+aclnnStatus aclnnAddRmsNormGetWorkspaceSize(const aclTensor *x, const aclTensor *residual, const aclTensor *gamma, double eps,
+                                            aclTensor *y, aclTensor *residualSum, uint64_t *ws, aclOpExecutor **ex) {
+    if (!x || !residual || !y || !residualSum || !ws || !ex) return ACLNN_ERR_PARAM_NULLPTR;
+    if (x->numel() > 0 && (!x->data || !residual->data || !y->data || !residualSum->data || (gamma && !gamma->data)))
+        return ACLNN_ERR_PARAM_NULLPTR;
+    if (x->dtype != ACL_FLOAT && x->dtype != ACL_FLOAT16 && x->dtype != ACL_BF16) return ACLNN_ERR_PARAM_INVALID;
+    if (residual->dtype != x->dtype || y->dtype != x->dtype || residualSum->dtype != x->dtype) return ACLNN_ERR_PARAM_INVALID;
+    if (x->viewDims.empty() || x->viewDims != residual->viewDims || x->viewDims != y->viewDims || x->viewDims != residualSum->viewDims)
+        return ACLNN_ERR_PARAM_INVALID;
+    const int64_t D = x->viewDims.back();
+    if (gamma) {
+        if (gamma->dtype != ACL_FLOAT && gamma->dtype != ACL_FLOAT16 && gamma->dtype != ACL_BF16) return ACLNN_ERR_PARAM_INVALID;
+        if (gamma->numel() != D || !dense(gamma)) return ACLNN_ERR_PARAM_INVALID;
+    }
+    if (!dense(x) || !dense(residual) || !dense(y) || !dense(residualSum)) return ACLNN_ERR_PARAM_INVALID;
+    auto *e = new aclOpExecutor();
+    e->op = PLAN_ADDRMSNORM; e->a = x; e->b = residual; e->scale = gamma; e->out = y; e->out2 = residualSum;
+    e->m = D > 0 ? x->numel() / D : 0; e->k = D; e->eps = eps;
+    *ws = 0; *ex = e;
+    return ACLNN_SUCCESS;
+}
+RUN_SIMPLE(aclnnAddRmsNorm)
 
 // SwiGLU fused with the per-token quantiser: x [..., 2 D] -> int8 [..., D] + fp32 scale per row
 // (cuda/src/ops/glu_ext.cu:118-141; V2 is the reference's alias).

@@ -173,6 +173,15 @@ B200_ACLNN_DYNQUANT(aclnnDynamicQuantV4)
 B200_ACLNN_DYNQUANT(aclnnSwiGluQuant)
 B200_ACLNN_DYNQUANT(aclnnSwiGluQuantV2)
 
+/* Residual add + RMS norm, the tail of the all-reduce matmuls: v = x + residual in fp32,
+ * residualSum = T(v), y = T(float(residualSum) * rsqrt(mean(v^2) + eps) * gamma) per row of the last
+ * dimension; x, residual, y, residualSum of one type (ACL_FLOAT, ACL_FLOAT16, ACL_BF16), gamma [D] or NULL.
+ * residualSum may alias residual and y may alias x.
+ * Replaces aclnnAddRmsNorm of aclnn_ops.h (cuda/src/ops/norm_ext.cu:123-139,233-247). */
+ACL_FUNC_VISIBILITY aclnnStatus aclnnAddRmsNormGetWorkspaceSize(const aclTensor *x, const aclTensor *residual,
+    const aclTensor *gamma, double eps, aclTensor *y, aclTensor *residualSum, uint64_t *workspaceSize, aclOpExecutor **executor);
+B200_ACLNN_RUN(aclnnAddRmsNorm)
+
 /* Block-wise dynamic int8 quantiser with power-of-two scales: per block of blockSize consecutive elements
  * scaleOut = 2^ceil(log2(max|x| / 127)) (1 for a zero block; ACL_FLOAT, one per block),
  * out = clamp(rint(x * (1 / scaleOut)), -128, 127) as ACL_INT8.

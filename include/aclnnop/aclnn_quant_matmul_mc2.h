@@ -32,6 +32,18 @@ ACL_FUNC_VISIBILITY aclnnStatus aclnnWeightQuantMatmulAllReduceGetWorkspaceSize(
 ACL_FUNC_VISIBILITY aclnnStatus aclnnWeightQuantMatmulAllReduce(void *workspace, uint64_t workspaceSize,
     aclOpExecutor *executor, aclrtStream stream);
 
+/* W8A8 matmul -> all-reduce (sum over the ranks of comm; none when comm == NULL) -> residual add + RMS
+ * norm: y = rmsnorm(allreduce(x @ weight * scale) + residual) * gamma, residualSum = the sum before the
+ * norm.  y, residual, residualSum [M,N] of one 16/32-bit float type; gamma [N] or NULL.  The partial
+ * output is kept in the workspace (phase 1 reports its size).  The reference's Inplace form (y over the
+ * int8 x) has no consistent types and is not exported.
+ * Same names and argument order as the reference's cuda/src/ops/matmul.cu:1344-1370 (its
+ * composition: matmul.cu:1222-1233). */
+ACL_FUNC_VISIBILITY aclnnStatus aclnnQuantMatmulAllReduceAddRmsNormGetWorkspaceSize(const aclTensor *x, const aclTensor *weight,
+    const aclTensor *scale, const aclTensor *residual, const aclTensor *gamma, double eps, HcclComm comm, aclTensor *y,
+    aclTensor *residualSum, uint64_t *workspaceSize, aclOpExecutor **executor);
+ACL_FUNC_VISIBILITY aclnnStatus aclnnQuantMatmulAllReduceAddRmsNorm(void *workspace, uint64_t workspaceSize,
+    aclOpExecutor *executor, aclrtStream stream);
 #ifdef __cplusplus
 }
 #endif

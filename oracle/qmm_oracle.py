@@ -301,6 +301,26 @@ def dynamic_quant(x):
     return np.clip(q, -128, 127).astype(np.int8), scale
 
 
+def add_rmsnorm(x, residual, gamma, eps, kind):
+    """Residual add + RMS norm, restating cuda/src/ops/norm_ext.cu:123-139: v = x + residual in fp32,
+    residual_sum = T(v), y = T(float(residual_sum) * rsqrt(mean(v^2) + eps) * gamma) per row, with T the
+    tensors' type (`kind`: "f32", "f16" or "bf16").  The mean is summed in float64 here (the device sums
+    in fp32 in its own order), so y agrees to rounding, not bitwise.  Returns (y, residual_sum) as float32
+    arrays holding T-representable values."""
+    def rt(v):
+        if kind == "f32":
+            return v.astype(np.float32)
+        if kind == "f16":
+            return v.astype(np.float16).astype(np.float32)
+        return bf16_bits_to_f32(f32_to_bf16_bits(v.astype(np.float32)))
+    v = (np.asarray(x, np.float32) + np.asarray(residual, np.float32)).astype(np.float32)
+    ysum = rt(v)
+    ms = (v.astype(np.float64) ** 2).mean(axis=-1, keepdims=True)
+    inv = (1.0 / np.sqrt(ms + eps)).astype(np.float32)
+    g = np.float32(1) if gamma is None else np.asarray(gamma, np.float32)
+    return rt((ysum * inv).astype(np.float32) * g), ysum
+
+
 def swiglu_quant(x):
     """SwiGLU fused with the per-token int8 quantiser, restating cuda/src/ops/glu_ext.cu:89-103 in fp32:
     x [..., 2D] = [a | b]; g = a / (1 + exp(-a)) * b; scale = max|g| / 127 per row (1 for a zero row);

@@ -91,6 +91,21 @@ def main():
     ref = oracle.qmm_epilogue_fast(acc, f32(q["scale"])).astype(np.float64)
     assert_close(to_np(out), ref, f"rank {rank}: aclnnQuantMatmulAllReduce")
 
+    # the same K-split followed by residual add + RMS norm: the sum over ranks must happen on the
+    # partial outputs, before the norm
+    g = torch.Generator().manual_seed(81)
+    res = torch.randn((16, 128), generator=g).to(torch.float16)
+    gamma = (torch.rand(128, generator=g) + 0.5).to(torch.float16)
+    y = torch.empty((16, 128), dtype=torch.float16, device=dev)
+    rs = torch.empty((16, 128), dtype=torch.float16, device=dev)
+    with pkg.use_library(hccl_path):
+        pkg.call("aclnnQuantMatmulAllReduceAddRmsNorm", pkg.AclTensor(qx), pkg.AclTensor(qw), pkg.AclTensor(q["scale"].to(dev)),
+                 pkg.AclTensor(res.to(dev)), pkg.AclTensor(gamma.to(dev)), ctypes.c_double(1e-5), comm, pkg.AclTensor(y), pkg.AclTensor(rs))
+    torch.cuda.synchronize()
+    want_y, want_sum = oracle.add_rmsnorm(out.float().cpu().numpy(), f32(res), f32(gamma), 1e-5, "f16")
+    assert np.array_equal(rs.float().cpu().numpy(), want_sum), f"rank {rank}: residual sum of the norm matmul"
+    assert_close(to_np(y), want_y.astype(np.float64), f"rank {rank}: aclnnQuantMatmulAllReduceAddRmsNorm")
+
     assert hccl.HcclCommDestroy(comm) == 0
     with open(os.path.join(tmp, f"ok.{rank}"), "w") as f:
         f.write("ok")

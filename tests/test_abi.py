@@ -92,8 +92,9 @@ def test_hccl_library_exports_allreduce_matmuls(pkg):
     except OSError as e:
         pytest.skip(f"libhccl.so not loadable here: {e}")
     hdr = open(os.path.join(INC, "aclnnop", "aclnn_quant_matmul_mc2.h")).read()
-    names = set(re.findall(r"^B200_ACLNN_QMM_ALLREDUCE\((\w+)\)", hdr, re.M)) | {"aclnnWeightQuantMatmulAllReduce"}
-    assert len(names) == 5
+    names = set(re.findall(r"^B200_ACLNN_QMM_ALLREDUCE\((\w+)\)", hdr, re.M)) | {"aclnnWeightQuantMatmulAllReduce",
+                                                                                     "aclnnQuantMatmulAllReduceAddRmsNorm"}
+    assert len(names) == 6
     for n in names:
         assert hasattr(lib, n) and hasattr(lib, n + "GetWorkspaceSize"), n
 

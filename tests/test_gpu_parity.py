@@ -585,6 +585,50 @@ def test_allreduce_matmuls_without_communicator(pkg, oracle, workloads, dev):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+def test_add_rmsnorm_and_the_allreduce_norm_matmul(pkg, oracle, workloads, dev, dtype):
+    """aclnnAddRmsNorm (cuda/src/ops/norm_ext.cu:123-139,233-247) against the oracle, with and without
+    gamma and with residualSum written over residual; then aclnnQuantMatmulAllReduceAddRmsNorm
+    with comm == NULL (the reference's one-rank case, cuda/src/ops/matmul.cu:1222-1233,
+    1344-1370): matmul -> residual add -> RMS norm, the partial output kept in the workspace."""
+    kind = {torch.float32: "f32", torch.float16: "f16", torch.bfloat16: "bf16"}[dtype]
+    g = torch.Generator().manual_seed(6600)
+    rows, D, eps = 37, 1000, 1e-5
+    x, res = torch.randn((rows, D), generator=g).to(dtype), torch.randn((rows, D), generator=g).to(dtype)
+    gamma = (torch.rand(D, generator=g) + 0.5).to(dtype)
+    for gm in (gamma, None):
+        want_y, want_sum = oracle.add_rmsnorm(f32(x), f32(res), None if gm is None else f32(gm), eps, kind)
+        y = torch.empty_like(x, device=dev)
+        rs = res.to(dev).clone()   # residualSum aliases residual
+        pkg.call("aclnnAddRmsNorm", pkg.AclTensor(x.to(dev)), pkg.AclTensor(rs), pkg.AclTensor(gm.to(dev)) if gm is not None else None,
+                 ctypes.c_double(eps), pkg.AclTensor(y), pkg.AclTensor(rs))
+        torch.cuda.synchronize()
+        assert np.array_equal(rs.float().cpu().numpy(), want_sum)
+        assert_close(to_np(y), want_y.astype(np.float64), f"aclnnAddRmsNorm {dtype} gamma={gm is not None}")
+    bad = torch.empty((rows, D + 1), dtype=dtype, device=dev)
+    assert pkg.call("aclnnAddRmsNorm", pkg.AclTensor(x.to(dev)), pkg.AclTensor(res.to(dev)), None, ctypes.c_double(eps),
+                    pkg.AclTensor(bad), pkg.AclTensor(res.to(dev)), return_status=True) == 161002
+
+    hccl = os.path.join(os.path.dirname(pkg.LIB_PATH), "libhccl.so")
+    if not os.path.exists(hccl) or dtype == torch.float32:
+        return
+    M, K, N = 24, 128, 128
+    d = workloads.w8a8(M=M, K=K, N=N, seed=6601, with_pertoken=False, with_bias=False, scale_dtype=torch.float16)
+    acc = oracle.qmm_acc_fast(d["x"].numpy(), d["w"].numpy(), M, K, N)
+    mm = torch.from_numpy(oracle.qmm_epilogue_fast(acc, f32(d["scale"]))).to(dtype)   # the partial output, rounded to its type
+    res2, gamma2 = torch.randn((M, N), generator=g).to(dtype), (torch.rand(N, generator=g) + 0.5).to(dtype)
+    want_y, want_sum = oracle.add_rmsnorm(f32(mm), f32(res2), f32(gamma2), eps, kind)
+    tx, tw, tsc = pkg.AclTensor(d["x"].to(dev)), pkg.AclTensor(d["w"].to(dev)), pkg.AclTensor(d["scale"].to(dev))
+    y, rs = torch.empty((M, N), dtype=dtype, device=dev), torch.empty((M, N), dtype=dtype, device=dev)
+    with pkg.use_library(hccl):
+        need = pkg.call("aclnnQuantMatmulAllReduceAddRmsNorm", tx, tw, tsc, pkg.AclTensor(res2.to(dev)), pkg.AclTensor(gamma2.to(dev)),
+                        ctypes.c_double(eps), ctypes.c_void_p(None), pkg.AclTensor(y), pkg.AclTensor(rs))
+        torch.cuda.synchronize()
+    assert need >= M * N * 2
+    assert np.array_equal(rs.float().cpu().numpy(), want_sum)
+    assert_close(to_np(y), want_y.astype(np.float64), f"aclnnQuantMatmulAllReduceAddRmsNorm {dtype}")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("shape", [(1, 1024), (8, 4096), (300, 8192), (5, 100), (3, 7, 520), (2, 16384), (2, 20000)])
 def test_dynamic_quant_bit_exact(pkg, oracle, dev, shape, dtype):
     """Per-token int8 quantiser (cuda/src/ops/quant.cu:37-49,99-111): int8 codes and fp32 scales are
