@@ -494,6 +494,16 @@ MmPlan mm_make_plan(const MatmulArgs &p) {
     pl.total_q = (long long)pl.tiles * pl.qpt;
     const int sms = mm_sm_count();
     pl.P = (int)(pl.total_q < sms ? pl.total_q : sms);
+    // Small problems: with one whole tile per CTA every tile is finished where it was computed and the
+    // finalize kernel (about 3 us at this scale) is not launched.  Worth it when streaming a whole tile
+    // into one SM (about 50 GB/s) costs less than an even share plus that launch.
+    // B200_QMM_WQ_WHOLE_TILES=0|1 overrides.
+    if (pl.tiles <= sms && pl.tiles < pl.P) {
+        const double tile_bytes = (double)p.K * tile_n * (p.b_type == ET_I8 ? 1.0 : 0.5);
+        bool whole = tile_bytes / 50e9 < tile_bytes * pl.tiles / pl.P / 50e9 + 3e-6;
+        if (const char *e = getenv("B200_QMM_WQ_WHOLE_TILES")) whole = atoi(e) != 0;
+        if (whole) pl.P = pl.tiles;
+    }
     pl.slot_bytes = (uint64_t)(pl.tiles + pl.P) * p.M * tile_n * sizeof(float);
     return pl;
 }
