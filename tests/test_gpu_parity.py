@@ -188,6 +188,33 @@ def test_w8a8_tensor_core_tails(pkg, oracle, workloads, dev, shape):
     assert torch.equal(out.cpu(), ref_out)
 
 
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("shape", [(129, 256, 264), (300, 1040, 520), (600, 2048, 8200), (1000, 144, 40000)])
+def test_w8a8_row_tile_kernel_equals_column_kernel(pkg, oracle, workloads, dev, shape, out_dtype):
+    """More than 128 rows run the row-tile dense kernel (rows on the accumulator lanes); with
+    B200_QMM_DENSE_ROWTILE=0 the column-per-lane kernel takes the same call.  Accumulators and outputs
+    must be the same bits for ragged M, N (multiples of 8 only) and K, for more tiles than SMs with a
+    K-split tail, with and without per-token scales and bias; the small shapes also against the oracle."""
+    M, K, N = shape
+    d = workloads.w8a8(M=M, K=K, N=N, seed=47)
+    x, w, sc, pt, bi = (d[k].to(dev) for k in ("x", "w", "scale", "pertoken", "bias"))
+    def run():
+        with forced_path("tc"):
+            r = [pkg.quant_matmul(x, w, None), pkg.quant_matmul(x, w, sc, pt, bi, out_dtype=out_dtype),
+                 pkg.quant_matmul(x, w, sc, None, None, out_dtype=out_dtype)]
+        torch.cuda.synchronize()
+        return r
+    got = run()
+    with env_set("B200_QMM_DENSE_ROWTILE", "0"):
+        want = run()
+    for g_, w_ in zip(got, want):
+        assert torch.equal(g_, w_)
+    if M * K * N <= 300 * 1040 * 520:
+        ref_acc, ref_out = ref_qmm(oracle, d, out_dtype)
+        assert np.array_equal(got[0].cpu().numpy(), ref_acc)
+        assert torch.equal(got[1].cpu(), ref_out)
+
+
 @pytest.mark.parametrize("shape", [(1, 32, 16), (33, 96, 48), (200, 544, 400)])
 @pytest.mark.parametrize("kinds", [(False, True), (True, False)])
 def test_mx_tensor_core_tails(pkg, oracle, workloads, dev, shape, kinds):
