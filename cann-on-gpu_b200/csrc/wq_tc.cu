@@ -81,7 +81,7 @@ struct WqSmem {
     static constexpr int NUM_BARS = 2 * NS + NR + ND + 10;
     static constexpr int MISC_OFF = BAR_OFF + NUM_BARS * 8;
     static constexpr int MERGE_OFF = (MISC_OFF + 16 + 15) / 16 * 16;    // [MT][128] fp32: epilogue set 1 -> set 0
-    static constexpr int TOTAL = MERGE_OFF + (MT == 64 ? 0 : MT * TILE_N * 4) + 1024;
+    static constexpr int TOTAL = MERGE_OFF + (MT >= 64 ? 0 : MT * TILE_N * 4) + 1024;
 };
 
 // Share of CTA c: quanta [c*T/P, (c+1)*T/P).
@@ -184,7 +184,7 @@ wq_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
         for (int s = 0; s < NS; ++s) { mbar_init(bar_sfull(s), 1); mbar_init(bar_sempty(s), 4); }
         for (int r = 0; r < NR; ++r) mbar_init(bar_ready(r), 5);   // 4 converter warps + the activation TMA
         for (int d = 0; d < ND; ++d) mbar_init(bar_done(d), 1);
-        for (int a = 0; a < 4; ++a) mbar_init(bar_acc_empty(a >> 1, a & 1), MT == 64 ? 8 : 4);
+        for (int a = 0; a < 4; ++a) mbar_init(bar_acc_empty(a >> 1, a & 1), MT >= 64 ? 8 : 4);
         for (int a = 0; a < 4; ++a) mbar_init(bar_acc_full(a >> 1, a & 1), 1);
         mbar_init(bar_merge(0), 4);
         mbar_init(bar_merge(1), 4);
@@ -317,11 +317,13 @@ wq_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
             const bool n_ok = n < p.N;
             const int folds = p.grouped ? len : 1;
             const int sb_per_fold = p.grouped ? p.sbq : nsb;
-            // MT = 64: the two sets split the 64 accumulator columns (32 registers each) and both take every
+            // MT >= 64: the two sets split the accumulator columns (MT / 2 registers each) and both take every
             // fold; smaller tiles: the sets split the folds when every fold belongs to one issuer.
-            constexpr bool COLSPLIT = MT == 64;
-            constexpr int CT = COLSPLIT ? 32 : MT;               // accumulator columns per thread
-            const int cb = COLSPLIT ? eset * 32 : 0;             // first of them
+            // (MT = 128 exists in the pre-scaled mode only: one fold per segment, no activation sums.)
+            static_assert(MT <= 64 || PRE, "128-row tiles only with pre-scaled weights");
+            constexpr bool COLSPLIT = MT >= 64;
+            constexpr int CT = COLSPLIT ? MT / 2 : MT;           // accumulator columns per thread
+            const int cb = COLSPLIT ? eset * CT : 0;             // first of them
             const bool single = sb_per_fold == 1;                // every fold has one issuer
             const bool split_sets = single && !COLSPLIT;         // folds alternate between the two sets
             constexpr int XR = (MT + 31) / 32;  // activation sums are shared by all lanes: lane l keeps rows l, l+32
@@ -437,7 +439,7 @@ wq_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
                             float acc = __uint_as_float(v[j]);
                             if (lanes_used == 2) acc += __uint_as_float(v2[j]);
                             if (p.offset) {
-                                const float xv = COLSPLIT ? __shfl_sync(0xffffffffu, xsel, c0 + j)
+                                const float xv = COLSPLIT ? __shfl_sync(0xffffffffu, xsel, (c0 + j) & 31)
                                                           : __shfl_sync(0xffffffffu, xs[(c0 + j) / 32], (c0 + j) % 32);
                                 acc -= of * xv;
                             }
@@ -775,6 +777,18 @@ WqPlan wq_make_plan(const MatmulArgs &p) {
     }
     pl.cv_gsb = pl.grouped ? (int)(p.group / SBK) : 1;
     if (pl.pre && (long long)pl.tiles * pl.num_sb >= (1ll << 31)) pl.pre = false;
+    if (pl.pre && p.M > 64 && (long long)pl.n_tiles * pl.num_sb >= 16LL * sm_count()) {
+        // 128-row tiles: the weights are converted once for up to 128 rows (8192 x 28672 at M = 128: 165 us
+        // with two 64-row tiles, 132 us with one of 128).  Its MMA ring is only two slots deep, which costs
+        // more than it saves when a CTA gets few super-blocks (4096 x 4096: 23.6 -> 26.9 us), hence the
+        // size condition.  B200_QMM_WQ_MT128=0 keeps 64-row tiles.
+        const char *e = getenv("B200_QMM_WQ_MT128");
+        if (!(e && atoi(e) == 0)) {
+            pl.mt = 128;
+            pl.m_tiles = (int)((p.M + pl.mt - 1) / pl.mt);
+            pl.tiles = pl.m_tiles * pl.n_tiles;
+        }
+    }
     if (pl.pre) pl.grouped = 0;
     pl.sbq = pl.grouped ? (int)(p.group / SBK) : 1;
     pl.qpt = pl.num_sb / pl.sbq;
@@ -812,7 +826,9 @@ cudaError_t wq_launch_one(const CUtensorMap &tx, const CUtensorMap &tw, const Wq
 
 template <bool BF16>
 cudaError_t wq_dispatch_pre(int mt, const CUtensorMap &tx, const CUtensorMap &tw, const WqParams &wp, int P, cudaStream_t s) {
-    (void)mt;   // more than 32 rows: 64-row tiles
+    // more than 32 rows: 64-row tiles; more than 64: one 128-row tile (two ring slots of 64 KB), so the
+    // weights are converted once instead of once per 64 rows
+    if (mt == 128) return wq_launch_one<true, BF16, 128, 4, 2, true>(tx, tw, wp, P, s);
     return wq_launch_one<true, BF16, 64, 4, 4, true>(tx, tw, wp, P, s);
 }
 
@@ -890,6 +906,7 @@ cudaError_t launch_wq_tc(const MatmulArgs &p, cudaStream_t s) {
         switch (pl.mt) {
             case 16: wq_finalize_kernel<16><<<blocks, 256, 0, s>>>(wp, pl.P); break;
             case 32: wq_finalize_kernel<32><<<blocks, 256, 0, s>>>(wp, pl.P); break;
+            case 128: wq_finalize_kernel<128><<<blocks, 256, 0, s>>>(wp, pl.P); break;
             default: wq_finalize_kernel<64><<<blocks, 256, 0, s>>>(wp, pl.P); break;
         }
         count_launch();

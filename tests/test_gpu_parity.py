@@ -131,11 +131,12 @@ def test_config1_w4a16_full_size(pkg, oracle, workloads, dev, M):
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("M,K,N,group", [(33, 1024, 512, 128), (64, 2048, 1056, 256), (100, 1024, 4096, 128),
-                                         (128, 4096, 20000 // 32 * 32, 128)])
+                                         (128, 4096, 20000 // 32 * 32, 128), (70, 2048, 20000 // 32 * 32, 256)])
 def test_w4a16_groupwise_mid_m(pkg, oracle, workloads, dev, dtype, M, K, N, group):
     """33..128 rows of group-wise int4: the streaming kernel's converters apply scale and offset
     themselves.  Covers a ragged last column tile (N % 128 = 32), two row tiles, two super-blocks per
-    scale group, and more tiles than SMs (shares cut tiles anywhere)."""
+    scale group, and more tiles than SMs (shares cut tiles anywhere); the two largest cases run one
+    128-row tile per column block, the others 64-row tiles."""
     d = workloads.w4a16(M=M, K=K, N=N, group=group, dtype=dtype, seed=5200 + M)
     assert_close_wq(oracle, to_np(run_wq(pkg, d, dev)), d, f"W4A16 g{group} M={M} K={K} N={N} {dtype}")
     d2 = workloads.w4a16(M=M, K=K, N=N, group=group, dtype=dtype, with_offset=False, with_bias=False, seed=5300 + M)
