@@ -230,6 +230,29 @@ def sweep(pkg, workloads, dev, pk, only=None):
             calls.append(lambda ws, a=args: pkg.call("aclnnWeightQuantBatchMatmulV2Ex", *a, workspace=ws, device=dev))
         return calls
 
+    if only is not None and only.startswith("case:"):
+        # one custom case, e.g. --sweep-only case:w4,128,8192,28672,128  (kind w4 | w8 | i8, M, K, N[, group])
+        kind, m, k, n, *rest = only[5:].split(",")
+        m, k, n = int(m), int(k), int(n)
+        group = int(rest[0]) if rest else 128
+        wb = k * n // 2 if kind == "w4" else k * n
+        ring = max(2, min(32, 300_000_000 // wb + 1))
+        if kind in ("w4", "w8"):
+            gen = workloads.w4a16 if kind == "w4" else workloads.w8a16
+            kw = dict(group=group, with_offset=False, with_bias=False) if kind == "w4" else dict(dtype=torch.bfloat16)
+            sets = [gen(M=m, K=k, N=n, seed=1100 + i, **kw) for i in range(ring)]
+            run_case(f"{kind} M={m} K={k} N={n} group={sets[0]['group']} bf16", wq_calls(sets, kind == "w4", sets[0]["group"]),
+                     2 * m * k * n, wb, 5)
+        else:
+            calls = []
+            for i in range(ring):
+                d = workloads.w8a8(M=m, K=k, N=n, seed=1100 + i)
+                out = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+                args = [pkg.AclTensor(d["x"].to(dev)), pkg.AclTensor(d["w"].to(dev)), pkg.AclTensor(d["scale"].to(dev)), None,
+                        pkg.AclTensor(d["pertoken"].to(dev)), pkg.AclTensor(d["bias"].to(dev)), pkg.AclTensor(out)]
+                calls.append(lambda ws, a=args: pkg.call("aclnnQuantMatmulV4Ex", *a, workspace=ws, device=dev))
+            run_case(f"W8A8 M={m} K={k} N={n} bf16 out", calls, 2 * m * k * n, wb, 5)
+        only = "\0"   # nothing else
     try:
         # config 0: W8A16 M=1 K=1024 N=3072 (3 MB per call: L2-resident and launch-bound)
         if wanted("cfg0 W8A16 per-channel M=1 K=1024 N=3072 fp16"):
@@ -377,7 +400,8 @@ def main():
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--ring", type=int, default=RING)
     ap.add_argument("--no-sweep", action="store_true")
-    ap.add_argument("--sweep-only", default=None, help="run only the sweep cases whose name contains this text, and nothing else")
+    ap.add_argument("--sweep-only", default=None, help="run only the sweep cases whose name contains this text, and nothing else; "
+                         "case:<w4|w8|i8>,M,K,N[,group] times one custom shape instead")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
