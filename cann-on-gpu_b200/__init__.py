@@ -214,13 +214,17 @@ def dynamic_quant(x, name="aclnnDynamicQuant", **kw):
 
 
 
-def swiglu_quant(x, name="aclnnSwiGluQuant", **kw):
-    """x [..., 2D] f32/f16/bf16 -> (int8 [..., D] of silu(x[..., :D]) * x[..., D:], fp32 per-row scales [...])."""
+def swiglu_quant(x, name="aclnnSwiGluQuant", dequant_scale=None, **kw):
+    """x [..., 2D] f32/f16/bf16 -> (int8 [..., D] of silu(x[..., :D]) * x[..., D:], fp32 per-row scales [...]).
+    With the aclnnDequantSwigluQuant names, `dequant_scale` (fp32 per row, or None) multiplies x first."""
     import torch
     D = x.shape[-1] // 2
     q = torch.empty(tuple(x.shape[:-1]) + (D,), dtype=torch.int8, device=x.device)
     scale = torch.empty(x.shape[:-1] if x.dim() > 1 else (1,), dtype=torch.float32, device=x.device)
-    call(name, AclTensor(x), AclTensor(q), AclTensor(scale), **kw)
+    if "Dequant" in name:
+        call(name, AclTensor(x), AclTensor(dequant_scale) if dequant_scale is not None else None, AclTensor(q), AclTensor(scale), **kw)
+    else:
+        call(name, AclTensor(x), AclTensor(q), AclTensor(scale), **kw)
     return q, scale
 
 def dynamic_mx_quant(x, block, name="aclnnDynamicMxQuant", **kw):

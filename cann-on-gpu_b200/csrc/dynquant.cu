@@ -149,7 +149,8 @@ __global__ void __launch_bounds__(DQ_THREADS) mxquant_generic_kernel(const void 
 // ---- SwiGLU fused with the per-token quantiser: the step between the gate/up projection and a W8A8
 // down projection.  Row layout [a (D) | b (D)]; g = a / (1 + exp(-a)) * b in fp32, evaluated with the
 // reference's expression (cuda/src/ops/glu_ext.cu:89-103); scale = max|g| / 127 (1 for an all-zero
-// row), q = clamp(rint(g * (1 / scale)), -127, 127).  The reference computes g twice (maximum, then
+// row), q = clamp(rint(g * (1 / scale)), -127, 127).  With a per-row dequant scale dq (DequantSwigluQuant,
+// cuda/src/ops/norm_ext.cu:1354-1369) a and b are first multiplied by dq[row].  The reference computes g twice (maximum, then
 // quantise); here a row of up to 16384 outputs keeps g in registers: one read of 2 D inputs, one
 // write of D codes.
 __device__ __forceinline__ float swiglu_of(float a, float b) { return a / (1.f + expf(-a)) * b; }
@@ -170,8 +171,9 @@ template <bool BF16> __device__ __forceinline__ void unpack8(const uint4 &v, flo
 // chunks each: the arithmetic per element (expf, an IEEE division) needs the occupancy more than the
 // per-token quantiser does.
 template <bool BF16, int CHUNKS, int THREADS>
-__global__ void __launch_bounds__(THREADS) swigluquant_row_kernel(const uint16_t *x, int8_t *q, float *scale_out, int64_t D) {
+__global__ void __launch_bounds__(THREADS) swigluquant_row_kernel(const uint16_t *x, const float *dq, int8_t *q, float *scale_out, int64_t D) {
     __shared__ float sh[THREADS / 32];
+    const float scl = dq ? __ldg(dq + blockIdx.x) : 1.f;   // optional per-row dequant scale (x * 1 is exact)
     const int64_t ib = (int64_t)blockIdx.x * 2 * D, ob = (int64_t)blockIdx.x * D;
     float g[CHUNKS][8];
     float amax = 0.f;
@@ -188,7 +190,7 @@ __global__ void __launch_bounds__(THREADS) swigluquant_row_kernel(const uint16_t
         unpack8<BF16>(vb, fb);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            g[c][i] = swiglu_of(fa[i], fb[i]);      // 0 beyond the row: silu(0) * 0
+            g[c][i] = swiglu_of(fa[i] * scl, fb[i] * scl);      // 0 beyond the row: silu(0) * 0
             amax = fmaxf(amax, fabsf(g[c][i]));
         }
     }
@@ -208,23 +210,25 @@ __global__ void __launch_bounds__(THREADS) swigluquant_row_kernel(const uint16_t
 }
 
 // Any type, any D: g is evaluated twice, the second read of the row hits L2.
-__global__ void __launch_bounds__(DQ_THREADS) swigluquant_generic_kernel(const void *x, int x_type, int8_t *q, float *scale_out, int64_t D) {
+__global__ void __launch_bounds__(DQ_THREADS) swigluquant_generic_kernel(const void *x, int x_type, const float *dq, int8_t *q, float *scale_out, int64_t D) {
     __shared__ float sh[DQ_THREADS / 32];
+    const float scl = dq ? __ldg(dq + blockIdx.x) : 1.f;
     const int64_t ib = (int64_t)blockIdx.x * 2 * D, ob = (int64_t)blockIdx.x * D;
     float amax = 0.f;
     for (int64_t d = threadIdx.x; d < D; d += DQ_THREADS)
-        amax = fmaxf(amax, fabsf(swiglu_of(load_as_float(x, x_type, ib + d), load_as_float(x, x_type, ib + D + d))));
+        amax = fmaxf(amax, fabsf(swiglu_of(load_as_float(x, x_type, ib + d) * scl, load_as_float(x, x_type, ib + D + d) * scl)));
     const float m = block_max(amax, sh);
     const float scale = m > 0.f ? m / 127.f : 1.f;
     if (threadIdx.x == 0) scale_out[blockIdx.x] = scale;
     const float inv = 1.f / scale;
     for (int64_t d = threadIdx.x; d < D; d += DQ_THREADS)
-        q[ob + d] = quant_i8_sym(swiglu_of(load_as_float(x, x_type, ib + d), load_as_float(x, x_type, ib + D + d)) * inv);
+        q[ob + d] = quant_i8_sym(swiglu_of(load_as_float(x, x_type, ib + d) * scl, load_as_float(x, x_type, ib + D + d) * scl) * inv);
 }
 
 }  // namespace
 
-cudaError_t launch_swiglu_quant(const void *x, int x_type, int8_t *q, float *scale_out, int64_t rows, int64_t D, cudaStream_t s) {
+cudaError_t launch_swiglu_quant(const void *x, int x_type, const float *dq, int8_t *q, float *scale_out, int64_t rows, int64_t D,
+                                cudaStream_t s) {
     if (rows <= 0 || D <= 0) return cudaSuccess;
     if (rows > 0x7fffffffLL) return cudaErrorInvalidValue;
     const bool vec = (x_type == ET_BF16 || x_type == ET_F16) && D % DQ_VEC == 0 && D <= (int64_t)512 * DQ_VEC * 4 &&
@@ -233,9 +237,9 @@ cudaError_t launch_swiglu_quant(const void *x, int x_type, int8_t *q, float *sca
     const uint16_t *x16 = static_cast<const uint16_t *>(x);
     const int64_t per = (int64_t)DQ_THREADS * DQ_VEC;
     const bool bf = x_type == ET_BF16;
-#define SGQ(C, T) do { if (bf) swigluquant_row_kernel<true, C, T><<<g, T, 0, s>>>(x16, q, scale_out, D); \
-                       else swigluquant_row_kernel<false, C, T><<<g, T, 0, s>>>(x16, q, scale_out, D); } while (0)
-    if (!vec) swigluquant_generic_kernel<<<g, DQ_THREADS, 0, s>>>(x, x_type, q, scale_out, D);
+#define SGQ(C, T) do { if (bf) swigluquant_row_kernel<true, C, T><<<g, T, 0, s>>>(x16, dq, q, scale_out, D); \
+                       else swigluquant_row_kernel<false, C, T><<<g, T, 0, s>>>(x16, dq, q, scale_out, D); } while (0)
+    if (!vec) swigluquant_generic_kernel<<<g, DQ_THREADS, 0, s>>>(x, x_type, dq, q, scale_out, D);
     else if (D <= per) SGQ(1, 256);
     else if (D <= per * 2) SGQ(2, 256);
     else if (D <= per * 4) SGQ(2, 512);

@@ -111,7 +111,8 @@ cudaError_t launch_qparam(const float *scale, const float *offset, int64_t *out,
 // Per-token dynamic int8 quantiser (dynquant.cu).
 cudaError_t launch_dynamic_quant(const void *x, int x_type, int8_t *q, float *scale_out, int64_t rows, int64_t D, cudaStream_t s);
 // SwiGLU + per-token int8: x [rows][2 D] -> q [rows][D], scale_out [rows].
-cudaError_t launch_swiglu_quant(const void *x, int x_type, int8_t *q, float *scale_out, int64_t rows, int64_t D, cudaStream_t s);
+cudaError_t launch_swiglu_quant(const void *x, int x_type, const float *dq, int8_t *q, float *scale_out, int64_t rows, int64_t D,
+                                cudaStream_t s);
 cudaError_t launch_dynamic_mx_quant(const void *x, int x_type, int8_t *q, float *scale_out, int64_t nblocks, int64_t blk, cudaStream_t s);
 cudaError_t launch_cast(const void *in, int in_type, void *out, int out_type, int64_t n, cudaStream_t s);
 

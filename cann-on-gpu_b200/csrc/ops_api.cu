@@ -274,7 +274,8 @@ aclnnStatus run_simple(aclOpExecutor *e, aclrtStream stream) {
                                        (float *)const_cast<void *>(data_of(e->out2)), e->m, e->k, s);
             break;
         case PLAN_SWIGLUQUANT:
-            err = launch_swiglu_quant(data_of(e->a), elem_type(e->a->dtype), (int8_t *)const_cast<void *>(data_of(e->out)),
+            err = launch_swiglu_quant(data_of(e->a), elem_type(e->a->dtype), e->pertoken ? (const float *)data_of(e->pertoken) : nullptr,
+                                      (int8_t *)const_cast<void *>(data_of(e->out)),
                                       (float *)const_cast<void *>(data_of(e->out2)), e->m, e->k, s);
             break;
         case PLAN_MXQUANT:
@@ -535,7 +536,8 @@ RUN_SIMPLE(aclnnAddRmsNorm)
 
 // SwiGLU fused with the per-token quantiser: x [..., 2 D] -> int8 [..., D] + fp32 scale per row
 // (cuda/src/ops/glu_ext.cu:118-141; V2 is the reference's alias).
-static aclnnStatus swigluquant_plan(const aclTensor *x, aclTensor *out, aclTensor *scaleOut, uint64_t *ws, aclOpExecutor **ex) {
+static aclnnStatus swigluquant_plan(const aclTensor *x, const aclTensor *dq, aclTensor *out, aclTensor *scaleOut, uint64_t *ws,
+                                    aclOpExecutor **ex) {
     if (!x || !out || !scaleOut || !ws || !ex) return ACLNN_ERR_PARAM_NULLPTR;
     if (x->viewDims.empty() || out->viewDims.size() != x->viewDims.size()) return ACLNN_ERR_PARAM_INVALID;
     if (x->numel() > 0 && (!x->data || !out->data || !scaleOut->data)) return ACLNN_ERR_PARAM_NULLPTR;
@@ -548,17 +550,31 @@ static aclnnStatus swigluquant_plan(const aclTensor *x, aclTensor *out, aclTenso
     if (!dense(x) || !dense(out) || !dense(scaleOut)) return ACLNN_ERR_PARAM_INVALID;
     const int64_t rows = D > 0 ? out->numel() / D : 0;
     if (scaleOut->numel() != rows) return ACLNN_ERR_PARAM_INVALID;
+    if (dq) {   // optional per-row dequant scale
+        if (x->numel() > 0 && !dq->data) return ACLNN_ERR_PARAM_NULLPTR;
+        if (dq->dtype != ACL_FLOAT || dq->numel() != rows || !dense(dq)) return ACLNN_ERR_PARAM_INVALID;
+    }
     auto *e = new aclOpExecutor();
-    e->op = PLAN_SWIGLUQUANT; e->a = x; e->out = out; e->out2 = scaleOut; e->m = rows; e->k = D;
+    e->op = PLAN_SWIGLUQUANT; e->a = x; e->pertoken = dq; e->out = out; e->out2 = scaleOut; e->m = rows; e->k = D;
     *ws = 0; *ex = e;
     return ACLNN_SUCCESS;
 }
 #define SWIGLUQUANT_ALIAS(NAME)                                                                                      \
     aclnnStatus NAME##GetWorkspaceSize(const aclTensor *x, aclTensor *out, aclTensor *scaleOut, uint64_t *ws,        \
-                                       aclOpExecutor **ex) { return swigluquant_plan(x, out, scaleOut, ws, ex); }   \
+                                       aclOpExecutor **ex) { return swigluquant_plan(x, nullptr, out, scaleOut, ws, ex); } \
     RUN_SIMPLE(NAME)
 SWIGLUQUANT_ALIAS(aclnnSwiGluQuant)
 SWIGLUQUANT_ALIAS(aclnnSwiGluQuantV2)
+// The same behind a per-row dequant scale: a and b are multiplied by dequantScale[row] first
+// (cuda/src/ops/norm_ext.cu:1354-1369,1416-1432; V2 is the reference's alias).
+#define DEQSWIGLUQUANT_ALIAS(NAME)                                                                                   \
+    aclnnStatus NAME##GetWorkspaceSize(const aclTensor *x, const aclTensor *dequantScale, aclTensor *out, aclTensor *scaleOut, \
+                                       uint64_t *ws, aclOpExecutor **ex) {                                           \
+        return swigluquant_plan(x, dequantScale, out, scaleOut, ws, ex);                                             \
+    }                                                                                                                \
+    RUN_SIMPLE(NAME)
+DEQSWIGLUQUANT_ALIAS(aclnnDequantSwigluQuant)
+DEQSWIGLUQUANT_ALIAS(aclnnDequantSwigluQuantV2)
 
 // Block-wise int8 quantiser with power-of-two scales (cuda/src/ops/quant.cu:380-389,496-514).
 static aclnnStatus mxquant_plan(const aclTensor *x, int64_t blockSize, aclTensor *out, aclTensor *scaleOut, uint64_t *ws,

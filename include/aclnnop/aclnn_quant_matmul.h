@@ -172,6 +172,15 @@ B200_ACLNN_DYNQUANT(aclnnDynamicQuantV4)
  * Replaces aclnn_ops.h:1275-1278 (cuda/src/ops/glu_ext.cu:89-103,118-141). */
 B200_ACLNN_DYNQUANT(aclnnSwiGluQuant)
 B200_ACLNN_DYNQUANT(aclnnSwiGluQuantV2)
+/* The same behind an optional per-row dequant scale (ACL_FLOAT, one per row, or NULL): a and b are
+ * multiplied by dequantScale[row] before the SwiGLU.
+ * Replaces aclnnDequantSwigluQuant[V2] of aclnn_ops.h (cuda/src/ops/norm_ext.cu:1354-1369,1416-1432). */
+#define B200_ACLNN_DEQSWIGLUQUANT(NAME) \
+    ACL_FUNC_VISIBILITY aclnnStatus NAME##GetWorkspaceSize(const aclTensor *x, const aclTensor *dequantScale, aclTensor *out, \
+        aclTensor *scaleOut, uint64_t *workspaceSize, aclOpExecutor **executor); \
+    B200_ACLNN_RUN(NAME)
+B200_ACLNN_DEQSWIGLUQUANT(aclnnDequantSwigluQuant)
+B200_ACLNN_DEQSWIGLUQUANT(aclnnDequantSwigluQuantV2)
 
 /* Residual add + RMS norm, the tail of the all-reduce matmuls: v = x + residual in fp32,
  * residualSum = T(v), y = T(float(residualSum) * rsqrt(mean(v^2) + eps) * gamma) per row of the last

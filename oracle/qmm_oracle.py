@@ -321,13 +321,15 @@ def add_rmsnorm(x, residual, gamma, eps, kind):
     return rt((ysum * inv).astype(np.float32) * g), ysum
 
 
-def swiglu_quant(x):
+def swiglu_quant(x, dequant_scale=None):
     """SwiGLU fused with the per-token int8 quantiser, restating cuda/src/ops/glu_ext.cu:89-103 in fp32:
     x [..., 2D] = [a | b]; g = a / (1 + exp(-a)) * b; scale = max|g| / 127 per row (1 for a zero row);
     q = clamp(rint(g * (1 / scale)), -127, 127).  exp here is numpy's float32 exp, the device uses
     CUDA's expf (both within a couple of ulp of the true value), so a code may differ by one where
     g / scale falls next to a rounding boundary.  Returns (int8 [..., D], float32 [...])."""
     x = np.ascontiguousarray(x, dtype=np.float32)
+    if dequant_scale is not None:   # DequantSwigluQuant (cuda/src/ops/norm_ext.cu:1354-1369): x * dq[row] first
+        x = (x * np.asarray(dequant_scale, np.float32)[..., None]).astype(np.float32)
     D = x.shape[-1] // 2
     a, b = x[..., :D], x[..., D:]
     with np.errstate(over="ignore"):

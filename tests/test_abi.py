@@ -14,7 +14,7 @@ def declared_symbols():
     names = set()
     qm = open(os.path.join(INC, "aclnnop", "aclnn_quant_matmul.h")).read()
     body = qm.split('extern "C"', 1)[1]
-    for m in re.finditer(r"^B200_ACLNN_(?:WQBMM|QMM|MX|QMM_GROUPED|QMM_COMM|QPARAM|DYNQUANT|MXQUANT)\((\w+)\)", body, re.M):
+    for m in re.finditer(r"^B200_ACLNN_(?:WQBMM|QMM|MX|QMM_GROUPED|QMM_COMM|QPARAM|DYNQUANT|DEQSWIGLUQUANT|MXQUANT)\((\w+)\)", body, re.M):
         names.update({m.group(1), m.group(1) + "GetWorkspaceSize"})
     for m in re.finditer(r"^B200_ACLNN_RUN\((\w+)\)", body, re.M):
         names.add(m.group(1))

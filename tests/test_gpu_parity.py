@@ -720,6 +720,31 @@ def test_swiglu_quant(pkg, oracle, dev, shape, dtype):
         assert (q.reshape(-1, D)[0] == 0).all() and sc.reshape(-1)[0] == 1
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_dequant_swiglu_quant(pkg, oracle, dev, dtype):
+    """aclnnDequantSwigluQuant[V2] (cuda/src/ops/norm_ext.cu:1354-1369,1416-1432): a per-row dequant scale
+    in front of the SwiGLU quantiser; without the scale it is the plain SwiGLU quantiser, bit for bit."""
+    g = torch.Generator().manual_seed(6450)
+    x = (torch.rand((33, 2 * 1536), generator=g) * 40 - 20).to(dtype)
+    dq = (torch.rand(33, generator=g) * 0.2 + 0.01).float()
+    want_q, want_s = oracle.swiglu_quant(x.float().numpy(), dq.numpy())
+    for name in ("aclnnDequantSwigluQuant", "aclnnDequantSwigluQuantV2"):
+        q, sc = pkg.swiglu_quant(x.to(dev), name=name, dequant_scale=dq.to(dev))
+        torch.cuda.synchronize()
+        q, sc = q.cpu().numpy(), sc.cpu().numpy()
+        assert np.allclose(sc, want_s, rtol=2e-6, atol=0), name
+        diff = np.abs(q.astype(int) - want_q.astype(int))
+        assert diff.max() <= 1 and (diff != 0).mean() < 1e-3, (name, diff.max(), (diff != 0).mean())
+    q0, s0 = pkg.swiglu_quant(x.to(dev), name="aclnnDequantSwigluQuant", dequant_scale=None)
+    q1, s1 = pkg.swiglu_quant(x.to(dev))
+    torch.cuda.synchronize()
+    assert torch.equal(q0, q1) and torch.equal(s0, s1)
+    bad = torch.ones(32, dtype=torch.float32, device=dev)
+    qb, sb = torch.empty((33, 1536), dtype=torch.int8, device=dev), torch.empty(33, dtype=torch.float32, device=dev)
+    assert pkg.call("aclnnDequantSwigluQuant", pkg.AclTensor(x.to(dev)), pkg.AclTensor(bad), pkg.AclTensor(qb), pkg.AclTensor(sb),
+                    return_status=True) == 161002
+
+
 def test_swiglu_quant_feeds_the_w8a8_matmul(pkg, oracle, workloads, dev):
     """gate/up output -> SwiGluQuant -> aclnnQuantMatmulV4 with the scales as pertokenScale: the matmul's
     result is bit-exact for the codes and scales the quantiser produced."""
