@@ -182,17 +182,31 @@ __global__ void __launch_bounds__(256) expand_mx_fast_kernel(const uint8_t *src,
 #pragma unroll
         for (int i = 0; i < 8; ++i) sc[i] = e8m0_to_float((sw[i >> 2] >> (8 * (i & 3))) & 0xFFu);
     }
+    // all loads of the thread first (the stores below would otherwise order them), then the conversions
+    uint2 rawv[4];
+    uint32_t srow[4];
+#pragma unroll
+    for (int rr = 0; rr < 4; ++rr) {
+        const int r = r0 + wid + 8 * rr;
+        rawv[rr] = make_uint2(0u, 0u);
+        srow[rr] = 127u;
+        if (r < rows) {
+            if constexpr (ELEM == 0) rawv[rr].x = __ldg(reinterpret_cast<const uint32_t *>(src + ((size_t)r * cols + c0) / 2));
+            else rawv[rr] = __ldg(reinterpret_cast<const uint2 *>(src + (size_t)r * cols + c0));
+            if constexpr (ALONG_COLS) srow[rr] = __ldg(scales + (size_t)r * (cols / 32) + c0 / 32);
+        }
+    }
 #pragma unroll
     for (int rr = 0; rr < 4; ++rr) {
         const int r = r0 + wid + 8 * rr;
         if (r >= rows) break;
         float v[8];
         if constexpr (ELEM == 0) {
-            const uint32_t word = __ldg(reinterpret_cast<const uint32_t *>(src + ((size_t)r * cols + c0) / 2));
+            const uint32_t word = rawv[rr].x;
 #pragma unroll
             for (int i = 0; i < 8; ++i) v[i] = e2m1_to_float((word >> (4 * i)) & 0xFu);
         } else {
-            const uint2 raw = __ldg(reinterpret_cast<const uint2 *>(src + (size_t)r * cols + c0));
+            const uint2 raw = rawv[rr];
             const uint32_t words[2] = {raw.x, raw.y};
 #pragma unroll
             for (int i = 0; i < 4; ++i) {   // two fp8 at a time through the hardware conversion
@@ -204,7 +218,7 @@ __global__ void __launch_bounds__(256) expand_mx_fast_kernel(const uint8_t *src,
             }
         }
         if constexpr (ALONG_COLS) {
-            const float s1 = e8m0_to_float(__ldg(scales + (size_t)r * (cols / 32) + c0 / 32));
+            const float s1 = e8m0_to_float(srow[rr]);
 #pragma unroll
             for (int i = 0; i < 8; ++i) v[i] *= s1;
         } else {
