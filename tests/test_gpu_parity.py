@@ -881,6 +881,43 @@ def test_capture_replay_of_the_two_phase_call(pkg, oracle, workloads, dev):
     assert lib.aclmdlRIDestroy(model) == 0
 
 
+def test_seeded_random_shapes_default_path_against_generic_kernel(pkg, workloads, dev):
+    """Seeded random shapes through whatever kernel the library picks (decode kernel with its whole-tile
+    and share-aligned schedules, streaming kernel in both modes and tile heights, expansion + dense,
+    row-tile dense) against the bounds-checked generic kernel on the same device: W8A8 bit for bit,
+    weight-only within the output bounds (the two sum in different orders; above 32 rows of group-wise
+    int4, and above 128 rows, the fast paths round the weights once, hence the wider mean bound)."""
+    rng = np.random.default_rng(20240607)
+    for case in range(36):
+        kind = ("w4g", "w4c", "w8c", "i8")[case % 4]
+        M = int(rng.choice([1, 3, 8, 13, 16, 17, 31, 40, 64, 77, 128, 130, 200, 333]))
+        K = int(rng.integers(1, 17)) * 128 * (2 if kind == "w4g" else 1)
+        N = int(rng.integers(1, 40)) * 32 * int(rng.choice([1, 1, 1, 9]))
+        if kind == "i8":
+            d = workloads.w8a8(M=M, K=K, N=N, seed=9000 + case)
+            args = [d[k].to(dev) for k in ("x", "w", "scale", "pertoken", "bias")]
+            got = pkg.quant_matmul(*args, out_dtype=torch.bfloat16)
+            with forced_path("generic"):
+                want = pkg.quant_matmul(*args, out_dtype=torch.bfloat16)
+            torch.cuda.synchronize()
+            assert torch.equal(got, want), (case, kind, M, K, N)
+            continue
+        dtype = torch.bfloat16 if case % 8 < 4 else torch.float16
+        if kind == "w4g":
+            d = workloads.w4a16(M=M, K=K, N=N, group=int(rng.choice([128, 256])), dtype=dtype, seed=9000 + case,
+                                with_offset=bool(case & 1), with_bias=bool(case & 2))
+        elif kind == "w4c":
+            d = workloads.w4a16(M=M, K=K, N=N, dtype=dtype, per_channel=True, seed=9000 + case, with_bias=bool(case & 2))
+        else:
+            d = workloads.w8a16(M=M, K=K, N=N, dtype=dtype, with_offset=bool(case & 1), seed=9000 + case)
+        got = run_wq(pkg, d, dev)
+        with forced_path("generic"):
+            want = run_wq(pkg, d, dev)
+        rounded = M > 128 or (M > 32 and kind == "w4g")
+        assert_close(to_np(got), to_np(want).astype(np.float64), f"case {case} {kind} M={M} K={K} N={N} {dtype}",
+                     mean_rel=4e-3 if rounded else 2e-3)
+
+
 def test_zz_no_bounded_wait_gave_up(pkg, dev):
     """Every spin inside the tensor-core kernels is bounded and records a code when it gives up;
     after the whole suite the device status word must still be 0."""
