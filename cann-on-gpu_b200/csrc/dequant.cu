@@ -9,6 +9,8 @@
 //   * Weight-only matmuls with many rows (prefill): wf = (w - offset) * scale rounded once to the
 //     activation type, as the reference does (matmul.cu:733-747,790-795), but without its per-call
 //     transposes.  With few rows the fused stream-K kernel (wq_tc.cu) is used instead.
+#include <cstdlib>
+
 #include "device_utils.cuh"
 
 namespace qmm {
@@ -26,7 +28,7 @@ template <bool BF16> __device__ __forceinline__ uint32_t pack2(float a, float b)
 
 // Weight-only: out[k][n] = T((w[k][n] - off[g][n]) * scale[g][n]), g = k / group.  One thread expands
 // 16 consecutive columns of one row (8 B of int4 or 16 B of int8) and writes 32 B.
-template <bool Q4, bool BF16>
+template <bool Q4, bool BF16, bool OUT_BF16 = BF16>
 __global__ void expand_wq_kernel(const uint8_t *w, const void *scale, const void *offset, int sc_type, uint16_t *out, int K, int N,
                                  int group) {
     const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -57,8 +59,8 @@ __global__ void expand_wq_kernel(const uint8_t *w, const void *scale, const void
         v[i] = (v[i] - o) * s;
     }
     uint4 o0, o1;
-    o0.x = pack2<BF16>(v[0], v[1]);   o0.y = pack2<BF16>(v[2], v[3]);   o0.z = pack2<BF16>(v[4], v[5]);   o0.w = pack2<BF16>(v[6], v[7]);
-    o1.x = pack2<BF16>(v[8], v[9]);   o1.y = pack2<BF16>(v[10], v[11]); o1.z = pack2<BF16>(v[12], v[13]); o1.w = pack2<BF16>(v[14], v[15]);
+    o0.x = pack2<OUT_BF16>(v[0], v[1]);   o0.y = pack2<OUT_BF16>(v[2], v[3]);   o0.z = pack2<OUT_BF16>(v[4], v[5]);   o0.w = pack2<OUT_BF16>(v[6], v[7]);
+    o1.x = pack2<OUT_BF16>(v[8], v[9]);   o1.y = pack2<OUT_BF16>(v[10], v[11]); o1.z = pack2<OUT_BF16>(v[12], v[13]); o1.w = pack2<OUT_BF16>(v[14], v[15]);
     uint4 *dst = reinterpret_cast<uint4 *>(out + (size_t)k * N + n0);
     dst[0] = o0;
     dst[1] = o1;
@@ -70,7 +72,7 @@ __global__ void expand_wq_kernel(const uint8_t *w, const void *scale, const void
 // become floats through the 2^23 mantissa trick instead of conversions.  Same fp32 expression per
 // element as above, so the same bits.  Needs 16-bit scales of the output type, N % 8 == 0 and a
 // group size that is a multiple of 32 (or per-channel scales).
-template <bool Q4, bool BF16, int RPT>   // RPT rows per thread: a block covers 8 * RPT rows of one scale group
+template <bool Q4, bool BF16, int RPT, bool OUT_BF16 = BF16>   // RPT rows per thread: a block covers 8 * RPT rows of one scale group
 __global__ void __launch_bounds__(256) expand_wq_fast_kernel(const uint8_t *w, const uint16_t *scale, const uint16_t *offset,
                                                              uint16_t *out, int K, int N, int group) {
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
@@ -119,8 +121,56 @@ __global__ void __launch_bounds__(256) expand_wq_fast_kernel(const uint8_t *w, c
         uint4 o;
         uint32_t *op = reinterpret_cast<uint32_t *>(&o);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) op[i] = pack2<BF16>((v[2 * i] - of[2 * i]) * sc[2 * i], (v[2 * i + 1] - of[2 * i + 1]) * sc[2 * i + 1]);
+        for (int i = 0; i < 4; ++i) op[i] = pack2<OUT_BF16>((v[2 * i] - of[2 * i]) * sc[2 * i], (v[2 * i + 1] - of[2 * i + 1]) * sc[2 * i + 1]);
         *reinterpret_cast<uint4 *>(out + (size_t)k * N + n0) = o;
+    }
+}
+
+// bf16 activations -> fp16 with one power-of-two scale per row: xh[m][k] = half(x[m][k] * 2^-e_m),
+// rowscale[m] = 2^e_m, e_m chosen so that the row's largest magnitude lands in [2^14, 2^15).  A bf16
+// value has 8 significant bits and fp16 holds 11, so the conversion is exact for every element within
+// 2^-29 of the row's maximum (smaller ones fall into fp16's subnormals and lose low bits; their share
+// of any dot product is below fp32 resolution).  Lets a bf16 problem run on the fp16 tensor-core path,
+// where the dequantised weights keep 11 significant bits instead of bf16's 8.  One CTA per row.
+__global__ void __launch_bounds__(256) rows_bf16_to_scaled_f16_kernel(const uint16_t *x, uint16_t *xh, float *rowscale, int K) {
+    const size_t row = blockIdx.x;
+    const uint16_t *xr = x + row * K;
+    uint16_t *hr = xh + row * K;
+    __shared__ float red[8];
+    float amax = 0.f;
+    // K % 8 == 0 and 16-byte aligned rows on this path
+    for (int k = threadIdx.x * 8; k < K; k += 256 * 8) {
+        const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(xr + k));
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            amax = fmaxf(amax, fabsf(__uint_as_float(w[i] << 16)));
+            amax = fmaxf(amax, fabsf(__uint_as_float(w[i] & 0xFFFF0000u)));
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    amax = red[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) amax = fmaxf(amax, red[i]);
+    // fmaxf drops NaNs; an infinite or zero row keeps scale 1 (inf and NaN convert to themselves)
+    int e = 0;
+    if (amax > 0.f && amax < __int_as_float(0x7f800000)) {
+        e = (int)((__float_as_uint(amax) >> 23) & 0xFF) - 127 - 14;
+        e = e < -100 ? -100 : e;
+    }
+    const float down = __uint_as_float((uint32_t)(127 - e) << 23), up = __uint_as_float((uint32_t)(127 + e) << 23);
+    if (threadIdx.x == 0) rowscale[row] = up;
+    for (int k = threadIdx.x * 8; k < K; k += 256 * 8) {
+        const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(xr + k));
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+        uint4 o;
+        uint32_t *op = reinterpret_cast<uint32_t *>(&o);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) op[i] = pack2<false>(__uint_as_float(w[i] << 16) * down, __uint_as_float(w[i] & 0xFFFF0000u) * down);
+        *reinterpret_cast<uint4 *>(hr + k) = o;
     }
 }
 
@@ -249,16 +299,40 @@ bool launch_expand_mx_fast(const uint8_t *src, int elem_type, const uint8_t *sca
 inline uint64_t up256(uint64_t x) { return (x + 255) / 256 * 256; }
 bool is_mx(const MatmulArgs &p) { return p.a_scale && p.b_scale; }
 
+// Weight-only matmuls with bf16 activations run their tensor-core product in fp16: the activations are
+// converted with a power-of-two scale per row (exact, see rows_bf16_to_scaled_f16_kernel), the weights
+// are expanded to fp16 -- (q - offset) * scale of a 4- or 8-bit integer and a bf16 scale then keeps 11
+// significant bits (exact without an offset for int4) instead of being rounded to bf16's 8 -- and the
+// epilogue multiplies the row scale back in fp32.  Against the exact product the mean error of the
+// bf16 output drops from 2.1e-3 (bf16 weights) to 1.4e-3 (its own rounding alone).
+// B200_QMM_WQ_BF16_VIA_F16=0 keeps bf16 weights.
+bool via_f16(const MatmulArgs &p) {
+    if (is_mx(p) || p.a_type != ET_BF16) return false;
+    const char *e = getenv("B200_QMM_WQ_BF16_VIA_F16");
+    return !(e && atoi(e) == 0);
+}
+
 // The dense problem that remains once the operands are expanded.
-MatmulArgs dense_args(const MatmulArgs &p, void *a16, void *b16) {
+MatmulArgs dense_args(const MatmulArgs &p, void *a16, void *b16, const float *rowscale = nullptr) {
     MatmulArgs d;
     d.a = a16; d.b = b16; d.out = p.out;
-    d.a_type = d.b_type = is_mx(p) ? (int)ET_BF16 : p.a_type;
+    d.a_type = d.b_type = is_mx(p) ? (int)ET_BF16 : (via_f16(p) ? (int)ET_F16 : p.a_type);
     d.out_type = p.out_type;
     d.bias = p.bias; d.bias_type = p.bias_type;
+    d.pertoken = rowscale;
     d.epilogue = EPI_PLAIN;
     d.M = p.M; d.N = p.N; d.K = p.K; d.group = p.K;
     return d;
+}
+
+struct ExpandLayout { uint64_t a_bytes, rs_bytes, b_bytes; };
+ExpandLayout expand_layout(const MatmulArgs &p) {
+    ExpandLayout l{};
+    const bool a_copy = is_mx(p) || via_f16(p);
+    l.a_bytes = a_copy ? up256((uint64_t)p.M * p.K * 2) : 0;
+    l.rs_bytes = via_f16(p) ? up256((uint64_t)p.M * sizeof(float)) : 0;
+    l.b_bytes = up256((uint64_t)p.K * p.N * 2);
+    return l;
 }
 
 }  // namespace
@@ -266,12 +340,9 @@ MatmulArgs dense_args(const MatmulArgs &p, void *a16, void *b16) {
 bool expand_supported(const MatmulArgs &p) {
     if (p.epilogue != EPI_PLAIN || p.batch != 1 || p.b_transposed || p.accumulate || p.M < 1) return false;
     if (p.K % 32 != 0 || p.N % 16 != 0) return false;
-    auto aligned16 = [](const void *q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
-    if (!aligned16(p.a) || !aligned16(p.b)) return false;
     if (is_mx(p)) {
         auto ok = [](int t) { return t == ET_E4M3 || t == ET_E5M2 || t == ET_E2M1; };
         if (!ok(p.a_type) || !ok(p.b_type)) return false;
-        if (!aligned16(p.b_scale)) return false;
     } else {
         if (!p.scale) return false;
         if (p.a_type != ET_F16 && p.a_type != ET_BF16) return false;
@@ -283,17 +354,23 @@ bool expand_supported(const MatmulArgs &p) {
 }
 
 uint64_t expand_workspace_bytes(const MatmulArgs &p) {
-    const uint64_t a_bytes = is_mx(p) ? up256((uint64_t)p.M * p.K * 2) : 0;
-    const uint64_t b_bytes = up256((uint64_t)p.K * p.N * 2);
-    return a_bytes + b_bytes + dense_tc_workspace_bytes(dense_args(p, nullptr, nullptr));
+    const ExpandLayout l = expand_layout(p);
+    return l.a_bytes + l.rs_bytes + l.b_bytes + dense_tc_workspace_bytes(dense_args(p, nullptr, nullptr));
 }
 
 cudaError_t launch_expand(const MatmulArgs &p, cudaStream_t s) {
     if (!p.workspace || p.workspace_bytes < expand_workspace_bytes(p)) return cudaErrorInvalidValue;
+    // refused before anything is launched: operands and output off the 16-byte alignment of the dense kernel
+    auto misaligned16 = [](const void *q) { return (reinterpret_cast<uintptr_t>(q) & 15) != 0; };
+    if (misaligned16(p.a) || misaligned16(p.b) || misaligned16(p.out) || misaligned16(p.workspace) ||
+        (is_mx(p) && misaligned16(p.b_scale)))
+        return cudaErrorMisalignedAddress;
     char *ws = (char *)p.workspace;
-    const uint64_t a_bytes = is_mx(p) ? up256((uint64_t)p.M * p.K * 2) : 0;
-    const uint64_t b_bytes = up256((uint64_t)p.K * p.N * 2);
+    const ExpandLayout l = expand_layout(p);
+    const uint64_t a_bytes = l.a_bytes + l.rs_bytes, b_bytes = l.b_bytes;
     uint16_t *a16 = (uint16_t *)ws, *b16 = (uint16_t *)(ws + a_bytes);
+    float *rowscale = l.rs_bytes ? (float *)(ws + l.a_bytes) : nullptr;
+    const bool f16w = via_f16(p);   // weights expanded to fp16 under bf16 scales
     const int K = (int)p.K, N = (int)p.N, M = (int)p.M;
     if (is_mx(p)) {
         const int64_t ta = (int64_t)M * (K / 16), tb = (int64_t)K * (N / 16);
@@ -311,6 +388,10 @@ cudaError_t launch_expand(const MatmulArgs &p, cudaStream_t s) {
         const bool fast = p.sc_type == p.a_type && N % 8 == 0 && (p.group >= p.K || p.group % 32 == 0) &&
                           (reinterpret_cast<uintptr_t>(p.scale) & 15) == 0 && (reinterpret_cast<uintptr_t>(p.offset) & 15) == 0 &&
                           (reinterpret_cast<uintptr_t>(p.b) & 7) == 0 && (K + 31) / 32 <= 65535;
+        if (f16w) {
+            rows_bf16_to_scaled_f16_kernel<<<(unsigned)M, 256, 0, s>>>((const uint16_t *)p.a, a16, rowscale, K);
+            count_launch();
+        }
         if (fast) {
             const uint16_t *sc16 = (const uint16_t *)p.scale, *of16 = (const uint16_t *)p.offset;
             // 8 rows per thread (64-row blocks) where a block still sits inside one scale group
@@ -319,14 +400,18 @@ cudaError_t launch_expand(const MatmulArgs &p, cudaStream_t s) {
             const int rows = 8 * rpt;
             const dim3 grid((unsigned)((N + 255) / 256), (unsigned)((K + rows - 1) / rows));
             const int grp = p.group >= p.K ? (K + rows - 1) / rows * rows : (int)p.group;   // per-channel: one group over all rows
-#define EXPAND_WQ(Q, B) do { if (rpt == 8) expand_wq_fast_kernel<Q, B, 8><<<grid, 256, 0, s>>>(w, sc16, of16, b16, K, N, grp); \
-                             else expand_wq_fast_kernel<Q, B, 4><<<grid, 256, 0, s>>>(w, sc16, of16, b16, K, N, grp); } while (0)
-            if (q4 && bf) EXPAND_WQ(true, true);
-            else if (q4) EXPAND_WQ(true, false);
-            else if (bf) EXPAND_WQ(false, true);
-            else EXPAND_WQ(false, false);
+#define EXPAND_WQ(Q, B, OB) do { if (rpt == 8) expand_wq_fast_kernel<Q, B, 8, OB><<<grid, 256, 0, s>>>(w, sc16, of16, b16, K, N, grp); \
+                                 else expand_wq_fast_kernel<Q, B, 4, OB><<<grid, 256, 0, s>>>(w, sc16, of16, b16, K, N, grp); } while (0)
+            if (q4 && bf && f16w) EXPAND_WQ(true, true, false);
+            else if (bf && f16w) EXPAND_WQ(false, true, false);
+            else if (q4 && bf) EXPAND_WQ(true, true, true);
+            else if (q4) EXPAND_WQ(true, false, false);
+            else if (bf) EXPAND_WQ(false, true, true);
+            else EXPAND_WQ(false, false, false);
 #undef EXPAND_WQ
-        } else if (q4 && bf) expand_wq_kernel<true, true><<<blocks, 256, 0, s>>>(w, p.scale, p.offset, p.sc_type, b16, K, N, (int)p.group);
+        } else if (q4 && bf && f16w) expand_wq_kernel<true, true, false><<<blocks, 256, 0, s>>>(w, p.scale, p.offset, p.sc_type, b16, K, N, (int)p.group);
+        else if (bf && f16w) expand_wq_kernel<false, true, false><<<blocks, 256, 0, s>>>(w, p.scale, p.offset, p.sc_type, b16, K, N, (int)p.group);
+        else if (q4 && bf) expand_wq_kernel<true, true><<<blocks, 256, 0, s>>>(w, p.scale, p.offset, p.sc_type, b16, K, N, (int)p.group);
         else if (q4) expand_wq_kernel<true, false><<<blocks, 256, 0, s>>>(w, p.scale, p.offset, p.sc_type, b16, K, N, (int)p.group);
         else if (bf) expand_wq_kernel<false, true><<<blocks, 256, 0, s>>>(w, p.scale, p.offset, p.sc_type, b16, K, N, (int)p.group);
         else expand_wq_kernel<false, false><<<blocks, 256, 0, s>>>(w, p.scale, p.offset, p.sc_type, b16, K, N, (int)p.group);
@@ -334,7 +419,7 @@ cudaError_t launch_expand(const MatmulArgs &p, cudaStream_t s) {
     }
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    MatmulArgs d = dense_args(p, is_mx(p) ? (void *)a16 : const_cast<void *>(p.a), b16);
+    MatmulArgs d = dense_args(p, (is_mx(p) || f16w) ? (void *)a16 : const_cast<void *>(p.a), b16, rowscale);
     d.workspace = ws + a_bytes + b_bytes;
     d.workspace_bytes = p.workspace_bytes - a_bytes - b_bytes;
     return launch_dense_tc(d, s);

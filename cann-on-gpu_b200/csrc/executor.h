@@ -18,6 +18,7 @@ enum PlanOp : int {
     PLAN_SWIGLUQUANT, // SwiGLU fused with the per-token quantiser
     PLAN_MXQUANT,     // block-wise power-of-two-scale int8 quantiser
     PLAN_ADDRMSNORM,  // residual add + RMS norm (tail of the all-reduce matmuls)
+    PLAN_WRAPPER,     // plan of a composite operator living in another library (payload + deleter below)
 };
 
 // Kernel families a plan can select.
@@ -49,4 +50,10 @@ struct aclOpExecutor {
     aclDataType cast_to = ACL_DT_UNDEFINED;
     double eps = 0.0;            // PLAN_ADDRMSNORM
     std::vector<int64_t> shape;  // PLAN_WEIGHT_SIZE
+    // PLAN_WRAPPER: state of a composite operator (the all-reduce matmuls of libhccl.so).  The executor
+    // owns it: aclDestroyAclOpExecutor calls payload_free(payload), so a plan abandoned after phase 1
+    // is released correctly, and the plain execute entries refuse such a plan.
+    void *payload = nullptr;
+    void (*payload_free)(void *) = nullptr;
+    ~aclOpExecutor() { if (payload && payload_free) payload_free(payload); }
 };

@@ -267,6 +267,9 @@ cudaError_t launch_gemv(const MatmulArgs &p, cudaStream_t s) {
     gp.partial = split > 1 ? (float *)p.workspace : nullptr;
     if (split > 1 && p.workspace_bytes < gemv_workspace_bytes(p)) return cudaErrorInvalidValue;
     if (gp.slice > MAX_SLICE_ROWS) return cudaErrorInvalidValue;
+    // The kernel reads the packed weights with 16-byte loads (8-byte ones for 3..4 rows): a weight
+    // pointer off that boundary would fault on the device, so it is refused here instead.
+    if (reinterpret_cast<uintptr_t>(p.b) & (p.M <= 2 ? 15 : 7)) return cudaErrorMisalignedAddress;
 
     cudaError_t e;
     const bool w4 = p.b_type == ET_I4;
@@ -308,6 +311,8 @@ size_t noalloc_scratch_bytes() { return NOALLOC_SCRATCH_FLOATS * sizeof(float); 
 // only a handle for the runtime, not a device pointer, so the address is looked up once per device
 // (with that device current) and cached.
 static cudaError_t noalloc_scratch_ptr(float **out) {
+    // Filled without a lock: two threads making the first call on a device may both look the address
+    // up; they store the same value, so the race is harmless.
     static float *cached[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);

@@ -12,16 +12,20 @@
 
 namespace {
 
-constexpr uint64_t WRAP_MAGIC = 0x4232303048434c41ull;
-
-// What phase 2 needs: the local operator's executor and what to all-reduce afterwards.
+// What phase 2 needs: the local operator's executor and what to all-reduce afterwards.  It rides in a
+// wrapper plan of libascendcl.so, which owns it: destroying the plan (a caller that gives up after
+// phase 1) ends up in free_allreduce.
 struct AllReduceExecutor {
-    uint64_t magic = WRAP_MAGIC;
     aclOpExecutor *inner = nullptr;
     HcclComm comm = nullptr;
     const aclTensor *out = nullptr;
     bool weight_only = false;
 };
+void free_allreduce(void *p) {
+    auto *w = static_cast<AllReduceExecutor *>(p);
+    if (w->inner) aclDestroyAclOpExecutor(w->inner);
+    delete w;
+}
 
 bool hccl_type(aclDataType d, HcclDataType *t) {
     switch (d) {
@@ -42,13 +46,16 @@ aclnnStatus wrap(aclnnStatus st, aclOpExecutor *inner, HcclComm comm, const aclT
     }
     auto *w = new AllReduceExecutor();
     w->inner = inner; w->comm = comm; w->out = out; w->weight_only = weight_only;
-    *ex = reinterpret_cast<aclOpExecutor *>(w);
+    *ex = aclnnB200CreateWrapperExecutor(w, free_allreduce);
+    if (!*ex) { free_allreduce(w); return ACLNN_ERR_RUNTIME_ERROR; }
     return ACLNN_SUCCESS;
 }
 
 aclnnStatus run(void *ws, uint64_t wsz, aclOpExecutor *e, aclrtStream s) {
-    auto *w = reinterpret_cast<AllReduceExecutor *>(e);
-    if (!w || w->magic != WRAP_MAGIC) return ACLNN_ERR_PARAM_INVALID;
+    if (!e) return ACLNN_ERR_PARAM_NULLPTR;
+    auto *w = static_cast<AllReduceExecutor *>(aclnnB200WrapperPayload(e, 1));
+    aclDestroyAclOpExecutor(e);   // phase 2 consumes the plan, whatever it was
+    if (!w) return ACLNN_ERR_PARAM_INVALID;
     // read what the all-reduce needs before the local operator runs: the tensors may go away after phase 2
     void *data = nullptr;
     int64_t *dims = nullptr;
@@ -62,7 +69,6 @@ aclnnStatus run(void *ws, uint64_t wsz, aclOpExecutor *e, aclrtStream s) {
     aclOpExecutor *inner = w->inner;
     HcclComm comm = w->comm;
     const bool weight_only = w->weight_only;
-    w->magic = 0;
     delete w;
     if (st != ACLNN_SUCCESS) {
         aclDestroyAclOpExecutor(inner);
@@ -81,16 +87,14 @@ aclnnStatus run(void *ws, uint64_t wsz, aclOpExecutor *e, aclrtStream s) {
 // The matmul's partial output lives at the start of the caller's workspace (the reference allocates it
 // with cudaMallocAsync inside phase 2); the norm is not linear, so the sum over ranks happens on that
 // partial before it.
-constexpr uint64_t NORM_MAGIC = 0x423230304e524d53ull;
-
 struct NormExecutor {
-    uint64_t magic = NORM_MAGIC;
     const aclTensor *x = nullptr, *weight = nullptr, *scale = nullptr, *residual = nullptr, *gamma = nullptr;
     aclTensor *y = nullptr, *residual_sum = nullptr;
     double eps = 0.0;
     HcclComm comm = nullptr;
     uint64_t tmp_bytes = 0;
 };
+void free_norm(void *p) { delete static_cast<NormExecutor *>(p); }
 
 // A tensor of y's shape and type over `data`.
 aclTensor *like(const aclTensor *y, void *data, uint64_t *count, aclDataType *dt) {
@@ -129,15 +133,17 @@ aclnnStatus norm_plan(const aclTensor *x, const aclTensor *weight, const aclTens
     n->eps = eps; n->comm = comm;
     n->tmp_bytes = (count * (dt == ACL_FLOAT ? 4 : 2) + 255) / 256 * 256;
     *ws = n->tmp_bytes + inner_ws;
-    *ex = reinterpret_cast<aclOpExecutor *>(n);
+    *ex = aclnnB200CreateWrapperExecutor(n, free_norm);
+    if (!*ex) { delete n; return ACLNN_ERR_RUNTIME_ERROR; }
     return ACLNN_SUCCESS;
 }
 
 aclnnStatus norm_run(void *ws, uint64_t wsz, aclOpExecutor *e, aclrtStream s) {
-    auto *np = reinterpret_cast<NormExecutor *>(e);
-    if (!np || np->magic != NORM_MAGIC) return ACLNN_ERR_PARAM_INVALID;
+    if (!e) return ACLNN_ERR_PARAM_NULLPTR;
+    auto *np = static_cast<NormExecutor *>(aclnnB200WrapperPayload(e, 1));
+    aclDestroyAclOpExecutor(e);
+    if (!np) return ACLNN_ERR_PARAM_INVALID;
     const NormExecutor n = *np;
-    np->magic = 0;
     delete np;
     if (!ws || wsz < n.tmp_bytes) return ACLNN_ERR_PARAM_INVALID;
     uint64_t count = 0;

@@ -5,6 +5,7 @@
 // phase 1 is host-only and returns 161001 for null arguments and 161002 for unsupported types or
 // shapes; phase 2 enqueues on the stream, never synchronises or allocates, reports launch errors as
 // 361001 and consumes the executor.
+#include <cstdint>
 #include <cstring>
 #include <new>
 
@@ -89,9 +90,27 @@ MatmulArgs args_of(const aclOpExecutor *e, void *ws, uint64_t ws_bytes) {
     return p;
 }
 
+// MatmulArgs for planning: every tensor that is present gets the same well-aligned stand-in address,
+// so the plan (kernel family, split, workspace bytes) depends on presence, types and shapes only and a
+// caller may hand over the data pointers later (aclSetRawTensorAddr between the phases).  If the real
+// pointers then miss the alignment the planned kernel needs, phase 2 runs the generic kernel instead.
+MatmulArgs plan_args_of(const aclOpExecutor *e) {
+    MatmulArgs p = args_of(e, nullptr, 0);
+    void *const here = reinterpret_cast<void *>(uintptr_t(1) << 20);
+    p.a = p.b = p.out = here;
+    if (e->bias) p.bias = here;
+    switch (e->op) {
+        case PLAN_WQBMM: p.scale = here; p.offset = e->scale2 ? here : nullptr; break;
+        case PLAN_QMM: if (e->scale) { p.scale = here; p.pertoken = e->pertoken ? (const float *)here : nullptr; } break;
+        case PLAN_MX: p.a_scale = p.b_scale = (const uint8_t *)here; break;
+        default: break;
+    }
+    return p;
+}
+
 // Chooses the kernel family for a plan and sizes its workspace.
 void choose_path(aclOpExecutor *e, uint64_t *ws) {
-    MatmulArgs p = args_of(e, nullptr, 0);
+    MatmulArgs p = plan_args_of(e);
     int want = forced_path();
     e->path = PATH_GENERIC; e->split_k = 1; e->ws_bytes = 0;
     const bool tc_ok = tc_supported(p), gemv_ok = gemv_supported(p);
@@ -117,13 +136,18 @@ void choose_path(aclOpExecutor *e, uint64_t *ws) {
 aclnnStatus run_matmul(void *ws, uint64_t ws_bytes, aclOpExecutor *e, aclrtStream stream) {
     if (!e) return ACLNN_ERR_PARAM_NULLPTR;
     aclnnStatus st = ACLNN_SUCCESS;
-    if (e->m == 0 || e->n == 0) {
+    if (e->op != PLAN_WQBMM && e->op != PLAN_QMM && e->op != PLAN_MX) {
+        st = ACLNN_ERR_PARAM_INVALID;   // a plan of another operator (or of a composite one) was handed in
+    } else if (e->m == 0 || e->n == 0) {
         // empty output: nothing to launch
     } else if (e->ws_bytes > 0 && (!ws || ws_bytes < e->ws_bytes)) {
         st = ACLNN_ERR_PARAM_INVALID;  // undersized workspace is rejected before anything is launched
     } else {
         MatmulArgs p = args_of(e, ws, ws_bytes);
-        if (!p.a || !p.b || !p.out) st = ACLNN_ERR_PARAM_NULLPTR;
+        const bool scales_missing = (e->op == PLAN_WQBMM && (!p.scale || (e->scale2 && !p.offset))) ||
+                                    (e->op == PLAN_QMM && e->scale && (!p.scale || (e->pertoken && !p.pertoken))) ||
+                                    (e->op == PLAN_MX && (!p.a_scale || !p.b_scale)) || (e->bias && !p.bias);
+        if (!p.a || !p.b || !p.out || scales_missing) st = ACLNN_ERR_PARAM_NULLPTR;
         else {
             cudaStream_t s = (cudaStream_t)stream;
             cudaError_t err;
@@ -132,6 +156,9 @@ aclnnStatus run_matmul(void *ws, uint64_t ws_bytes, aclOpExecutor *e, aclrtStrea
                 case PATH_TC: err = launch_tc(p, s); break;
                 default: err = launch_generic(p, s); break;
             }
+            // The fast kernels refuse pointers off their load/store alignment before launching anything;
+            // the bounds-checked generic kernel takes any address and needs no workspace.
+            if (err == cudaErrorMisalignedAddress && e->path != PATH_GENERIC) err = launch_generic(p, s);
             if (err != cudaSuccess) {
                 fprintf(stderr, "[b200-qmm] launch failed: %s\n", cudaGetErrorString(err));
                 st = ACLNN_ERR_RUNTIME_ERROR;
@@ -228,7 +255,6 @@ bool is_mx_operand(aclDataType t) { return t == ACL_FLOAT8_E4M3FN || t == ACL_FL
 aclnnStatus mx_plan(const aclTensor *self, const aclTensor *selfScale, const aclTensor *other, const aclTensor *otherScale,
                     aclTensor *out, uint64_t *ws, aclOpExecutor **ex) {
     if (!self || !selfScale || !other || !otherScale || !out || !ws || !ex) return ACLNN_ERR_PARAM_NULLPTR;
-    if (!self->data || !other->data || !selfScale->data || !otherScale->data || !out->data) return ACLNN_ERR_PARAM_NULLPTR;
     if (!is_mx_operand(self->dtype) || !is_mx_operand(other->dtype)) return ACLNN_ERR_PARAM_INVALID;
     if (selfScale->dtype != ACL_FLOAT8_E8M0 || otherScale->dtype != ACL_FLOAT8_E8M0) return ACLNN_ERR_PARAM_INVALID;
     if (!is_float_act(out->dtype)) return ACLNN_ERR_PARAM_INVALID;

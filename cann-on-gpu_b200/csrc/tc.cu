@@ -252,7 +252,8 @@ tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUte
                                 store_from_float(p.out, p.out_type, o, f);
                             }
                         } else {
-                            store_from_float(p.out, p.out_type, o, __uint_as_float(v[j]) + bf);
+                            // optional per-row scale (1 without): fmaf(acc, 1, bias) rounds like acc + bias
+                            store_from_float(p.out, p.out_type, o, fmaf(__uint_as_float(v[j]), pt, bf));
                         }
                     }
                 }
@@ -338,7 +339,7 @@ __device__ __forceinline__ void rt_store_row(uint32_t taddr, const TcParams &p, 
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     if constexpr (INT8) f[j] = ((float)((int)v[8 * g + j] + bi[j]) * sc[j]) * pt;   // pt is 1 without per-token scales
-                    else f[j] = __uint_as_float(v[8 * g + j]) + __int_as_float(bi[j]);
+                    else f[j] = fmaf(__uint_as_float(v[8 * g + j]), pt, __int_as_float(bi[j]));   // pt: optional per-row scale
                 }
                 if constexpr (OUT == RO_F32) {
                     float4 *o = reinterpret_cast<float4 *>(orow + (size_t)c * 4);
@@ -549,6 +550,7 @@ __global__ void tc_finalize_kernel(TcParams p) {
     if (p.epilogue == EPI_PLAIN) {
         float v = 0.f;
         for (int z = 0; z < p.split; ++z) v += ((const float *)p.partial)[z * stride + off];
+        if (p.pertoken) v *= p.pertoken[m];
         if (p.bias) v += load_as_float(p.bias, p.bias_type, n);
         store_from_float(p.out, p.out_type, i, v);
         return;
@@ -596,10 +598,10 @@ TcPlan make_plan(const MatmulArgs &p) {
     while (pl.mt < p.M && pl.mt < 256) pl.mt *= 2;
     pl.tn = TILE_N;
     // Many rows: 128-row x 256-column tiles with the rows on the accumulator lanes (tc_rowtile_kernel),
-    // where the output type and alignment allow its 16-byte stores.  B200_QMM_DENSE_ROWTILE=0 keeps the
-    // column-per-lane kernel.
+    // where the output type allows its 16-byte stores (an output pointer off that alignment is refused at
+    // launch).  B200_QMM_DENSE_ROWTILE=0 keeps the column-per-lane kernel.
     pl.rowtile = false;
-    if (p.M > 128 && p.N % 8 == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0) {
+    if (p.M > 128 && p.N % 8 == 0) {
         const bool out_ok = p.epilogue == EPI_RAW_I32 ? p.out_type == ET_I32
                                                       : (p.out_type == ET_BF16 || p.out_type == ET_F16 || p.out_type == ET_F32);
         const char *e = getenv("B200_QMM_DENSE_ROWTILE");
@@ -697,14 +699,17 @@ cudaError_t dispatch_mt(int mt, const CUtensorMap &tx, const CUtensorMap &tw, co
 // Weight-only matmuls with few rows go to the persistent stream-K kernel with fused dequant
 // (wq_tc.cu); with many rows to the expand-then-dense path (dequant.cu).  B200_QMM_WQ_DENSE_M sets
 // the switch point.
-int wq_dense_threshold() {
-    const char *e = getenv("B200_QMM_WQ_DENSE_M");
-    return e ? atoi(e) : 128;
+int wq_dense_threshold(const MatmulArgs &p) {
+    if (const char *e = getenv("B200_QMM_WQ_DENSE_M")) return atoi(e);
+    // Group-wise int4 under bf16 activations keeps the exact per-group fold in the streaming kernel (its
+    // pre-scaled mode would round the weights to bf16), which falls behind expansion above 64 rows.
+    if (p.a_type == ET_BF16 && p.b_type == ET_I4 && p.group < p.K) return 64;
+    return 128;
 }
 bool is_wq(const MatmulArgs &p) { return p.epilogue == EPI_PLAIN && p.scale && !p.a_scale && !p.b_scale; }
 bool is_mx(const MatmulArgs &p) { return p.epilogue == EPI_PLAIN && p.a_scale && p.b_scale; }
 bool use_stream_wq(const MatmulArgs &p) {
-    return is_wq(p) && wq_tc_supported(p) && (p.M <= wq_dense_threshold() || !expand_supported(p));
+    return is_wq(p) && wq_tc_supported(p) && (p.M <= wq_dense_threshold(p) || !expand_supported(p));
 }
 bool use_expand(const MatmulArgs &p) { return (is_mx(p) || is_wq(p)) && !use_stream_wq(p) && expand_supported(p); }
 // Decode shapes of int4 weights: register-dequant kernel (wq_mma.cu).
@@ -733,6 +738,7 @@ cudaError_t launch_dense_tc(const MatmulArgs &p, cudaStream_t s) {
     const TcPlan pl = make_plan(p);
     if (p.workspace_bytes < pl.partial_bytes) return cudaErrorInvalidValue;
     if ((reinterpret_cast<uintptr_t>(p.a) & 15) || (reinterpret_cast<uintptr_t>(p.b) & 15)) return cudaErrorMisalignedAddress;
+    if (pl.rowtile && (reinterpret_cast<uintptr_t>(p.out) & 15)) return cudaErrorMisalignedAddress;
 
     CUtensorMap tx, tw;
     bool ok;

@@ -107,8 +107,10 @@ def llama70b_shard(M, which, n_shards=1, shard=0, dtype=torch.bfloat16, seed=100
     K, N = (8192, 28672) if which == "gate_up" else (28672, 8192)
     assert N % n_shards == 0 and (N // n_shards) % 2 == 0
     Ns = N // n_shards
-    # x is the same on every rank; the weight shard has its own stream of the generator.
-    d = w4a16(M=M, K=K, N=Ns, group=128, dtype=dtype, seed=seed * 100 + shard, with_offset=False, with_bias=False)
+    # x is the same on every rank; the weight shard has its own stream of the generator and does not
+    # depend on M (the shard is drawn as an M = 1 problem, then given its activations).
+    d = w4a16(M=1, K=K, N=Ns, group=128, dtype=dtype, seed=seed * 100 + shard, with_offset=False, with_bias=False)
+    d["M"] = M
     d["x"] = torch.randn((M, K), generator=_gen(seed)).to(dtype)
     d["N_total"] = N
     return d

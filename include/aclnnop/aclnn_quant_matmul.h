@@ -234,13 +234,26 @@ B200_ACLNN_RUN(aclnnCast)
  *   aclnnWeightQuantBatchMatmulV2Ex; x/scale/offset/bias/out are all of xType (ACL_FLOAT16, ACL_BF16 or
  *   ACL_FLOAT), weightType is ACL_INT8 or ACL_INT4, antiquantGroupSize 0 = per-channel [N] scales.
  * Limits: M <= 4, N a multiple of 32, and split * M * N partial sums must fit the 2 MiB (larger
- * problems return 161002 with a message on stderr).  The first call on each device looks up the
- * array's device address (make that call before any stream capture).  All calls share the array:
- * calls whose kernels could overlap on the GPU must be serialised by the caller. */
+ * problems return 161002 with a message on stderr).  The weight pointer must be 16-byte aligned
+ * (8-byte for M = 3..4): the kernel reads the packed weights with vector loads, and a pointer off that
+ * boundary is refused with 361001 before anything is launched.  The first call on each device looks up
+ * the array's device address, and the first call of each (weightType, M = 1 | 2 | 3..4) form sets that
+ * kernel's attributes: warm up every form you will use once per device before any stream capture.  First
+ * calls from two threads may both look the address up (they store the same value).  All calls share
+ * the array: calls whose kernels could overlap on the GPU must be serialised by the caller. */
 ACL_FUNC_VISIBILITY aclnnStatus aclnnB200WeightQuantMatmulNoAlloc(const void *x, const void *weight,
     const void *antiquantScale, const void *antiquantOffsetOptional, const void *biasOptional, void *out,
     int64_t m, int64_t k, int64_t n, int64_t antiquantGroupSize, aclDataType xType, aclDataType weightType,
     aclrtStream stream);
+
+/* Plans of composite operators that live in another library (the all-reduce matmuls of libhccl.so;
+ * no counterpart in the reference, which keeps such state in process-wide maps, cuda/src/ops/mc2_ext.cu:17).
+ * aclnnB200CreateWrapperExecutor returns a real executor that owns `payload`: aclDestroyAclOpExecutor
+ * calls payload_free(payload), and the plain execute entries refuse such a plan with 161002.
+ * aclnnB200WrapperPayload returns the payload (NULL for any other executor); with release != 0 the
+ * executor gives up ownership of it. */
+ACL_FUNC_VISIBILITY aclOpExecutor *aclnnB200CreateWrapperExecutor(void *payload, void (*payload_free)(void *));
+ACL_FUNC_VISIBILITY void *aclnnB200WrapperPayload(aclOpExecutor *executor, int release);
 
 /* Diagnostics (no counterpart in the reference): number of kernels this library has launched in the
  * calling process so far.  Benchmarks use the difference around a timed region. */

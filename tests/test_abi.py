@@ -21,7 +21,7 @@ def declared_symbols():
     for m in re.finditer(r"aclnnStatus (\w+GetWorkspaceSize)\(", body):
         if "##" not in m.group(0) and m.group(1) != "GetWorkspaceSize":
             names.add(m.group(1))
-    for m in re.finditer(r"^ACL_FUNC_VISIBILITY u?int\d+_t (\w+)\(", body, re.M):
+    for m in re.finditer(r"^ACL_FUNC_VISIBILITY [\w \*]*?(\w+)\(", body, re.M):   # the library's own entry points
         names.add(m.group(1))
     for h in ("acl/acl.h", "aclnn/acl_meta.h"):
         for m in re.finditer(r"^ACL_FUNC_VISIBILITY\s+[\w ]+?\*?\s*\*?(\w+)\(", open(os.path.join(INC, h)).read(), re.M):
@@ -201,3 +201,56 @@ def test_meta_objects_round_trip(pkg):
     assert lib.aclGetViewShape(None, ctypes.byref(dims), ctypes.byref(num)) == 161001
     lib.aclDataTypeSize.restype = ctypes.c_size_t
     assert lib.aclDataTypeSize(pkg.ACL_BF16) == 2 and lib.aclDataTypeSize(pkg.ACL_INT4) == 1
+
+
+def test_abandoned_collective_plan_is_released(pkg):
+    """A caller may give up after phase 1.  The plans of the all-reduce matmuls (libhccl.so) are real
+    executors that own their state, so aclDestroyAclOpExecutor releases them like any other plan, and a
+    plain execute entry refuses them instead of reading them as a matmul plan."""
+    if not os.path.exists(pkg.HCCL_PATH):
+        pytest.skip("libhccl.so not built (nccl.h absent)")
+    try:
+        hccl = ctypes.CDLL(pkg.HCCL_PATH)
+    except OSError as e:
+        pytest.skip(f"libhccl.so not loadable here: {e}")
+    lib = pkg.load()
+    x, w = FakeTensor(pkg, (8, 64), pkg.ACL_INT8), FakeTensor(pkg, (64, 32), pkg.ACL_INT8)
+    sc, out = FakeTensor(pkg, (32,), pkg.ACL_FLOAT16), FakeTensor(pkg, (8, 32), pkg.ACL_FLOAT16)
+    lib.aclnnB200WrapperPayload.restype = ctypes.c_void_p
+    lib.aclnnB200WrapperPayload.argtypes = [ctypes.c_void_p, ctypes.c_int]
+    for _ in range(3):
+        ws, ex = ctypes.c_uint64(0), ctypes.c_void_p(0)
+        st = hccl.aclnnQuantMatmulAllReduceGetWorkspaceSize(ctypes.c_void_p(x.h), ctypes.c_void_p(w.h), ctypes.c_void_p(sc.h), None,
+                                                            ctypes.c_void_p(out.h), ctypes.byref(ws), ctypes.byref(ex))
+        assert st == 0 and ex.value
+        assert lib.aclnnB200WrapperPayload(ex, 0)            # it is a wrapper plan ...
+        assert lib.aclDestroyAclOpExecutor(ex) == 0          # ... and destroying it releases the inner plan too
+    ws, ex = ctypes.c_uint64(0), ctypes.c_void_p(0)
+    assert hccl.aclnnQuantMatmulAllReduceGetWorkspaceSize(ctypes.c_void_p(x.h), ctypes.c_void_p(w.h), ctypes.c_void_p(sc.h), None,
+                                                          ctypes.c_void_p(out.h), ctypes.byref(ws), ctypes.byref(ex)) == 0
+    # handed to a non-collective execute entry: refused (and consumed) before anything is launched
+    assert lib.aclnnQuantMatmul(None, ctypes.c_uint64(0), ex, None) == 161002
+    # an ordinary plan is not a wrapper
+    ws, ex = ctypes.c_uint64(0), ctypes.c_void_p(0)
+    assert lib.aclnnQuantMatmulGetWorkspaceSize(ctypes.c_void_p(x.h), ctypes.c_void_p(w.h), ctypes.c_void_p(sc.h),
+                                                ctypes.c_void_p(out.h), ctypes.byref(ws), ctypes.byref(ex)) == 0
+    assert not lib.aclnnB200WrapperPayload(ex, 0)
+    assert lib.aclDestroyAclOpExecutor(ex) == 0
+
+
+def test_phase1_does_not_depend_on_data_pointers(pkg):
+    """Workspace size and kernel choice come from presence, types and shapes only: the same call with
+    null, odd and aligned data pointers reports the same workspace."""
+    lib = pkg.load()
+    sizes = set()
+    for addr in (0, 0x7F0000000002, 0x7F0000000100):
+        x, w = FakeTensor(pkg, (40, 1024), pkg.ACL_BF16, addr), FakeTensor(pkg, (1024, 512), pkg.ACL_INT4, addr)
+        sc, of = FakeTensor(pkg, (8, 512), pkg.ACL_BF16, addr), FakeTensor(pkg, (8, 512), pkg.ACL_BF16, addr)
+        out = FakeTensor(pkg, (40, 512), pkg.ACL_BF16, addr)
+        ws, ex = ctypes.c_uint64(0), ctypes.c_void_p(0)
+        assert lib.aclnnWeightQuantBatchMatmulV2GetWorkspaceSize(ctypes.c_void_p(x.h), ctypes.c_void_p(w.h), ctypes.c_void_p(sc.h),
+                                                                 ctypes.c_void_p(of.h), ctypes.c_void_p(out.h), ctypes.byref(ws),
+                                                                 ctypes.byref(ex)) == 0
+        sizes.add(ws.value)
+        lib.aclDestroyAclOpExecutor(ex)
+    assert len(sizes) == 1

@@ -35,7 +35,10 @@ def _call(pkg, d, dev, group, int4):
 def test_no_alloc_entry_point_twice_in_a_row(pkg, workloads, dev):
     cases = [workloads.w4a16(M=1, K=4096, N=4096, group=128, seed=7001),            # 8 x 1 x 4096 partial sums
              workloads.w4a16(M=4, K=2048, N=1024, group=128, seed=7002, with_bias=False),
-             workloads.w8a16(M=2, K=1024, N=3072, dtype=torch.float16, seed=7003, with_offset=True)]
+             workloads.w8a16(M=2, K=1024, N=3072, dtype=torch.float16, seed=7003, with_offset=True),
+             workloads.w4a16(M=3, K=1024, N=512, group=128, seed=7005),                 # the 3..4-row form of the kernel
+             workloads.w4a16(M=1, K=128, N=256, group=128, seed=7006),                  # one K slice: no partial sums at all
+             workloads.w8a16(M=2, K=512, N=256, dtype=torch.float32, seed=7007, with_offset=True)]   # fp32 activations
     for d in cases:  # back to back on one stream: each call reuses the array the previous one left dirty
         st, got = _call(pkg, d, dev, d["group"], d["int4"])
         assert st == 0
