@@ -143,15 +143,20 @@ class Runner:
     """Pre-built aclTensor handles for the ring so the timed loop is phase 1 + phase 2 only.  With a
     communicator every call is followed by HcclAllGather of the output shard on the same stream."""
 
-    def __init__(self, pkg, sets, dev, passes=1, gather=None):
+    def __init__(self, pkg, sets, dev, passes=1, gather=None, packed=True):
         self.pkg, self.dev, self.passes, self.gather = pkg, dev, passes, gather
         m, ns = sets[0]["M"], sets[0]["N"]
         self.out = torch.empty((m, ns), dtype=torch.bfloat16, device=dev)
         self.t_out = pkg.AclTensor(self.out)
         self.items = []
         for d in sets:
-            self.items.append((pkg.AclTensor(d["x"]), pkg.AclTensor(d["w"], pkg.ACL_INT4, (K, ns)), pkg.AclTensor(d["scale"]),
-                               None, None, d))
+            if packed:   # the weights in the library's on-device format, re-laid once at load time (aclnnTransMatmulWeight)
+                if "w_nz" not in d:
+                    d["w_nz"] = pkg.pack_weight_nz(d["w"], K, ns)
+                tw = pkg.AclTensor(d["w_nz"], pkg.ACL_INT4, (K, ns), fmt=pkg.ACL_FORMAT_FRACTAL_NZ, storage=(d["w_nz"].numel() * 2,))
+            else:
+                tw = pkg.AclTensor(d["w"], pkg.ACL_INT4, (K, ns))
+            self.items.append((pkg.AclTensor(d["x"]), tw, pkg.AclTensor(d["scale"]), None, None, d))
         self.ws = pkg.Workspace()
         if gather is not None:
             self.hccl, self.comm, world = gather
@@ -666,6 +671,17 @@ def main():
     calls = args.steps * runner.calls_per_step
     value = calls * WEIGHT_BYTES / ms / 1e6  # GB/s of the whole layer (all ranks' column blocks together)
 
+    # the same calls on weights left in the caller's [K,N] layout (no pre-pack)
+    nd_runner = Runner(pkg, sets, dev, passes, packed=False)
+    for _ in range(args.warmup):
+        nd_runner.step()
+    torch.cuda.synchronize()
+    nd_runner.capture()
+    for _ in range(args.warmup):
+        nd_runner.replay()
+    ms_nd = timed(nd_runner.replay, args.steps, world, dev)
+    del nd_runner
+
     # ---- the other measurements of the partition (every N, so that t_1 / (N t_N) can be formed per variant)
     sharded = {"columns_per_rank": ns, "m1_us_per_call": round(ms / calls * 1e3, 3)}
     if world > 1:
@@ -828,6 +844,8 @@ def main():
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 5), "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": WORKLOAD, "M": M, "K": K, "N": N, "group": GROUP, "calls_per_step": runner.calls_per_step,
+                       "weight_format": "int4 pre-packed once at load time by aclnnTransMatmulWeight into the on-device tile format "
+                                        "(ACL_FORMAT_FRACTAL_NZ tensor), resident in HBM; the call is aclnnWeightQuantBatchMatmulV2Ex",
                        "launch": f"one CUDA graph per step ({passes} passes over the ring), replayed",
                        "cache": f"ring of {ring} distinct weight sets per GPU ({ring * (K * ns // 2) >> 20} MiB) larger than 2x L2",
                        "parallelism": (f"N-shard x{world}: rank r owns columns [r*{ns}, (r+1)*{ns}) of the fixed layer, no collective"
@@ -838,6 +856,10 @@ def main():
                          "algorithmic_bytes_per_launch": algo, "us_per_call": round(per_call_ms * 1e3, 3),
                          "traffic_record": rec if world == 1 else "captured on the whole layer (one GPU) only"},
             "tflops": round(calls * 2 * M * K * N / ms / 1e9, 3),
+            "caller_layout": {"value": round(calls * WEIGHT_BYTES / ms_nd / 1e6, 2), "us_per_call": round(ms_nd / calls * 1e3, 3),
+                              "frac": round(algo / (ms_nd / calls) / 1e6 / pk["hbm_gbs"], 4),
+                              "what": "the same calls on weights left in the caller's [K,N] layout (2-D TMA boxes at the row pitch) "
+                                      "instead of the pre-packed on-device format"},
             "sharded": sharded,
         }
         if world == 1 and not args.no_cpu_baseline:

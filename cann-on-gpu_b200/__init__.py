@@ -17,6 +17,7 @@ ACL_FLOAT, ACL_FLOAT16, ACL_INT8, ACL_INT32, ACL_UINT8 = 0, 1, 2, 3, 4
 ACL_INT64, ACL_BF16, ACL_INT4 = 9, 27, 29
 ACL_FLOAT8_E5M2, ACL_FLOAT8_E4M3FN, ACL_FLOAT8_E8M0, ACL_FLOAT4_E2M1 = 35, 36, 37, 40
 ACL_FORMAT_ND = 2
+ACL_FORMAT_FRACTAL_NZ = 29
 
 ACLNN_SUCCESS = 0
 ACLNN_ERR_PARAM_NULLPTR = 161001
@@ -91,13 +92,15 @@ def torch_acl_dtype(t):
 class AclTensor:
     """An aclTensor handle over a torch tensor's storage (kept alive by this object)."""
 
-    def __init__(self, t, dtype=None, shape=None):
+    def __init__(self, t, dtype=None, shape=None, fmt=ACL_FORMAT_ND, storage=None):
         self.t = t
         self.dtype = torch_acl_dtype(t) if dtype is None else dtype
         dims = list(t.shape) if shape is None else list(shape)
         arr = (ctypes.c_int64 * max(1, len(dims)))(*dims)
+        sdims = dims if storage is None else list(storage)
+        sarr = (ctypes.c_int64 * max(1, len(sdims)))(*sdims)
         self.lib = load()
-        self.h = self.lib.aclCreateTensor(arr, len(dims), self.dtype, None, 0, ACL_FORMAT_ND, arr, len(dims),
+        self.h = self.lib.aclCreateTensor(arr, len(dims), self.dtype, None, 0, fmt, sarr, len(sdims),
                                         ctypes.c_void_p(t.data_ptr()))
         if not self.h:
             raise RuntimeError("aclCreateTensor failed")
@@ -161,15 +164,37 @@ def call(name, *args, stream=None, workspace=None, device=None, return_status=Fa
 
 
 # ---------------------------------------------------------------- operator wrappers (device tensors in, device tensor out)
+def pack_weight_nz(w, K, N):
+    """One-time re-layout of packed int4 weights [K,N] (bytes, two per byte) into the tile-packed on-device
+    format: aclnnCalculateMatmulWeightSizeV2 for the size, aclnnTransMatmulWeight into an
+    ACL_FORMAT_FRACTAL_NZ tensor.  Returns the packed buffer (uint8)."""
+    import torch
+    lib = load()
+    shp = (ctypes.c_int64 * 2)(K, N)
+    ia = ctypes.c_void_p(lib.aclCreateIntArray(shp, 2))
+    n_out = torch.zeros(1, dtype=torch.int64, device=w.device)
+    call("aclnnCalculateMatmulWeightSizeV2", ia, ctypes.c_int64(ACL_INT4), AclTensor(n_out), device=w.device)
+    lib.aclDestroyIntArray(ia)
+    elems = int(n_out.item())
+    packed = torch.empty(elems // 2, dtype=torch.uint8, device=w.device)
+    call("aclnnTransMatmulWeight", AclTensor(w, ACL_INT4, (K, N)),
+         AclTensor(packed, ACL_INT4, (K, N), fmt=ACL_FORMAT_FRACTAL_NZ, storage=(elems,)))
+    return packed
+
+
 def weight_quant_matmul(x, w, scale, offset=None, bias=None, int4=False, group=0, name="aclnnWeightQuantBatchMatmulV2Ex",
-                        out=None, **kw):
-    """x [M,K] f16/bf16/f32; w int8 [K,N] or packed int4 bytes [K*N/2]; scale/offset [N] or [G,N]."""
+                        out=None, nz=False, **kw):
+    """x [M,K] f16/bf16/f32; w int8 [K,N] or packed int4 bytes [K*N/2]; scale/offset [N] or [G,N].
+    nz: w is the tile-packed buffer pack_weight_nz returned (int4 only)."""
     import torch
     M, K = x.shape
     N = scale.shape[-1]
     if out is None:
         out = torch.empty((M, N), dtype=x.dtype, device=x.device)
-    tw = AclTensor(w, ACL_INT4 if int4 else ACL_INT8, (K, N))
+    if nz:
+        tw = AclTensor(w, ACL_INT4, (K, N), fmt=ACL_FORMAT_FRACTAL_NZ, storage=(w.numel() * 2,))
+    else:
+        tw = AclTensor(w, ACL_INT4 if int4 else ACL_INT8, (K, N))
     targs = [AclTensor(x), tw, AclTensor(scale), AclTensor(offset) if offset is not None else None]
     if name.endswith("Ex"):
         targs += [AclTensor(bias) if bias is not None else None, ctypes.c_int64(group)]

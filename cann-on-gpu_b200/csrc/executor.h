@@ -11,6 +11,7 @@ enum PlanOp : int {
     PLAN_MX,          // MX block-scaled matmul
     PLAN_INT4_PACK,   // two int8 -> one packed byte
     PLAN_COPY,        // weight copy (identity pre-pack)
+    PLAN_PACK_NZ,     // int4 weight [K,N] -> tile-packed layout
     PLAN_WEIGHT_SIZE, // element count of a weight shape
     PLAN_CAST,        // element-wise dtype cast
     PLAN_QPARAM,      // fp32 scale (+ offset) -> packed int64 quant parameter

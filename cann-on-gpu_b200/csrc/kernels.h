@@ -49,6 +49,7 @@ struct MatmulArgs {
     int64_t batch = 1, M = 0, N = 0, K = 0, group = 0;
     int64_t a_batch_stride = 0, b_batch_stride = 0, out_batch_stride = 0;  // elements
     bool b_transposed = false;
+    bool b_nz = false;             // int4 weights in the tile-packed layout (see wq_mma.cu), not [K,N] row-major
     bool accumulate = false;       // out = T(float(out) + float(T(result)))
     int split_k = 1;
     void *workspace = nullptr;
@@ -94,6 +95,11 @@ bool wq_mma_supported(const MatmulArgs &p);
 uint64_t wq_mma_workspace_bytes(const MatmulArgs &p);
 cudaError_t launch_wq_mma(const MatmulArgs &p, cudaStream_t s);
 unsigned int wq_mma_device_status();
+// The tile-packed int4 weight layout the decode kernel streams with contiguous 16 KB copies: bytes it
+// occupies for a [K,N] weight, the one-time re-layout from the caller's layout, and the way back.
+uint64_t wq_nz_bytes(int64_t K, int64_t N);
+cudaError_t launch_wq_pack_nz(const void *w_nd, void *w_nz, int64_t K, int64_t N, cudaStream_t s);
+cudaError_t launch_wq_unpack_nz(const void *w_nz, void *w_nd, int64_t K, int64_t N, cudaStream_t s);
 // 0, or the code of the first bounded wait that gave up on the current device (synchronises).
 unsigned int tc_device_status();
 

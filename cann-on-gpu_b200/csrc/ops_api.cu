@@ -63,6 +63,7 @@ MatmulArgs args_of(const aclOpExecutor *e, void *ws, uint64_t ws_bytes) {
     p.batch = e->batch; p.M = e->m; p.N = e->n; p.K = e->k; p.group = e->group;
     p.a_batch_stride = e->m * e->k; p.b_batch_stride = e->k * e->n; p.out_batch_stride = e->m * e->n;
     p.b_transposed = e->b_transposed; p.accumulate = e->accumulate;
+    p.b_nz = e->op == PLAN_WQBMM && e->b->format == ACL_FORMAT_FRACTAL_NZ && e->b->dtype == ACL_INT4;
     p.split_k = e->split_k; p.workspace = ws; p.workspace_bytes = ws_bytes;
     if (e->bias) { p.bias = data_of(e->bias); p.bias_type = elem_type(e->bias->dtype); }
     switch (e->op) {
@@ -113,7 +114,8 @@ void choose_path(aclOpExecutor *e, uint64_t *ws) {
     MatmulArgs p = plan_args_of(e);
     int want = forced_path();
     e->path = PATH_GENERIC; e->split_k = 1; e->ws_bytes = 0;
-    const bool tc_ok = tc_supported(p), gemv_ok = gemv_supported(p);
+    const bool tc_ok = tc_supported(p), gemv_ok = !p.b_nz && gemv_supported(p);
+    if (p.b_nz) want = PATH_TC;   // only the tensor-core family reads the tile-packed weight layout
     if (want == PATH_TC && tc_ok) e->path = PATH_TC;
     else if (want == PATH_GEMV && gemv_ok) e->path = PATH_GEMV;
     else if (want == PATH_GENERIC) e->path = PATH_GENERIC;
@@ -204,6 +206,11 @@ aclnnStatus wqbmm_plan(const aclTensor *x, const aclTensor *weight, const aclTen
     e->op = PLAN_WQBMM; e->a = x; e->b = weight; e->scale = scale; e->scale2 = offset; e->bias = bias; e->out = out;
     e->m = M; e->n = N; e->k = K; e->group = K / G;
     choose_path(e, ws);
+    if (weight->format == ACL_FORMAT_FRACTAL_NZ && weight->dtype == ACL_INT4 && e->path != PATH_TC) {
+        // tile-packed int4 weights and a shape (or a device) the tensor-core family does not take
+        delete e;
+        return ACLNN_ERR_PARAM_INVALID;
+    }
     *ex = e;
     return ACLNN_SUCCESS;
 }
@@ -284,6 +291,9 @@ aclnnStatus run_simple(aclOpExecutor *e, aclrtStream stream) {
     switch (e->op) {
         case PLAN_INT4_PACK:
             err = launch_int4_pack((const int8_t *)data_of(e->a), (uint8_t *)const_cast<void *>(data_of(e->out)), e->n, s);
+            break;
+        case PLAN_PACK_NZ:
+            err = launch_wq_pack_nz(data_of(e->a), const_cast<void *>(data_of(e->out)), e->k, e->n, s);
             break;
         case PLAN_COPY:
             err = cudaMemcpyAsync(const_cast<void *>(data_of(e->out)), data_of(e->a), (size_t)e->n, cudaMemcpyDeviceToDevice, s);
@@ -478,34 +488,62 @@ aclnnStatus aclnnConvertWeightToINT4PackGetWorkspaceSize(const aclTensor *weight
 }
 RUN_SIMPLE(aclnnConvertWeightToINT4Pack)
 
+// Elements a tensor's storage holds (the product of its storage dimensions; the view's when none were given).
+static int64_t storage_elems(const aclTensor *t) {
+    if (t->storageDims.empty()) return t->numel();
+    int64_t n = 1;
+    for (auto d : t->storageDims) n *= d;
+    return n;
+}
+
+// One-time re-layout of a weight into the on-device format its `out` tensor names.  An int4 [K,N] weight
+// into an ACL_FORMAT_FRACTAL_NZ tensor becomes the tile-packed layout the decode kernel streams with
+// contiguous 16 KB copies (out keeps the view shape [K,N]; its storage must hold the element count
+// aclnnCalculateMatmulWeightSizeV2 reports for ACL_INT4).  Everything else is an identity copy, as in the
+// reference (cuda/src/ops/matmul.cu:1162-1165).
 aclnnStatus aclnnTransMatmulWeightGetWorkspaceSize(const aclTensor *weight, aclTensor *out, uint64_t *ws, aclOpExecutor **ex) {
     if (!weight || !out || !ws || !ex) return ACLNN_ERR_PARAM_NULLPTR;
     if (!weight->data || !out->data) return ACLNN_ERR_PARAM_NULLPTR;
     if (weight->dtype != out->dtype || weight->numel() != out->numel() || !dense(weight) || !dense(out)) return ACLNN_ERR_PARAM_INVALID;
     auto *e = new aclOpExecutor();
-    e->op = PLAN_COPY; e->a = weight; e->out = out;
-    e->n = (weight->numel() * elem_bits(elem_type(weight->dtype)) + 7) / 8;
+    e->a = weight; e->out = out;
+    if (out->format == ACL_FORMAT_FRACTAL_NZ && weight->dtype == ACL_INT4 && weight->format != ACL_FORMAT_FRACTAL_NZ) {
+        if (weight->rank() != 2 || out->viewDims != weight->viewDims || (weight->viewDims[1] & 1) || (weight->offset & 1) || out->offset != 0 ||
+            storage_elems(out) < (int64_t)(2 * wq_nz_bytes(weight->viewDims[0], weight->viewDims[1]))) {
+            delete e;
+            return ACLNN_ERR_PARAM_INVALID;
+        }
+        e->op = PLAN_PACK_NZ; e->k = weight->viewDims[0]; e->n = weight->viewDims[1];
+    } else {
+        e->op = PLAN_COPY;
+        e->n = (weight->numel() * elem_bits(elem_type(weight->dtype)) + 7) / 8;
+    }
     *ws = 0; *ex = e;
     return ACLNN_SUCCESS;
 }
 RUN_SIMPLE(aclnnTransMatmulWeight)
 
-static aclnnStatus weight_size_plan(const aclIntArray *shape, aclTensor *out, uint64_t *ws, aclOpExecutor **ex) {
+// Element count of the on-device form of a weight of the given shape.  Without a type (or for any type but
+// int4) that is the product of the dimensions, as in the reference (cuda/src/ops/matmul.cu:1166-1170); for
+// ACL_INT4 [K,N] it is the element count of the tile-packed layout (K padded to 128, N to 256).
+static aclnnStatus weight_size_plan(const aclIntArray *shape, int64_t dtype, aclTensor *out, uint64_t *ws, aclOpExecutor **ex) {
     if (!shape || !out || !ws || !ex) return ACLNN_ERR_PARAM_NULLPTR;
     if (!out->data) return ACLNN_ERR_PARAM_NULLPTR;
     if (out->dtype != ACL_INT64 || out->numel() < 1) return ACLNN_ERR_PARAM_INVALID;
     auto *e = new aclOpExecutor();
     e->op = PLAN_WEIGHT_SIZE; e->out = out; e->n = 1;
     for (auto d : shape->v) e->n *= d;
+    if (dtype == (int64_t)ACL_INT4 && shape->v.size() == 2 && shape->v[0] > 0 && shape->v[1] > 0)
+        e->n = (int64_t)(2 * wq_nz_bytes(shape->v[0], shape->v[1]));
     *ws = 0; *ex = e;
     return ACLNN_SUCCESS;
 }
 aclnnStatus aclnnCalculateMatmulWeightSizeGetWorkspaceSize(const aclIntArray *weightShape, aclTensor *out, uint64_t *ws, aclOpExecutor **ex) {
-    return weight_size_plan(weightShape, out, ws, ex);
+    return weight_size_plan(weightShape, -1, out, ws, ex);
 }
 RUN_SIMPLE(aclnnCalculateMatmulWeightSize)
-aclnnStatus aclnnCalculateMatmulWeightSizeV2GetWorkspaceSize(const aclIntArray *weightShape, int64_t, aclTensor *out, uint64_t *ws, aclOpExecutor **ex) {
-    return weight_size_plan(weightShape, out, ws, ex);
+aclnnStatus aclnnCalculateMatmulWeightSizeV2GetWorkspaceSize(const aclIntArray *weightShape, int64_t dtype, aclTensor *out, uint64_t *ws, aclOpExecutor **ex) {
+    return weight_size_plan(weightShape, dtype, out, ws, ex);
 }
 RUN_SIMPLE(aclnnCalculateMatmulWeightSizeV2)
 

@@ -789,15 +789,37 @@ cudaError_t launch_dense_tc(const MatmulArgs &p, cudaStream_t s) {
 }
 
 // ---- dispatch of the tensor-core family ----------------------------------------------------------
+// int4 weights in the tile-packed layout are read directly by the decode kernel (M <= 16).  Every other
+// kernel reads the caller's [K,N] layout, so for them the weights are first laid back into that layout at
+// the head of the workspace (one pass over the packed bytes) and the call proceeds as usual.
+namespace {
+inline uint64_t nz_copy_bytes(const MatmulArgs &p) { return align_up_u64((uint64_t)p.K * p.N / 2, 256); }
+inline bool nz_direct(const MatmulArgs &p) { return p.b_nz && is_wq(p) && wq_mma_supported(p); }
+inline MatmulArgs as_nd(const MatmulArgs &p, const void *w_nd) {
+    MatmulArgs q = p;
+    q.b_nz = false;
+    if (w_nd) q.b = w_nd;
+    return q;
+}
+}  // namespace
+
 bool tc_supported(const MatmulArgs &p) {
     if (dev_info().sm100 != 1 || !encode_fn()) return false;
+    if (p.b_nz) {
+        if (!is_wq(p) || p.b_type != ET_I4) return false;
+        return nz_direct(p) || (p.N % 8 == 0 && tc_supported(as_nd(p, nullptr)));
+    }
     if (use_stream_wq(p) || use_expand(p)) return true;
     return dense_tc_supported(p);
 }
 
-void tc_plan(MatmulArgs &p) { p.split_k = (use_stream_wq(p) || use_expand(p)) ? 1 : make_plan(p).split; }
+void tc_plan(MatmulArgs &p) {
+    if (p.b_nz) { p.split_k = 1; return; }
+    p.split_k = (use_stream_wq(p) || use_expand(p)) ? 1 : make_plan(p).split;
+}
 
 uint64_t tc_workspace_bytes(const MatmulArgs &p) {
+    if (p.b_nz) return nz_direct(p) ? wq_mma_workspace_bytes(p) : nz_copy_bytes(p) + tc_workspace_bytes(as_nd(p, nullptr));
     if (use_decode_wq(p)) return wq_mma_workspace_bytes(p);
     if (use_stream_wq(p)) return wq_tc_workspace_bytes(p);
     if (use_expand(p)) return expand_workspace_bytes(p);
@@ -805,6 +827,18 @@ uint64_t tc_workspace_bytes(const MatmulArgs &p) {
 }
 
 cudaError_t launch_tc(const MatmulArgs &p, cudaStream_t s) {
+    if (p.b_nz) {
+        if (nz_direct(p)) return launch_wq_mma(p, s);
+        const uint64_t copy = nz_copy_bytes(p);
+        if (!p.workspace || p.workspace_bytes < copy) return cudaErrorInvalidValue;
+        if ((reinterpret_cast<uintptr_t>(p.b) & 15) || (reinterpret_cast<uintptr_t>(p.workspace) & 15)) return cudaErrorMisalignedAddress;
+        cudaError_t e = launch_wq_unpack_nz(p.b, p.workspace, p.K, p.N, s);
+        if (e != cudaSuccess) return e;
+        MatmulArgs q = as_nd(p, p.workspace);
+        q.workspace = (char *)p.workspace + copy;
+        q.workspace_bytes = p.workspace_bytes - copy;
+        return launch_tc(q, s);
+    }
     if (use_decode_wq(p)) return launch_wq_mma(p, s);
     if (use_stream_wq(p)) return launch_wq_tc(p, s);
     if (use_expand(p)) return launch_expand(p, s);

@@ -1,5 +1,6 @@
-// W4A16 / W8A16 decode kernel (M <= 16): TMA-staged packed weights, dequantised in registers, multiplied
-// on the warp-level tensor-core path (mma.sync m16n8k16), group scales folded in fp32, stream-K.
+// W4A16 / W8A16 decode kernel (M <= 16): packed weights streamed by TMA, dequantised in registers,
+// multiplied on the warp-level tensor-core path (mma.sync m16n8k16, fp16), scales folded in fp32,
+// stream-K over (tile, 128-row stage) units.
 //
 // Why not tcgen05 here: at decode shapes the matmul is a stream of weights from HBM, and feeding the
 // 5th-generation tensor core means writing every dequantised weight back to shared memory (2 B per
@@ -7,35 +8,41 @@
 // stream itself.  Here a packed weight is read from shared memory once (0.5 B), expanded by one
 // lop3 per pair of weights, and goes to the tensor core from registers.
 //
-// Per CTA (one per SM, 14 warps):
-//   warp 0       producer: one TMA per super-block (128 K rows x 256 columns of packed int4 = 16 KB,
-//                128-byte swizzle, no L2 promotion) plus the activation rows of the same K range, into
-//                a ring of two to four slots per team (as many as fit beside the partial tiles).
-//   warps 1-12   three teams of four warps.  A team owns one quantum (= one scale group, or one
-//                super-block for per-channel scales) at a time; each of its warps covers 64 of the
-//                tile's 256 columns.  Per 16 K rows a lane reads four 32-bit words (rows 2t, 2t+1,
-//                2t+8, 2t+9 of its 8 columns -- bank-conflict free under the swizzle), interleaves row
-//                pairs with two byte-permutes and extracts each (k, k+1) nibble pair with one lop3
-//                into a bf16x2 / fp16x2 register holding the exact integers 136+q / 1032+q; these are
-//                the A fragments (weights^T) of mma.sync, the activations are the B fragments, and
-//                one more mma with an all-ones A accumulates the activation sums.  At the end of the
-//                group:   tot += s_g[n] * (acc - (136 + off_g[n]) * sum_g x)
-//                which is the reference's algebra (cuda/src/ops/matmul.cu:334-335) per group, in fp32.
+// The product always runs in fp16.  A 4-bit integer is exact in fp16, and the 10-bit mantissa has
+// room for a nibble at bits 0-3 and another at bits 4-7, so one 32-bit word of eight nibbles becomes four
+// fp16x2 registers with four lop3 and one shift (bf16's 7-bit mantissa would need a shift per
+// register).  bf16 activations are converted to fp16 per stage with a power-of-two scale per row, which
+// is exact (8 significant bits into 11) for every element within 2^-29 of the row's largest in that
+// stage; the fold multiplies the scale back in fp32.
+//
+// Per CTA (one per SM, 15 warps):
+//   warp 0       weight producer: one copy per stage (128 K rows x 256 columns of packed int4 = 16 KB)
+//                into a ring of 6-9 slots.  Weights in the caller's [K,N] layout come as a 2-D TMA box
+//                (128 rows x 128 B, 128-byte swizzle, no L2 promotion); weights in the tile-packed
+//                layout (see wq_pack_nz_kernel) as one contiguous 16 KB bulk copy.
+//   warp 14      activation producer: loads the stage's 128 K columns of every activation row from
+//                global memory (L2), converts them to scaled fp16, and writes them into the slot in
+//                B-fragment order together with the row's scale and the row's sum over the stage.
+//   warps 1-12   three teams of four warps; a team owns every third stage, each of its warps 64 of the
+//                tile's 256 columns.  Per 16 K rows a lane turns 32 nibbles into 16 fp16x2 A-fragment
+//                registers holding the exact integers 1032 + q (even columns) and 1152 + 16 q (odd
+//                columns); the activations are the B fragments.  At the end of the stage
+//                    tot += s_g[n] * 2^e[m] * (acc - (1032 + off_g[n]) * sum_stage x[m])
+//                which is the reference's algebra (cuda/src/ops/matmul.cu:334-335) per stage, in fp32.
 //   warp 13      reducer: when all teams have finished a tile (or this CTA's piece of it) it sums the
 //                teams' partial tiles from shared memory in a fixed order and writes the output
-//                (whole tile) or an fp32 slot (piece; summed by wq_mma_finalize_kernel).
-// Work split: the (tile, quantum) space is cut into gridDim.x equal contiguous shares (stream-K).
-// Every ring slot belongs to one team, so a team meets the phases of a slot's barrier in order and a
-// parity wait can never be asked about a phase that is two ahead.
-//
-// What bounds it: the integer pipe (prmt, shift, lop3: one op per weight, issued at half rate) and the
-// issue slots run at 60-70 % while the weight stream is kept 128-192 KB deep per SM; a version that
-// skips the arithmetic streams the same bytes only 20 % faster.
+//                (whole tile) or an fp32 partial tile in the workspace (piece); the CTA that finds all pieces of a
+//                tile published sums them and writes the tile, so one launch does everything.
+// Work split: the (tile, stage) space is cut into gridDim.x equal contiguous shares (stream-K).
+// The ring depth is a multiple of the team count, so every slot belongs to one team, which meets the
+// phases of the slot's barrier in order: a parity wait is never asked about a phase that is two ahead.
 //
 // int8 weights use the same path: a byte is lo + 16 * hi (unsigned low nibble, signed high nibble); the
 // two nibbles ride rows g and g+8 of one mma and are recombined in the fold (tile = 128 columns).
 //
 // Replaces the reference's k_wq_fused (cuda/src/ops/matmul.cu:337-352).
+#include <atomic>
+#include <chrono>
 #include <mutex>
 #include <type_traits>
 
@@ -44,69 +51,90 @@
 namespace qmm {
 namespace {
 
-constexpr int MM_TILE_N = 256;      // output columns per tile
-constexpr int MM_SBK = 128;         // K rows per super-block (the unit scale groups are counted in)
-constexpr int MM_W_BYTES = 16384;   // packed weights of one super-block: 128 rows x 128 B
+constexpr int MM_TILE_N = 256;      // nibble columns per tile
+constexpr int MM_SBK = 128;         // K rows per stage
+constexpr int MM_W_BYTES = 16384;   // packed weights of one stage: 128 rows x 128 B
+constexpr int MM_TEAMS = 3;
+constexpr int MM_THREADS = (4 * MM_TEAMS + 3) * 32;
 
 struct MmParams {
     void *out;
-    float *slots;            // [tiles + P][M][tile_n] fp32 partial tiles
+    float *slots;            // [tiles + P][M][tile_n] fp32 partial tiles of tiles shared between CTAs
+    unsigned long long *tags;   // [tiles + P] arrival tags of those partial tiles
+    unsigned long long nonce;   // this launch's tag value (never 0)
+    const void *x;           // activations [M,K], bf16 or fp16
     const void *scale, *offset, *bias;
-    int sc_type, out_type;
+    const uint8_t *wnz;      // tile-packed weights (blocks of 16 KB, [tile][stage]) or null
+    int x_bf16;              // activation / scale / output type: 1 = bf16, 0 = fp16
     int M, N, K;
-    int sbq;                 // super-blocks per quantum
-    int qpt;                 // quanta per tile
-    long long total_q;       // tiles * qpt
-    int grouped;
-    int ns;                  // ring slots (a multiple of the team count, see mm_ring_slots)
+    int num_sb;              // stages per tile = ceil(K / 128)
+    long long total_u;       // tiles * num_sb
+    int gsb;                 // stages per scale row (num_sb for per-channel scales)
+    int ns;                  // ring slots (a multiple of the team count)
     int tile_n;              // output columns per tile: 256 (int4) or 128 (int8: two nibbles per column)
+    int weights_early;       // weights, scales and offsets may be read before the preceding kernel has completed
 };
 
 // Shared memory of one CTA: [ring: ns slots][partial tiles: teams x M rows x 256 fp32][barriers][flag].
+// A slot: [packed weights 16 KB][activations in B-fragment order, MF x 2 KB][row scales 16 f32][row sums 16 f32]
+// [the stage's scale row for the tile's columns, 512 B][its offset row, 512 B].
 template <int MF>
 struct MmSmem {
-    static constexpr int XBOX = MF * 8 * 128;                 // one activation box: MF*8 rows x 64 k
-    static constexpr int SLOT = MM_W_BYTES + 2 * XBOX;        // multiple of 1024
-    __host__ __device__ static int part_bytes(int teams, int M) { return teams * M * MM_TILE_N * 4; }   // sized for the wider (int4) tile
-    __host__ __device__ static int bar_off(int ns, int teams, int M) { return ns * SLOT + part_bytes(teams, M); }
-    __host__ __device__ static int total(int ns, int teams, int M) { return bar_off(ns, teams, M) + (2 * ns + 2) * 8 + 16 + 1024; }
+    static constexpr int XF_OFF = MM_W_BYTES;
+    static constexpr int META_OFF = XF_OFF + MF * 2048;
+    static constexpr int SC_OFF = META_OFF + 128;
+    static constexpr int OF_OFF = SC_OFF + 512;
+    static constexpr int SLOT = (OF_OFF + 512 + 1023) / 1024 * 1024;
+    __host__ __device__ static int part_bytes(int M) { return MM_TEAMS * M * MM_TILE_N * 4; }   // sized for the wider (int4) tile
+    __host__ __device__ static int bar_off(int ns, int M) { return ns * SLOT + part_bytes(M); }
+    __host__ __device__ static int total(int ns, int M) { return bar_off(ns, M) + (2 * ns + 2) * 8 + 16 + 1024; }
 };
 
-__host__ __device__ inline long long mm_share_begin(long long c, long long total_q, int P) { return c * total_q / P; }
-__host__ __device__ inline int mm_share_owner(long long q, long long total_q, int P) { return (int)(((q + 1) * P - 1) / total_q); }
+__host__ __device__ inline long long mm_share_begin(long long c, long long total, int P) { return c * total / P; }
+__host__ __device__ inline int mm_share_owner(long long u, long long total, int P) { return (int)(((u + 1) * P - 1) / total); }
 
 __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
     uint32_t v;
     asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
     return v;
 }
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts64(uint32_t addr, uint32_t a, uint32_t b) {
+    asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(a), "r"(b) : "memory");
+}
+__device__ __forceinline__ void sts32f(uint32_t addr, float v) { asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory"); }
+__device__ __forceinline__ float2 lds64f(uint32_t addr) {
+    float2 v;
+    asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
 
-template <bool BF16>
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    if constexpr (BF16) {
-        asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
-            : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-    } else {
-        asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
-            : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-    }
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-
-// The same with a zero C operand: the first step of a group needs no cleared accumulators.
-template <bool BF16>
+// The same with a zero C operand: the first step of a stage needs no cleared accumulators.
 __device__ __forceinline__ void mma16816_first(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    if constexpr (BF16) {
-        asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %10, %10, %10};"
-            : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
-    } else {
-        asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %10, %10, %10};"
-            : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
-    }
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %10, %10, %10};"
+        : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
 }
 
-// Two nibbles (bits 0-3 and 16-19) -> two 16-bit floats holding the integers MAGIC + q, q the signed
-// 4-bit value: xor 8 turns the two's-complement nibble into q + 8 in the low mantissa bits of
-// 128.0 (bf16) or 1024.0 (fp16).  One lop3, (v & mask) ^ magic, with both constants in registers.
+// Two nibbles of a word -> two fp16 holding integers above a power of two: (v & mask) ^ magic in one
+// lop3, both constants in registers.  mask 0x000F000F, magic 0x6408: 1024 + (nibble ^ 8) = 1032 + q for a
+// two's-complement nibble q; mask 0x00F000F0, magic 0x6480: 1024 + 16 * (nibble ^ 8) = 1152 + 16 q.
 __device__ __forceinline__ uint32_t dq_pair(uint32_t v, uint32_t mask, uint32_t magic) {
     uint32_t r;
     asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(r) : "r"(v), "r"(mask), "r"(magic));
@@ -118,16 +146,27 @@ __device__ __forceinline__ uint4 ldg16_now(const void *ptr) {
     asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(ptr));
     return v;
 }
-template <bool BF16> __device__ __forceinline__ float half_bits_to_float(uint32_t h) {
-    if constexpr (BF16) return __uint_as_float(h << 16);
-    return __half2float(__ushort_as_half((unsigned short)h));
-}
-
 __device__ __forceinline__ uint2 ldg8_now(const void *ptr) {
     uint2 v;
     asm volatile("ld.global.nc.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(ptr));
     return v;
 }
+template <bool BF16> __device__ __forceinline__ float half_bits_to_float(uint32_t h) {
+    if constexpr (BF16) return __uint_as_float(h << 16);
+    return __half2float(__ushort_as_half((unsigned short)h));
+}
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&v);
+}
+
+// Programmatic dependent launch: with the launch attribute set, a CTA of this kernel may start on an SM as
+// soon as the kernel before it in the stream has let go of that SM (instead of after the whole grid has
+// drained), so its start-up -- barrier initialisation, clearing shared memory -- overlaps the predecessor's
+// tail.  Nothing of this kernel touches global memory before pdl_wait_for_prerequisites(), which returns once the
+// predecessor has completed and its writes are visible; without the attribute both calls do nothing.
+__device__ __forceinline__ void pdl_wait_for_prerequisites() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // Bounded wait that ignores the abort flag (used only to let copies in flight land before exit).
 __device__ __forceinline__ void mbar_drain(uint32_t bar, uint32_t parity) {
@@ -137,96 +176,236 @@ __device__ __forceinline__ void mbar_drain(uint32_t bar, uint32_t parity) {
     }
 }
 
-template <bool Q8, bool BF16, int MF, int MM_TEAMS>
-__global__ void __launch_bounds__((4 * MM_TEAMS + 2) * 32, 1)
-wq_mma_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w, const MmParams p) {
+// The activation producer (one warp).  For every stage of the CTA's share, in order: the stage's 128 K
+// columns of every activation row, from global memory (L2) to scaled fp16 in the slot, in B-fragment order
+// (step st of 16 K, lane (g = row, t): {k = 2t, 2t+1}, {k = 2t+8, 2t+9}), plus the row's scale 2^e and the
+// row's sum over the stage.  A lane owns EPL consecutive elements of one row, so 128 / EPL lanes share a row
+// and 32 / (128 / EPL) rows are handled per pass: EPL = 4 serves one row with all 32 lanes, 32 serves eight
+// rows (two passes for nine to sixteen).  Rows the passes never touch stay zero from the kernel's start.
+// Loads run D stages ahead of the conversion so that the L2 round trip is not paid per stage.
+template <bool BF16, int MF, int EPL>
+__device__ __forceinline__ void mm_activation_producer(const MmParams &p, uint32_t base, int NS, uint32_t bars, volatile int *abort_flag,
+                                                       int sb0, int nu, int lane) {
+    using L = MmSmem<MF>;
+    constexpr int LPR = 128 / EPL, R = 32 / LPR, V = EPL / 4, D = EPL <= 8 ? 4 : 2;
+    const int q = lane % LPR, rsub = lane / LPR;
+    const uint16_t *xg = static_cast<const uint16_t *>(p.x);
+    uint2 buf[D][MF][V];
+    auto load_stage = [&](int sbi, uint2 (&v)[MF][V]) {
+        const int k = sbi * MM_SBK + EPL * q;
+#pragma unroll
+        for (int f = 0; f < MF; ++f) {
+            const int m = (MF == 2 ? 8 * f : 0) + rsub;
+#pragma unroll
+            for (int j = 0; j < V; ++j) {
+                v[f][j] = make_uint2(0u, 0u);
+                if (m < p.M && k + 4 * j < p.K) v[f][j] = ldg8_now(xg + (size_t)m * p.K + k + 4 * j);   // K % 8 == 0
+            }
+        }
+    };
+    auto next_sb = [&](int sbi, int by) { int s2 = sbi + by; while (s2 >= p.num_sb) s2 -= p.num_sb; return s2; };
+    pdl_wait_for_prerequisites();   // the activations are the predecessor's output
+    int sb_load = sb0;
+#pragma unroll
+    for (int d = 0; d < D; ++d) {
+        if (d < nu) load_stage(sb_load, buf[d]);
+        sb_load = next_sb(sb_load, 1);
+    }
+    int slot = 0, round = 0;
+    for (int i0 = 0; i0 < nu; i0 += D) {
+#pragma unroll
+        for (int d = 0; d < D; ++d) {
+            const int i = i0 + d;
+            if (i >= nu) break;
+            uint2 cur[MF][V];
+#pragma unroll
+            for (int f = 0; f < MF; ++f)
+#pragma unroll
+                for (int j = 0; j < V; ++j) cur[f][j] = buf[d][f][j];
+            if (i + D < nu) load_stage(sb_load, buf[d]);
+            sb_load = next_sb(sb_load, 1);
+            // convert first (registers only), then wait for the slot: what remains after the wait is a few stores
+            uint32_t h[MF][EPL / 2];
+            float up[MF], sum[MF];
+#pragma unroll
+            for (int f = 0; f < MF; ++f) {
+                float v[EPL];
+#pragma unroll
+                for (int j = 0; j < V; ++j) {
+                    const uint32_t w[2] = {cur[f][j].x, cur[f][j].y};
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        if constexpr (BF16) {
+                            v[4 * j + 2 * c] = __uint_as_float(w[c] << 16);
+                            v[4 * j + 2 * c + 1] = __uint_as_float(w[c] & 0xFFFF0000u);
+                        } else {
+                            const float2 h2 = __half22float2(*reinterpret_cast<const __half2 *>(&w[c]));
+                            v[4 * j + 2 * c] = h2.x;
+                            v[4 * j + 2 * c + 1] = h2.y;
+                        }
+                    }
+                }
+                float down = 1.f;
+                up[f] = 1.f;
+                if constexpr (BF16) {
+                    float amax = 0.f;
+#pragma unroll
+                    for (int c = 0; c < EPL; ++c) amax = fmaxf(amax, fabsf(v[c]));
+                    // non-negative floats order like their bit patterns: one warp-wide integer maximum per row
+                    uint32_t abits = __float_as_uint(amax);
+                    if constexpr (LPR == 32) abits = __reduce_max_sync(0xffffffffu, abits);
+                    else {
+#pragma unroll
+                        for (int o = 1; o < LPR; o <<= 1) abits = max(abits, __shfl_xor_sync(0xffffffffu, abits, o));
+                    }
+                    // the row's largest magnitude lands in [2^14, 2^15); zero rows keep scale 1; an infinite (or NaN)
+                    // row is clamped (its result is not finite either way)
+                    int e = 0;
+                    if (abits != 0u) {
+                        e = (int)((abits >> 23) & 0xFFu) - 127 - 14;
+                        e = e < -100 ? -100 : (e > 100 ? 100 : e);
+                    }
+                    down = __uint_as_float((uint32_t)(127 - e) << 23);
+                    up[f] = __uint_as_float((uint32_t)(127 + e) << 23);
+                }
+                float sm = 0.f;
+#pragma unroll
+                for (int c = 0; c < EPL / 2; ++c) {
+                    h[f][c] = pack_f16x2(v[2 * c] * down, v[2 * c + 1] * down);
+                    const float2 back = __half22float2(*reinterpret_cast<const __half2 *>(&h[f][c]));
+                    sm += back.x + back.y;   // the sum of what the tensor core will see
+                }
+#pragma unroll
+                for (int o = 1; o < LPR; o <<= 1) sm += __shfl_xor_sync(0xffffffffu, sm, o);
+                sum[f] = sm;
+            }
+            if (round > 0 && !mbar_wait(bars + 8u * (NS + slot), (round - 1) & 1, abort_flag, 0x340u + slot)) return;
+            const uint32_t sb = base + slot * L::SLOT;
+#pragma unroll
+            for (int f = 0; f < MF; ++f) {
+                const int row = (MF == 2 ? 8 * f : 0) + rsub;
+#pragma unroll
+                for (int c = 0; c < EPL / 2; ++c) {
+                    const int kk = EPL * q + 2 * c, st = kk >> 4, kr = kk & 15;
+                    asm volatile("st.shared.b32 [%0], %1;" ::"r"(sb + L::XF_OFF + f * 2048 + (((st * 32 + 4 * rsub + ((kr & 7) >> 1)) << 3) + 4 * (kr >> 3))), "r"(h[f][c]) : "memory");
+                }
+                if (q == 0) {
+                    sts32f(sb + L::META_OFF + 4 * row, up[f]);
+                    sts32f(sb + L::META_OFF + 64 + 4 * row, sum[f]);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bars + 8u * slot);
+            if (++slot == NS) { slot = 0; ++round; }
+        }
+    }
+}
+
+template <bool Q8, bool BF16, int MF, bool NZ>
+__global__ void __launch_bounds__(MM_THREADS, 1)
+wq_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const MmParams p) {
     using L = MmSmem<MF>;
     constexpr int TN = Q8 ? 128 : 256;   // output columns per tile (the tile is 256 nibble columns wide)
-    const int MM_NS = p.ns;
+    const int NS = p.ns;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *gen_base = smem_raw + (base - smem_u32(smem_raw));
-    const int bar_off = L::bar_off(MM_NS, MM_TEAMS, p.M);
+    const int bar_off = L::bar_off(NS, p.M);
     const uint32_t bars = base + bar_off;
     auto full_bar = [&](int s) { return bars + 8u * s; };
-    auto empty_bar = [&](int s) { return bars + 8u * (MM_NS + s); };
-    const uint32_t seg_done = bars + 8u * (2 * MM_NS), seg_free = bars + 8u * (2 * MM_NS + 1);
-    volatile int *abort_flag = reinterpret_cast<volatile int *>(gen_base + bar_off + (2 * MM_NS + 2) * 8);
-    float *part = reinterpret_cast<float *>(gen_base + MM_NS * L::SLOT);
+    auto empty_bar = [&](int s) { return bars + 8u * (NS + s); };
+    const uint32_t seg_done = bars + 8u * (2 * NS), seg_free = bars + 8u * (2 * NS + 1);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(gen_base + bar_off + (2 * NS + 2) * 8);
+    float *part = reinterpret_cast<float *>(gen_base + NS * L::SLOT);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int P = gridDim.x, cta = blockIdx.x;
-    const long long qb = mm_share_begin(cta, p.total_q, P), qe = mm_share_begin(cta + 1, p.total_q, P);
-    const int nq = (int)(qe - qb);
-    const int tile_first = (int)(qb / p.qpt), tile_last = (int)((qe - 1) / p.qpt);
+    const bool has_off = p.offset != nullptr;
+    const long long ub = mm_share_begin(cta, p.total_u, P), ue = mm_share_begin(cta + 1, p.total_u, P);
+    const int nu = (int)(ue - ub);
+    const int tile_first = (int)(ub / p.num_sb), tile_last = (int)((ue - 1) / p.num_sb);
 
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < MM_NS; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 4); }
-        mbar_init(seg_done, 4 * MM_TEAMS);
-        mbar_init(seg_free, 1);
-        *abort_flag = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    // activation rows the producer never writes (beyond M) must read as zero
+    for (int i = threadIdx.x; i < NS * (MF * 512 + 32); i += MM_THREADS) {
+        const int sl = i / (MF * 512 + 32), w = i % (MF * 512 + 32);
+        *reinterpret_cast<uint32_t *>(gen_base + sl * L::SLOT + L::XF_OFF + 4 * w) = 0u;
     }
+    // a stage is full when the weight copy has landed (producer's arrive + bytes) and the activation
+    // producer has arrived; it is empty when the team's four warps have arrived
+    if ((int)threadIdx.x < NS) mbar_init(full_bar(threadIdx.x), 2);
+    else if ((int)threadIdx.x < 2 * NS) mbar_init(empty_bar(threadIdx.x - NS), 4);
+    else if ((int)threadIdx.x == 2 * NS) mbar_init(seg_done, 4 * MM_TEAMS);
+    else if ((int)threadIdx.x == 2 * NS + 1) { mbar_init(seg_free, 1); *abort_flag = 0; }
+    if ((int)threadIdx.x < 2 * NS + 2) asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     __syncthreads();
+    if (threadIdx.x == 0) pdl_launch_dependents();   // the next kernel in the stream may take over SMs as they free up
 
     if (warp == 0) {
-        // ------------------------------------------------------------------ producer
+        // ------------------------------------------------------------------ weight producer
         if (lane == 0) {
+            if (!p.weights_early) pdl_wait_for_prerequisites();
             int i = 0, slot = 0, round = 0;
-            int tile = tile_first, qi = (int)(qb - (long long)tile_first * p.qpt);
+            int tile = tile_first, sbi = (int)(ub - (long long)tile_first * p.num_sb);
             bool ok = true;
-            for (int j = 0; j < nq && ok; ++j) {
-                for (int u = 0; u < p.sbq; ++u, ++i) {
-                    const int k0 = (qi * p.sbq + u) * MM_SBK;
-                    if (round > 0 && !mbar_wait(empty_bar(slot), (round - 1) & 1, abort_flag, 0x300u + slot)) { ok = false; break; }
-                    const uint32_t dst = base + slot * L::SLOT;
-                    mbar_expect_tx(full_bar(slot), L::SLOT);
-                    tma_load_2d(dst, &tm_w, full_bar(slot), tile * 128, k0);
-                    tma_load_2d(dst + MM_W_BYTES, &tm_x, full_bar(slot), k0, 0);
-                    tma_load_2d(dst + MM_W_BYTES + L::XBOX, &tm_x, full_bar(slot), k0 + 64, 0);
-                    if (++slot == MM_NS) { slot = 0; ++round; }
-                }
-                if (++qi == p.qpt) { qi = 0; ++tile; }
+            for (; i < nu; ++i) {
+                if (round > 0 && !mbar_wait(empty_bar(slot), (round - 1) & 1, abort_flag, 0x300u + slot)) { ok = false; break; }
+                const uint32_t dst = base + slot * L::SLOT;
+                // the stage's scale (and offset) row for this tile's columns rides with the weights, so the
+                // consumers never wait on a global load
+                const int ncols = min(TN, p.N - tile * TN);
+                const uint32_t row_bytes = (uint32_t)ncols * 2u;
+                const size_t row_at = (size_t)(sbi / p.gsb) * p.N + (size_t)tile * TN;
+                mbar_expect_tx(full_bar(slot), MM_W_BYTES + (has_off ? 2u : 1u) * row_bytes);
+                if constexpr (NZ) bulk_load_1d(dst, p.wnz + ((size_t)tile * p.num_sb + sbi) * MM_W_BYTES, MM_W_BYTES, full_bar(slot));
+                else tma_load_2d(dst, &tm_w, full_bar(slot), tile * 128, sbi * MM_SBK);
+                bulk_load_1d(dst + L::SC_OFF, static_cast<const uint16_t *>(p.scale) + row_at, row_bytes, full_bar(slot));
+                if (has_off) bulk_load_1d(dst + L::OF_OFF, static_cast<const uint16_t *>(p.offset) + row_at, row_bytes, full_bar(slot));
+                if (++slot == NS) { slot = 0; ++round; }
+                if (++sbi == p.num_sb) { sbi = 0; ++tile; }
             }
             if (!ok) {   // let the copies already issued land before the CTA's shared memory goes away
-                for (int b = (i > MM_NS ? i - MM_NS : 0); b < i; ++b) mbar_drain(full_bar(b % MM_NS), (b / MM_NS) & 1);
+                for (int b = (i > NS ? i - NS : 0); b < i; ++b) mbar_drain(full_bar(b % NS), (b / NS) & 1);
             }
+        }
+    } else if (warp == 4 * MM_TEAMS + 2) {
+        // ------------------------------------------------------------------ activation producer
+        const int sb0 = (int)(ub - (long long)tile_first * p.num_sb);
+        if constexpr (MF == 2) {
+            mm_activation_producer<BF16, 2, 32>(p, base, NS, bars, abort_flag, sb0, nu, lane);
+        } else {
+            if (p.M == 1) mm_activation_producer<BF16, 1, 4>(p, base, NS, bars, abort_flag, sb0, nu, lane);
+            else if (p.M == 2) mm_activation_producer<BF16, 1, 8>(p, base, NS, bars, abort_flag, sb0, nu, lane);
+            else if (p.M <= 4) mm_activation_producer<BF16, 1, 16>(p, base, NS, bars, abort_flag, sb0, nu, lane);
+            else mm_activation_producer<BF16, 1, 32>(p, base, NS, bars, abort_flag, sb0, nu, lane);
         }
     } else if (warp <= 4 * MM_TEAMS) {
         // ------------------------------------------------------------------ compute
         const int cw = warp - 1, team = cw >> 2, wq = cw & 3;
         const int g = lane >> 2, t = lane & 3;
-        // byte offsets inside a slot of the four weight words of step 0 (rows 2t, 2t+1, 2t+8, 2t+9)
+        // caller's layout: byte offsets inside a slot of the four weight words of step 0 (rows 2t, 2t+1,
+        // 2t+8, 2t+9 of this lane's 8 columns, under the 128-byte swizzle); packed layout: one 16-byte vector
         uint32_t woff[4];
         {
             const int c16 = 2 * wq + (g >> 2), inb = 4 * (g & 3);
             const int rows[4] = {2 * t, 2 * t + 1, 2 * t + 8, 2 * t + 9};
 #pragma unroll
             for (int j = 0; j < 4; ++j) woff[j] = 128 * rows[j] + (((c16 ^ (rows[j] & 7)) << 4)) + inb;
+            if constexpr (NZ) woff[0] = (uint32_t)(wq * 8 * 512 + lane * 16);
         }
-        // activation words: slot + xrow, with the 16-byte chunk index xor-ed in (the swizzle); + box,
-        // + 1024 for the second fragment
-        const uint32_t xrow = MM_W_BYTES + 128 * g + 16 * g + 4 * t;
-        constexpr uint32_t ONES = BF16 ? 0x3F803F80u : 0x3C003C00u;
-        // int4: every nibble is a signed weight (xor 8 -> q + 8 above 128.0 / 1024.0).  int8: the byte
-        // is q = lo + 16 * hi with lo the unsigned low nibble (no xor) and hi the signed high nibble.
-        uint32_t dq_mask = 0x000F000Fu, dq_magic = BF16 ? 0x43084308u : 0x64086408u;
-        uint32_t dq_magic_even = Q8 ? (BF16 ? 0x43004300u : 0x64006400u) : dq_magic;
-        uint32_t dq_mask2 = 0x00F000F0u, dq_magic2 = 0x64806480u;   // fp16 only: nibble at bits 4-7
-        asm volatile("" : "+r"(dq_mask), "+r"(dq_magic), "+r"(dq_magic_even), "+r"(dq_mask2), "+r"(dq_magic2));   // keep the constants in registers
-        constexpr float MAGIC = BF16 ? 136.f : 1032.f;
+        // int4: every nibble is a signed weight (xor 8 -> q + 8 above 1024).  int8: the byte is
+        // q = lo + 16 * hi with lo the unsigned low nibble (no xor) and hi the signed high nibble.
+        uint32_t m1 = 0x000F000Fu, g1 = Q8 ? 0x64006400u : 0x64086408u, m2 = 0x00F000F0u, g2 = 0x64806480u;
+        asm volatile("" : "+r"(m1), "+r"(g1), "+r"(m2), "+r"(g2));   // keep the constants in registers
         // first of this lane's columns inside the tile: 8 nibble columns = 8 (int4) or 4 (int8) outputs
         const int n_lane = Q8 ? 32 * wq + 4 * g : 64 * wq + 8 * g;
+        const uint32_t xf_lane = L::XF_OFF + lane * 8, meta_lane = L::META_OFF + 8 * t;
 
-        float acc[MF][4][4], tot[MF][4][4], xs[MF][4];
+        float acc[MF][4][4], tot[MF][4][4];
         bool ok = true;
         int sg = 0;
-        // This team's stages are i = j * sbq + u for its quanta j = team, team + TEAMS, ...; their ring
-        // slot and pass number are kept incrementally.
-        int slot = team * p.sbq, round = 0;
         for (int tile = tile_first; tile <= tile_last && ok; ++tile, ++sg) {
-            const long long t_lo = (long long)tile * p.qpt, t_hi = t_lo + p.qpt;
-            const int j_lo = (int)((t_lo > qb ? t_lo : qb) - qb), j_hi = (int)((t_hi < qe ? t_hi : qe) - qb);
+            const long long t_lo = (long long)tile * p.num_sb, t_hi = t_lo + p.num_sb;
+            const int j_lo = (int)((t_lo > ub ? t_lo : ub) - ub), j_hi = (int)((t_hi < ue ? t_hi : ue) - ub);
             const int n_glob = tile * TN + n_lane;
             const bool n_ok = n_glob < p.N;
             bool had = false;
@@ -236,136 +415,116 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
                 for (int r = 0; r < 4; ++r)
 #pragma unroll
                     for (int e = 0; e < 4; ++e) tot[f][r][e] = 0.f;
-            // scale / offset rows of a group: 8 consecutive columns = 16 bytes per lane (8 bytes for int8
-            // weights), fetched one quantum ahead of their use.  Lanes beyond N read column 0 (unused).
-            const int n_safe = n_ok ? n_glob : 0;
-            const int qi_seg = (int)(qb + j_lo - t_lo);   // quantum index inside the tile of local quantum j_lo
             const int j_first = j_lo + (team - j_lo % MM_TEAMS + MM_TEAMS) % MM_TEAMS;
-            const size_t row_step = p.grouped ? (size_t)MM_TEAMS * p.N : 0;
-            const uint16_t *sc_ptr = static_cast<const uint16_t *>(p.scale) + n_safe +
-                                     (p.grouped ? (size_t)(qi_seg + j_first - j_lo) * p.N : 0);
-            const uint16_t *of_base = p.offset ? static_cast<const uint16_t *>(p.offset) : nullptr;
-            const ptrdiff_t of_delta = of_base ? reinterpret_cast<const uint16_t *>(p.offset) - reinterpret_cast<const uint16_t *>(p.scale) : 0;
-            auto fetch_rows = [&](const uint16_t *sp, uint4 &sr, uint4 &orr) {
-                if constexpr (Q8) {
-                    const uint2 a = ldg8_now(sp);
-                    sr.x = a.x; sr.y = a.y;
-                    if (of_base) { const uint2 b = ldg8_now(sp + of_delta); orr.x = b.x; orr.y = b.y; }
-                } else {
-                    sr = ldg16_now(sp);
-                    if (of_base) orr = ldg16_now(sp + of_delta);
-                }
-            };
-            uint4 sraw = make_uint4(0, 0, 0, 0), oraw = sraw, snext = sraw, onext = sraw;
-            if (j_first < j_hi) fetch_rows(sc_ptr, snext, onext);
             for (int j = j_first; j < j_hi && ok; j += MM_TEAMS) {
                 had = true;
-                sraw = snext;
-                oraw = onext;
-                if (j + MM_TEAMS < j_hi) sc_ptr += row_step;   // the last quantum fetches its own row again
-                fetch_rows(sc_ptr, snext, onext);
-                for (int u = 0; u < p.sbq && ok; ++u) {
-                    const bool first_sb = u == 0;
-                    if (!mbar_wait(full_bar(slot), round & 1, abort_flag, 0x310u + slot)) { ok = false; break; }
-                    const uint32_t sb = base + slot * L::SLOT, xb = sb + xrow;
+                const int slot = j % NS, round = j / NS;
+                if (!mbar_wait(full_bar(slot), round & 1, abort_flag, 0x310u + slot)) { ok = false; break; }
+                const uint32_t sb = base + slot * L::SLOT;
 #pragma unroll
-                    for (int st = 0; st < 8; ++st) {
+                for (int st = 0; st < 8; ++st) {
+                    // caller's layout: lo[i] / hi[i] hold rows (2t, 2t+1) / (2t+8, 2t+9) side by side in their two
+                    // halves, columns 4i .. 4i+3; packed layout: word r holds both row pairs of columns 2r, 2r+1
+                    uint32_t wv[4];
+                    if constexpr (NZ) {
+                        const uint4 v = lds128(sb + woff[0] + st * 512);
+                        wv[0] = v.x; wv[1] = v.y; wv[2] = v.z; wv[3] = v.w;
+                    } else {
                         const uint32_t w0 = lds32(sb + woff[0] + st * 2048), w1 = lds32(sb + woff[1] + st * 2048);
                         const uint32_t w2 = lds32(sb + woff[2] + st * 2048), w3 = lds32(sb + woff[3] + st * 2048);
-                        uint32_t b0[MF], b1[MF];
-                        {
-                            const uint32_t xa0 = xb ^ ((uint32_t)(2 * (st & 3)) << 4), xa1 = xb ^ ((uint32_t)(2 * (st & 3) + 1) << 4);
+                        wv[0] = __byte_perm(w0, w1, 0x5410); wv[1] = __byte_perm(w0, w1, 0x7632);
+                        wv[2] = __byte_perm(w2, w3, 0x5410); wv[3] = __byte_perm(w2, w3, 0x7632);
+                    }
+                    uint2 b[MF];
 #pragma unroll
-                            for (int f = 0; f < MF; ++f) {
-                                b0[f] = lds32(xa0 + (st >> 2) * L::XBOX + f * 1024);
-                                b1[f] = lds32(xa1 + (st >> 2) * L::XBOX + f * 1024);
-                            }
-                        }
-                        // rows (k, k+1) side by side: low halves = nibbles 0-3, high halves = nibbles 4-7
-                        const uint32_t lo[2] = {__byte_perm(w0, w1, 0x5410), __byte_perm(w0, w1, 0x7632)};
-                        const uint32_t hi[2] = {__byte_perm(w2, w3, 0x5410), __byte_perm(w2, w3, 0x7632)};
+                    for (int f = 0; f < MF; ++f) b[f] = lds64(sb + xf_lane + f * 2048 + st * 256);
 #pragma unroll
-                        for (int r = 0; r < 4; ++r) {
-                            const int sh = (r & 1) * 8;
-                            uint32_t a0, a1, a2, a3;
-                            if constexpr (BF16) {
-                                a0 = dq_pair(lo[r >> 1] >> sh, dq_mask, dq_magic_even);
-                                a1 = dq_pair(lo[r >> 1] >> (sh + 4), dq_mask, dq_magic);
-                                a2 = dq_pair(hi[r >> 1] >> sh, dq_mask, dq_magic_even);
-                                a3 = dq_pair(hi[r >> 1] >> (sh + 4), dq_mask, dq_magic);
-                            } else {
-                                // fp16 has room for a nibble at mantissa bits 4-7 too: the odd column of
-                                // each pair is taken in place as 1152 + 16 q (undone in the fold), which
-                                // saves its shift
-                                const uint32_t l = lo[r >> 1] >> sh, h = hi[r >> 1] >> sh;
-                                a0 = dq_pair(l, dq_mask, dq_magic_even);
-                                a1 = dq_pair(l, dq_mask2, dq_magic2);
-                                a2 = dq_pair(h, dq_mask, dq_magic_even);
-                                a3 = dq_pair(h, dq_mask2, dq_magic2);
-                            }
-#pragma unroll
-                            for (int f = 0; f < MF; ++f) {
-                                if (st == 0 && first_sb) mma16816_first<BF16>(acc[f][r], a0, a1, a2, a3, b0[f], b1[f]);
-                                else mma16816<BF16>(acc[f][r], a0, a1, a2, a3, b0[f], b1[f]);
-                            }
+                    for (int r = 0; r < 4; ++r) {
+                        // a0 / a2: column 2r (even: 1032 + q) at rows (2t, 2t+1) / (2t+8, 2t+9); a1 / a3: column 2r+1
+                        // (odd: 1152 + 16 q, taken in place from bits 4-7)
+                        uint32_t a0, a1, a2, a3;
+                        if constexpr (NZ) {
+                            const uint32_t hi = wv[r] >> 8;
+                            a0 = dq_pair(wv[r], m1, g1);
+                            a1 = dq_pair(wv[r], m2, g2);
+                            a2 = dq_pair(hi, m1, g1);
+                            a3 = dq_pair(hi, m2, g2);
+                        } else {
+                            const uint32_t l = (r & 1) ? wv[r >> 1] >> 8 : wv[r >> 1], h = (r & 1) ? wv[2 + (r >> 1)] >> 8 : wv[2 + (r >> 1)];
+                            a0 = dq_pair(l, m1, g1);
+                            a1 = dq_pair(l, m2, g2);
+                            a2 = dq_pair(h, m1, g1);
+                            a3 = dq_pair(h, m2, g2);
                         }
 #pragma unroll
                         for (int f = 0; f < MF; ++f) {
-                            if (st == 0 && first_sb) mma16816_first<BF16>(xs[f], ONES, ONES, ONES, ONES, b0[f], b1[f]);
-                            else mma16816<BF16>(xs[f], ONES, ONES, ONES, ONES, b0[f], b1[f]);
+                            if (st == 0) mma16816_first(acc[f][r], a0, a1, a2, a3, b[f].x, b[f].y);
+                            else mma16816(acc[f][r], a0, a1, a2, a3, b[f].x, b[f].y);
                         }
                     }
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(empty_bar(slot));
-                    if (++slot == MM_NS) { slot = 0; ++round; }
                 }
-                // skip the other teams' stages of this round robin
-                slot += (MM_TEAMS - 1) * p.sbq;
-                while (slot >= MM_NS) { slot -= MM_NS; ++round; }
-                // fold the finished group (one uniform branch on the presence of offsets, so that the
+                // row scales 2^e and row sums of this lane's two activation rows (m = 8 f + 2 t, + 1)
+                float2 xsc[MF], xs[MF];
+#pragma unroll
+                for (int f = 0; f < MF; ++f) {
+                    xsc[f] = lds64f(sb + meta_lane + 32 * f);
+                    xs[f] = lds64f(sb + meta_lane + 64 + 32 * f);
+                }
+                // this lane's 8 columns of the stage's scale / offset row (4 columns for int8 weights)
+                uint4 sraw = make_uint4(0, 0, 0, 0), oraw = sraw;
+                if constexpr (Q8) {
+                    const uint2 a = lds64(sb + L::SC_OFF + 2 * n_lane);
+                    sraw.x = a.x; sraw.y = a.y;
+                    if (has_off) { const uint2 c = lds64(sb + L::OF_OFF + 2 * n_lane); oraw.x = c.x; oraw.y = c.y; }
+                } else {
+                    sraw = lds128(sb + L::SC_OFF + 2 * n_lane);
+                    if (has_off) oraw = lds128(sb + L::OF_OFF + 2 * n_lane);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty_bar(slot));
+                // fold the finished stage (one uniform branch on the presence of offsets, so that the
                 // common offset-free form carries no conversions or selects for them)
                 const uint32_t sw[4] = {sraw.x, sraw.y, sraw.z, sraw.w}, ow[4] = {oraw.x, oraw.y, oraw.z, oraw.w};
-                auto fold = [&](auto has_off) {
-                    constexpr bool OFF = decltype(has_off)::value;
+                auto fold = [&](auto off_tag) {
+                    constexpr bool OFF = decltype(off_tag)::value;
                     if constexpr (Q8) {
-                        // column r of this lane: rows g (low nibbles, MAGIC_LO + lo) and g+8 (high nibbles,
-                        // bf16: 136 + hi, to be taken 16 times; fp16: 1152 + 16 hi) of the same mma
-                        constexpr float HM = BF16 ? 16.f : 1.f, C = BF16 ? 128.f + 16.f * 136.f : 1024.f + 1152.f;
+                        // column r of this lane: rows g (low nibbles, 1024 + lo) and g+8 (high nibbles, 1152 + 16 hi)
+                        // of the same mma
+                        constexpr float C = 1024.f + 1152.f;
 #pragma unroll
                         for (int r = 0; r < 4; ++r) {
                             const float sn = half_bits_to_float<BF16>((r & 1) ? sw[r >> 1] >> 16 : sw[r >> 1] & 0xFFFFu);
                             float cn = C;
                             if constexpr (OFF) cn += half_bits_to_float<BF16>((r & 1) ? ow[r >> 1] >> 16 : ow[r >> 1] & 0xFFFFu);
 #pragma unroll
-                            for (int f = 0; f < MF; ++f)
-#pragma unroll
-                                for (int e = 0; e < 2; ++e)
-                                    tot[f][r][e] = fmaf(sn, fmaf(-cn, xs[f][e], fmaf(HM, acc[f][r][2 + e], acc[f][r][e])), tot[f][r][e]);
+                            for (int f = 0; f < MF; ++f) {
+                                tot[f][r][0] = fmaf(sn * xsc[f].x, fmaf(-cn, xs[f].x, acc[f][r][2] + acc[f][r][0]), tot[f][r][0]);
+                                tot[f][r][1] = fmaf(sn * xsc[f].y, fmaf(-cn, xs[f].y, acc[f][r][3] + acc[f][r][1]), tot[f][r][1]);
+                            }
                         }
                     } else {
 #pragma unroll
                         for (int r = 0; r < 4; ++r) {
 #pragma unroll
                             for (int h = 0; h < 2; ++h) {
+                                // column 2r + h; odd columns were accumulated as 1152 + 16 q
                                 float sn = half_bits_to_float<BF16>(h ? sw[r] >> 16 : sw[r] & 0xFFFFu);
-                                // odd columns of the fp16 form were accumulated as 1152 + 16 q
-                                const bool scaled = !BF16 && h;
-                                float cn = scaled ? 1152.f : MAGIC;
+                                float cn = h ? 1152.f : 1032.f;
                                 if constexpr (OFF) {
                                     const float off = half_bits_to_float<BF16>(h ? ow[r] >> 16 : ow[r] & 0xFFFFu);
-                                    cn += scaled ? 16.f * off : off;
+                                    cn += h ? 16.f * off : off;
                                 }
-                                if (scaled) sn *= 0.0625f;
+                                if (h) sn *= 0.0625f;
 #pragma unroll
-                                for (int f = 0; f < MF; ++f)
-#pragma unroll
-                                    for (int e = 0; e < 2; ++e)
-                                        tot[f][r][2 * h + e] = fmaf(sn, fmaf(-cn, xs[f][e], acc[f][r][2 * h + e]), tot[f][r][2 * h + e]);
+                                for (int f = 0; f < MF; ++f) {
+                                    tot[f][r][2 * h] = fmaf(sn * xsc[f].x, fmaf(-cn, xs[f].x, acc[f][r][2 * h]), tot[f][r][2 * h]);
+                                    tot[f][r][2 * h + 1] = fmaf(sn * xsc[f].y, fmaf(-cn, xs[f].y, acc[f][r][2 * h + 1]), tot[f][r][2 * h + 1]);
+                                }
                             }
                         }
                     }
                 };
-                if (of_base) fold(std::true_type{});
+                if (has_off) fold(std::true_type{});
                 else fold(std::false_type{});
             }
             if (!ok) break;
@@ -389,55 +548,179 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
         // ------------------------------------------------------------------ reducer
         int sg = 0;
         for (int tile = tile_first; tile <= tile_last; ++tile, ++sg) {
-            const long long t_lo = (long long)tile * p.qpt, t_hi = t_lo + p.qpt;
-            const int j_lo = (int)((t_lo > qb ? t_lo : qb) - qb), j_hi = (int)((t_hi < qe ? t_hi : qe) - qb);
+            const long long t_lo = (long long)tile * p.num_sb, t_hi = t_lo + p.num_sb;
+            const int j_lo = (int)((t_lo > ub ? t_lo : ub) - ub), j_hi = (int)((t_hi < ue ? t_hi : ue) - ub);
             const int cnt = j_hi - j_lo;
-            const bool whole = cnt == p.qpt;
-            if (!mbar_wait(seg_done, sg & 1, abort_flag, 0x330u)) break;
+            const bool whole = cnt == p.num_sb;
             // each lane owns CPL consecutive columns
             constexpr int CPL = TN / 32;
             const int n = CPL * lane, n_glob = tile * TN + n;
-            if (n_glob < p.N) {
-                for (int m = 0; m < p.M; ++m) {
-                    float v[CPL];
+            const bool n_ok = n_glob < p.N;
+            const int c_first = mm_share_owner(t_lo, p.total_u, P), c_last = mm_share_owner(t_hi - 1, p.total_u, P);
+            auto others_published = [&]() {
+                bool all = true;
+                for (int c = c_first + lane; c <= c_last; c += 32) {
+                    if (c == cta) continue;
+                    unsigned long long tg;
+                    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(tg) : "l"(p.tags + tile + c) : "memory");
+                    all = all && tg == p.nonce;
+                }
+                all = __all_sync(0xffffffffu, all);
+                __syncwarp();
+                return all;
+            };
+            // While the teams still work on this CTA's piece of a shared tile, see whether the other contributors
+            // have published theirs already (the usual case for the piece a CTA works on last: its neighbour did
+            // that tile first), and with one or two rows fetch their partial tiles right away: the hand-over below
+            // then needs no global round trip.
+            bool early = false;
+            constexpr int PRE_M = 2;
+            float pre[PRE_M][2][CPL];   // [row][contributors before / after this CTA][column]
+            if (!whole) {
+                if (sg == 0) pdl_wait_for_prerequisites();   // first touch of the workspace
+                early = others_published();
+                if (early && p.M <= PRE_M && c_last - cta <= 1) {
+                    __threadfence();
 #pragma unroll
-                    for (int c = 0; c < CPL; ++c) v[c] = 0.f;
+                    for (int m = 0; m < PRE_M; ++m) {
 #pragma unroll
-                    for (int tm = 0; tm < MM_TEAMS; ++tm) {
-                        if (cnt >= MM_TEAMS || (tm - j_lo % MM_TEAMS + MM_TEAMS) % MM_TEAMS < cnt) {
-                            const float4 *src = reinterpret_cast<const float4 *>(part + (tm * p.M + m) * TN + n);
+                        for (int c = 0; c < CPL; ++c) pre[m][0][c] = pre[m][1][c] = 0.f;
+                        if (m < p.M && n_ok) {
+                            for (int c = c_first; c <= c_last; ++c) {
+                                if (c == cta) continue;
+                                const float4 *src = reinterpret_cast<const float4 *>(p.slots + ((size_t)(tile + c) * p.M + m) * TN + n);
 #pragma unroll
-                            for (int c = 0; c < CPL / 4; ++c) {
-                                const float4 a = src[c];
-                                v[4 * c] += a.x; v[4 * c + 1] += a.y; v[4 * c + 2] += a.z; v[4 * c + 3] += a.w;
+                                for (int q4 = 0; q4 < CPL / 4; ++q4) {
+                                    const float4 a = __ldcg(src + q4);
+                                    if (c > cta) {
+                                        pre[m][1][4 * q4] += a.x; pre[m][1][4 * q4 + 1] += a.y; pre[m][1][4 * q4 + 2] += a.z; pre[m][1][4 * q4 + 3] += a.w;
+                                    } else {
+                                        pre[m][0][4 * q4] += a.x; pre[m][0][4 * q4 + 1] += a.y; pre[m][0][4 * q4 + 2] += a.z; pre[m][0][4 * q4 + 3] += a.w;
+                                    }
+                                }
                             }
                         }
                     }
-                    if (whole) {
-                        uint32_t o[CPL / 2];
+                }
+            }
+            if (!mbar_wait(seg_done, sg & 1, abort_flag, 0x330u)) break;
+            if (whole && sg == 0) pdl_wait_for_prerequisites();   // first write to the output
+            // this CTA's sum over its teams for row m of the tile
+            auto own_row = [&](int m, float (&v)[CPL]) {
 #pragma unroll
-                        for (int c = 0; c < CPL / 2; ++c) {
-                            float lo = v[2 * c], hi = v[2 * c + 1];
-                            if (p.bias) {
-                                lo += load_as_float(p.bias, p.sc_type, n_glob + 2 * c);
-                                hi += load_as_float(p.bias, p.sc_type, n_glob + 2 * c + 1);
-                            }
-                            if constexpr (BF16) {
-                                __nv_bfloat162 t2 = __floats2bfloat162_rn(lo, hi);
-                                o[c] = *reinterpret_cast<uint32_t *>(&t2);
-                            } else {
-                                __half2 t2 = __floats2half2_rn(lo, hi);
-                                o[c] = *reinterpret_cast<uint32_t *>(&t2);
-                            }
+                for (int c = 0; c < CPL; ++c) v[c] = 0.f;
+#pragma unroll
+                for (int tm = 0; tm < MM_TEAMS; ++tm) {
+                    if (cnt >= MM_TEAMS || (tm - j_lo % MM_TEAMS + MM_TEAMS) % MM_TEAMS < cnt) {
+                        const float4 *src = reinterpret_cast<const float4 *>(part + (tm * p.M + m) * TN + n);
+#pragma unroll
+                        for (int c = 0; c < CPL / 4; ++c) {
+                            const float4 a = src[c];
+                            v[4 * c] += a.x; v[4 * c + 1] += a.y; v[4 * c + 2] += a.z; v[4 * c + 3] += a.w;
                         }
-                        uint16_t *dst = static_cast<uint16_t *>(p.out) + (size_t)m * p.N + n_glob;
-                        if constexpr (Q8) *reinterpret_cast<uint2 *>(dst) = make_uint2(o[0], o[1]);
-                        else *reinterpret_cast<uint4 *>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
+                    }
+                }
+            };
+            auto write_row = [&](int m, const float (&v)[CPL]) {
+                uint32_t o[CPL / 2];
+#pragma unroll
+                for (int c = 0; c < CPL / 2; ++c) {
+                    float lo = v[2 * c], hi = v[2 * c + 1];
+                    if (p.bias) {
+                        lo += load_as_float(p.bias, BF16 ? ET_BF16 : ET_F16, n_glob + 2 * c);
+                        hi += load_as_float(p.bias, BF16 ? ET_BF16 : ET_F16, n_glob + 2 * c + 1);
+                    }
+                    if constexpr (BF16) {
+                        __nv_bfloat162 t2 = __floats2bfloat162_rn(lo, hi);
+                        o[c] = *reinterpret_cast<uint32_t *>(&t2);
                     } else {
-                        float4 *dst = reinterpret_cast<float4 *>(p.slots + ((size_t)(tile + cta) * p.M + m) * TN + n);
-#pragma unroll
-                        for (int c = 0; c < CPL / 4; ++c) dst[c] = make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+                        o[c] = pack_f16x2(lo, hi);
                     }
+                }
+                uint16_t *dst = static_cast<uint16_t *>(p.out) + (size_t)m * p.N + n_glob;
+                if constexpr (Q8) *reinterpret_cast<uint2 *>(dst) = make_uint2(o[0], o[1]);
+                else *reinterpret_cast<uint4 *>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
+            };
+            if (whole) {
+                if (n_ok) {
+                    for (int m = 0; m < p.M; ++m) {
+                        float v[CPL];
+                        own_row(m, v);
+                        write_row(m, v);
+                    }
+                }
+            } else {
+                // A tile shared between CTAs.  Each contributor looks whether all the OTHERS have published their
+                // partial tiles; if so it adds its own (still in shared memory) in contributor order and writes the
+                // tile.  Otherwise it publishes its own partial tile and looks again; whoever then sees them all sums
+                // them.  No CTA ever waits for another; two contributors that publish together may both see all tags
+                // and both write the (identical) tile.  The tag is a value unique to this launch, so whatever an
+                // earlier use left in the workspace never matches; the finisher clears the tags again so that a replay
+                // of the same launch (a captured graph) starts clean.
+                // sum in contributor order, this CTA's own part from shared memory
+                auto finish = [&]() {
+                    __threadfence();   // every lane's reads below come after the tags this warp has seen
+                    if (n_ok) {
+                        for (int m = 0; m < p.M; ++m) {
+                            float own[CPL], v[CPL];
+                            own_row(m, own);
+#pragma unroll
+                            for (int c = 0; c < CPL; ++c) v[c] = 0.f;
+                            for (int c = c_first; c <= c_last; ++c) {
+                                if (c == cta) {
+#pragma unroll
+                                    for (int q4 = 0; q4 < CPL; ++q4) v[q4] += own[q4];
+                                } else {
+                                    const float4 *src = reinterpret_cast<const float4 *>(p.slots + ((size_t)(tile + c) * p.M + m) * TN + n);
+#pragma unroll
+                                    for (int q4 = 0; q4 < CPL / 4; ++q4) {
+                                        const float4 a = __ldcg(src + q4);   // written by other SMs: read at L2
+                                        v[4 * q4] += a.x; v[4 * q4 + 1] += a.y; v[4 * q4 + 2] += a.z; v[4 * q4 + 3] += a.w;
+                                    }
+                                }
+                            }
+                            write_row(m, v);
+                        }
+                    }
+                    __syncwarp();
+                    for (int c = c_first + lane; c <= c_last; c += 32) p.tags[tile + c] = 0ull;
+                };
+                if (early && p.M <= PRE_M && c_last - cta <= 1) {
+                    // the others' sums are in registers: (before + own) + after is finish()'s order exactly when at
+                    // most one contributor comes after this CTA, so the bits do not depend on who finishes the tile
+                    if (n_ok) {
+#pragma unroll
+                        for (int m = 0; m < PRE_M; ++m) {
+                            if (m >= p.M) break;
+                            float own[CPL], v[CPL];
+                            own_row(m, own);
+#pragma unroll
+                            for (int c = 0; c < CPL; ++c) v[c] = (pre[m][0][c] + own[c]) + pre[m][1][c];
+                            write_row(m, v);
+                        }
+                    }
+                    __syncwarp();
+                    for (int c = c_first + lane; c <= c_last; c += 32) p.tags[tile + c] = 0ull;
+                } else if (early || others_published()) {
+                    finish();
+                } else {
+                    if (n_ok) {
+                        for (int m = 0; m < p.M; ++m) {
+                            float v[CPL];
+                            own_row(m, v);
+                            float4 *dst = reinterpret_cast<float4 *>(p.slots + ((size_t)(tile + cta) * p.M + m) * TN + n);
+#pragma unroll
+                            for (int c = 0; c < CPL / 4; ++c) dst[c] = make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+                        }
+                    }
+                    __threadfence();
+                    __syncwarp();
+                    if (lane == 0) {
+                        asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(p.tags + tile + cta), "l"(p.nonce) : "memory");
+                        asm volatile("fence.sc.gpu;" ::: "memory");
+                    }
+                    __syncwarp();
+                    if (others_published()) finish();
                 }
             }
             __syncwarp();
@@ -446,19 +729,60 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
     }
 }
 
-// Sums the partial tiles of every output tile that was shared between CTAs, adds the bias, casts.
-__global__ void wq_mma_finalize_kernel(MmParams p, int P) {
-    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= (size_t)p.M * p.N) return;
-    const int n = (int)(i % p.N), m = (int)(i / p.N);
-    const int tile = n / p.tile_n;
-    const long long qa = (long long)tile * p.qpt;
-    const int c_first = mm_share_owner(qa, p.total_q, P), c_last = mm_share_owner(qa + p.qpt - 1, p.total_q, P);
-    if (c_first == c_last) return;  // written directly by its only owner
-    float v = 0.f;
-    for (int c = c_first; c <= c_last; ++c) v += p.slots[((size_t)(tile + c) * p.M + m) * p.tile_n + (n % p.tile_n)];
-    if (p.bias) v += load_as_float(p.bias, p.sc_type, n);
-    store_from_float(p.out, p.out_type, i, v);
+// ---- the tile-packed weight layout --------------------------------------------------------------
+// int4 weights [K,N] re-laid as blocks of 16 KB, one per (tile of 256 columns, stage of 128 K rows),
+// tile-major ([tile][stage]) so that a CTA's stream-K share is one contiguous range.  Inside a block
+// the order is [warp quarter wq = 64 columns][step st = 16 K rows][lane = (g, t)][word r]: the 16 bytes
+// a lane of the decode kernel needs for one step, so a step is one 16-byte shared-memory load and no
+// byte shuffling.  Word r covers the lane's columns c + 2r, c + 2r + 1 (c = 256 tile + 64 wq + 8 g) and
+// rows k + 2t, k + 2t + 1, k + 2t + 8, k + 2t + 9 (k = 128 stage + 16 st): nibble 0 / 4 = column 2r at
+// rows 2t / 2t+1, nibble 1 / 5 = column 2r+1, nibbles 2 / 6 and 3 / 7 the same at rows 2t+8 / 2t+9.
+// Columns beyond N and rows beyond K are zero.
+__host__ __device__ inline void nz_source(int nib, int &dk, int &dc) {
+    dc = nib & 1;                                  // column 2r + dc
+    dk = ((nib >> 2) & 1) + ((nib >> 1) & 1) * 8;  // row 2t + dk
+}
+
+__global__ void wq_pack_nz_kernel(const uint8_t *w, uint32_t *out, int K, int N, int num_sb, long long words) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= words) return;
+    const int r = (int)(i & 3), lane = (int)((i >> 2) & 31), st = (int)((i >> 7) & 7), wq = (int)((i >> 10) & 3);
+    const long long blk = i >> 12;
+    const int sb = (int)(blk % num_sb), tile = (int)(blk / num_sb);
+    const int g = lane >> 2, t = lane & 3;
+    const int c = tile * 256 + wq * 64 + 8 * g + 2 * r, k = sb * 128 + st * 16 + 2 * t;
+    uint32_t word = 0;
+#pragma unroll
+    for (int nib = 0; nib < 8; ++nib) {
+        int dk, dc;
+        nz_source(nib, dk, dc);
+        const int kk = k + dk, cc = c + dc;
+        if (kk < K && cc < N) {
+            const size_t idx = (size_t)kk * N + cc;
+            word |= (uint32_t)((w[idx >> 1] >> ((idx & 1) * 4)) & 0xF) << (4 * nib);
+        }
+    }
+    out[i] = word;
+}
+
+// Back to the caller's layout (one thread per 8 consecutive columns of a row = one packed word).
+__global__ void wq_unpack_nz_kernel(const uint32_t *nz, uint32_t *out, int K, int N, int num_sb) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const int wpr = N / 8;
+    if (i >= (long long)K * wpr) return;
+    const int k = (int)(i / wpr), c = (int)(i % wpr) * 8;
+    const int tile = c >> 8, wq = (c >> 6) & 3, g = (c >> 3) & 7;
+    const int sb = k >> 7, st = (k >> 4) & 7, kr = k & 15, t = (kr & 7) >> 1;
+    const int nib_base = (kr & 1) * 4 + (kr >> 3) * 2;   // + dc
+    const uint4 v = *reinterpret_cast<const uint4 *>(nz + ((((size_t)tile * num_sb + sb) * 4 + wq) * 8 + st) * 128 + (4 * g + t) * 4);
+    const uint32_t src[4] = {v.x, v.y, v.z, v.w};
+    uint32_t word = 0;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        word |= ((src[r] >> (4 * nib_base)) & 0xFu) << (8 * r);
+        word |= ((src[r] >> (4 * (nib_base + 1))) & 0xFu) << (8 * r + 4);
+    }
+    out[i] = word;
 }
 
 int mm_sm_count() {
@@ -477,9 +801,9 @@ int mm_sm_count() {
 }
 
 struct MmPlan {
-    int mf, tiles, sbq, qpt, grouped, P;
-    long long total_q;
-    uint64_t slot_bytes;
+    int mf, tiles, num_sb, gsb, P;
+    long long total_u;
+    uint64_t slot_bytes, tag_bytes;
 };
 
 MmPlan mm_make_plan(const MatmulArgs &p) {
@@ -487,13 +811,11 @@ MmPlan mm_make_plan(const MatmulArgs &p) {
     pl.mf = p.M <= 8 ? 1 : 2;
     const int tile_n = p.b_type == ET_I8 ? 128 : 256;
     pl.tiles = (int)((p.N + tile_n - 1) / tile_n);
-    const int num_sb = (int)((p.K + MM_SBK - 1) / MM_SBK);
-    pl.grouped = p.group < p.K ? 1 : 0;
-    pl.sbq = pl.grouped ? (int)(p.group / MM_SBK) : 1;
-    pl.qpt = num_sb / pl.sbq;
-    pl.total_q = (long long)pl.tiles * pl.qpt;
+    pl.num_sb = (int)((p.K + MM_SBK - 1) / MM_SBK);
+    pl.gsb = p.group < p.K ? (int)(p.group / MM_SBK) : pl.num_sb;
+    pl.total_u = (long long)pl.tiles * pl.num_sb;
     const int sms = mm_sm_count();
-    pl.P = (int)(pl.total_q < sms ? pl.total_q : sms);
+    pl.P = (int)(pl.total_u < sms ? pl.total_u : sms);
     // Small problems: with one whole tile per CTA every tile is finished where it was computed and the
     // finalize kernel (about 3 us at this scale) is not launched.  Worth it when streaming a whole tile
     // into one SM (about 50 GB/s) costs less than an even share plus that launch.
@@ -505,45 +827,57 @@ MmPlan mm_make_plan(const MatmulArgs &p) {
         if (whole) pl.P = pl.tiles;
     }
     // Shares that do not straddle tiles: with a few CTAs fewer, every share can be an equal divisor (or
-    // multiple) of a tile's quanta, so each CTA adds to one tile only and fewer partial tiles are written and
+    // multiple) of a tile's stages, so each CTA adds to one tile only and fewer partial tiles are written and
     // summed (4096 x 4096 int4 at M = 16: 16.7 us on 148 CTAs, 14.9 us on 128).  Take the largest such CTA
     // count within 15 % of the SM count.  B200_QMM_WQ_MMA_P=<n> overrides.
-    if (pl.P == sms && pl.total_q < 8LL * sms) {   // small problems only: large ones are bound by the work per SM
+    if (pl.P == sms && pl.total_u < 8LL * sms) {   // small problems only: large ones are bound by the work per SM
         for (int c = sms; c >= sms - sms * 15 / 100; --c) {
-            if (pl.total_q % c != 0) continue;
-            const long long share = pl.total_q / c;
-            if (pl.qpt % share == 0 || share % pl.qpt == 0) { pl.P = c; break; }
+            if (pl.total_u % c != 0) continue;
+            const long long share = pl.total_u / c;
+            if (pl.num_sb % share == 0 || share % pl.num_sb == 0) { pl.P = c; break; }
         }
     }
-    if (const char *e = getenv("B200_QMM_WQ_MMA_P")) { const int v = atoi(e); if (v >= 1 && v <= sms && v <= pl.total_q) pl.P = v; }
-    pl.slot_bytes = (uint64_t)(pl.tiles + pl.P) * p.M * tile_n * sizeof(float);
+    if (const char *e = getenv("B200_QMM_WQ_MMA_P")) { const int v = atoi(e); if (v >= 1 && v <= sms && v <= pl.total_u) pl.P = v; }
+    pl.slot_bytes = align_up_u64((uint64_t)(pl.tiles + pl.P) * p.M * tile_n * sizeof(float), 256);
+    pl.tag_bytes = align_up_u64((uint64_t)(pl.tiles + pl.P) * sizeof(unsigned long long), 256);
     return pl;
 }
 
-constexpr int MM_TEAMS_USED = 3;
 constexpr int MM_SMEM_LIMIT = 232448;
 
-// Ring depth: every slot must belong to one team (a team then meets the phases of a slot's barrier in
-// order), so the depth is c x teams, and with two super-blocks per quantum c must be even.  Three or
-// four slots per team hide the HBM round trip (one being read, the others in flight); take the
-// deepest ring that fits beside the partial tiles.
+// A 64-bit value no earlier launch of this process has used and that stale workspace contents match with
+// probability 2^-64: a counter run through a bijective mixer, seeded once from the clock and an address.
+unsigned long long mm_next_nonce() {
+    static std::atomic<unsigned long long> counter{[] {
+        unsigned long long seed = (unsigned long long)std::chrono::steady_clock::now().time_since_epoch().count();
+        int probe = 0;
+        return seed ^ ((unsigned long long)(uintptr_t)&probe << 17) ^ 0x9E3779B97F4A7C15ull;
+    }()};
+    unsigned long long z = counter.fetch_add(0x9E3779B97F4A7C15ull) + 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    z ^= z >> 31;
+    return z ? z : 1ull;
+}
+
+// Ring depth: every slot must belong to one team, so the depth is c x teams.  Three slots per team hide
+// the HBM round trip (one being read, the others in flight); take the deepest ring up to that which fits
+// beside the partial tiles.
 template <int MF>
-int mm_ring_slots(int M, int sbq) {
-    for (int c = 4; c >= 2; --c) {
-        if (sbq == 2 && (c & 1)) continue;
-        if (MmSmem<MF>::total(c * MM_TEAMS_USED, MM_TEAMS_USED, M) <= MM_SMEM_LIMIT) return c * MM_TEAMS_USED;
-    }
+int mm_ring_slots(int M) {
+    for (int c = 3; c >= 2; --c)
+        if (MmSmem<MF>::total(c * MM_TEAMS, M) <= MM_SMEM_LIMIT) return c * MM_TEAMS;
     return 0;
 }
 
-template <bool Q8, bool BF16, int MF>
-cudaError_t mm_launch_one(const CUtensorMap &tx, const CUtensorMap &tw, MmParams mp, int P, cudaStream_t s) {
+template <bool Q8, bool BF16, int MF, bool NZ>
+cudaError_t mm_launch_one(const CUtensorMap &tw, MmParams mp, int P, cudaStream_t s) {
     using L = MmSmem<MF>;
     static_assert(L::SLOT % 1024 == 0, "slots keep the swizzle alignment");
-    mp.ns = mm_ring_slots<MF>(mp.M, mp.sbq);
+    mp.ns = mm_ring_slots<MF>(mp.M);
     if (mp.ns == 0) return cudaErrorInvalidValue;
-    const int smem = L::total(mp.ns, MM_TEAMS_USED, mp.M);
-    auto kern = wq_mma_kernel<Q8, BF16, MF, MM_TEAMS_USED>;
+    const int smem = L::total(mp.ns, mp.M);
+    auto kern = wq_mma_kernel<Q8, BF16, MF, NZ>;
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -552,9 +886,24 @@ cudaError_t mm_launch_one(const CUtensorMap &tx, const CUtensorMap &tw, MmParams
         if (e != cudaSuccess) return e;
         attr_set[dev & 63] = true;
     }
-    kern<<<P, (4 * MM_TEAMS_USED + 2) * 32, smem, s>>>(tx, tw, mp);
+    // Programmatic stream serialisation (see pdl_wait_for_prerequisites).  B200_QMM_PDL=0 launches the plain way;
+    // B200_QMM_PDL=2 additionally lets the weight stream start before the preceding kernel has completed, which is
+    // only right when that kernel does not write this call's weights, scales or offsets.
+    static const int pdl = [] { const char *e = getenv("B200_QMM_PDL"); return e ? atoi(e) : 1; }();
+    mp.weights_early = pdl >= 2 ? 1 : 0;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)P);
+    cfg.blockDim = dim3(MM_THREADS);
+    cfg.dynamicSmemBytes = (size_t)smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl >= 1 ? 1 : 0;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tw, mp);
     count_launch();
-    return cudaGetLastError();
+    return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 }  // namespace
@@ -564,13 +913,10 @@ bool wq_mma_supported(const MatmulArgs &p) {
     if (p.batch != 1 || p.b_transposed || p.accumulate || p.M < 1 || p.M > 16) return false;
     if (p.a_type != ET_F16 && p.a_type != ET_BF16) return false;
     if (p.b_type != ET_I4 && p.b_type != ET_I8) return false;
+    if (p.b_nz && p.b_type != ET_I4) return false;
     if (p.sc_type != p.a_type || p.out_type != p.a_type || (p.bias && p.bias_type != p.a_type)) return false;
     if (p.K % 8 != 0 || p.K < MM_SBK || p.N % (p.b_type == ET_I4 ? 32 : 16) != 0) return false;
-    if (p.group < p.K) {
-        if (p.group % MM_SBK != 0 || p.K % p.group != 0) return false;
-        // a ring slot must belong to one team: the ring is two quanta per team deep
-        if (p.group / MM_SBK > 2) return false;
-    }
+    if (p.group < p.K && (p.group % MM_SBK != 0 || p.K % p.group != 0)) return false;
     if (p.N > (1 << 24) || p.K > (1 << 24)) return false;
     if (const char *e = getenv("B200_QMM_WQ_MMA")) {
         if (atoi(e) == 0) return false;
@@ -578,55 +924,78 @@ bool wq_mma_supported(const MatmulArgs &p) {
     return true;
 }
 
-uint64_t wq_mma_workspace_bytes(const MatmulArgs &p) { return mm_make_plan(p).slot_bytes; }
+uint64_t wq_mma_workspace_bytes(const MatmulArgs &p) {
+    const MmPlan pl = mm_make_plan(p);
+    return pl.slot_bytes + pl.tag_bytes;
+}
 
 cudaError_t launch_wq_mma(const MatmulArgs &p, cudaStream_t s) {
     const MmPlan pl = mm_make_plan(p);
-    if (p.workspace_bytes < pl.slot_bytes || !p.workspace) return cudaErrorInvalidValue;
-    // TMA sources, the 16-byte scale / offset loads, the 16-byte output stores and the float4 partial
-    // tiles all need 16-byte aligned bases (every row pitch already is a multiple of 16 bytes).
+    if (p.workspace_bytes < pl.slot_bytes + pl.tag_bytes || !p.workspace) return cudaErrorInvalidValue;
+    // TMA / bulk-copy sources, the 16-byte activation, scale and offset loads, the 16-byte output stores and
+    // the float4 partial tiles all need 16-byte aligned bases (every row pitch already is a multiple of 16 bytes).
     if ((reinterpret_cast<uintptr_t>(p.a) & 15) || (reinterpret_cast<uintptr_t>(p.b) & 15) ||
         (reinterpret_cast<uintptr_t>(p.scale) & 15) || (reinterpret_cast<uintptr_t>(p.offset) & 15) ||
         (reinterpret_cast<uintptr_t>(p.out) & 15) || (reinterpret_cast<uintptr_t>(p.workspace) & 15))
         return cudaErrorMisalignedAddress;
-    const bool bf = p.a_type == ET_BF16;
-    CUtensorMap tx, tw;
-    // No L2 promotion: every byte of the weight stream is used exactly once by exactly one CTA, and
-    // fetching wider L2 lines than asked for measurably slows the stream down.
-    bool ok = make_map(&tx, p.a, bf ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, p.K, p.M, p.K * 2, 64,
-                       pl.mf * 8, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE);
-    const bool q8 = p.b_type == ET_I8;
-    const uint64_t row_bytes = q8 ? (uint64_t)p.N : (uint64_t)p.N / 2;
-    ok = ok && make_map(&tw, p.b, CU_TENSOR_MAP_DATA_TYPE_UINT8, row_bytes, p.K, row_bytes, 128, MM_SBK, CU_TENSOR_MAP_SWIZZLE_128B,
-                        CU_TENSOR_MAP_L2_PROMOTION_NONE);
-    if (!ok) return cudaErrorInvalidValue;
+    const bool bf = p.a_type == ET_BF16, q8 = p.b_type == ET_I8;
+    CUtensorMap tw{};
+    if (!p.b_nz) {
+        // No L2 promotion: every byte of the weight stream is used exactly once by exactly one CTA, and
+        // fetching wider L2 lines than asked for measurably slows the stream down.
+        const uint64_t row_bytes = q8 ? (uint64_t)p.N : (uint64_t)p.N / 2;
+        if (!make_map(&tw, p.b, CU_TENSOR_MAP_DATA_TYPE_UINT8, row_bytes, p.K, row_bytes, 128, MM_SBK, CU_TENSOR_MAP_SWIZZLE_128B,
+                      CU_TENSOR_MAP_L2_PROMOTION_NONE))
+            return cudaErrorInvalidValue;
+    }
 
     MmParams mp{};
     mp.out = p.out;
     mp.slots = (float *)p.workspace;
+    mp.tags = (unsigned long long *)((char *)p.workspace + pl.slot_bytes);
+    mp.nonce = mm_next_nonce();
+    mp.x = p.a;
     mp.scale = p.scale; mp.offset = p.offset; mp.bias = p.bias;
-    mp.sc_type = p.sc_type; mp.out_type = p.out_type;
+    mp.wnz = p.b_nz ? (const uint8_t *)p.b : nullptr;
+    mp.x_bf16 = bf ? 1 : 0;
     mp.M = (int)p.M; mp.N = (int)p.N; mp.K = (int)p.K;
-    mp.sbq = pl.sbq; mp.qpt = pl.qpt; mp.total_q = pl.total_q; mp.grouped = pl.grouped;
+    mp.num_sb = pl.num_sb; mp.total_u = pl.total_u; mp.gsb = pl.gsb;
     mp.tile_n = q8 ? 128 : 256;
 
     cudaError_t e;
-    if (q8) {
-        if (pl.mf == 1) e = bf ? mm_launch_one<true, true, 1>(tx, tw, mp, pl.P, s) : mm_launch_one<true, false, 1>(tx, tw, mp, pl.P, s);
-        else e = bf ? mm_launch_one<true, true, 2>(tx, tw, mp, pl.P, s) : mm_launch_one<true, false, 2>(tx, tw, mp, pl.P, s);
-    } else {
-        if (pl.mf == 1) e = bf ? mm_launch_one<false, true, 1>(tx, tw, mp, pl.P, s) : mm_launch_one<false, false, 1>(tx, tw, mp, pl.P, s);
-        else e = bf ? mm_launch_one<false, true, 2>(tx, tw, mp, pl.P, s) : mm_launch_one<false, false, 2>(tx, tw, mp, pl.P, s);
-    }
-    if (e != cudaSuccess) return e;
-    // Tiles shared between CTAs exist unless every share boundary falls on a tile boundary.
-    if (pl.total_q % pl.P != 0 || (pl.total_q / pl.P) % pl.qpt != 0) {
-        const size_t mn = (size_t)p.M * p.N;
-        wq_mma_finalize_kernel<<<(unsigned)((mn + 255) / 256), 256, 0, s>>>(mp, pl.P);
-        count_launch();
-        e = cudaGetLastError();
-    }
+#define MM_GO(Q8_, NZ_) (pl.mf == 1 ? (bf ? mm_launch_one<Q8_, true, 1, NZ_>(tw, mp, pl.P, s) : mm_launch_one<Q8_, false, 1, NZ_>(tw, mp, pl.P, s)) \
+                                    : (bf ? mm_launch_one<Q8_, true, 2, NZ_>(tw, mp, pl.P, s) : mm_launch_one<Q8_, false, 2, NZ_>(tw, mp, pl.P, s)))
+    if (q8) e = MM_GO(true, false);
+    else if (p.b_nz) e = MM_GO(false, true);
+    else e = MM_GO(false, false);
+#undef MM_GO
     return e;
+}
+
+// ---- the tile-packed layout: size, pack, unpack -----------------------------------------------------
+uint64_t wq_nz_bytes(int64_t K, int64_t N) {
+    const uint64_t tiles = (uint64_t)(N + MM_TILE_N - 1) / MM_TILE_N, num_sb = (uint64_t)(K + MM_SBK - 1) / MM_SBK;
+    return tiles * num_sb * MM_W_BYTES;
+}
+
+cudaError_t launch_wq_pack_nz(const void *w_nd, void *w_nz, int64_t K, int64_t N, cudaStream_t s) {
+    if ((N & 1) || K < 1 || N < 1 || K > (1 << 24) || N > (1 << 24)) return cudaErrorInvalidValue;
+    if (reinterpret_cast<uintptr_t>(w_nz) & 15) return cudaErrorMisalignedAddress;
+    const long long words = (long long)(wq_nz_bytes(K, N) / 4);
+    const int num_sb = (int)((K + MM_SBK - 1) / MM_SBK);
+    wq_pack_nz_kernel<<<(unsigned)((words + 255) / 256), 256, 0, s>>>((const uint8_t *)w_nd, (uint32_t *)w_nz, (int)K, (int)N, num_sb, words);
+    count_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t launch_wq_unpack_nz(const void *w_nz, void *w_nd, int64_t K, int64_t N, cudaStream_t s) {
+    if ((N & 7) || K < 1 || N < 1) return cudaErrorInvalidValue;
+    if ((reinterpret_cast<uintptr_t>(w_nz) & 15) || (reinterpret_cast<uintptr_t>(w_nd) & 3)) return cudaErrorMisalignedAddress;
+    const long long words = (long long)K * (N / 8);
+    const int num_sb = (int)((K + MM_SBK - 1) / MM_SBK);
+    wq_unpack_nz_kernel<<<(unsigned)((words + 255) / 256), 256, 0, s>>>((const uint32_t *)w_nz, (uint32_t *)w_nd, (int)K, (int)N, num_sb);
+    count_launch();
+    return cudaGetLastError();
 }
 
 unsigned int wq_mma_device_status() {

@@ -7,7 +7,7 @@ import numpy as np
 import pytest
 import torch
 
-from util import assert_close, dev_or_none, errors, f32, to_np
+from util import assert_close, dev_or_none, errors, f32, nz_layout_model, to_np
 
 pytestmark = pytest.mark.gpu
 
@@ -517,6 +517,78 @@ def test_mx_matmul(pkg, oracle, workloads, dev, path, kinds, shape):
             with forced_path(path):
                 out = run_mx(pkg, d, dev, odt, name)
             assert_close(to_np(out), want, f"{name} {kinds} {shape} {odt} path={path}")
+
+
+# ------------------------------------------------------------------ the tile-packed weight layout
+@pytest.mark.parametrize("shape", [(128, 256), (1024, 512), (1160, 800), (264, 32)])
+def test_weight_pack_layout_and_round_trip(pkg, workloads, dev, shape):
+    """aclnnCalculateMatmulWeightSizeV2 + aclnnTransMatmulWeight into an ACL_FORMAT_FRACTAL_NZ tensor:
+    the packed bytes equal the layout's definition word for word (ragged K and N are zero-padded), and a
+    matmul with more rows than the decode kernel takes -- which lays the weights back into [K,N] first --
+    gives the same bits as the call on the original weights."""
+    K, N = shape
+    d = workloads.w4a16(M=40, K=K, N=N, per_channel=True, dtype=torch.float16, seed=8400 + K)
+    w = d["w"].to(dev)
+    packed = pkg.pack_weight_nz(w, K, N)
+    torch.cuda.synchronize()
+    tiles, num_sb = (N + 255) // 256, (K + 127) // 128
+    assert packed.numel() == tiles * num_sb * 16384
+    want = nz_layout_model(d["w_vals"].numpy())
+    assert np.array_equal(packed.cpu().numpy().view(np.uint32), want)
+    x, sc, of, bi = (d[k].to(dev) for k in ("x", "scale", "offset", "bias"))
+    a = pkg.weight_quant_matmul(x, w, sc, of, bi, int4=True)
+    b = pkg.weight_quant_matmul(x, packed, sc, of, bi, int4=True, nz=True)
+    torch.cuda.synchronize()
+    assert torch.equal(a, b)
+    # an identity copy for everything else, as before: int8 weights, or an ND destination
+    o = torch.empty_like(w)
+    pkg.call("aclnnTransMatmulWeight", pkg.AclTensor(w, pkg.ACL_INT4, (K, N)), pkg.AclTensor(o, pkg.ACL_INT4, (K, N)))
+    torch.cuda.synchronize()
+    assert torch.equal(o, w)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M", [1, 2, 5, 8, 9, 16])
+@pytest.mark.parametrize("case", [
+    dict(K=1024, N=512, group=128),
+    dict(K=2048, N=1536, group=256, with_offset=False),
+    dict(K=1160, N=800, per_channel=True),               # K and N off every tile size: zero padding
+    dict(K=8192, N=256, group=128, with_bias=False),     # one tile cut into many K shares
+    dict(K=128, N=8192, group=128),                      # one stage per tile, more tiles than SMs
+])
+def test_w4a16_decode_kernel_packed_weights(pkg, oracle, workloads, dev, case, M, dtype):
+    """The decode kernel on tile-packed weights (contiguous 16 KB copies, one 16-byte shared-memory load per
+    step) against the oracle, and bit for bit against the same call on the caller's layout: both feed the
+    tensor core the same fragments in the same order."""
+    d = workloads.w4a16(M=M, dtype=dtype, seed=8500 + M, **case)
+    K, N = d["K"], d["N"]
+    w = d["w"].to(dev)
+    packed = pkg.pack_weight_nz(w, K, N)
+    args = (d["x"].to(dev),)
+    rest = (d["scale"].to(dev), dev_or_none(d["offset"], dev), dev_or_none(d["bias"], dev))
+    got = pkg.weight_quant_matmul(args[0], packed, *rest, int4=True, group=d["group"], nz=True)
+    plain = pkg.weight_quant_matmul(args[0], w, *rest, int4=True, group=d["group"])
+    torch.cuda.synchronize()
+    assert_close(to_np(got), ref_wq(oracle, d), f"packed weights M={M} {case} {dtype}")
+    assert torch.equal(got, plain)
+
+
+def test_packed_weights_large_m_and_rejections(pkg, oracle, workloads, dev):
+    """More rows than the decode kernel takes: the weights are laid back into [K,N] in the workspace and the
+    usual kernels run (17..128 rows: streaming kernel; more: expansion + dense).  int8 weights have no packed
+    form (the format tag is ignored, identity copy), and a packed tensor whose storage is too small is refused."""
+    for M in (17, 100, 300):
+        d = workloads.w4a16(M=M, K=1024, N=1024, group=128, seed=8600 + M)
+        packed = pkg.pack_weight_nz(d["w"].to(dev), 1024, 1024)
+        got = pkg.weight_quant_matmul(d["x"].to(dev), packed, d["scale"].to(dev), d["offset"].to(dev), d["bias"].to(dev), int4=True,
+                                      group=128, nz=True)
+        torch.cuda.synchronize()
+        assert_close(to_np(got), ref_wq(oracle, d), f"packed weights, M={M}")
+    w = torch.zeros(256 * 256 // 2, dtype=torch.uint8, device=dev)
+    small = torch.zeros(100, dtype=torch.uint8, device=dev)
+    st = pkg.call("aclnnTransMatmulWeight", pkg.AclTensor(w, pkg.ACL_INT4, (256, 256)),
+                  pkg.AclTensor(small, pkg.ACL_INT4, (256, 256), fmt=pkg.ACL_FORMAT_FRACTAL_NZ, storage=(200,)), return_status=True)
+    assert st == 161002
 
 
 # ------------------------------------------------------------------ benchmark configurations at full size

@@ -31,3 +31,22 @@ def f32(t):
 
 def dev_or_none(t, dev):
     return None if t is None else t.to(dev)
+
+
+def nz_layout_model(w_vals):
+    """The tile-packed int4 layout as plain index arithmetic: int values [K,N] in -8..7 -> uint32 words.
+    Blocks of 4096 words per (tile of 256 columns, stage of 128 rows), tile-major; inside a block
+    [wq = 64 columns][st = 16 rows][lane = 4 g + t][r]; word r of lane (g, t) holds columns
+    c + 2r, c + 2r + 1 (c = 256 tile + 64 wq + 8 g) at rows k + 2t + {0, 1, 8, 9} (k = 128 stage + 16 st):
+    nibble 0 / 4 = column 2r at rows 2t / 2t+1, 1 / 5 = column 2r+1, 2 / 6 and 3 / 7 the same 8 rows on."""
+    K, N = w_vals.shape
+    tiles, num_sb = (N + 255) // 256, (K + 127) // 128
+    pad = np.zeros((num_sb * 128, tiles * 256), dtype=np.uint32)
+    pad[:K, :N] = w_vals.astype(np.int64) & 0xF
+    v = pad.reshape(num_sb, 8, 2, 4, 2, tiles, 4, 8, 4, 2)   # [sb][st][half8][t][j] x [tile][wq][g][r][dc]
+    words = np.zeros((tiles, num_sb, 4, 8, 8, 4, 4), dtype=np.uint32)   # [tile][sb][wq][st][g][t][r]
+    for nib in range(8):
+        dc, j, half = nib & 1, (nib >> 2) & 1, (nib >> 1) & 1
+        src = v[:, :, half, :, j, :, :, :, :, dc]          # [sb][st][t][tile][wq][g][r]
+        words |= src.transpose(3, 0, 4, 1, 5, 2, 6) << np.uint32(4 * nib)
+    return words.reshape(-1)
