@@ -10,8 +10,14 @@
 #include <dlfcn.h>
 #include <nccl.h>
 
+#include <chrono>
+#include <condition_variable>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
+#include <memory>
+#include <mutex>
+#include <thread>
 
 #include "hccl/hccl.h"
 
@@ -34,7 +40,11 @@ struct Nccl {
 const Nccl &nccl() {
     static Nccl n = [] {
         Nccl t;
-        void *h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD);  // a copy the process already holds
+        void *h = nullptr;
+        // B200_HCCL_NCCL_LIB names the library to bind instead (the tests hand in a stand-in whose rendezvous
+        // never completes, to exercise the bootstrap time limit without a GPU)
+        if (const char *over = getenv("B200_HCCL_NCCL_LIB")) h = dlopen(over, RTLD_NOW | RTLD_LOCAL);
+        if (!h) h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD);  // a copy the process already holds
         if (!h) h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
         if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
         if (!h) {
@@ -106,10 +116,46 @@ HcclResult HcclCommInitRootInfo(uint32_t nRanks, const HcclRootInfo *rootInfo, u
     if (nRanks == 0 || rank >= nRanks) return HCCL_E_PARA;
     ncclUniqueId id;
     memcpy(&id, rootInfo->internal, sizeof(id));
-    ncclComm_t c = nullptr;
-    ncclResult_t r = nccl().CommInitRank(&c, (int)nRanks, id, (int)rank);
-    if (r != ncclSuccess) return from_nccl(r);
-    *comm = (HcclComm)c;
+    // The rendezvous blocks until every rank has joined.  A rank that never joins (it died, or was never started)
+    // would hold the others forever, so the call runs on a helper thread and is given up after
+    // B200_HCCL_INIT_TIMEOUT_S seconds (default 120; 0 = wait without limit): HCCL_E_TIMEOUT, and the caller can
+    // report the failure instead of hanging.  The helper thread stays behind in that case (it cannot be cancelled
+    // inside the library call); it keeps its own copy of everything it touches.
+    double limit_s = 120.0;
+    if (const char *e = getenv("B200_HCCL_INIT_TIMEOUT_S")) limit_s = atof(e);
+    int dev = -1;
+    cudaGetDevice(&dev);   // the helper thread must bind the communicator to the caller's device
+    struct Job {
+        std::mutex mu;
+        std::condition_variable cv;
+        bool done = false;
+        ncclComm_t comm = nullptr;
+        ncclResult_t result = ncclInternalError;
+    };
+    auto job = std::make_shared<Job>();
+    const auto init = nccl().CommInitRank;
+    std::thread worker([job, init, id, nRanks, rank, dev] {
+        if (dev >= 0) cudaSetDevice(dev);
+        ncclComm_t c = nullptr;
+        const ncclResult_t r = init(&c, (int)nRanks, id, (int)rank);
+        std::lock_guard<std::mutex> lk(job->mu);
+        job->comm = c; job->result = r; job->done = true;
+        job->cv.notify_all();
+    });
+    {
+        std::unique_lock<std::mutex> lk(job->mu);
+        if (limit_s <= 0) job->cv.wait(lk, [&] { return job->done; });
+        else if (!job->cv.wait_for(lk, std::chrono::duration<double>(limit_s), [&] { return job->done; })) {
+            lk.unlock();
+            worker.detach();
+            fprintf(stderr, "[b200-hccl] HcclCommInitRootInfo: rank %u of %u gave up after %.1f s waiting for the other ranks\n",
+                    rank, nRanks, limit_s);
+            return HCCL_E_TIMEOUT;
+        }
+    }
+    worker.join();
+    if (job->result != ncclSuccess) return from_nccl(job->result);
+    *comm = (HcclComm)job->comm;
     return HCCL_SUCCESS;
 }
 

@@ -90,11 +90,13 @@ bool wq_tc_supported(const MatmulArgs &p);
 uint64_t wq_tc_workspace_bytes(const MatmulArgs &p);
 cudaError_t launch_wq_tc(const MatmulArgs &p, cudaStream_t s);
 unsigned int wq_tc_device_status();
+void wq_tc_device_status_reset();
 // Decode kernel for int4 weights at M <= 16 (wq_mma.cu): register dequant + mma.sync, stream-K.
 bool wq_mma_supported(const MatmulArgs &p);
 uint64_t wq_mma_workspace_bytes(const MatmulArgs &p);
 cudaError_t launch_wq_mma(const MatmulArgs &p, cudaStream_t s);
 unsigned int wq_mma_device_status();
+void wq_mma_device_status_reset();
 // The tile-packed int4 weight layout the decode kernel streams with contiguous 16 KB copies: bytes it
 // occupies for a [K,N] weight, the one-time re-layout from the caller's layout, and the way back.
 uint64_t wq_nz_bytes(int64_t K, int64_t N);
@@ -102,6 +104,8 @@ cudaError_t launch_wq_pack_nz(const void *w_nd, void *w_nz, int64_t K, int64_t N
 cudaError_t launch_wq_unpack_nz(const void *w_nz, void *w_nd, int64_t K, int64_t N, cudaStream_t s);
 // 0, or the code of the first bounded wait that gave up on the current device (synchronises).
 unsigned int tc_device_status();
+// Clears the status words of every kernel family on the current device (synchronises).
+void tc_device_status_reset();
 
 // Host-side tally of kernels this library has launched (diagnostics for benchmarks).
 void count_launch(int n = 1);

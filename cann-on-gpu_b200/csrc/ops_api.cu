@@ -5,6 +5,7 @@
 // phase 1 is host-only and returns 161001 for null arguments and 161002 for unsupported types or
 // shapes; phase 2 enqueues on the stream, never synchronises or allocates, reports launch errors as
 // 361001 and consumes the executor.
+#include <atomic>
 #include <cstdint>
 #include <cstring>
 #include <new>
@@ -135,10 +136,25 @@ void choose_path(aclOpExecutor *e, uint64_t *ws) {
                 (long)e->n, (long)e->k, (long)e->group, (int)e->path, e->split_k, (unsigned long)e->ws_bytes);
 }
 
+// Per device: the code of a bounded wait that gave up, as last seen by aclnnB200DeviceStatus().  While it is set the
+// matmul entry points refuse to launch (361001): the results of the launch that gave up are undefined, and the
+// application is expected to find out why before it goes on (aclnnB200ResetDeviceStatus() clears it).
+std::atomic<uint32_t> g_latched_status[64];
+
+uint32_t latched_status_of_current_device() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+    return g_latched_status[dev].load(std::memory_order_relaxed);
+}
+
 aclnnStatus run_matmul(void *ws, uint64_t ws_bytes, aclOpExecutor *e, aclrtStream stream) {
     if (!e) return ACLNN_ERR_PARAM_NULLPTR;
     aclnnStatus st = ACLNN_SUCCESS;
-    if (e->op != PLAN_WQBMM && e->op != PLAN_QMM && e->op != PLAN_MX) {
+    if (const uint32_t code = latched_status_of_current_device()) {
+        fprintf(stderr, "[b200-qmm] refusing to launch: an earlier kernel on this device gave up a bounded wait (code 0x%x); "
+                        "call aclnnB200ResetDeviceStatus() once the cause is understood\n", code);
+        st = ACLNN_ERR_RUNTIME_ERROR;
+    } else if (e->op != PLAN_WQBMM && e->op != PLAN_QMM && e->op != PLAN_MX) {
         st = ACLNN_ERR_PARAM_INVALID;   // a plan of another operator (or of a composite one) was handed in
     } else if (e->m == 0 || e->n == 0) {
         // empty output: nothing to launch
@@ -338,7 +354,18 @@ aclnnStatus run_simple(aclOpExecutor *e, aclrtStream stream) {
 extern "C" {
 
 uint64_t aclnnB200KernelLaunchCount(void) { return qmm::launch_count(); }
-uint32_t aclnnB200DeviceStatus(void) { return qmm::tc_device_status(); }
+uint32_t aclnnB200DeviceStatus(void) {
+    const uint32_t v = qmm::tc_device_status();
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return v;
+    if (v) g_latched_status[dev].store(v, std::memory_order_relaxed);
+    return v ? v : g_latched_status[dev].load(std::memory_order_relaxed);
+}
+void aclnnB200ResetDeviceStatus(void) {
+    qmm::tc_device_status_reset();
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64) g_latched_status[dev].store(0, std::memory_order_relaxed);
+}
 
 #define RUN_MATMUL(NAME) \
     aclnnStatus NAME(void *ws, uint64_t wsz, aclOpExecutor *e, aclrtStream s) { return run_matmul(ws, wsz, e, s); }

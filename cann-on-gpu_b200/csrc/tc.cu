@@ -845,6 +845,13 @@ cudaError_t launch_tc(const MatmulArgs &p, cudaStream_t s) {
     return launch_dense_tc(p, s);
 }
 
+void tc_device_status_reset() {
+    const unsigned int z = 0;
+    cudaMemcpyToSymbol(g_tc_status, &z, sizeof(z));
+    wq_tc_device_status_reset();
+    wq_mma_device_status_reset();
+}
+
 unsigned int tc_device_status() {
     unsigned int v = 0;
     if (cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(v)) != cudaSuccess) return 0xFFFFFFFFu;

@@ -15,12 +15,12 @@
 // is exact (8 significant bits into 11) for every element within 2^-29 of the row's largest in that
 // stage; the fold multiplies the scale back in fp32.
 //
-// Per CTA (one per SM, 15 warps):
+// Per CTA (one per SM, 16 warps):
 //   warp 0       weight producer: one copy per stage (128 K rows x 256 columns of packed int4 = 16 KB)
 //                into a ring of 6-9 slots.  Weights in the caller's [K,N] layout come as a 2-D TMA box
 //                (128 rows x 128 B, 128-byte swizzle, no L2 promotion); weights in the tile-packed
 //                layout (see wq_pack_nz_kernel) as one contiguous 16 KB bulk copy.
-//   warp 14      activation producer: loads the stage's 128 K columns of every activation row from
+//   warps 14-15  activation producers (alternate stages): each loads its stage's 128 K columns of every activation row from
 //                global memory (L2), converts them to scaled fp16, and writes them into the slot in
 //                B-fragment order together with the row's scale and the row's sum over the stage.
 //   warps 1-12   three teams of four warps; a team owns every third stage, each of its warps 64 of the
@@ -55,7 +55,8 @@ constexpr int MM_TILE_N = 256;      // nibble columns per tile
 constexpr int MM_SBK = 128;         // K rows per stage
 constexpr int MM_W_BYTES = 16384;   // packed weights of one stage: 128 rows x 128 B
 constexpr int MM_TEAMS = 3;
-constexpr int MM_THREADS = (4 * MM_TEAMS + 3) * 32;
+constexpr int MM_XP = 2;            // activation producer warps (they take alternate stages)
+constexpr int MM_THREADS = (4 * MM_TEAMS + 2 + MM_XP) * 32;
 
 struct MmParams {
     void *out;
@@ -73,6 +74,8 @@ struct MmParams {
     int ns;                  // ring slots (a multiple of the team count)
     int tile_n;              // output columns per tile: 256 (int4) or 128 (int8: two nibbles per column)
     int weights_early;       // weights, scales and offsets may be read before the preceding kernel has completed
+    unsigned long long wait_ns;   // time limit of every wait (0 = about a second)
+    int test_drop;           // test hook: CTA 0 never fetches its first stage, so the wait for it runs out
 };
 
 // Shared memory of one CTA: [ring: ns slots][partial tiles: teams x M rows x 256 fp32][barriers][flag].
@@ -168,6 +171,25 @@ __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
 __device__ __forceinline__ void pdl_wait_for_prerequisites() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// The bounded wait of this kernel: like mbar_wait, with the time limit a launch parameter (0 = the common limit of
+// about a second) so that a test can make every wait run out at once and see the kernel come back with a status.
+__device__ __forceinline__ bool mm_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, unsigned code, unsigned long long limit_ns) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns(), limit = limit_ns ? limit_ns : WAIT_LIMIT_NS;
+    unsigned it = 0;
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((++it & 63u) == 0) {
+            if (*abort_flag) return false;
+            if (global_ns() - t0 > limit) {
+                *abort_flag = 1;
+                atomicCAS(&g_tc_status, 0u, code);
+                return false;
+            }
+        }
+    }
+}
+
 // Bounded wait that ignores the abort flag (used only to let copies in flight land before exit).
 __device__ __forceinline__ void mbar_drain(uint32_t bar, uint32_t parity) {
     const unsigned long long t0 = global_ns();
@@ -185,7 +207,7 @@ __device__ __forceinline__ void mbar_drain(uint32_t bar, uint32_t parity) {
 // Loads run D stages ahead of the conversion so that the L2 round trip is not paid per stage.
 template <bool BF16, int MF, int EPL>
 __device__ __forceinline__ void mm_activation_producer(const MmParams &p, uint32_t base, int NS, uint32_t bars, volatile int *abort_flag,
-                                                       int sb0, int nu, int lane) {
+                                                       int sb0, int nu, int lane, int xp) {
     using L = MmSmem<MF>;
     constexpr int LPR = 128 / EPL, R = 32 / LPR, V = EPL / 4, D = EPL <= 8 ? 4 : 2;
     const int q = lane % LPR, rsub = lane / LPR;
@@ -205,25 +227,26 @@ __device__ __forceinline__ void mm_activation_producer(const MmParams &p, uint32
     };
     auto next_sb = [&](int sbi, int by) { int s2 = sbi + by; while (s2 >= p.num_sb) s2 -= p.num_sb; return s2; };
     pdl_wait_for_prerequisites();   // the activations are the predecessor's output
-    int sb_load = sb0;
+    // this warp's stages are xp, xp + MM_XP, ... of the share
+    int sb_load = next_sb(sb0, xp % p.num_sb);
 #pragma unroll
     for (int d = 0; d < D; ++d) {
-        if (d < nu) load_stage(sb_load, buf[d]);
-        sb_load = next_sb(sb_load, 1);
+        if (xp + MM_XP * d < nu) load_stage(sb_load, buf[d]);
+        sb_load = next_sb(sb_load, MM_XP % p.num_sb);
     }
-    int slot = 0, round = 0;
-    for (int i0 = 0; i0 < nu; i0 += D) {
+    int slot = xp % NS, round = xp / NS;
+    for (int i0 = xp; i0 < nu; i0 += MM_XP * D) {
 #pragma unroll
         for (int d = 0; d < D; ++d) {
-            const int i = i0 + d;
+            const int i = i0 + MM_XP * d;
             if (i >= nu) break;
             uint2 cur[MF][V];
 #pragma unroll
             for (int f = 0; f < MF; ++f)
 #pragma unroll
                 for (int j = 0; j < V; ++j) cur[f][j] = buf[d][f][j];
-            if (i + D < nu) load_stage(sb_load, buf[d]);
-            sb_load = next_sb(sb_load, 1);
+            if (i + MM_XP * D < nu) load_stage(sb_load, buf[d]);
+            sb_load = next_sb(sb_load, MM_XP % p.num_sb);
             // convert first (registers only), then wait for the slot: what remains after the wait is a few stores
             uint32_t h[MF][EPL / 2];
             float up[MF], sum[MF];
@@ -279,7 +302,7 @@ __device__ __forceinline__ void mm_activation_producer(const MmParams &p, uint32
                 for (int o = 1; o < LPR; o <<= 1) sm += __shfl_xor_sync(0xffffffffu, sm, o);
                 sum[f] = sm;
             }
-            if (round > 0 && !mbar_wait(bars + 8u * (NS + slot), (round - 1) & 1, abort_flag, 0x340u + slot)) return;
+            if (round > 0 && !mm_wait(bars + 8u * (NS + slot), (round - 1) & 1, abort_flag, 0x340u + slot, p.wait_ns)) return;
             const uint32_t sb = base + slot * L::SLOT;
 #pragma unroll
             for (int f = 0; f < MF; ++f) {
@@ -296,7 +319,8 @@ __device__ __forceinline__ void mm_activation_producer(const MmParams &p, uint32
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(bars + 8u * slot);
-            if (++slot == NS) { slot = 0; ++round; }
+            slot += MM_XP;
+            while (slot >= NS) { slot -= NS; ++round; }
         }
     }
 }
@@ -344,39 +368,54 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const MmParams p) {
         // ------------------------------------------------------------------ weight producer
         if (lane == 0) {
             if (!p.weights_early) pdl_wait_for_prerequisites();
+            // Everything the loop needs is kept incrementally (this is one thread competing with fifteen warps for
+            // issue slots: every instruction here is paid in full, per stage).
             int i = 0, slot = 0, round = 0;
             int tile = tile_first, sbi = (int)(ub - (long long)tile_first * p.num_sb);
+            int gcnt = sbi % p.gsb;                                          // stages into the current scale group
+            const uint16_t *sc_src = static_cast<const uint16_t *>(p.scale) + (size_t)(sbi / p.gsb) * p.N + (size_t)tile * TN;
+            const ptrdiff_t of_delta = has_off ? static_cast<const uint16_t *>(p.offset) - static_cast<const uint16_t *>(p.scale) : 0;
+            const uint8_t *w_src = NZ ? p.wnz + ((size_t)tile * p.num_sb + sbi) * MM_W_BYTES : nullptr;   // blocks are [tile][stage]
+            uint32_t row_bytes = (uint32_t)min(TN, p.N - tile * TN) * 2u;
+            uint32_t dst = base, fbar = bars, ebar = bars + 8u * NS;
             bool ok = true;
             for (; i < nu; ++i) {
-                if (round > 0 && !mbar_wait(empty_bar(slot), (round - 1) & 1, abort_flag, 0x300u + slot)) { ok = false; break; }
-                const uint32_t dst = base + slot * L::SLOT;
+                if (round > 0 && !mm_wait(ebar, (round - 1) & 1, abort_flag, 0x300u + slot, p.wait_ns)) { ok = false; break; }
                 // the stage's scale (and offset) row for this tile's columns rides with the weights, so the
                 // consumers never wait on a global load
-                const int ncols = min(TN, p.N - tile * TN);
-                const uint32_t row_bytes = (uint32_t)ncols * 2u;
-                const size_t row_at = (size_t)(sbi / p.gsb) * p.N + (size_t)tile * TN;
-                mbar_expect_tx(full_bar(slot), MM_W_BYTES + (has_off ? 2u : 1u) * row_bytes);
-                if constexpr (NZ) bulk_load_1d(dst, p.wnz + ((size_t)tile * p.num_sb + sbi) * MM_W_BYTES, MM_W_BYTES, full_bar(slot));
-                else tma_load_2d(dst, &tm_w, full_bar(slot), tile * 128, sbi * MM_SBK);
-                bulk_load_1d(dst + L::SC_OFF, static_cast<const uint16_t *>(p.scale) + row_at, row_bytes, full_bar(slot));
-                if (has_off) bulk_load_1d(dst + L::OF_OFF, static_cast<const uint16_t *>(p.offset) + row_at, row_bytes, full_bar(slot));
-                if (++slot == NS) { slot = 0; ++round; }
-                if (++sbi == p.num_sb) { sbi = 0; ++tile; }
+                if (!(p.test_drop && cta == 0 && i == 0)) {   // test hook: CTA 0 never fetches its first stage
+                    mbar_expect_tx(fbar, MM_W_BYTES + (has_off ? 2u : 1u) * row_bytes);
+                    if constexpr (NZ) bulk_load_1d(dst, w_src, MM_W_BYTES, fbar);
+                    else tma_load_2d(dst, &tm_w, fbar, tile * 128, sbi * MM_SBK);
+                    bulk_load_1d(dst + L::SC_OFF, sc_src, row_bytes, fbar);
+                    if (has_off) bulk_load_1d(dst + L::OF_OFF, sc_src + of_delta, row_bytes, fbar);
+                }
+                if constexpr (NZ) w_src += MM_W_BYTES;
+                dst += L::SLOT; fbar += 8u; ebar += 8u;
+                if (++slot == NS) { slot = 0; ++round; dst = base; fbar = bars; ebar = bars + 8u * NS; }
+                if (++gcnt == p.gsb) { gcnt = 0; sc_src += p.N; }
+                if (++sbi == p.num_sb) {
+                    sbi = 0; gcnt = 0; ++tile;
+                    sc_src = static_cast<const uint16_t *>(p.scale) + (size_t)tile * TN;
+                    row_bytes = (uint32_t)min(TN, p.N - tile * TN) * 2u;
+                }
             }
-            if (!ok) {   // let the copies already issued land before the CTA's shared memory goes away
-                for (int b = (i > NS ? i - NS : 0); b < i; ++b) mbar_drain(full_bar(b % NS), (b / NS) & 1);
-            }
+            // Let the copies of the last ring's worth of stages land before the CTA's shared memory goes away.  In a
+            // normal run the consumers have seen all of them (this returns at once); after a wait gave up anywhere in
+            // the CTA the consumers may be gone while copies are still in flight.
+            (void)ok;
+            for (int b = (i > NS ? i - NS : 0); b < i; ++b) mbar_drain(full_bar(b % NS), (b / NS) & 1);
         }
-    } else if (warp == 4 * MM_TEAMS + 2) {
-        // ------------------------------------------------------------------ activation producer
-        const int sb0 = (int)(ub - (long long)tile_first * p.num_sb);
+    } else if (warp >= 4 * MM_TEAMS + 2) {
+        // ------------------------------------------------------------------ activation producers
+        const int sb0 = (int)(ub - (long long)tile_first * p.num_sb), xp = warp - (4 * MM_TEAMS + 2);
         if constexpr (MF == 2) {
-            mm_activation_producer<BF16, 2, 32>(p, base, NS, bars, abort_flag, sb0, nu, lane);
+            mm_activation_producer<BF16, 2, 32>(p, base, NS, bars, abort_flag, sb0, nu, lane, xp);
         } else {
-            if (p.M == 1) mm_activation_producer<BF16, 1, 4>(p, base, NS, bars, abort_flag, sb0, nu, lane);
-            else if (p.M == 2) mm_activation_producer<BF16, 1, 8>(p, base, NS, bars, abort_flag, sb0, nu, lane);
-            else if (p.M <= 4) mm_activation_producer<BF16, 1, 16>(p, base, NS, bars, abort_flag, sb0, nu, lane);
-            else mm_activation_producer<BF16, 1, 32>(p, base, NS, bars, abort_flag, sb0, nu, lane);
+            if (p.M == 1) mm_activation_producer<BF16, 1, 4>(p, base, NS, bars, abort_flag, sb0, nu, lane, xp);
+            else if (p.M == 2) mm_activation_producer<BF16, 1, 8>(p, base, NS, bars, abort_flag, sb0, nu, lane, xp);
+            else if (p.M <= 4) mm_activation_producer<BF16, 1, 16>(p, base, NS, bars, abort_flag, sb0, nu, lane, xp);
+            else mm_activation_producer<BF16, 1, 32>(p, base, NS, bars, abort_flag, sb0, nu, lane, xp);
         }
     } else if (warp <= 4 * MM_TEAMS) {
         // ------------------------------------------------------------------ compute
@@ -419,7 +458,7 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const MmParams p) {
             for (int j = j_first; j < j_hi && ok; j += MM_TEAMS) {
                 had = true;
                 const int slot = j % NS, round = j / NS;
-                if (!mbar_wait(full_bar(slot), round & 1, abort_flag, 0x310u + slot)) { ok = false; break; }
+                if (!mm_wait(full_bar(slot), round & 1, abort_flag, 0x310u + slot, p.wait_ns)) { ok = false; break; }
                 const uint32_t sb = base + slot * L::SLOT;
 #pragma unroll
                 for (int st = 0; st < 8; ++st) {
@@ -529,7 +568,7 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const MmParams p) {
             }
             if (!ok) break;
             // hand this team's partial tile to the reducer
-            if (sg >= 1 && !mbar_wait(seg_free, (sg - 1) & 1, abort_flag, 0x320u)) { ok = false; break; }
+            if (sg >= 1 && !mm_wait(seg_free, (sg - 1) & 1, abort_flag, 0x320u, p.wait_ns)) { ok = false; break; }
             if (had) {
 #pragma unroll
                 for (int f = 0; f < MF; ++f)
@@ -557,17 +596,17 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const MmParams p) {
             const int n = CPL * lane, n_glob = tile * TN + n;
             const bool n_ok = n_glob < p.N;
             const int c_first = mm_share_owner(t_lo, p.total_u, P), c_last = mm_share_owner(t_hi - 1, p.total_u, P);
+            // every lane reads every tag itself (acquire), so the reads of the partial tiles that follow are ordered
+            // after the tags lane by lane and no fence is needed on this side
             auto others_published = [&]() {
                 bool all = true;
-                for (int c = c_first + lane; c <= c_last; c += 32) {
+                for (int c = c_first; c <= c_last && all; ++c) {
                     if (c == cta) continue;
                     unsigned long long tg;
                     asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(tg) : "l"(p.tags + tile + c) : "memory");
-                    all = all && tg == p.nonce;
+                    all = tg == p.nonce;
                 }
-                all = __all_sync(0xffffffffu, all);
-                __syncwarp();
-                return all;
+                return __all_sync(0xffffffffu, all);
             };
             // While the teams still work on this CTA's piece of a shared tile, see whether the other contributors
             // have published theirs already (the usual case for the piece a CTA works on last: its neighbour did
@@ -576,11 +615,8 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const MmParams p) {
             bool early = false;
             constexpr int PRE_M = 2;
             float pre[PRE_M][2][CPL];   // [row][contributors before / after this CTA][column]
-            if (!whole) {
-                if (sg == 0) pdl_wait_for_prerequisites();   // first touch of the workspace
-                early = others_published();
-                if (early && p.M <= PRE_M && c_last - cta <= 1) {
-                    __threadfence();
+            auto fetch_others = [&]() {
+                if (p.M <= PRE_M && c_last - cta <= 1) {
 #pragma unroll
                     for (int m = 0; m < PRE_M; ++m) {
 #pragma unroll
@@ -602,8 +638,13 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const MmParams p) {
                         }
                     }
                 }
+            };
+            if (!whole) {
+                if (sg == 0) pdl_wait_for_prerequisites();   // first touch of the workspace
+                early = others_published();
+                if (early) fetch_others();
             }
-            if (!mbar_wait(seg_done, sg & 1, abort_flag, 0x330u)) break;
+            if (!mm_wait(seg_done, sg & 1, abort_flag, 0x330u, p.wait_ns)) break;
             if (whole && sg == 0) pdl_wait_for_prerequisites();   // first write to the output
             // this CTA's sum over its teams for row m of the tile
             auto own_row = [&](int m, float (&v)[CPL]) {
@@ -659,7 +700,6 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const MmParams p) {
                 // of the same launch (a captured graph) starts clean.
                 // sum in contributor order, this CTA's own part from shared memory
                 auto finish = [&]() {
-                    __threadfence();   // every lane's reads below come after the tags this warp has seen
                     if (n_ok) {
                         for (int m = 0; m < p.M; ++m) {
                             float own[CPL], v[CPL];
@@ -713,7 +753,9 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const MmParams p) {
                             for (int c = 0; c < CPL / 4; ++c) dst[c] = make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
                         }
                     }
-                    __threadfence();
+                    // the warp barrier orders every lane's stores before lane 0's release of the tag (release is
+                    // cumulative); the sequentially consistent fence orders that store before the tag reads below, so
+                    // of two contributors that publish together at least one sees the other
                     __syncwarp();
                     if (lane == 0) {
                         asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(p.tags + tile + cta), "l"(p.nonce) : "memory");
@@ -961,6 +1003,11 @@ cudaError_t launch_wq_mma(const MatmulArgs &p, cudaStream_t s) {
     mp.M = (int)p.M; mp.N = (int)p.N; mp.K = (int)p.K;
     mp.num_sb = pl.num_sb; mp.total_u = pl.total_u; mp.gsb = pl.gsb;
     mp.tile_n = q8 ? 128 : 256;
+    // test hooks: B200_QMM_TEST_WAIT_LIMIT_NS=<n> gives every wait of the decode kernel n nanoseconds instead of about a
+    // second; B200_QMM_TEST_DROP_STAGE=1 makes CTA 0 leave out the copy of its first stage, so that the consumers' wait
+    // for it is a wait for something that never comes
+    if (const char *e = getenv("B200_QMM_TEST_WAIT_LIMIT_NS")) mp.wait_ns = strtoull(e, nullptr, 10);
+    if (const char *e = getenv("B200_QMM_TEST_DROP_STAGE")) mp.test_drop = atoi(e);
 
     cudaError_t e;
 #define MM_GO(Q8_, NZ_) (pl.mf == 1 ? (bf ? mm_launch_one<Q8_, true, 1, NZ_>(tw, mp, pl.P, s) : mm_launch_one<Q8_, false, 1, NZ_>(tw, mp, pl.P, s)) \
@@ -996,6 +1043,11 @@ cudaError_t launch_wq_unpack_nz(const void *w_nz, void *w_nd, int64_t K, int64_t
     wq_unpack_nz_kernel<<<(unsigned)((words + 255) / 256), 256, 0, s>>>((const uint32_t *)w_nz, (uint32_t *)w_nd, (int)K, (int)N, num_sb);
     count_launch();
     return cudaGetLastError();
+}
+
+void wq_mma_device_status_reset() {
+    const unsigned int z = 0;
+    cudaMemcpyToSymbol(g_tc_status, &z, sizeof(z));
 }
 
 unsigned int wq_mma_device_status() {

@@ -927,6 +927,11 @@ extern "C" __attribute__((visibility("default"))) void wqProfileRead(unsigned lo
 }
 #endif
 
+void wq_tc_device_status_reset() {
+    const unsigned int z = 0;
+    cudaMemcpyToSymbol(g_tc_status, &z, sizeof(z));
+}
+
 unsigned int wq_tc_device_status() {
     unsigned int v = 0;
     if (cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(v)) != cudaSuccess) return 0xFFFFFFFFu;

@@ -261,6 +261,12 @@ ACL_FUNC_VISIBILITY uint64_t aclnnB200KernelLaunchCount(void);
 /* Diagnostics (no counterpart in the reference): 0, or the code of the first bounded wait inside a
  * tensor-core kernel that gave up on the current device.  Synchronises the device. */
 ACL_FUNC_VISIBILITY uint32_t aclnnB200DeviceStatus(void);
+/* Failure handling (no counterpart in the reference, whose kernels have no waits): every wait inside a
+ * kernel of this library is bounded; a wait that runs out makes its kernel return early with undefined
+ * results and records a code.  Once aclnnB200DeviceStatus() has reported a non-zero code, every matmul
+ * execute call on that device returns ACLNN_ERR_RUNTIME_ERROR (361001) without launching, until
+ * aclnnB200ResetDeviceStatus() clears the code.  Synchronises the device. */
+ACL_FUNC_VISIBILITY void aclnnB200ResetDeviceStatus(void);
 
 #ifdef __cplusplus
 }

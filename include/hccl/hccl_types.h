@@ -27,6 +27,7 @@ typedef enum {
     HCCL_E_NOT_SUPPORT = 5,
     HCCL_E_NOT_FOUND = 6,
     HCCL_E_UNAVAIL = 7,
+    HCCL_E_TIMEOUT = 9,      /* a rank did not join within the bootstrap time limit */
     HCCL_E_NETWORK = 19
 } HcclResult;
 

@@ -1166,6 +1166,41 @@ def test_seeded_random_shapes_default_path_against_generic_kernel(pkg, workloads
         assert_close(to_np(got), to_np(want).astype(np.float64), f"case {case} {kind} M={M} K={K} N={N} {dtype}")
 
 
+def test_a_wait_that_runs_out_is_reported_and_latched(pkg, oracle, workloads, dev):
+    """Failure detection without a fault: a test hook makes one CTA of the decode kernel leave out the copy of its
+    first stage, so its consumers wait for a barrier that nothing completes; with the wait limit set to 200 us (a
+    second test hook) the wait runs out, the kernel comes back by itself, the context stays usable,
+    aclnnB200DeviceStatus() names the wait, and from then on matmul calls are refused with 361001 until
+    aclnnB200ResetDeviceStatus(); after the reset the same call gives the right result."""
+    lib = pkg.load()
+    lib.aclnnB200DeviceStatus.restype = ctypes.c_uint32
+    lib.aclnnB200ResetDeviceStatus.restype = None
+    d = workloads.w4a16(M=2, K=4096, N=1024, group=128, seed=8700)
+    args = (d["x"].to(dev), d["w"].to(dev), d["scale"].to(dev), d["offset"].to(dev), d["bias"].to(dev))
+    torch.cuda.synchronize()
+    assert lib.aclnnB200DeviceStatus() == 0
+    try:
+        with env_set("B200_QMM_TEST_WAIT_LIMIT_NS", "200000"), env_set("B200_QMM_TEST_DROP_STAGE", "1"):
+            pkg.weight_quant_matmul(*args, int4=True, group=128)     # launches; CTA 0's wait for its first stage runs out
+        torch.cuda.synchronize()                                     # the kernel returned by itself
+        code = lib.aclnnB200DeviceStatus()
+        assert 0x300 <= code < 0x400, hex(code)                      # a wait of the decode kernel
+        out = torch.empty((2, 1024), dtype=torch.bfloat16, device=dev)
+        st = pkg.call("aclnnWeightQuantBatchMatmulV2Ex", pkg.AclTensor(args[0]), pkg.AclTensor(args[1], pkg.ACL_INT4, (4096, 1024)),
+                      pkg.AclTensor(args[2]), pkg.AclTensor(args[3]), pkg.AclTensor(args[4]), ctypes.c_int64(128), pkg.AclTensor(out),
+                      return_status=True)
+        assert st == 361001
+        q = workloads.w8a8(M=8, K=64, N=32, seed=8701)
+        assert pkg.call("aclnnQuantMatmulV4", pkg.AclTensor(q["x"].to(dev)), pkg.AclTensor(q["w"].to(dev)), pkg.AclTensor(q["scale"].to(dev)),
+                        pkg.AclTensor(torch.empty((8, 32), dtype=torch.bfloat16, device=dev)), return_status=True) == 361001
+    finally:
+        lib.aclnnB200ResetDeviceStatus()
+    assert lib.aclnnB200DeviceStatus() == 0
+    got = pkg.weight_quant_matmul(*args, int4=True, group=128)
+    torch.cuda.synchronize()
+    assert_close(to_np(got), ref_wq(oracle, d), "after the reset")
+
+
 def test_zz_no_bounded_wait_gave_up(pkg, dev):
     """Every spin inside the tensor-core kernels is bounded and records a code when it gives up;
     after the whole suite the device status word must still be 0."""
