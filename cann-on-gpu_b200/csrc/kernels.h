@@ -85,6 +85,12 @@ cudaError_t launch_dense_tc(const MatmulArgs &p, cudaStream_t s);
 bool expand_supported(const MatmulArgs &p);
 uint64_t expand_workspace_bytes(const MatmulArgs &p);
 cudaError_t launch_expand(const MatmulArgs &p, cudaStream_t s);
+// Native block-scaled MX matmul (mx_tc.cu): tcgen05.mma kind::mxf8f6f4.block_scale with the e8m0 scales in tensor memory.
+bool mx_native_supported(const MatmulArgs &p);
+uint64_t mx_native_workspace_bytes(const MatmulArgs &p);
+cudaError_t launch_mx_native(const MatmulArgs &p, cudaStream_t s);
+unsigned int mx_tc_device_status();
+void mx_tc_device_status_reset();
 // Persistent stream-K tensor-core kernel for weight-only matmuls (wq_tc.cu).
 bool wq_tc_supported(const MatmulArgs &p);
 uint64_t wq_tc_workspace_bytes(const MatmulArgs &p);

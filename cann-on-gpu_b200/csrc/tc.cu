@@ -711,7 +711,9 @@ bool is_mx(const MatmulArgs &p) { return p.epilogue == EPI_PLAIN && p.a_scale &&
 bool use_stream_wq(const MatmulArgs &p) {
     return is_wq(p) && wq_tc_supported(p) && (p.M <= wq_dense_threshold(p) || !expand_supported(p));
 }
-bool use_expand(const MatmulArgs &p) { return (is_mx(p) || is_wq(p)) && !use_stream_wq(p) && expand_supported(p); }
+// MX matmuls whose shape the native block-scaled kernel takes (mx_tc.cu); the others are expanded to bf16.
+bool use_mx_native(const MatmulArgs &p) { return is_mx(p) && mx_native_supported(p); }
+bool use_expand(const MatmulArgs &p) { return (is_mx(p) || is_wq(p)) && !use_stream_wq(p) && !use_mx_native(p) && expand_supported(p); }
 // Decode shapes of int4 weights: register-dequant kernel (wq_mma.cu).
 bool use_decode_wq(const MatmulArgs &p) { return use_stream_wq(p) && wq_mma_supported(p); }
 
@@ -809,19 +811,20 @@ bool tc_supported(const MatmulArgs &p) {
         if (!is_wq(p) || p.b_type != ET_I4) return false;
         return nz_direct(p) || (p.N % 8 == 0 && tc_supported(as_nd(p, nullptr)));
     }
-    if (use_stream_wq(p) || use_expand(p)) return true;
+    if (use_stream_wq(p) || use_expand(p) || use_mx_native(p)) return true;
     return dense_tc_supported(p);
 }
 
 void tc_plan(MatmulArgs &p) {
     if (p.b_nz) { p.split_k = 1; return; }
-    p.split_k = (use_stream_wq(p) || use_expand(p)) ? 1 : make_plan(p).split;
+    p.split_k = (use_stream_wq(p) || use_expand(p) || use_mx_native(p)) ? 1 : make_plan(p).split;
 }
 
 uint64_t tc_workspace_bytes(const MatmulArgs &p) {
     if (p.b_nz) return nz_direct(p) ? wq_mma_workspace_bytes(p) : nz_copy_bytes(p) + tc_workspace_bytes(as_nd(p, nullptr));
     if (use_decode_wq(p)) return wq_mma_workspace_bytes(p);
     if (use_stream_wq(p)) return wq_tc_workspace_bytes(p);
+    if (use_mx_native(p)) return mx_native_workspace_bytes(p);
     if (use_expand(p)) return expand_workspace_bytes(p);
     return dense_tc_workspace_bytes(p);
 }
@@ -841,6 +844,7 @@ cudaError_t launch_tc(const MatmulArgs &p, cudaStream_t s) {
     }
     if (use_decode_wq(p)) return launch_wq_mma(p, s);
     if (use_stream_wq(p)) return launch_wq_tc(p, s);
+    if (use_mx_native(p)) return launch_mx_native(p, s);
     if (use_expand(p)) return launch_expand(p, s);
     return launch_dense_tc(p, s);
 }
@@ -850,13 +854,14 @@ void tc_device_status_reset() {
     cudaMemcpyToSymbol(g_tc_status, &z, sizeof(z));
     wq_tc_device_status_reset();
     wq_mma_device_status_reset();
+    mx_tc_device_status_reset();
 }
 
 unsigned int tc_device_status() {
     unsigned int v = 0;
     if (cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(v)) != cudaSuccess) return 0xFFFFFFFFu;
-    const unsigned int w = wq_tc_device_status(), d = wq_mma_device_status();
-    return v ? v : (w ? w : d);
+    const unsigned int w = wq_tc_device_status(), d = wq_mma_device_status(), x = mx_tc_device_status();
+    return v ? v : (w ? w : (d ? d : x));
 }
 
 }  // namespace qmm

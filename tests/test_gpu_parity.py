@@ -519,6 +519,42 @@ def test_mx_matmul(pkg, oracle, workloads, dev, path, kinds, shape):
             assert_close(to_np(out), want, f"{name} {kinds} {shape} {odt} path={path}")
 
 
+@pytest.mark.parametrize("kinds", [(False, False), (False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("shape", [(300, 1024, 800), (1, 128, 32), (129, 2048, 288), (520, 384, 1056)])
+def test_mx_native_block_scaled_kernel(pkg, oracle, workloads, dev, kinds, shape):
+    """The native block-scaled kernel (tcgen05.mma kind::mxf8f6f4.block_scale, e8m0 scales in tensor memory) on
+    shapes with ragged M and N (zero-filled tiles, padded scale groups), every fp8 / fp4 operand mix, fp32 and bf16
+    outputs, scale exponents over the whole benchmark range and beyond: against the oracle, and against the
+    expand-then-bf16 path (B200_QMM_MX_NATIVE=0), which multiplies the same exact operand values."""
+    M, K, N = shape
+    d = workloads.mx(M=M, K=K, N=N, a_fp4=kinds[0], b_fp4=kinds[1], seed=5400 + M)
+    g = torch.Generator().manual_seed(5401)
+    d["sa"] = torch.randint(127 - 20, 127 + 21, d["sa"].shape, generator=g, dtype=torch.int32).to(torch.uint8)   # 2^-20 .. 2^20
+    want = ref_mx(oracle, d)
+    for odt in (torch.float32, torch.bfloat16):
+        got = run_mx(pkg, d, dev, odt, "aclnnMatmulMxFp8Hw")
+        assert_close(to_np(got), want, f"native MX {kinds} {shape} {odt}")
+        with env_set("B200_QMM_MX_NATIVE", "0"):
+            other = run_mx(pkg, d, dev, odt, "aclnnMatmulMxFp8Hw")
+        assert_close(to_np(got), to_np(other), f"native vs expanded {kinds} {shape} {odt}", max_rel=2e-3 if odt == torch.float32 else 1e-2,
+                     mean_rel=1e-5 if odt == torch.float32 else 2e-3)
+
+
+def test_mx_native_e5m2_operand(pkg, oracle, dev):
+    """fp8 e5m2 elements (the reference's other fp8 kind, cuda/src/ops/matmul.cu:437) through the native kernel."""
+    M, K, N = 200, 512, 320
+    g = torch.Generator().manual_seed(5500)
+    a = torch.randn((M, K), generator=g).to(torch.float8_e5m2).view(torch.uint8)
+    b = torch.randn((K, N), generator=g).to(torch.float8_e4m3fn).view(torch.uint8)
+    sa = torch.randint(123, 132, (M, K // 32), generator=g, dtype=torch.int32).to(torch.uint8)
+    sb = torch.randint(123, 132, (K // 32, N), generator=g, dtype=torch.int32).to(torch.uint8)
+    want = oracle.mx_matmul_fast(a.numpy(), oracle.MXK_E5M2, sa.numpy(), b.numpy(), oracle.MXK_E4M3, sb.numpy(), M, K, N)
+    out = pkg.mx_matmul(a.reshape(-1).to(dev), pkg.ACL_FLOAT8_E5M2, sa.to(dev), b.reshape(-1).to(dev), pkg.ACL_FLOAT8_E4M3FN, sb.to(dev),
+                        M, K, N, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    assert_close(to_np(out), want, "MX e5m2 x e4m3")
+
+
 # ------------------------------------------------------------------ the tile-packed weight layout
 @pytest.mark.parametrize("shape", [(128, 256), (1024, 512), (1160, 800), (264, 32)])
 def test_weight_pack_layout_and_round_trip(pkg, workloads, dev, shape):
