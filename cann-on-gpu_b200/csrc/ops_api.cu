@@ -411,16 +411,115 @@ QMM_ALIAS(aclnnQuantBatchMatmulInplaceAdd, (QmmOpts{false, true, false}))
 QMM_ALIAS(aclnnTransposeQuantBatchMatMul, (QmmOpts{true, false, false}))
 QMM_ALIAS(aclnnBatchMatmulQuant, (QmmOpts{false, false, true}))
 
-// Grouped forms: like the reference (cuda/src/ops/matmul.cu:1195-1202,1402-1413) the group list is
-// accepted and not used -- one group spanning every row.
+// Grouped (mixture-of-experts) forms.  With a 2-D weight [K,N] the group list is accepted and not used -- one
+// group spanning every row -- exactly like the reference's placeholder (cuda/src/ops/matmul.cu:1195-1202,
+// 1402-1413).  With a 3-D weight [E,K,N] the group list is honoured: it holds E entries, either the rows per
+// group or their running totals (both must end at M), the rows of group g are multiplied by weight[g] and
+// dequantised with scale[g] (scale [E,N], or [N] shared by all groups).  Each group is planned as a W8A8 matmul
+// of its own over views of the caller's tensors; the workspace is the largest any group needs (they run one
+// after the other on the stream).
+}  // extern "C"
+namespace {
+struct GroupedPlan {
+    struct Child {
+        aclTensor x, w, scale, out;
+        aclOpExecutor *ex = nullptr;
+    };
+    const aclTensor *x = nullptr, *w = nullptr, *scale = nullptr;
+    aclTensor *out = nullptr;
+    std::vector<Child *> children;
+    ~GroupedPlan() {
+        for (Child *c : children) { delete c->ex; delete c; }
+    }
+};
+void free_grouped(void *p) { delete static_cast<GroupedPlan *>(p); }
+
+aclTensor view_of(const aclTensor *t, std::vector<int64_t> dims, int64_t elem_offset) {
+    aclTensor v;
+    v.viewDims = dims; v.storageDims = dims;
+    v.strides.resize(dims.size());
+    int64_t st = 1;
+    for (int i = (int)dims.size() - 1; i >= 0; --i) { v.strides[i] = st; st *= dims[i]; }
+    v.offset = t->offset + elem_offset; v.dtype = t->dtype; v.format = ACL_FORMAT_ND; v.data = t->data;
+    return v;
+}
+
+aclnnStatus grouped_plan(const aclTensor *x, const aclTensor *weight, const aclTensor *scale, const aclIntArray *groupList,
+                         aclTensor *out, QmmOpts o, uint64_t *ws, aclOpExecutor **ex) {
+    if (!x || !weight || !scale || !out || !ws || !ex) return ACLNN_ERR_PARAM_NULLPTR;
+    if (weight->rank() != 3) return qmm_plan(x, weight, scale, nullptr, nullptr, out, o, ws, ex);
+    if (!groupList || x->rank() != 2 || out->rank() != 2) return ACLNN_ERR_PARAM_INVALID;
+    const int64_t E = weight->viewDims[0], K = weight->viewDims[1], N = weight->viewDims[2], M = x->viewDims[0];
+    if ((int64_t)groupList->v.size() != E || E < 1 || x->viewDims[1] != K || !shape_is(out, {M, N})) return ACLNN_ERR_PARAM_INVALID;
+    const bool per_group_scale = scale->rank() == 2;
+    if (per_group_scale ? !shape_is(scale, {E, N}) : !shape_is(scale, {N})) return ACLNN_ERR_PARAM_INVALID;
+    for (const aclTensor *t : {x, weight, scale, (const aclTensor *)out})
+        if (!dense(t)) return ACLNN_ERR_PARAM_INVALID;
+    // rows per group: counts (sum = M) or running totals (non-decreasing, last = M)
+    std::vector<int64_t> rows(E);
+    int64_t sum = 0;
+    bool counts_ok = true, totals_ok = true;
+    for (int64_t g = 0; g < E; ++g) {
+        const int64_t v = groupList->v[g];
+        if (v < 0) return ACLNN_ERR_PARAM_INVALID;
+        sum += v;
+        if (g > 0 && v < groupList->v[g - 1]) totals_ok = false;
+    }
+    counts_ok = sum == M;
+    totals_ok = totals_ok && groupList->v[E - 1] == M;
+    if (!counts_ok && !totals_ok) return ACLNN_ERR_PARAM_INVALID;
+    for (int64_t g = 0; g < E; ++g) rows[g] = counts_ok ? groupList->v[g] : groupList->v[g] - (g ? groupList->v[g - 1] : 0);
+
+    auto *plan = new GroupedPlan();
+    plan->x = x; plan->w = weight; plan->scale = scale; plan->out = out;
+    uint64_t need = 0;
+    int64_t r0 = 0;
+    for (int64_t g = 0; g < E; ++g) {
+        if (rows[g] == 0) continue;
+        auto *c = new GroupedPlan::Child();
+        c->x = view_of(x, {rows[g], K}, r0 * K);
+        c->w = view_of(weight, {K, N}, g * K * N);
+        c->scale = view_of(scale, {N}, per_group_scale ? g * N : 0);
+        c->out = view_of(out, {rows[g], N}, r0 * N);
+        plan->children.push_back(c);
+        uint64_t w1 = 0;
+        const aclnnStatus st = qmm_plan(&c->x, &c->w, &c->scale, nullptr, nullptr, &c->out, o, &w1, &c->ex);
+        if (st != ACLNN_SUCCESS) { delete plan; return st; }
+        need = w1 > need ? w1 : need;
+        r0 += rows[g];
+    }
+    auto *e = new (std::nothrow) aclOpExecutor();
+    if (!e) { delete plan; return ACLNN_ERR_RUNTIME_ERROR; }
+    e->op = PLAN_WRAPPER; e->payload = plan; e->payload_free = free_grouped;
+    *ws = need; *ex = e;
+    return ACLNN_SUCCESS;
+}
+
+aclnnStatus run_grouped(void *ws, uint64_t ws_bytes, aclOpExecutor *e, aclrtStream stream) {
+    if (!e) return ACLNN_ERR_PARAM_NULLPTR;
+    if (e->op != PLAN_WRAPPER || e->payload_free != free_grouped) return run_matmul(ws, ws_bytes, e, stream);   // 2-D weight: one plain matmul
+    auto *plan = static_cast<GroupedPlan *>(e->payload);
+    aclnnStatus st = ACLNN_SUCCESS;
+    for (GroupedPlan::Child *c : plan->children) {
+        // the caller may have handed over the data pointers after phase 1
+        c->x.data = plan->x->data; c->w.data = plan->w->data; c->scale.data = plan->scale->data; c->out.data = plan->out->data;
+        aclOpExecutor *child = c->ex;
+        c->ex = nullptr;   // run_matmul consumes it
+        const aclnnStatus s1 = run_matmul(ws, ws_bytes, child, stream);
+        if (s1 != ACLNN_SUCCESS && st == ACLNN_SUCCESS) st = s1;
+    }
+    delete e;
+    return st;
+}
+}  // namespace
+extern "C" {
+
 #define QMM_GROUPED_ALIAS(NAME, OPTS)                                                                                \
     aclnnStatus NAME##GetWorkspaceSize(const aclTensor *x, const aclTensor *weight, const aclTensor *scale,          \
                                        const aclIntArray *groupList, aclTensor *out, uint64_t *ws, aclOpExecutor **ex) { \
-        (void)groupList;                                                                                             \
-        if (!scale) return ACLNN_ERR_PARAM_NULLPTR;                                                                  \
-        return qmm_plan(x, weight, scale, nullptr, nullptr, out, OPTS, ws, ex);                                      \
+        return grouped_plan(x, weight, scale, groupList, out, OPTS, ws, ex);                                         \
     }                                                                                                                \
-    RUN_MATMUL(NAME)
+    aclnnStatus NAME(void *ws, uint64_t wsz, aclOpExecutor *e, aclrtStream s) { return run_grouped(ws, wsz, e, s); }
 QMM_GROUPED_ALIAS(aclnnQuantGroupedMatmulDequant, QmmOpts{})
 QMM_GROUPED_ALIAS(aclnnQuantGroupedMatmulDequantWeightNZ, QmmOpts{})
 QMM_GROUPED_ALIAS(aclnnQuantGroupedMatmulInplaceAdd, (QmmOpts{false, true, false}))

@@ -55,6 +55,7 @@ constexpr int MM_TILE_N = 256;      // nibble columns per tile
 constexpr int MM_SBK = 128;         // K rows per stage
 constexpr int MM_W_BYTES = 16384;   // packed weights of one stage: 128 rows x 128 B
 constexpr int MM_TEAMS = 3;
+constexpr int MM_MAX_ROWS = 16;     // rows of one pass (two activation fragments of 8)
 constexpr int MM_XP = 2;            // activation producer warps (they take alternate stages)
 constexpr int MM_THREADS = (4 * MM_TEAMS + 2 + MM_XP) * 32;
 
@@ -952,7 +953,7 @@ cudaError_t mm_launch_one(const CUtensorMap &tw, MmParams mp, int P, cudaStream_
 
 bool wq_mma_supported(const MatmulArgs &p) {
     if (p.epilogue != EPI_PLAIN || !p.scale || p.a_scale || p.b_scale) return false;
-    if (p.batch != 1 || p.b_transposed || p.accumulate || p.M < 1 || p.M > 16) return false;
+    if (p.batch != 1 || p.b_transposed || p.accumulate || p.M < 1 || p.M > 2 * MM_MAX_ROWS) return false;
     if (p.a_type != ET_F16 && p.a_type != ET_BF16) return false;
     if (p.b_type != ET_I4 && p.b_type != ET_I8) return false;
     if (p.b_nz && p.b_type != ET_I4) return false;
@@ -966,12 +967,28 @@ bool wq_mma_supported(const MatmulArgs &p) {
     return true;
 }
 
+// 17 to 32 rows run as two passes of up to 16 rows over the weights (the second pass streams them again): twice
+// the HBM traffic of one pass, and still well ahead of staging dequantised tiles in shared memory for tcgen05
+// at this row count (8192 x 28672 int4 at 32 rows: 2 x 29 us against 84 us).
+inline MatmulArgs mm_pass(const MatmulArgs &p, int pass) {
+    MatmulArgs q = p;
+    const int64_t r0 = (int64_t)pass * MM_MAX_ROWS;
+    q.M = p.M - r0 < MM_MAX_ROWS ? p.M - r0 : MM_MAX_ROWS;
+    q.a = (const char *)p.a + (size_t)r0 * p.K * 2;
+    q.out = (char *)p.out + (size_t)r0 * p.N * 2;
+    return q;
+}
+
 uint64_t wq_mma_workspace_bytes(const MatmulArgs &p) {
-    const MmPlan pl = mm_make_plan(p);
+    const MmPlan pl = mm_make_plan(mm_pass(p, 0));
     return pl.slot_bytes + pl.tag_bytes;
 }
 
 cudaError_t launch_wq_mma(const MatmulArgs &p, cudaStream_t s) {
+    if (p.M > MM_MAX_ROWS) {
+        cudaError_t e = launch_wq_mma(mm_pass(p, 0), s);
+        return e != cudaSuccess ? e : launch_wq_mma(mm_pass(p, 1), s);
+    }
     const MmPlan pl = mm_make_plan(p);
     if (p.workspace_bytes < pl.slot_bytes + pl.tag_bytes || !p.workspace) return cudaErrorInvalidValue;
     // TMA / bulk-copy sources, the 16-byte activation, scale and offset loads, the 16-byte output stores and

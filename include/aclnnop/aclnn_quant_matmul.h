@@ -90,9 +90,11 @@ B200_ACLNN_QMM(aclnnTransposeQuantBatchMatMul)
  * (cuda/src/ops/matmul.cu:1097-1149). */
 B200_ACLNN_QMM(aclnnBatchMatmulQuant)
 
-/* Grouped forms: the group list is accepted and ignored, as in the reference (one group over all
- * rows) -- replaces aclnn_ops.h:2023-2036 (cuda/src/ops/matmul.cu:1195-1202,1402-1413).
- * ...InplaceAdd: out += result. */
+/* Grouped (mixture-of-experts) forms -- replace aclnn_ops.h:2023-2036 (cuda/src/ops/matmul.cu:1195-1202,
+ * 1402-1413).  weight [K,N]: the group list is accepted and ignored, as in the reference (one group over all
+ * rows).  weight [E,K,N]: the group list holds E entries -- rows per group, or their running totals; either
+ * way they end at M -- and the rows of group g are multiplied by weight[g] and dequantised with scale[g]
+ * (scale [E,N], or [N] shared by all groups).  ...InplaceAdd: out += result. */
 #define B200_ACLNN_QMM_GROUPED(NAME) \
     ACL_FUNC_VISIBILITY aclnnStatus NAME##GetWorkspaceSize(const aclTensor *x, const aclTensor *weight, \
         const aclTensor *scale, const aclIntArray *groupList, aclTensor *out, uint64_t *workspaceSize, \
@@ -147,8 +149,15 @@ B200_ACLNN_MX(aclnnMatmulMxFp4Hw)
 ACL_FUNC_VISIBILITY aclnnStatus aclnnConvertWeightToINT4PackGetWorkspaceSize(const aclTensor *weight, aclTensor *out,
     uint64_t *workspaceSize, aclOpExecutor **executor);
 B200_ACLNN_RUN(aclnnConvertWeightToINT4Pack)
-/* Weight copy into the on-device format (identity layout, like the reference) and its size query.
- * Replaces aclnn_ops.h:2009-2014 (cuda/src/ops/matmul.cu:1162-1170). */
+/* One-time re-layout of a weight into the on-device format its `out` tensor names, and the size query that goes
+ * with it.  Replaces aclnn_ops.h:2009-2014 (cuda/src/ops/matmul.cu:1162-1170), where both are identities.
+ * An ACL_INT4 weight [K,N] copied into an out tensor of format ACL_FORMAT_FRACTAL_NZ (same view shape [K,N],
+ * storage of aclnnCalculateMatmulWeightSizeV2(shape, ACL_INT4) elements) becomes the tile-packed layout the
+ * decode kernel streams with contiguous 16 KB copies: blocks of 256 columns x 128 rows, tile-major, padded with
+ * zeros.  The aclnnWeightQuantBatchMatmul* entry points recognise the format on the weight tensor (any of the
+ * names, not only ...Nz) and give the same bits as on the caller's layout.  Every other case -- other types,
+ * ND destination -- is the identity copy of the reference, and aclnnCalculateMatmulWeightSize (no type) the
+ * product of the dimensions. */
 ACL_FUNC_VISIBILITY aclnnStatus aclnnTransMatmulWeightGetWorkspaceSize(const aclTensor *weight, aclTensor *out,
     uint64_t *workspaceSize, aclOpExecutor **executor);
 B200_ACLNN_RUN(aclnnTransMatmulWeight)

@@ -8,7 +8,7 @@
 # The reference's vendor headers (acl/acl.h, aclnn/acl_meta.h, hccl/hccl_types.h) are not shipped
 # with it; this repository's self-declared subset under include/ stands in for them.
 set -euo pipefail
-REF=${REFERENCE_ROOT:-/root/reference}
+REF=${REFERENCE_ROOT:?set REFERENCE_ROOT to the reference source tree}
 HERE=$(cd "$(dirname "$0")" && pwd)
 OUT=$HERE/_ref
 [ -d "$REF/cuda/src" ] || { echo "reference tree not found at $REF"; exit 1; }

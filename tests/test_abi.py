@@ -254,3 +254,17 @@ def test_phase1_does_not_depend_on_data_pointers(pkg):
         sizes.add(ws.value)
         lib.aclDestroyAclOpExecutor(ex)
     assert len(sizes) == 1
+
+
+def test_operator_archive_holds_the_operators(pkg):
+    """lib/libascendcl_qmm.a (what the reference-side build links in the interposed configuration) defines the
+    operator entry points and leaves the runtime / meta objects to the host library."""
+    import subprocess
+    path = os.path.join(os.path.dirname(pkg.LIB_PATH), "libascendcl_qmm.a")
+    assert os.path.exists(path), "run __graft_entry__.build()"
+    out = subprocess.run(["nm", "-g", "--defined-only", path], stdout=subprocess.PIPE, text=True, check=True).stdout
+    defined = {ln.split()[-1] for ln in out.splitlines() if len(ln.split()) >= 3}
+    for name in ("aclnnWeightQuantBatchMatmulV2GetWorkspaceSize", "aclnnWeightQuantBatchMatmulV2", "aclnnQuantMatmulV4",
+                 "aclnnMatmulMxFp8Hw", "aclnnTransMatmulWeight", "aclnnDynamicQuant", "aclnnQuantGroupedMatmulDequant"):
+        assert name in defined, name
+    assert "aclrtMalloc" not in defined and "aclCreateTensor" not in defined

@@ -854,6 +854,66 @@ def test_grouped_and_collective_signature_forwards(pkg, oracle, workloads, dev):
         assert torch.equal(out.cpu(), want), name
 
 
+def test_grouped_matmul_honours_the_group_list(pkg, oracle, workloads, dev):
+    """Mixture-of-experts form: weight [E,K,N], scale [E,N], group list as rows per group or as running totals
+    (one empty group among them): the rows of group g times weight[g], bit for bit the per-group W8A8 matmul of
+    the oracle.  The reference's own form (2-D weight, list ignored, cuda/src/ops/matmul.cu:1195-1202) is covered by
+    test_grouped_and_collective_signature_forwards."""
+    E, K, N = 4, 256, 192
+    counts = [40, 0, 130, 7]
+    M = sum(counts)
+    g = torch.Generator().manual_seed(8800)
+    x = torch.randint(-127, 128, (M, K), generator=g, dtype=torch.int8)
+    w = torch.randint(-127, 128, (E, K, N), generator=g, dtype=torch.int8)
+    sc = (torch.rand((E, N), generator=g) * 0.009 + 0.001).to(torch.float16)
+    want = torch.empty((M, N), dtype=torch.float16)
+    r0 = 0
+    for e, c in enumerate(counts):
+        if c:
+            acc = oracle.qmm_acc_fast(x[r0:r0 + c].numpy(), w[e].numpy(), c, K, N)
+            want[r0:r0 + c] = torch.from_numpy(oracle.qmm_epilogue_fast(acc, f32(sc[e]))).to(torch.float16)
+        r0 += c
+    lib = pkg.load()
+    xd, wd, sd = x.to(dev), w.to(dev), sc.to(dev)
+    totals = [sum(counts[:i + 1]) for i in range(E)]
+    for lst in (counts, totals):
+        arr = (ctypes.c_int64 * E)(*lst)
+        gl = ctypes.c_void_p(lib.aclCreateIntArray(arr, E))
+        for name in ("aclnnQuantGroupedMatmulDequant", "aclnnQuantGroupedMatmulDequantWeightNZ"):
+            out = torch.zeros((M, N), dtype=torch.float16, device=dev)
+            pkg.call(name, pkg.AclTensor(xd), pkg.AclTensor(wd), pkg.AclTensor(sd), gl, pkg.AclTensor(out))
+            torch.cuda.synchronize()
+            assert torch.equal(out.cpu(), want), (name, lst)
+        acc0 = torch.full((M, N), 0.5, dtype=torch.float16)
+        out = acc0.clone().to(dev)
+        pkg.call("aclnnQuantGroupedMatmulInplaceAdd", pkg.AclTensor(xd), pkg.AclTensor(wd), pkg.AclTensor(sd), gl, pkg.AclTensor(out))
+        torch.cuda.synchronize()
+        assert torch.equal(out.cpu(), (acc0.float() + want.float()).to(torch.float16))
+        lib.aclDestroyIntArray(gl)
+    bad = (ctypes.c_int64 * E)(40, 0, 130, 8)     # neither counts nor totals of M rows
+    gl = ctypes.c_void_p(lib.aclCreateIntArray(bad, E))
+    out = torch.zeros((M, N), dtype=torch.float16, device=dev)
+    assert pkg.call("aclnnQuantGroupedMatmulDequant", pkg.AclTensor(xd), pkg.AclTensor(wd), pkg.AclTensor(sd), gl, pkg.AclTensor(out),
+                    return_status=True) == 161002
+    lib.aclDestroyIntArray(gl)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M", [17, 24, 32])
+def test_w4a16_17_to_32_rows_in_two_passes(pkg, oracle, workloads, dev, M, dtype):
+    """17 to 32 rows: two passes of the decode kernel (rows 0-15, then the rest), int4 group-wise with offset and
+    bias, int8 per-channel, and tile-packed weights; weights stay exact, so the usual bounds against the oracle."""
+    d = workloads.w4a16(M=M, K=2048, N=1536, group=128, dtype=dtype, seed=8900 + M)
+    got = run_wq(pkg, d, dev)
+    assert_close(to_np(got), ref_wq(oracle, d), f"two passes M={M} {dtype}")
+    packed = pkg.pack_weight_nz(d["w"].to(dev), 2048, 1536)
+    nz = pkg.weight_quant_matmul(d["x"].to(dev), packed, d["scale"].to(dev), d["offset"].to(dev), d["bias"].to(dev), int4=True, group=128, nz=True)
+    torch.cuda.synchronize()
+    assert torch.equal(nz, got)
+    d8 = workloads.w8a16(M=M, K=1024, N=768, dtype=dtype, with_offset=True, seed=8950 + M)
+    assert_close(to_np(run_wq(pkg, d8, dev)), ref_wq(oracle, d8), f"two passes W8A16 M={M} {dtype}")
+
+
 def test_trans_quant_param_known_answers(pkg, dev):
     """fp32 scale (+ offset) -> int64 word: low half the scale's bits, high half the offset rounded
     to the nearest int32 (cuda/src/ops/quant.cu:572-576)."""
