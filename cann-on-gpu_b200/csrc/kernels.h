@@ -108,6 +108,12 @@ void wq_mma_device_status_reset();
 uint64_t wq_nz_bytes(int64_t K, int64_t N);
 cudaError_t launch_wq_pack_nz(const void *w_nd, void *w_nz, int64_t K, int64_t N, cudaStream_t s);
 cudaError_t launch_wq_unpack_nz(const void *w_nz, void *w_nd, int64_t K, int64_t N, cudaStream_t s);
+// Decode kernel for 3 to 16 rows on weights in the caller's layout (wq_rows.cu): activations in their own type.
+bool wq_rows_supported(const MatmulArgs &p);
+uint64_t wq_rows_workspace_bytes(const MatmulArgs &p);
+cudaError_t launch_wq_rows(const MatmulArgs &p, cudaStream_t s);
+unsigned int wq_rows_device_status();
+void wq_rows_device_status_reset();
 // 0, or the code of the first bounded wait that gave up on the current device (synchronises).
 unsigned int tc_device_status();
 // Clears the status words of every kernel family on the current device (synchronises).

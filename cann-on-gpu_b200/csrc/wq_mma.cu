@@ -67,6 +67,7 @@ struct MmParams {
     const void *x;           // activations [M,K], bf16 or fp16
     const void *scale, *offset, *bias;
     const uint8_t *wnz;      // tile-packed weights (blocks of 16 KB, [tile][stage]) or null
+    const uint8_t *xf;       // nine to sixteen rows: the activations converted per stage by wq_mma_activation_kernel
     int x_bf16;              // activation / scale / output type: 1 = bf16, 0 = fp16
     int M, N, K;
     int num_sb;              // stages per tile = ceil(K / 128)
@@ -199,6 +200,106 @@ __device__ __forceinline__ void mbar_drain(uint32_t bar, uint32_t parity) {
     }
 }
 
+// EPL consecutive elements of one activation row (V = EPL / 4 packed 8-byte words per lane; 128 / EPL lanes share
+// the row) -> scaled fp16 pairs h, the row's scale 2^e (up) and the row's sum of the converted values.
+template <bool BF16, int EPL>
+__device__ __forceinline__ void mm_convert_rows(const uint2 (&cur)[EPL / 4], uint32_t (&h)[EPL / 2], float &up, float &sum) {
+    constexpr int LPR = 128 / EPL, V = EPL / 4;
+    float v[EPL];
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+        const uint32_t w[2] = {cur[j].x, cur[j].y};
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+            if constexpr (BF16) {
+                v[4 * j + 2 * c] = __uint_as_float(w[c] << 16);
+                v[4 * j + 2 * c + 1] = __uint_as_float(w[c] & 0xFFFF0000u);
+            } else {
+                const float2 h2 = __half22float2(*reinterpret_cast<const __half2 *>(&w[c]));
+                v[4 * j + 2 * c] = h2.x;
+                v[4 * j + 2 * c + 1] = h2.y;
+            }
+        }
+    }
+    float down = 1.f;
+    up = 1.f;
+    if constexpr (BF16) {
+        // the largest magnitude of the row: bf16 magnitudes order like their 15-bit patterns, two per word
+        uint32_t mx2 = 0u;
+#pragma unroll
+        for (int j = 0; j < V; ++j) mx2 = __vmaxu2(mx2, __vmaxu2(cur[j].x & 0x7FFF7FFFu, cur[j].y & 0x7FFF7FFFu));
+        uint32_t abits = max(mx2 & 0xFFFFu, mx2 >> 16) << 16;
+        if constexpr (LPR == 32) abits = __reduce_max_sync(0xffffffffu, abits);
+        else {
+#pragma unroll
+            for (int o = 1; o < LPR; o <<= 1) abits = max(abits, __shfl_xor_sync(0xffffffffu, abits, o));
+        }
+        // it lands in [2^14, 2^15); zero rows keep scale 1; an infinite (or NaN) row is clamped (its result is not
+        // finite either way)
+        int e = 0;
+        if (abits != 0u) {
+            e = (int)((abits >> 23) & 0xFFu) - 127 - 14;
+            e = e < -100 ? -100 : (e > 100 ? 100 : e);
+        }
+        down = __uint_as_float((uint32_t)(127 - e) << 23);
+        up = __uint_as_float((uint32_t)(127 + e) << 23);
+    }
+    float sm = 0.f;
+#pragma unroll
+    for (int c = 0; c < EPL / 2; ++c) {
+        h[c] = pack_f16x2(v[2 * c] * down, v[2 * c + 1] * down);
+        const float2 back = __half22float2(*reinterpret_cast<const __half2 *>(&h[c]));
+        sm += back.x + back.y;   // the sum of what the tensor core will see
+    }
+#pragma unroll
+    for (int o = 1; o < LPR; o <<= 1) sm += __shfl_xor_sync(0xffffffffu, sm, o);
+    sum = sm;
+}
+// Writes them in B-fragment order (step st of 16 K, lane (g = row, t): {k = 2t, 2t+1}, {k = 2t+8, 2t+9}) behind `xf`,
+// followed by the 16 row scales and the 16 row sums (the layout of a slot's activation region).
+template <int MF, int EPL>
+__device__ __forceinline__ void mm_store_rows(uint8_t *xf, int f, int lane, const uint32_t (&h)[EPL / 2], float up, float sum) {
+    constexpr int LPR = 128 / EPL;
+    const int q = lane % LPR, rsub = lane / LPR;
+#pragma unroll
+    for (int c = 0; c < EPL / 2; ++c) {
+        const int kk = EPL * q + 2 * c, st = kk >> 4, kr = kk & 15;
+        *reinterpret_cast<uint32_t *>(xf + f * 2048 + (((st * 32 + 4 * rsub + ((kr & 7) >> 1)) << 3) + 4 * (kr >> 3))) = h[c];
+    }
+    if (q == 0) {
+        const int row = (MF == 2 ? 8 * f : 0) + rsub;
+        *reinterpret_cast<float *>(xf + MF * 2048 + 4 * row) = up;
+        *reinterpret_cast<float *>(xf + MF * 2048 + 64 + 4 * row) = sum;
+    }
+}
+
+// Nine to sixteen rows: converting sixteen rows per stage in every CTA is more than two warps can keep up with, and
+// it is the same work in all of them (the activations do not depend on the tile).  One small kernel converts each
+// 128-column stage of the activations once into the layout of a slot's activation region; the main kernel then
+// copies that region with the weights.
+template <bool BF16>
+__global__ void __launch_bounds__(32) wq_mma_activation_kernel(const uint16_t *x, uint8_t *xf_all, int M, int K) {
+    pdl_launch_dependents();
+    const int sbi = blockIdx.x, lane = threadIdx.x;
+    constexpr int EPL = 32, V = EPL / 4, LPR = 128 / EPL;
+    const int q = lane % LPR, rsub = lane / LPR, k = sbi * MM_SBK + EPL * q;
+    uint8_t *xf = xf_all + (size_t)sbi * (2 * 2048 + 128);
+#pragma unroll
+    for (int f = 0; f < 2; ++f) {
+        const int m = 8 * f + rsub;
+        uint2 cur[V];
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+            cur[j] = make_uint2(0u, 0u);
+            if (m < M && k + 4 * j < K) cur[j] = ldg8_now(x + (size_t)m * K + k + 4 * j);
+        }
+        uint32_t h[EPL / 2];
+        float up, sum;
+        mm_convert_rows<BF16, EPL>(cur, h, up, sum);
+        mm_store_rows<2, EPL>(xf, f, lane, h, up, sum);
+    }
+}
+
 // The activation producer (one warp).  For every stage of the CTA's share, in order: the stage's 128 K
 // columns of every activation row, from global memory (L2) to scaled fp16 in the slot, in B-fragment order
 // (step st of 16 K, lane (g = row, t): {k = 2t, 2t+1}, {k = 2t+8, 2t+9}), plus the row's scale 2^e and the
@@ -252,72 +353,11 @@ __device__ __forceinline__ void mm_activation_producer(const MmParams &p, uint32
             uint32_t h[MF][EPL / 2];
             float up[MF], sum[MF];
 #pragma unroll
-            for (int f = 0; f < MF; ++f) {
-                float v[EPL];
-#pragma unroll
-                for (int j = 0; j < V; ++j) {
-                    const uint32_t w[2] = {cur[f][j].x, cur[f][j].y};
-#pragma unroll
-                    for (int c = 0; c < 2; ++c) {
-                        if constexpr (BF16) {
-                            v[4 * j + 2 * c] = __uint_as_float(w[c] << 16);
-                            v[4 * j + 2 * c + 1] = __uint_as_float(w[c] & 0xFFFF0000u);
-                        } else {
-                            const float2 h2 = __half22float2(*reinterpret_cast<const __half2 *>(&w[c]));
-                            v[4 * j + 2 * c] = h2.x;
-                            v[4 * j + 2 * c + 1] = h2.y;
-                        }
-                    }
-                }
-                float down = 1.f;
-                up[f] = 1.f;
-                if constexpr (BF16) {
-                    float amax = 0.f;
-#pragma unroll
-                    for (int c = 0; c < EPL; ++c) amax = fmaxf(amax, fabsf(v[c]));
-                    // non-negative floats order like their bit patterns: one warp-wide integer maximum per row
-                    uint32_t abits = __float_as_uint(amax);
-                    if constexpr (LPR == 32) abits = __reduce_max_sync(0xffffffffu, abits);
-                    else {
-#pragma unroll
-                        for (int o = 1; o < LPR; o <<= 1) abits = max(abits, __shfl_xor_sync(0xffffffffu, abits, o));
-                    }
-                    // the row's largest magnitude lands in [2^14, 2^15); zero rows keep scale 1; an infinite (or NaN)
-                    // row is clamped (its result is not finite either way)
-                    int e = 0;
-                    if (abits != 0u) {
-                        e = (int)((abits >> 23) & 0xFFu) - 127 - 14;
-                        e = e < -100 ? -100 : (e > 100 ? 100 : e);
-                    }
-                    down = __uint_as_float((uint32_t)(127 - e) << 23);
-                    up[f] = __uint_as_float((uint32_t)(127 + e) << 23);
-                }
-                float sm = 0.f;
-#pragma unroll
-                for (int c = 0; c < EPL / 2; ++c) {
-                    h[f][c] = pack_f16x2(v[2 * c] * down, v[2 * c + 1] * down);
-                    const float2 back = __half22float2(*reinterpret_cast<const __half2 *>(&h[f][c]));
-                    sm += back.x + back.y;   // the sum of what the tensor core will see
-                }
-#pragma unroll
-                for (int o = 1; o < LPR; o <<= 1) sm += __shfl_xor_sync(0xffffffffu, sm, o);
-                sum[f] = sm;
-            }
+            for (int f = 0; f < MF; ++f) mm_convert_rows<BF16, EPL>(cur[f], h[f], up[f], sum[f]);
             if (round > 0 && !mm_wait(bars + 8u * (NS + slot), (round - 1) & 1, abort_flag, 0x340u + slot, p.wait_ns)) return;
-            const uint32_t sb = base + slot * L::SLOT;
+            uint8_t *xf = static_cast<uint8_t *>(__cvta_shared_to_generic(base + slot * L::SLOT + L::XF_OFF));
 #pragma unroll
-            for (int f = 0; f < MF; ++f) {
-                const int row = (MF == 2 ? 8 * f : 0) + rsub;
-#pragma unroll
-                for (int c = 0; c < EPL / 2; ++c) {
-                    const int kk = EPL * q + 2 * c, st = kk >> 4, kr = kk & 15;
-                    asm volatile("st.shared.b32 [%0], %1;" ::"r"(sb + L::XF_OFF + f * 2048 + (((st * 32 + 4 * rsub + ((kr & 7) >> 1)) << 3) + 4 * (kr >> 3))), "r"(h[f][c]) : "memory");
-                }
-                if (q == 0) {
-                    sts32f(sb + L::META_OFF + 4 * row, up[f]);
-                    sts32f(sb + L::META_OFF + 64 + 4 * row, sum[f]);
-                }
-            }
+            for (int f = 0; f < MF; ++f) mm_store_rows<MF, EPL>(xf, f, lane, h[f], up[f], sum[f]);
             __syncwarp();
             if (lane == 0) mbar_arrive(bars + 8u * slot);
             slot += MM_XP;
@@ -411,7 +451,19 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const MmParams p) {
         // ------------------------------------------------------------------ activation producers
         const int sb0 = (int)(ub - (long long)tile_first * p.num_sb), xp = warp - (4 * MM_TEAMS + 2);
         if constexpr (MF == 2) {
-            mm_activation_producer<BF16, 2, 32>(p, base, NS, bars, abort_flag, sb0, nu, lane, xp);
+            // converted once per call by wq_mma_activation_kernel: one bulk copy per stage
+            if (xp == 0 && lane == 0) {
+                pdl_wait_for_prerequisites();
+                constexpr uint32_t XB = 2 * 2048 + 128;
+                int slot = 0, round = 0, sbi = sb0;
+                for (int i = 0; i < nu; ++i) {
+                    if (round > 0 && !mm_wait(empty_bar(slot), (round - 1) & 1, abort_flag, 0x340u + slot, p.wait_ns)) break;
+                    mbar_expect_tx(full_bar(slot), XB);
+                    bulk_load_1d(base + slot * L::SLOT + L::XF_OFF, p.xf + (size_t)sbi * XB, XB, full_bar(slot));
+                    if (++slot == NS) { slot = 0; ++round; }
+                    if (++sbi == p.num_sb) sbi = 0;
+                }
+            }
         } else {
             if (p.M == 1) mm_activation_producer<BF16, 1, 4>(p, base, NS, bars, abort_flag, sb0, nu, lane, xp);
             else if (p.M == 2) mm_activation_producer<BF16, 1, 8>(p, base, NS, bars, abort_flag, sb0, nu, lane, xp);
@@ -846,7 +898,7 @@ int mm_sm_count() {
 struct MmPlan {
     int mf, tiles, num_sb, gsb, P;
     long long total_u;
-    uint64_t slot_bytes, tag_bytes;
+    uint64_t slot_bytes, tag_bytes, xf_bytes;
 };
 
 MmPlan mm_make_plan(const MatmulArgs &p) {
@@ -883,6 +935,7 @@ MmPlan mm_make_plan(const MatmulArgs &p) {
     if (const char *e = getenv("B200_QMM_WQ_MMA_P")) { const int v = atoi(e); if (v >= 1 && v <= sms && v <= pl.total_u) pl.P = v; }
     pl.slot_bytes = align_up_u64((uint64_t)(pl.tiles + pl.P) * p.M * tile_n * sizeof(float), 256);
     pl.tag_bytes = align_up_u64((uint64_t)(pl.tiles + pl.P) * sizeof(unsigned long long), 256);
+    pl.xf_bytes = pl.mf == 2 ? align_up_u64((uint64_t)pl.num_sb * (2 * 2048 + 128), 256) : 0;
     return pl;
 }
 
@@ -953,7 +1006,7 @@ cudaError_t mm_launch_one(const CUtensorMap &tw, MmParams mp, int P, cudaStream_
 
 bool wq_mma_supported(const MatmulArgs &p) {
     if (p.epilogue != EPI_PLAIN || !p.scale || p.a_scale || p.b_scale) return false;
-    if (p.batch != 1 || p.b_transposed || p.accumulate || p.M < 1 || p.M > 2 * MM_MAX_ROWS) return false;
+    if (p.batch != 1 || p.b_transposed || p.accumulate || p.M < 1 || p.M > MM_MAX_ROWS) return false;
     if (p.a_type != ET_F16 && p.a_type != ET_BF16) return false;
     if (p.b_type != ET_I4 && p.b_type != ET_I8) return false;
     if (p.b_nz && p.b_type != ET_I4) return false;
@@ -967,30 +1020,24 @@ bool wq_mma_supported(const MatmulArgs &p) {
     return true;
 }
 
-// 17 to 32 rows run as two passes of up to 16 rows over the weights (the second pass streams them again): twice
-// the HBM traffic of one pass, and still well ahead of staging dequantised tiles in shared memory for tcgen05
-// at this row count (8192 x 28672 int4 at 32 rows: 2 x 29 us against 84 us).
-inline MatmulArgs mm_pass(const MatmulArgs &p, int pass) {
-    MatmulArgs q = p;
-    const int64_t r0 = (int64_t)pass * MM_MAX_ROWS;
-    q.M = p.M - r0 < MM_MAX_ROWS ? p.M - r0 : MM_MAX_ROWS;
-    q.a = (const char *)p.a + (size_t)r0 * p.K * 2;
-    q.out = (char *)p.out + (size_t)r0 * p.N * 2;
-    return q;
+// Three to sixteen rows on weights in the caller's layout go to the kernel that takes the activations as they are
+// (wq_rows.cu): converting that many rows per stage inside this kernel does not keep up with the weight stream.
+inline bool mm_use_rows_kernel(const MatmulArgs &p) {
+    if (p.b_nz || p.M < 3 || !wq_rows_supported(p)) return false;
+    const char *e = getenv("B200_QMM_WQ_ROWS");
+    return !(e && atoi(e) == 0);
 }
 
 uint64_t wq_mma_workspace_bytes(const MatmulArgs &p) {
-    const MmPlan pl = mm_make_plan(mm_pass(p, 0));
-    return pl.slot_bytes + pl.tag_bytes;
+    if (mm_use_rows_kernel(p)) return wq_rows_workspace_bytes(p);
+    const MmPlan pl = mm_make_plan(p);
+    return pl.slot_bytes + pl.tag_bytes + pl.xf_bytes;
 }
 
 cudaError_t launch_wq_mma(const MatmulArgs &p, cudaStream_t s) {
-    if (p.M > MM_MAX_ROWS) {
-        cudaError_t e = launch_wq_mma(mm_pass(p, 0), s);
-        return e != cudaSuccess ? e : launch_wq_mma(mm_pass(p, 1), s);
-    }
+    if (mm_use_rows_kernel(p)) return launch_wq_rows(p, s);
     const MmPlan pl = mm_make_plan(p);
-    if (p.workspace_bytes < pl.slot_bytes + pl.tag_bytes || !p.workspace) return cudaErrorInvalidValue;
+    if (p.workspace_bytes < pl.slot_bytes + pl.tag_bytes + pl.xf_bytes || !p.workspace) return cudaErrorInvalidValue;
     // TMA / bulk-copy sources, the 16-byte activation, scale and offset loads, the 16-byte output stores and
     // the float4 partial tiles all need 16-byte aligned bases (every row pitch already is a multiple of 16 bytes).
     if ((reinterpret_cast<uintptr_t>(p.a) & 15) || (reinterpret_cast<uintptr_t>(p.b) & 15) ||
@@ -1013,6 +1060,13 @@ cudaError_t launch_wq_mma(const MatmulArgs &p, cudaStream_t s) {
     mp.slots = (float *)p.workspace;
     mp.tags = (unsigned long long *)((char *)p.workspace + pl.slot_bytes);
     mp.nonce = mm_next_nonce();
+    if (pl.mf == 2) {
+        uint8_t *xf = (uint8_t *)p.workspace + pl.slot_bytes + pl.tag_bytes;
+        if (p.a_type == ET_BF16) wq_mma_activation_kernel<true><<<pl.num_sb, 32, 0, s>>>((const uint16_t *)p.a, xf, (int)p.M, (int)p.K);
+        else wq_mma_activation_kernel<false><<<pl.num_sb, 32, 0, s>>>((const uint16_t *)p.a, xf, (int)p.M, (int)p.K);
+        count_launch();
+        mp.xf = xf;
+    }
     mp.x = p.a;
     mp.scale = p.scale; mp.offset = p.offset; mp.bias = p.bias;
     mp.wnz = p.b_nz ? (const uint8_t *)p.b : nullptr;

