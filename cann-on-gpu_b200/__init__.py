@@ -220,12 +220,33 @@ def quant_matmul(x, w, scale, pertoken=None, bias=None, out_dtype=None, name="ac
     return out
 
 
-def mx_matmul(a, a_kind, sa, b, b_kind, sb, M, K, N, out_dtype=None, name="aclnnMatmulMxFp8", **kw):
-    """a/b: uint8 buffers of MX elements (fp8: one byte each; fp4: two per byte); sa [M,K/32], sb [K/32,N] e8m0."""
+def widen_fp4_weight(b, K, N):
+    """One-time re-layout of an fp4 (e2m1, two per byte) weight [K,N] of a block-scaled matmul into its on-device
+    format, one fp8 e4m3 byte per element: aclnnCalculateMatmulWeightSizeV2 for the size, aclnnTransMatmulWeight
+    into an ACL_FORMAT_FRACTAL_NZ tensor.  Returns the widened buffer (uint8, K * N bytes)."""
+    import torch
+    lib = load()
+    shp = (ctypes.c_int64 * 2)(K, N)
+    ia = ctypes.c_void_p(lib.aclCreateIntArray(shp, 2))
+    n_out = torch.zeros(1, dtype=torch.int64, device=b.device)
+    call("aclnnCalculateMatmulWeightSizeV2", ia, ctypes.c_int64(ACL_FLOAT4_E2M1), AclTensor(n_out), device=b.device)
+    lib.aclDestroyIntArray(ia)
+    elems = int(n_out.item())
+    wide = torch.empty(elems // 2, dtype=torch.uint8, device=b.device)
+    call("aclnnTransMatmulWeight", AclTensor(b, ACL_FLOAT4_E2M1, (K, N)),
+         AclTensor(wide, ACL_FLOAT4_E2M1, (K, N), fmt=ACL_FORMAT_FRACTAL_NZ, storage=(elems,)))
+    return wide
+
+
+def mx_matmul(a, a_kind, sa, b, b_kind, sb, M, K, N, out_dtype=None, name="aclnnMatmulMxFp8", b_widened=False, **kw):
+    """a/b: uint8 buffers of MX elements (fp8: one byte each; fp4: two per byte); sa [M,K/32], sb [K/32,N] e8m0.
+    b_widened: b is the buffer widen_fp4_weight returned."""
     import torch
     out = torch.empty((M, N), dtype=out_dtype or torch.bfloat16, device=a.device)
+    tb = (AclTensor(b, b_kind, (K, N), fmt=ACL_FORMAT_FRACTAL_NZ, storage=(b.numel() * 2,)) if b_widened
+          else AclTensor(b, b_kind, (K, N)))
     call(name, AclTensor(a, a_kind, (M, K)), AclTensor(sa, ACL_FLOAT8_E8M0, (M, K // 32)),
-         AclTensor(b, b_kind, (K, N)), AclTensor(sb, ACL_FLOAT8_E8M0, (K // 32, N)), AclTensor(out), **kw)
+         tb, AclTensor(sb, ACL_FLOAT8_E8M0, (K // 32, N)), AclTensor(out), **kw)
     return out
 
 

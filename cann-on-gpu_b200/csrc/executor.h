@@ -12,6 +12,7 @@ enum PlanOp : int {
     PLAN_INT4_PACK,   // two int8 -> one packed byte
     PLAN_COPY,        // weight copy (identity pre-pack)
     PLAN_PACK_NZ,     // int4 weight [K,N] -> tile-packed layout
+    PLAN_WIDEN_FP4,   // fp4 weight -> one e4m3 byte per element
     PLAN_WEIGHT_SIZE, // element count of a weight shape
     PLAN_CAST,        // element-wise dtype cast
     PLAN_QPARAM,      // fp32 scale (+ offset) -> packed int64 quant parameter

@@ -49,7 +49,7 @@ struct MatmulArgs {
     int64_t batch = 1, M = 0, N = 0, K = 0, group = 0;
     int64_t a_batch_stride = 0, b_batch_stride = 0, out_batch_stride = 0;  // elements
     bool b_transposed = false;
-    bool b_nz = false;             // int4 weights in the tile-packed layout (see wq_mma.cu), not [K,N] row-major
+    bool b_nz = false;             // the weight is in its on-device format: int4 tile-packed (wq_mma.cu), or fp4 widened to e4m3 bytes (mx_tc.cu)
     bool accumulate = false;       // out = T(float(out) + float(T(result)))
     int split_k = 1;
     void *workspace = nullptr;
@@ -89,6 +89,7 @@ cudaError_t launch_expand(const MatmulArgs &p, cudaStream_t s);
 bool mx_native_supported(const MatmulArgs &p);
 uint64_t mx_native_workspace_bytes(const MatmulArgs &p);
 cudaError_t launch_mx_native(const MatmulArgs &p, cudaStream_t s);
+cudaError_t launch_mx_widen_fp4(const void *src, void *dst, int64_t elems, cudaStream_t s);
 unsigned int mx_tc_device_status();
 void mx_tc_device_status_reset();
 // Persistent stream-K tensor-core kernel for weight-only matmuls (wq_tc.cu).

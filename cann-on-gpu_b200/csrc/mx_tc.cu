@@ -272,19 +272,23 @@ __global__ void __launch_bounds__(256) mx_widen_fp4_kernel(const uint4 *src, uin
 
 // Scales into 512-byte groups of 128 rows x 4 K blocks: byte (r % 32) * 16 + (r / 32) * 4 + block.
 // along_rows: the source is [rows][kblocks] (operand A), groups ordered [row tile][k chunk]; otherwise the source is
-// [kblocks][rows] (operand B: rows = output columns), groups ordered [k chunk][row tile], row tiles padded to `tiles_pad`.
-// Rows beyond the matrix get 127 (a scale of one; their elements are zero).
-__global__ void __launch_bounds__(256) mx_group_scales_kernel(const uint8_t *src, uint8_t *dst, int rows, int kblocks, int along_rows,
+// [kblocks][rows] (operand B: rows = output columns), groups ordered [k chunk][row tile], row tiles padded to `row_tiles`.
+// Rows beyond the matrix get 127 (a scale of one; their elements are zero).  One CTA of 512 threads per group: the
+// reads follow the source's contiguous direction, the re-ordering goes through shared memory, the writes are contiguous.
+__global__ void __launch_bounds__(512) mx_group_scales_kernel(const uint8_t *src, uint8_t *dst, int rows, int kblocks, int along_rows,
                                                               int row_tiles, int kchunks) {
-    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const size_t total = (size_t)row_tiles * kchunks * 512;
-    if (i >= total) return;
-    const int in = (int)(i & 511), grp = (int)(i >> 9);
+    __shared__ uint8_t tile[4][128];   // [block][row]
+    const int grp = blockIdx.x, t = threadIdx.x;
     const int rt = along_rows ? grp / kchunks : grp % row_tiles, kc = along_rows ? grp % kchunks : grp / row_tiles;
-    const int r = rt * 128 + (in >> 4) + 32 * ((in >> 2) & 3), kb = kc * 4 + (in & 3);
-    uint8_t v = 127;
-    if (r < rows && kb < kblocks) v = along_rows ? src[(size_t)r * kblocks + kb] : src[(size_t)kb * rows + r];
-    dst[i] = v;
+    {
+        const int rl = along_rows ? t >> 2 : t & 127, kl = along_rows ? t & 3 : t >> 7;
+        const int r = rt * 128 + rl, kb = kc * 4 + kl;
+        uint8_t v = 127;
+        if (r < rows && kb < kblocks) v = along_rows ? src[(size_t)r * kblocks + kb] : src[(size_t)kb * rows + r];
+        tile[kl][rl] = v;
+    }
+    __syncthreads();
+    dst[(size_t)grp * 512 + t] = tile[t & 3][(t >> 4) + 32 * ((t >> 2) & 3)];
 }
 
 inline uint64_t mx_up256(uint64_t x) { return (x + 255) / 256 * 256; }
@@ -300,7 +304,7 @@ MxLayout mx_layout(const MatmulArgs &p) {
     l.n128e = 2 * l.n_tiles;
     l.kchunks = (int)(p.K / MX_BK);
     l.a8 = p.a_type == ET_E2M1 ? mx_up256((uint64_t)p.M * p.K) : 0;
-    l.b8 = p.b_type == ET_E2M1 ? mx_up256((uint64_t)p.K * p.N) : 0;
+    l.b8 = (p.b_type == ET_E2M1 && !p.b_nz) ? mx_up256((uint64_t)p.K * p.N) : 0;   // b_nz: widened once at load time
     l.sfa = mx_up256((uint64_t)l.m_tiles * l.kchunks * 512);
     l.sfb = mx_up256((uint64_t)l.kchunks * l.n128e * 512);
     l.total = l.a8 + l.b8 + l.sfa + l.sfb;
@@ -338,7 +342,7 @@ cudaError_t launch_mx_native(const MatmulArgs &p, cudaStream_t s) {
         count_launch();
         a_src = a8;
     }
-    if (p.b_type == ET_E2M1) {
+    if (p.b_type == ET_E2M1 && !p.b_nz) {
         const size_t n16 = (size_t)p.K * p.N / 32;   // N % 32 == 0
         mx_widen_fp4_kernel<<<(unsigned)((n16 + 255) / 256), 256, 0, s>>>((const uint4 *)p.b, (uint4 *)b8, n16);
         count_launch();
@@ -346,9 +350,8 @@ cudaError_t launch_mx_native(const MatmulArgs &p, cudaStream_t s) {
     }
     const int kblocks = (int)(p.K / 32);
     {
-        const size_t ta = (size_t)l.m_tiles * l.kchunks * 512, tb = (size_t)l.kchunks * l.n128e * 512;
-        mx_group_scales_kernel<<<(unsigned)((ta + 255) / 256), 256, 0, s>>>(p.a_scale, sfa, (int)p.M, kblocks, 1, l.m_tiles, l.kchunks);
-        mx_group_scales_kernel<<<(unsigned)((tb + 255) / 256), 256, 0, s>>>(p.b_scale, sfb, (int)p.N, kblocks, 0, l.n128e, l.kchunks);
+        mx_group_scales_kernel<<<(unsigned)(l.m_tiles * l.kchunks), 512, 0, s>>>(p.a_scale, sfa, (int)p.M, kblocks, 1, l.m_tiles, l.kchunks);
+        mx_group_scales_kernel<<<(unsigned)(l.kchunks * l.n128e), 512, 0, s>>>(p.b_scale, sfb, (int)p.N, kblocks, 0, l.n128e, l.kchunks);
         count_launch(2);
     }
     cudaError_t e = cudaGetLastError();
@@ -379,6 +382,16 @@ cudaError_t launch_mx_native(const MatmulArgs &p, cudaStream_t s) {
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int P = mp.tiles < sms ? mp.tiles : sms;
     mx_tc_kernel<<<P, 320, MxSmem::TOTAL, s>>>(ta, tb, mp, idesc);
+    count_launch();
+    return cudaGetLastError();
+}
+
+// One-time widening of an fp4 weight [K,N] to its e4m3 bytes (the on-device format of fp4 weights: K * N bytes).
+cudaError_t launch_mx_widen_fp4(const void *src, void *dst, int64_t elems, cudaStream_t s) {
+    if (elems % 32 != 0) return cudaErrorInvalidValue;
+    if ((reinterpret_cast<uintptr_t>(src) & 15) || (reinterpret_cast<uintptr_t>(dst) & 15)) return cudaErrorMisalignedAddress;
+    const size_t n16 = (size_t)elems / 32;
+    mx_widen_fp4_kernel<<<(unsigned)((n16 + 255) / 256), 256, 0, s>>>((const uint4 *)src, (uint4 *)dst, n16);
     count_launch();
     return cudaGetLastError();
 }

@@ -64,7 +64,8 @@ MatmulArgs args_of(const aclOpExecutor *e, void *ws, uint64_t ws_bytes) {
     p.batch = e->batch; p.M = e->m; p.N = e->n; p.K = e->k; p.group = e->group;
     p.a_batch_stride = e->m * e->k; p.b_batch_stride = e->k * e->n; p.out_batch_stride = e->m * e->n;
     p.b_transposed = e->b_transposed; p.accumulate = e->accumulate;
-    p.b_nz = e->op == PLAN_WQBMM && e->b->format == ACL_FORMAT_FRACTAL_NZ && e->b->dtype == ACL_INT4;
+    p.b_nz = e->b->format == ACL_FORMAT_FRACTAL_NZ &&
+             ((e->op == PLAN_WQBMM && e->b->dtype == ACL_INT4) || (e->op == PLAN_MX && e->b->dtype == ACL_FLOAT4_E2M1));
     p.split_k = e->split_k; p.workspace = ws; p.workspace_bytes = ws_bytes;
     if (e->bias) { p.bias = data_of(e->bias); p.bias_type = elem_type(e->bias->dtype); }
     switch (e->op) {
@@ -296,6 +297,11 @@ aclnnStatus mx_plan(const aclTensor *self, const aclTensor *selfScale, const acl
     e->op = PLAN_MX; e->a = self; e->b = other; e->scale = selfScale; e->scale2 = otherScale; e->out = out;
     e->m = M; e->n = N; e->k = K; e->group = 32;
     choose_path(e, ws);
+    if (other->format == ACL_FORMAT_FRACTAL_NZ && other->dtype == ACL_FLOAT4_E2M1 &&
+        (e->path != PATH_TC || !mx_native_supported(plan_args_of(e)))) {
+        delete e;   // widened fp4 weights are read by the native block-scaled kernel only
+        return ACLNN_ERR_PARAM_INVALID;
+    }
     *ex = e;
     return ACLNN_SUCCESS;
 }
@@ -310,6 +316,9 @@ aclnnStatus run_simple(aclOpExecutor *e, aclrtStream stream) {
             break;
         case PLAN_PACK_NZ:
             err = launch_wq_pack_nz(data_of(e->a), const_cast<void *>(data_of(e->out)), e->k, e->n, s);
+            break;
+        case PLAN_WIDEN_FP4:
+            err = launch_mx_widen_fp4(data_of(e->a), const_cast<void *>(data_of(e->out)), e->n, s);
             break;
         case PLAN_COPY:
             err = cudaMemcpyAsync(const_cast<void *>(data_of(e->out)), data_of(e->a), (size_t)e->n, cudaMemcpyDeviceToDevice, s);
@@ -640,6 +649,14 @@ aclnnStatus aclnnTransMatmulWeightGetWorkspaceSize(const aclTensor *weight, aclT
             return ACLNN_ERR_PARAM_INVALID;
         }
         e->op = PLAN_PACK_NZ; e->k = weight->viewDims[0]; e->n = weight->viewDims[1];
+    } else if (out->format == ACL_FORMAT_FRACTAL_NZ && weight->dtype == ACL_FLOAT4_E2M1 && weight->format != ACL_FORMAT_FRACTAL_NZ) {
+        // fp4 weight of a block-scaled matmul: one byte per element, the fp8 e4m3 code of the same value
+        if (weight->rank() != 2 || out->viewDims != weight->viewDims || (weight->numel() % 32) || (weight->offset & 1) || out->offset != 0 ||
+            storage_elems(out) < 2 * weight->numel()) {
+            delete e;
+            return ACLNN_ERR_PARAM_INVALID;
+        }
+        e->op = PLAN_WIDEN_FP4; e->n = weight->numel();
     } else {
         e->op = PLAN_COPY;
         e->n = (weight->numel() * elem_bits(elem_type(weight->dtype)) + 7) / 8;
@@ -661,6 +678,7 @@ static aclnnStatus weight_size_plan(const aclIntArray *shape, int64_t dtype, acl
     for (auto d : shape->v) e->n *= d;
     if (dtype == (int64_t)ACL_INT4 && shape->v.size() == 2 && shape->v[0] > 0 && shape->v[1] > 0)
         e->n = (int64_t)(2 * wq_nz_bytes(shape->v[0], shape->v[1]));
+    if (dtype == (int64_t)ACL_FLOAT4_E2M1) e->n *= 2;   // widened to one byte per element = the storage of two packed ones
     *ws = 0; *ex = e;
     return ACLNN_SUCCESS;
 }

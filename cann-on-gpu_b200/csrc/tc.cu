@@ -807,6 +807,7 @@ inline MatmulArgs as_nd(const MatmulArgs &p, const void *w_nd) {
 
 bool tc_supported(const MatmulArgs &p) {
     if (dev_info().sm100 != 1 || !encode_fn()) return false;
+    if (p.b_nz && is_mx(p)) return mx_native_supported(p);   // fp4 weights widened at load time: the native kernel only
     if (p.b_nz) {
         if (!is_wq(p) || p.b_type != ET_I4) return false;
         return nz_direct(p) || (p.N % 8 == 0 && tc_supported(as_nd(p, nullptr)));
@@ -816,11 +817,12 @@ bool tc_supported(const MatmulArgs &p) {
 }
 
 void tc_plan(MatmulArgs &p) {
-    if (p.b_nz) { p.split_k = 1; return; }
+    if (p.b_nz) { p.split_k = 1; return; }   // either on-device weight format: no K split
     p.split_k = (use_stream_wq(p) || use_expand(p) || use_mx_native(p)) ? 1 : make_plan(p).split;
 }
 
 uint64_t tc_workspace_bytes(const MatmulArgs &p) {
+    if (p.b_nz && is_mx(p)) return mx_native_workspace_bytes(p);
     if (p.b_nz) return nz_direct(p) ? wq_mma_workspace_bytes(p) : nz_copy_bytes(p) + tc_workspace_bytes(as_nd(p, nullptr));
     if (use_decode_wq(p)) return wq_mma_workspace_bytes(p);
     if (use_stream_wq(p)) return wq_tc_workspace_bytes(p);
@@ -830,6 +832,7 @@ uint64_t tc_workspace_bytes(const MatmulArgs &p) {
 }
 
 cudaError_t launch_tc(const MatmulArgs &p, cudaStream_t s) {
+    if (p.b_nz && is_mx(p)) return launch_mx_native(p, s);
     if (p.b_nz) {
         if (nz_direct(p)) return launch_wq_mma(p, s);
         const uint64_t copy = nz_copy_bytes(p);

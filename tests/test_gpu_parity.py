@@ -540,6 +540,35 @@ def test_mx_native_block_scaled_kernel(pkg, oracle, workloads, dev, kinds, shape
                      mean_rel=1e-5 if odt == torch.float32 else 2e-3)
 
 
+def test_mx_fp4_weight_widened_at_load_time(pkg, oracle, workloads, dev):
+    """aclnnTransMatmulWeight of an fp4 weight into an ACL_FORMAT_FRACTAL_NZ tensor stores one e4m3 byte per element
+    (every e2m1 value is exact in e4m3); the block-scaled matmul on it gives the bits of the call on the packed
+    weight, without the per-call widening pass.  A shape the native kernel does not take is refused."""
+    M, K, N = 300, 1024, 800
+    d = workloads.mx(M=M, K=K, N=N, a_fp4=False, b_fp4=True, seed=5450)
+    b = d["b"].reshape(-1).to(dev)
+    wide = pkg.widen_fp4_weight(b, K, N)
+    torch.cuda.synchronize()
+    assert wide.numel() == K * N
+    codes = oracle.unpack_nibbles(d["b"].numpy(), K * N)
+    vals = oracle.decode_table(oracle.MXK_E2M1)[codes]
+    assert np.array_equal(oracle.decode_table(oracle.MXK_E4M3)[wide.cpu().numpy()], vals)
+    a, sa, sb = d["a"].reshape(-1).to(dev), d["sa"].to(dev), d["sb"].to(dev)
+    plain = pkg.mx_matmul(a, pkg.ACL_FLOAT8_E4M3FN, sa, b, pkg.ACL_FLOAT4_E2M1, sb, M, K, N, out_dtype=torch.float32)
+    pre = pkg.mx_matmul(a, pkg.ACL_FLOAT8_E4M3FN, sa, wide, pkg.ACL_FLOAT4_E2M1, sb, M, K, N, out_dtype=torch.float32, b_widened=True)
+    torch.cuda.synchronize()
+    assert torch.equal(plain, pre)
+    assert_close(to_np(pre), ref_mx(oracle, d), "widened fp4 weight")
+    d2 = workloads.mx(M=8, K=96, N=64, a_fp4=False, b_fp4=True, seed=5451)      # K not a multiple of 128
+    w2 = pkg.widen_fp4_weight(d2["b"].reshape(-1).to(dev), 96, 64)
+    out = torch.empty((8, 64), dtype=torch.float32, device=dev)
+    st = pkg.call("aclnnMatmulMxFp8", pkg.AclTensor(d2["a"].reshape(-1).to(dev), pkg.ACL_FLOAT8_E4M3FN, (8, 96)),
+                  pkg.AclTensor(d2["sa"].to(dev), pkg.ACL_FLOAT8_E8M0, (8, 3)),
+                  pkg.AclTensor(w2, pkg.ACL_FLOAT4_E2M1, (96, 64), fmt=pkg.ACL_FORMAT_FRACTAL_NZ, storage=(w2.numel() * 2,)),
+                  pkg.AclTensor(d2["sb"].to(dev), pkg.ACL_FLOAT8_E8M0, (3, 64)), pkg.AclTensor(out), return_status=True)
+    assert st == 161002
+
+
 def test_mx_native_e5m2_operand(pkg, oracle, dev):
     """fp8 e5m2 elements (the reference's other fp8 kind, cuda/src/ops/matmul.cu:437) through the native kernel."""
     M, K, N = 200, 512, 320
