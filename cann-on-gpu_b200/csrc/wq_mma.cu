@@ -95,6 +95,18 @@ struct MmSmem {
     __host__ __device__ static int total(int ns, int M) { return bar_off(ns, M) + (2 * ns + 2) * 8 + 16 + 1024; }
 };
 
+#ifdef WQ_MMA_PROFILE
+// Time stamps per CTA (development aid, compiled only with -DWQ_MMA_PROFILE): row 0 entry, 1 barriers initialised,
+// 2 weight producer past its dependency wait, 3 first stage full, 4 last stage multiplied (latest team), 5 reducer
+// has the teams' last partial tile, 6 reducer done, 7 nanoseconds the reducer spent on tiles shared between CTAs.
+__device__ unsigned long long g_mm_prof[8][160];
+#define MM_STAMP(row) do { g_mm_prof[row][blockIdx.x < 160 ? blockIdx.x : 159] = global_ns(); } while (0)
+#define MM_STAMP_MAX(row) do { atomicMax(&g_mm_prof[row][blockIdx.x < 160 ? blockIdx.x : 159], global_ns()); } while (0)
+#else
+#define MM_STAMP(row) do { } while (0)
+#define MM_STAMP_MAX(row) do { } while (0)
+#endif
+
 __host__ __device__ inline long long mm_share_begin(long long c, long long total, int P) { return c * total / P; }
 __host__ __device__ inline int mm_share_owner(long long u, long long total, int P) { return (int)(((u + 1) * P - 1) / total); }
 
@@ -385,6 +397,7 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const MmParams p) {
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int P = gridDim.x, cta = blockIdx.x;
+    if (threadIdx.x == 0) MM_STAMP(0);
     const bool has_off = p.offset != nullptr;
     const long long ub = mm_share_begin(cta, p.total_u, P), ue = mm_share_begin(cta + 1, p.total_u, P);
     const int nu = (int)(ue - ub);
@@ -404,11 +417,13 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const MmParams p) {
     if ((int)threadIdx.x < 2 * NS + 2) asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     __syncthreads();
     if (threadIdx.x == 0) pdl_launch_dependents();   // the next kernel in the stream may take over SMs as they free up
+    if (threadIdx.x == 0) MM_STAMP(1);
 
     if (warp == 0) {
         // ------------------------------------------------------------------ weight producer
         if (lane == 0) {
             if (!p.weights_early) pdl_wait_for_prerequisites();
+            MM_STAMP(2);
             // Everything the loop needs is kept incrementally (this is one thread competing with fifteen warps for
             // issue slots: every instruction here is paid in full, per stage).
             int i = 0, slot = 0, round = 0;
@@ -512,6 +527,7 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const MmParams p) {
                 had = true;
                 const int slot = j % NS, round = j / NS;
                 if (!mm_wait(full_bar(slot), round & 1, abort_flag, 0x310u + slot, p.wait_ns)) { ok = false; break; }
+                if (warp == 1 && lane == 0 && sg == 0 && j == j_first) MM_STAMP(3);
                 const uint32_t sb = base + slot * L::SLOT;
 #pragma unroll
                 for (int st = 0; st < 8; ++st) {
@@ -620,6 +636,7 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const MmParams p) {
                 else fold(std::false_type{});
             }
             if (!ok) break;
+            if (wq == 0 && lane == 0 && tile == tile_last) MM_STAMP_MAX(4);
             // hand this team's partial tile to the reducer
             if (sg >= 1 && !mm_wait(seg_free, (sg - 1) & 1, abort_flag, 0x320u, p.wait_ns)) { ok = false; break; }
             if (had) {
@@ -649,17 +666,22 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const MmParams p) {
             const int n = CPL * lane, n_glob = tile * TN + n;
             const bool n_ok = n_glob < p.N;
             const int c_first = mm_share_owner(t_lo, p.total_u, P), c_last = mm_share_owner(t_hi - 1, p.total_u, P);
-            // every lane reads every tag itself (acquire), so the reads of the partial tiles that follow are ordered
-            // after the tags lane by lane and no fence is needed on this side
+            // One tag per lane (a tile of a short problem has ten and more contributors, and reading their tags one
+            // after the other costs an L2 round trip each).  Each tag is read with acquire semantics by one lane; the
+            // warp barrier after the vote orders every lane's later reads of the partial tiles behind those loads.
             auto others_published = [&]() {
                 bool all = true;
-                for (int c = c_first; c <= c_last && all; ++c) {
-                    if (c == cta) continue;
-                    unsigned long long tg;
-                    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(tg) : "l"(p.tags + tile + c) : "memory");
-                    all = tg == p.nonce;
+                for (int c0 = c_first; c0 <= c_last; c0 += 32) {
+                    const int c = c0 + lane;
+                    if (c <= c_last && c != cta) {
+                        unsigned long long tg;
+                        asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(tg) : "l"(p.tags + tile + c) : "memory");
+                        all = all && tg == p.nonce;
+                    }
                 }
-                return __all_sync(0xffffffffu, all);
+                all = __all_sync(0xffffffffu, all);
+                __syncwarp();
+                return all;
             };
             // While the teams still work on this CTA's piece of a shared tile, see whether the other contributors
             // have published theirs already (the usual case for the piece a CTA works on last: its neighbour did
@@ -698,6 +720,10 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const MmParams p) {
                 if (early) fetch_others();
             }
             if (!mm_wait(seg_done, sg & 1, abort_flag, 0x330u, p.wait_ns)) break;
+            if (lane == 0 && tile == tile_last) MM_STAMP(5);
+#ifdef WQ_MMA_PROFILE
+            const unsigned long long prof_t0 = global_ns();
+#endif
             if (whole && sg == 0) pdl_wait_for_prerequisites();   // first write to the output
             // this CTA's sum over its teams for row m of the tile
             auto own_row = [&](int m, float (&v)[CPL]) {
@@ -757,20 +783,28 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const MmParams p) {
                         for (int m = 0; m < p.M; ++m) {
                             float own[CPL], v[CPL];
                             own_row(m, own);
+                            // four contributors' loads are issued before the first is added (the sum stays in
+                            // contributor order), so their L2 round trips overlap; four columns at a time keeps the
+                            // loads in flight within the register budget
 #pragma unroll
-                            for (int c = 0; c < CPL; ++c) v[c] = 0.f;
-                            for (int c = c_first; c <= c_last; ++c) {
-                                if (c == cta) {
+                            for (int q4 = 0; q4 < CPL / 4; ++q4) {
+                                float4 acc4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                                for (int c0 = c_first; c0 <= c_last; c0 += 4) {
+                                    float4 a[4];
 #pragma unroll
-                                    for (int q4 = 0; q4 < CPL; ++q4) v[q4] += own[q4];
-                                } else {
-                                    const float4 *src = reinterpret_cast<const float4 *>(p.slots + ((size_t)(tile + c) * p.M + m) * TN + n);
+                                    for (int u = 0; u < 4; ++u) {
+                                        const int c = c0 + u;
+                                        a[u] = make_float4(own[4 * q4], own[4 * q4 + 1], own[4 * q4 + 2], own[4 * q4 + 3]);
+                                        if (c <= c_last && c != cta)   // written by other SMs: read at L2
+                                            a[u] = __ldcg(reinterpret_cast<const float4 *>(p.slots + ((size_t)(tile + c) * p.M + m) * TN + n) + q4);
+                                    }
 #pragma unroll
-                                    for (int q4 = 0; q4 < CPL / 4; ++q4) {
-                                        const float4 a = __ldcg(src + q4);   // written by other SMs: read at L2
-                                        v[4 * q4] += a.x; v[4 * q4 + 1] += a.y; v[4 * q4 + 2] += a.z; v[4 * q4 + 3] += a.w;
+                                    for (int u = 0; u < 4; ++u) {
+                                        if (c0 + u > c_last) break;
+                                        acc4.x += a[u].x; acc4.y += a[u].y; acc4.z += a[u].z; acc4.w += a[u].w;
                                     }
                                 }
+                                v[4 * q4] = acc4.x; v[4 * q4 + 1] = acc4.y; v[4 * q4 + 2] = acc4.z; v[4 * q4 + 3] = acc4.w;
                             }
                             write_row(m, v);
                         }
@@ -820,7 +854,11 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const MmParams p) {
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(seg_free);
+#ifdef WQ_MMA_PROFILE
+            if (lane == 0 && !whole) g_mm_prof[7][cta < 160 ? cta : 159] += global_ns() - prof_t0;
+#endif
         }
+        if (lane == 0) MM_STAMP(6);
     }
 }
 
@@ -1003,6 +1041,15 @@ cudaError_t mm_launch_one(const CUtensorMap &tw, MmParams mp, int P, cudaStream_
 }
 
 }  // namespace
+
+#ifdef WQ_MMA_PROFILE
+// Copies the stamps of the launches so far to `host` (8 x 160 values) and clears rows 4 and 7.
+extern "C" __attribute__((visibility("default"))) int aclnnB200DecodeProfile(unsigned long long *host) {
+    if (cudaMemcpyFromSymbol(host, g_mm_prof, sizeof(g_mm_prof)) != cudaSuccess) return 1;
+    static unsigned long long zero[8][160] = {};
+    return cudaMemcpyToSymbol(g_mm_prof, zero, sizeof(zero)) == cudaSuccess ? 0 : 1;
+}
+#endif
 
 bool wq_mma_supported(const MatmulArgs &p) {
     if (p.epilogue != EPI_PLAIN || !p.scale || p.a_scale || p.b_scale) return false;
