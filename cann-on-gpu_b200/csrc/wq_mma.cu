@@ -62,8 +62,8 @@ constexpr int MM_THREADS = (4 * MM_TEAMS + 2 + MM_XP) * 32;
 struct MmParams {
     void *out;
     float *slots;            // [tiles + P][M][tile_n] fp32 partial tiles of tiles shared between CTAs
-    unsigned long long *tags;   // [tiles + P] arrival tags of those partial tiles
-    unsigned long long nonce;   // this launch's tag value (never 0)
+    unsigned long long *tags;   // [tiles] per tile: this launch's key | number of partial tiles published
+    unsigned long long nonce;   // this launch's key: upper 48 bits, never 0; the lower 16 are zero
     const void *x;           // activations [M,K], bf16 or fp16
     const void *scale, *offset, *bias;
     const uint8_t *wnz;      // tile-packed weights (blocks of 16 KB, [tile][stage]) or null
@@ -666,22 +666,20 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const MmParams p) {
             const int n = CPL * lane, n_glob = tile * TN + n;
             const bool n_ok = n_glob < p.N;
             const int c_first = mm_share_owner(t_lo, p.total_u, P), c_last = mm_share_owner(t_hi - 1, p.total_u, P);
-            // One tag per lane (a tile of a short problem has ten and more contributors, and reading their tags one
-            // after the other costs an L2 round trip each).  Each tag is read with acquire semantics by one lane; the
-            // warp barrier after the vote orders every lane's later reads of the partial tiles behind those loads.
+            // A tile shared between CTAs has one 64-bit word in the workspace: this launch's key in the upper 48 bits
+            // and the number of contributors that have published their partial tile in the lower 16.  The key is
+            // unique to the launch, so whatever an earlier use left there never counts.  The first contributor to
+            // look at the word installs the key (compare-and-swap against what it saw; losing that race means somebody
+            // else installed it); from then on the word only ever changes by atomic increments, and whoever finishes
+            // the tile clears it, so a replay of the same launch (a captured graph) starts clean.
+            unsigned long long *word = p.tags + tile;
+            const int n_contrib = c_last - c_first + 1;
+            const unsigned long long all_but_me = p.nonce | (unsigned long long)(n_contrib - 1);
+            unsigned long long seen = 0ull;   // the word as this CTA last saw it
+            // every lane reads the word itself (acquire), so its later reads of the partial tiles are ordered behind it
             auto others_published = [&]() {
-                bool all = true;
-                for (int c0 = c_first; c0 <= c_last; c0 += 32) {
-                    const int c = c0 + lane;
-                    if (c <= c_last && c != cta) {
-                        unsigned long long tg;
-                        asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(tg) : "l"(p.tags + tile + c) : "memory");
-                        all = all && tg == p.nonce;
-                    }
-                }
-                all = __all_sync(0xffffffffu, all);
-                __syncwarp();
-                return all;
+                asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(seen) : "l"(word) : "memory");
+                return seen == all_but_me;
             };
             // While the teams still work on this CTA's piece of a shared tile, see whether the other contributors
             // have published theirs already (the usual case for the piece a CTA works on last: its neighbour did
@@ -717,9 +715,35 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const MmParams p) {
             if (!whole) {
                 if (sg == 0) pdl_wait_for_prerequisites();   // first touch of the workspace
                 early = others_published();
+                if ((seen & ~0xFFFFull) != p.nonce) {
+                    if (lane == 0) {
+                        unsigned long long old;
+                        asm volatile("atom.relaxed.gpu.global.cas.b64 %0, [%1], %2, %3;" : "=l"(old) : "l"(word), "l"(seen), "l"(p.nonce) : "memory");
+                    }
+                    __syncwarp();
+                    early = others_published();
+                }
                 if (early) fetch_others();
             }
-            if (!mm_wait(seg_done, sg & 1, abort_flag, 0x330u, p.wait_ns)) break;
+            // Wait for the teams, and meanwhile keep an eye on the word: once every other contributor has published, their
+            // partial tiles are fetched while the teams still work.
+            {
+                bool got = mbar_try_wait(seg_done, sg & 1);
+                if (!got) {
+                    const unsigned long long t0 = global_ns(), limit = p.wait_ns ? p.wait_ns : WAIT_LIMIT_NS;
+                    while (true) {
+                        if (mbar_try_wait_for(seg_done, sg & 1, 400u)) { got = true; break; }
+                        if (!whole && !early && others_published()) { early = true; fetch_others(); }
+                        if (*abort_flag) break;
+                        if (global_ns() - t0 > limit) {
+                            *abort_flag = 1;
+                            atomicCAS(&g_tc_status, 0u, 0x330u);
+                            break;
+                        }
+                    }
+                }
+                if (!got) break;
+            }
             if (lane == 0 && tile == tile_last) MM_STAMP(5);
 #ifdef WQ_MMA_PROFILE
             const unsigned long long prof_t0 = global_ns();
@@ -770,13 +794,10 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const MmParams p) {
                     }
                 }
             } else {
-                // A tile shared between CTAs.  Each contributor looks whether all the OTHERS have published their
-                // partial tiles; if so it adds its own (still in shared memory) in contributor order and writes the
-                // tile.  Otherwise it publishes its own partial tile and looks again; whoever then sees them all sums
-                // them.  No CTA ever waits for another; two contributors that publish together may both see all tags
-                // and both write the (identical) tile.  The tag is a value unique to this launch, so whatever an
-                // earlier use left in the workspace never matches; the finisher clears the tags again so that a replay
-                // of the same launch (a captured graph) starts clean.
+                // A tile shared between CTAs.  A contributor that found all the OTHERS published when it looked (while its
+                // teams were still working) adds its own part, still in shared memory, in contributor order and writes the
+                // tile.  Otherwise it publishes its partial tile and counts itself in; whoever completes the count sums the
+                // partial tiles and writes the tile.  No CTA ever waits for another.
                 // sum in contributor order, this CTA's own part from shared memory
                 auto finish = [&]() {
                     if (n_ok) {
@@ -810,7 +831,7 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const MmParams p) {
                         }
                     }
                     __syncwarp();
-                    for (int c = c_first + lane; c <= c_last; c += 32) p.tags[tile + c] = 0ull;
+                    if (lane == 0) *word = 0ull;
                 };
                 if (early && p.M <= PRE_M && c_last - cta <= 1) {
                     // the others' sums are in registers: (before + own) + after is finish()'s order exactly when at
@@ -827,8 +848,8 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const MmParams p) {
                         }
                     }
                     __syncwarp();
-                    for (int c = c_first + lane; c <= c_last; c += 32) p.tags[tile + c] = 0ull;
-                } else if (early || others_published()) {
+                    if (lane == 0) *word = 0ull;
+                } else if (early) {
                     finish();
                 } else {
                     if (n_ok) {
@@ -840,16 +861,20 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const MmParams p) {
                             for (int c = 0; c < CPL / 4; ++c) dst[c] = make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
                         }
                     }
-                    // the warp barrier orders every lane's stores before lane 0's release of the tag (release is
-                    // cumulative); the sequentially consistent fence orders that store before the tag reads below, so
-                    // of two contributors that publish together at least one sees the other
+                    // Publish: the warp barrier orders every lane's stores before lane 0's increment, whose release half
+                    // makes them visible with the new count (release is cumulative) and whose acquire half orders the
+                    // reads of finish() behind every earlier contributor's increment (they form one chain of
+                    // read-modify-writes on the word).  The contributor that brings the count to n_contrib finishes the
+                    // tile: exactly one does, and it waits for nobody.
                     __syncwarp();
+                    unsigned long long now = 0ull;
                     if (lane == 0) {
-                        asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(p.tags + tile + cta), "l"(p.nonce) : "memory");
-                        asm volatile("fence.sc.gpu;" ::: "memory");
+                        asm volatile("atom.acq_rel.gpu.global.add.u64 %0, [%1], %2;" : "=l"(now) : "l"(word), "l"(1ull) : "memory");
+                        now += 1ull;
                     }
+                    now = __shfl_sync(0xffffffffu, now, 0);
                     __syncwarp();
-                    if (others_published()) finish();
+                    if (now == (p.nonce | (unsigned long long)n_contrib)) finish();
                 }
             }
             __syncwarp();
@@ -972,7 +997,7 @@ MmPlan mm_make_plan(const MatmulArgs &p) {
     }
     if (const char *e = getenv("B200_QMM_WQ_MMA_P")) { const int v = atoi(e); if (v >= 1 && v <= sms && v <= pl.total_u) pl.P = v; }
     pl.slot_bytes = align_up_u64((uint64_t)(pl.tiles + pl.P) * p.M * tile_n * sizeof(float), 256);
-    pl.tag_bytes = align_up_u64((uint64_t)(pl.tiles + pl.P) * sizeof(unsigned long long), 256);
+    pl.tag_bytes = align_up_u64((uint64_t)pl.tiles * sizeof(unsigned long long), 256);
     pl.xf_bytes = pl.mf == 2 ? align_up_u64((uint64_t)pl.num_sb * (2 * 2048 + 128), 256) : 0;
     return pl;
 }
@@ -1106,7 +1131,8 @@ cudaError_t launch_wq_mma(const MatmulArgs &p, cudaStream_t s) {
     mp.out = p.out;
     mp.slots = (float *)p.workspace;
     mp.tags = (unsigned long long *)((char *)p.workspace + pl.slot_bytes);
-    mp.nonce = mm_next_nonce();
+    mp.nonce = mm_next_nonce() & ~0xFFFFull;
+    if (mp.nonce == 0ull) mp.nonce = 1ull << 16;
     if (pl.mf == 2) {
         uint8_t *xf = (uint8_t *)p.workspace + pl.slot_bytes + pl.tag_bytes;
         if (p.a_type == ET_BF16) wq_mma_activation_kernel<true><<<pl.num_sb, 32, 0, s>>>((const uint16_t *)p.a, xf, (int)p.M, (int)p.K);
