@@ -403,21 +403,33 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const MmParams p) {
     const int nu = (int)(ue - ub);
     const int tile_first = (int)(ub / p.num_sb), tile_last = (int)((ue - 1) / p.num_sb);
 
-    // activation rows the producer never writes (beyond M) must read as zero
-    for (int i = threadIdx.x; i < NS * (MF * 512 + 32); i += MM_THREADS) {
-        const int sl = i / (MF * 512 + 32), w = i % (MF * 512 + 32);
-        *reinterpret_cast<uint32_t *>(gen_base + sl * L::SLOT + L::XF_OFF + 4 * w) = 0u;
+    // Start-up.  The weight producer (thread 0) initialises the barriers itself and goes straight on to issue its first
+    // copies; it only announces itself at the CTA barrier (warp 0 arrives without waiting).  The other fifteen warps
+    // meanwhile clear the activation regions (rows the activation producers never write, those beyond M, must read as
+    // zero) and wait at the barrier, after which they see the initialised barriers.  The first stage is thereby on its
+    // way about a microsecond earlier than with a barrier for all, and that is time on the call's critical path.
+    // A stage is full when the weight copy has landed (producer's arrive + bytes) and the activation producer has
+    // arrived; it is empty when the team's four warps have arrived.
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int sl = 0; sl < NS; ++sl) { mbar_init(full_bar(sl), 2); mbar_init(empty_bar(sl), 4); }
+            mbar_init(seg_done, 4 * MM_TEAMS);
+            mbar_init(seg_free, 1);
+            *abort_flag = 0;
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            __threadfence_block();
+        }
+        __syncwarp();
+        asm volatile("bar.arrive 0, %0;" ::"r"(MM_THREADS) : "memory");
+    } else {
+        for (int i = threadIdx.x - 32; i < NS * (MF * 512 + 32); i += MM_THREADS - 32) {
+            const int sl = i / (MF * 512 + 32), w = i % (MF * 512 + 32);
+            *reinterpret_cast<uint32_t *>(gen_base + sl * L::SLOT + L::XF_OFF + 4 * w) = 0u;
+        }
+        asm volatile("bar.sync 0, %0;" ::"r"(MM_THREADS) : "memory");
     }
-    // a stage is full when the weight copy has landed (producer's arrive + bytes) and the activation
-    // producer has arrived; it is empty when the team's four warps have arrived
-    if ((int)threadIdx.x < NS) mbar_init(full_bar(threadIdx.x), 2);
-    else if ((int)threadIdx.x < 2 * NS) mbar_init(empty_bar(threadIdx.x - NS), 4);
-    else if ((int)threadIdx.x == 2 * NS) mbar_init(seg_done, 4 * MM_TEAMS);
-    else if ((int)threadIdx.x == 2 * NS + 1) { mbar_init(seg_free, 1); *abort_flag = 0; }
-    if ((int)threadIdx.x < 2 * NS + 2) asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    __syncthreads();
     if (threadIdx.x == 0) pdl_launch_dependents();   // the next kernel in the stream may take over SMs as they free up
-    if (threadIdx.x == 0) MM_STAMP(1);
+    if (threadIdx.x == 32) MM_STAMP(1);
 
     if (warp == 0) {
         // ------------------------------------------------------------------ weight producer
