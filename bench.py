@@ -773,6 +773,47 @@ def main():
             sharded["weak_error"] = repr(e)[:200]
         torch.cuda.empty_cache()
 
+    if world > 1 and gather is not None:
+        # The reference's other multi-GPU form, for comparison: K split over the ranks and an all-reduce of the
+        # output (W8A8 prefill 4096 x 4096 x 14336, bf16 out), as the plain sequence (the library's default) and with the
+        # all-reduce of a row chunk overlapping the next chunk's matmul (two chunks, 20 SMs left to the all-reduce).
+        try:
+            hccl_path = os.path.join(os.path.dirname(pkg.LIB_PATH), "libhccl.so")
+            comm = gather[1]
+            kr = 4096 // world
+            gq = torch.Generator().manual_seed(5200 + rank)
+            qx = torch.randint(-127, 128, (4096, kr), generator=gq, dtype=torch.int8).to(dev)
+            qw = torch.randint(-127, 128, (kr, 14336), generator=gq, dtype=torch.int8).to(dev)
+            qs = (torch.rand(14336, generator=torch.Generator().manual_seed(5199)) * 1e-3 + 1e-4).to(torch.bfloat16).to(dev)
+            qo = torch.empty((4096, 14336), dtype=torch.bfloat16, device=dev)
+            ws_q = pkg.Workspace()
+            targs = [pkg.AclTensor(qx), pkg.AclTensor(qw), pkg.AclTensor(qs), comm, pkg.AclTensor(qo)]
+
+            def ksplit_step():
+                with pkg.use_library(hccl_path):
+                    for _ in range(4):
+                        pkg.call("aclnnQuantMatmulAllReduce", *targs, workspace=ws_q, device=dev)
+            res = {}
+            for label, chunks in (("plain", None), ("overlapped", "2")):
+                if chunks is None:
+                    os.environ.pop("B200_HCCL_OVERLAP_CHUNKS", None)
+                else:
+                    os.environ["B200_HCCL_OVERLAP_CHUNKS"] = chunks
+                for _ in range(3):
+                    ksplit_step()
+                torch.cuda.synchronize()
+                res[label] = round(timed(ksplit_step, 5, world, dev) / (5 * 4) * 1e3, 2)
+            os.environ.pop("B200_HCCL_OVERLAP_CHUNKS", None)
+            sharded["ksplit_allreduce_w8a8_m4096"] = {
+                "plain_us_per_call": res["plain"], "overlapped_us_per_call": res["overlapped"],
+                "what": "aclnnQuantMatmulAllReduce, x int8 [4096, 4096/N] @ w int8 [4096/N, 14336] -> bf16 [4096, 14336] summed over "
+                        "the ranks by HcclAllReduce (NCCL); overlapped = B200_HCCL_OVERLAP_CHUNKS=2: all-reduce of chunk i on a second "
+                        "stream beside the matmul of chunk i+1 (off by default: it measures slower); direct calls, no graph"}
+            del qx, qw, qo
+        except Exception as e:
+            sharded["ksplit_allreduce_w8a8_m4096"] = {"error": repr(e)[:200]}
+        torch.cuda.empty_cache()
+
     # End to end through the C ABI with host buffers: activations come from pinned host memory and
     # the result goes back to pinned host memory on every call; weights stay resident.
     hx = [d["x"].cpu().pin_memory() for *_, d in runner.items]

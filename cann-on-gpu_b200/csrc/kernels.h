@@ -119,6 +119,7 @@ void wq_rows_device_status_reset();
 unsigned int tc_device_status();
 // Clears the status words of every kernel family on the current device (synchronises).
 void tc_device_status_reset();
+void tc_reserve_sms(int n);   // the calling thread's dense-kernel plans leave n SMs free (0 = none)
 
 // Host-side tally of kernels this library has launched (diagnostics for benchmarks).
 void count_launch(int n = 1);

@@ -370,6 +370,8 @@ uint32_t aclnnB200DeviceStatus(void) {
     if (v) g_latched_status[dev].store(v, std::memory_order_relaxed);
     return v ? v : g_latched_status[dev].load(std::memory_order_relaxed);
 }
+void aclnnB200ReserveSms(int32_t sms) { tc_reserve_sms(sms); }
+
 void aclnnB200ResetDeviceStatus(void) {
     qmm::tc_device_status_reset();
     int dev = 0;

@@ -565,6 +565,7 @@ __global__ void tc_finalize_kernel(TcParams p) {
 }
 
 // ------------------------------------------------------------------------------------------------ host
+thread_local int g_reserved_sms = 0;
 struct DevInfo { int sm100 = -1, sms = 0; };
 
 DevInfo &dev_info() {
@@ -612,7 +613,10 @@ TcPlan make_plan(const MatmulArgs &p) {
     const int n_tiles = (int)((p.N + pl.tn - 1) / pl.tn);
     pl.m_tiles = (int)((p.M + pl.mt - 1) / pl.mt);
     pl.tiles = n_tiles * pl.m_tiles;
-    const int sms = dev_info().sms > 0 ? dev_info().sms : 148;
+    int sms = dev_info().sms > 0 ? dev_info().sms : 148;
+    // SMs the caller wants left free for a kernel that runs beside this one (aclnnB200ReserveSms): a persistent
+    // kernel on every SM would keep a concurrent collective from starting until it has finished.
+    if (g_reserved_sms > 0) sms = sms - g_reserved_sms > 8 ? sms - g_reserved_sms : 8;
     // Whole rounds of one tile per SM run unsplit.  The tiles left over (all of them when there are
     // fewer tiles than SMs) are cut along K so that the last round is short instead of leaving most
     // SMs idle -- but only where that pays.  A unit pulls kb * bk * (mt + 128) operand bytes into its SM
@@ -851,6 +855,8 @@ cudaError_t launch_tc(const MatmulArgs &p, cudaStream_t s) {
     if (use_expand(p)) return launch_expand(p, s);
     return launch_dense_tc(p, s);
 }
+
+void tc_reserve_sms(int n) { g_reserved_sms = n > 0 ? n : 0; }
 
 void tc_device_status_reset() {
     const unsigned int z = 0;

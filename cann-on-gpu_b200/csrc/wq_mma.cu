@@ -695,10 +695,10 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const MmParams p) {
             };
             // While the teams still work on this CTA's piece of a shared tile, see whether the other contributors
             // have published theirs already (the usual case for the piece a CTA works on last: its neighbour did
-            // that tile first), and with one or two rows fetch their partial tiles right away: the hand-over below
+            // that tile first), and with one row fetch their partial tiles right away: the hand-over below
             // then needs no global round trip.
             bool early = false;
-            constexpr int PRE_M = 2;
+            constexpr int PRE_M = 1;
             float pre[PRE_M][2][CPL];   // [row][contributors before / after this CTA][column]
             auto fetch_others = [&]() {
                 if (p.M <= PRE_M && c_last - cta <= 1) {
@@ -816,28 +816,31 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const MmParams p) {
                         for (int m = 0; m < p.M; ++m) {
                             float own[CPL], v[CPL];
                             own_row(m, own);
-                            // four contributors' loads are issued before the first is added (the sum stays in
-                            // contributor order), so their L2 round trips overlap; four columns at a time keeps the
-                            // loads in flight within the register budget
+                            // four contributors' loads (the lane's eight columns each) are issued before the first is
+                            // added, so their L2 round trips overlap; the sum stays in contributor order
 #pragma unroll
-                            for (int q4 = 0; q4 < CPL / 4; ++q4) {
-                                float4 acc4 = make_float4(0.f, 0.f, 0.f, 0.f);
-                                for (int c0 = c_first; c0 <= c_last; c0 += 4) {
-                                    float4 a[4];
+                            for (int c = 0; c < CPL; ++c) v[c] = 0.f;
+                            for (int c0 = c_first; c0 <= c_last; c0 += 4) {
+                                float4 a[4][CPL / 4];
 #pragma unroll
-                                    for (int u = 0; u < 4; ++u) {
-                                        const int c = c0 + u;
-                                        a[u] = make_float4(own[4 * q4], own[4 * q4 + 1], own[4 * q4 + 2], own[4 * q4 + 3]);
-                                        if (c <= c_last && c != cta)   // written by other SMs: read at L2
-                                            a[u] = __ldcg(reinterpret_cast<const float4 *>(p.slots + ((size_t)(tile + c) * p.M + m) * TN + n) + q4);
-                                    }
+                                for (int u = 0; u < 4; ++u) {
+                                    const int c = c0 + u;
 #pragma unroll
-                                    for (int u = 0; u < 4; ++u) {
-                                        if (c0 + u > c_last) break;
-                                        acc4.x += a[u].x; acc4.y += a[u].y; acc4.z += a[u].z; acc4.w += a[u].w;
+                                    for (int q4 = 0; q4 < CPL / 4; ++q4) a[u][q4] = make_float4(own[4 * q4], own[4 * q4 + 1], own[4 * q4 + 2], own[4 * q4 + 3]);
+                                    if (c <= c_last && c != cta) {   // written by other SMs: read at L2
+                                        const float4 *src = reinterpret_cast<const float4 *>(p.slots + ((size_t)(tile + c) * p.M + m) * TN + n);
+#pragma unroll
+                                        for (int q4 = 0; q4 < CPL / 4; ++q4) a[u][q4] = __ldcg(src + q4);
                                     }
                                 }
-                                v[4 * q4] = acc4.x; v[4 * q4 + 1] = acc4.y; v[4 * q4 + 2] = acc4.z; v[4 * q4 + 3] = acc4.w;
+#pragma unroll
+                                for (int u = 0; u < 4; ++u) {
+                                    if (c0 + u > c_last) break;
+#pragma unroll
+                                    for (int q4 = 0; q4 < CPL / 4; ++q4) {
+                                        v[4 * q4] += a[u][q4].x; v[4 * q4 + 1] += a[u][q4].y; v[4 * q4 + 2] += a[u][q4].z; v[4 * q4 + 3] += a[u][q4].w;
+                                    }
+                                }
                             }
                             write_row(m, v);
                         }

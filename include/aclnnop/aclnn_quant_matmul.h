@@ -262,6 +262,15 @@ ACL_FUNC_VISIBILITY aclnnStatus aclnnB200WeightQuantMatmulNoAlloc(const void *x,
  * aclnnB200WrapperPayload returns the payload (NULL for any other executor); with release != 0 the
  * executor gives up ownership of it. */
 ACL_FUNC_VISIBILITY aclOpExecutor *aclnnB200CreateWrapperExecutor(void *payload, void (*payload_free)(void *));
+/* A view of rows [firstRow, firstRow + rows) of the leading dimension of `tensor` over the same buffer (the
+ * composite operators cut their work into row chunks with it; the public meta API has no stride getters).
+ * NULL for a range outside the tensor.  Destroyed with aclDestroyTensor. */
+ACL_FUNC_VISIBILITY aclTensor *aclnnB200CreateRowSlice(const aclTensor *tensor, int64_t firstRow, int64_t rows);
+/* The dense tensor-core kernels are persistent, one CTA per SM; a kernel enqueued on another stream (a
+ * collective) could then not start before they finish.  After aclnnB200ReserveSms(n) the plans the CALLING
+ * THREAD makes (both phases must see the same value) leave n SMs unused; 0 restores the default.  Used by the
+ * all-reduce matmuls of libhccl.so around their row chunks. */
+ACL_FUNC_VISIBILITY void aclnnB200ReserveSms(int32_t sms);
 ACL_FUNC_VISIBILITY void *aclnnB200WrapperPayload(aclOpExecutor *executor, int release);
 
 /* Diagnostics (no counterpart in the reference): number of kernels this library has launched in the

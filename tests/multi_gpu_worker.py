@@ -6,7 +6,9 @@ then every rank calls HcclCommInitRootInfo.  Checks:
   1. column sharding: each rank multiplies its [K, N/g] shard, HcclAllGather returns [g][M][N/g], the
      interleave is the [M, N] result of the whole problem;
   2. K-split all-reduce forms: aclnnWeightQuantMatmulAllReduce and aclnnQuantMatmulAllReduce sum the
-     ranks' partial products.
+     ranks' partial products;
+  3. the same with many rows and B200_HCCL_OVERLAP_CHUNKS set, where the all-reduce of a row chunk overlaps the
+     next chunk's matmul.
 """
 import ctypes
 import os
@@ -105,6 +107,38 @@ def main():
     want_y, want_sum = oracle.add_rmsnorm(out.float().cpu().numpy(), f32(res), f32(gamma), 1e-5, "f16")
     assert np.array_equal(rs.float().cpu().numpy(), want_sum), f"rank {rank}: residual sum of the norm matmul"
     assert_close(to_np(y), want_y.astype(np.float64), f"rank {rank}: aclnnQuantMatmulAllReduceAddRmsNorm")
+
+    # 3. many rows: the all-reduce of one row chunk overlaps the matmul of the next (second stream, events);
+    # the chunked form must give the bits of the plain sequence, and both the oracle's result
+    big = workloads.w8a8(M=1100, K=256 * world, N=512, seed=83, with_pertoken=False, with_bias=False, scale_dtype=torch.float16)
+    bx, bw = big["x"][:, ks].contiguous().to(dev), big["w"][ks, :].contiguous().to(dev)
+    outs = {}
+    for chunks in ("1", "4", None):     # plain, four chunks, the default (plain)
+        if chunks is None:
+            os.environ.pop("B200_HCCL_OVERLAP_CHUNKS", None)
+        else:
+            os.environ["B200_HCCL_OVERLAP_CHUNKS"] = chunks
+        o = torch.empty((1100, 512), dtype=torch.float16, device=dev)
+        with pkg.use_library(hccl_path):
+            pkg.call("aclnnQuantMatmulAllReduce", pkg.AclTensor(bx), pkg.AclTensor(bw), pkg.AclTensor(big["scale"].to(dev)), comm,
+                     pkg.AclTensor(o))
+        torch.cuda.synchronize()
+        outs[chunks] = o
+    assert torch.equal(outs["1"], outs["4"]) and torch.equal(outs["1"], outs[None]), f"rank {rank}: chunked all-reduce differs from the plain one"
+    acc = oracle.qmm_acc_fast(big["x"].numpy(), big["w"].numpy(), 1100, big["K"], 512)
+    assert_close(to_np(outs[None]), oracle.qmm_epilogue_fast(acc, f32(big["scale"])).astype(np.float64), f"rank {rank}: chunked aclnnQuantMatmulAllReduce")
+    os.environ["B200_HCCL_OVERLAP_CHUNKS"] = "3"
+    dw = workloads.w4a16(M=1030, K=512 * world, N=256, group=128, dtype=torch.float16, per_channel=True, with_bias=False, seed=84)
+    kw = slice(rank * 512, (rank + 1) * 512)
+    w_r = workloads.pack_int4(dw["w_vals"][kw].contiguous()).to(dev)
+    o = torch.empty((1030, 256), dtype=torch.float16, device=dev)
+    with pkg.use_library(hccl_path):
+        pkg.call("aclnnWeightQuantMatmulAllReduce", pkg.AclTensor(dw["x"][:, kw].contiguous().to(dev)), pkg.AclTensor(w_r, pkg.ACL_INT4, (512, 256)),
+                 pkg.AclTensor(dw["scale"].to(dev)), pkg.AclTensor(dw["offset"].to(dev)), comm, pkg.AclTensor(o))
+    torch.cuda.synchronize()
+    os.environ.pop("B200_HCCL_OVERLAP_CHUNKS", None)
+    ref = oracle.wqbmm_fast(f32(dw["x"]), dw["w"].numpy(), True, f32(dw["scale"]), f32(dw["offset"]), None, 1030, dw["K"], 256, 0)
+    assert_close(to_np(o), ref, f"rank {rank}: chunked aclnnWeightQuantMatmulAllReduce")
 
     assert hccl.HcclCommDestroy(comm) == 0
     with open(os.path.join(tmp, f"ok.{rank}"), "w") as f:
