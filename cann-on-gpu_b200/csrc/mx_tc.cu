@@ -20,8 +20,11 @@
 //
 // Kernel: persistent, one CTA per SM, 320 threads.  Warp 0 = TMA producer (ring of 4 stages of 128 K),
 // warp 1 = MMA issuer and tensor-memory owner, warps 2-9 = epilogue (two sets of four warps, 128 columns
-// each).  Tile = 128 rows x 256 columns, one accumulator of 256 tensor-memory columns; the scale groups take
-// 2 x 16 further columns.  Every wait is bounded and records a code in the device status word.
+// each).  Tile = 128 rows x 256 columns with one accumulator of 256 tensor-memory columns; the scale groups take
+// 2 x 16 further columns.  (The tile width is a launch parameter: up to 240 columns two accumulators fit and the
+// epilogue of one tile overlaps the MMAs of the next; the weight boxes and scale groups stay 256 columns wide, the
+// columns beyond the tile belong to the next one and are not multiplied.  mx_layout says why 256 is the default.)
+// Every wait is bounded and records a code in the device status word.
 //
 // Replaces aclnnMatmulMxFp8Hw / aclnnMatmulMxFp4Hw of the reference (cuBLASLt VEC32_UE8M0 behind per-call
 // transpose and scale passes, cuda/src/ops/matmul.cu:538-597,657-730).
@@ -42,7 +45,7 @@ struct MxSmem {
     static constexpr int STAGE_BYTES = (SFB_OFF + 1024 + 1023) / 1024 * 1024;
     static constexpr int PAYLOAD = X_BYTES + W_BYTES + 512 + 1024;
     static constexpr int BAR_OFF = MX_STAGES * STAGE_BYTES;
-    static constexpr int NUM_BARS = 2 * MX_STAGES + 2;
+    static constexpr int NUM_BARS = 2 * MX_STAGES + 4;
     static constexpr int MISC_OFF = BAR_OFF + NUM_BARS * 8;
     static constexpr int TOTAL = MISC_OFF + 16 + 1024;
 };
@@ -53,13 +56,15 @@ struct MxParams {
     int out_type;
     int M, N, K;
     int m_tiles, tiles, num_kb;     // tiles are numbered n_tile * m_tiles + m_tile; num_kb = K / 128
+    int tile_n;                     // output columns per tile: 256, or less (a multiple of 16)
+    int nacc;                       // accumulators in tensor memory, tile_n columns apart
     const uint8_t *sfa;             // [m_tile][k chunk][512] scale groups of A
-    const uint8_t *sfb;             // [k chunk][n128e][512] scale groups of B (n128e = even count of 128-column groups)
-    int n128e;
+    const uint8_t *sfb;             // [k chunk][n_tile][2][512] scale groups of B: columns tile_n * n_tile + 128 * h ...
+    int n128e;                      // 2 * n_tiles
 };
 
 constexpr uint32_t MX_TMEM_COLS = 512;
-constexpr uint32_t MX_SF_COL = 256;   // scale groups live behind the accumulator: two buffers of 16 columns
+constexpr uint32_t MX_SF_COL = 480;   // scale groups live behind the accumulators: two buffers of 16 columns
 
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -107,7 +112,8 @@ mx_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
     auto b_tile = [&](int s) { return base + s * L::STAGE_BYTES + L::X_BYTES; };
     auto bar_full = [&](int s) { return base + L::BAR_OFF + 8 * s; };
     auto bar_empty = [&](int s) { return base + L::BAR_OFF + 8 * (MX_STAGES + s); };
-    const uint32_t bar_acc_full = base + L::BAR_OFF + 8 * (2 * MX_STAGES), bar_acc_empty = bar_acc_full + 8;
+    auto bar_acc_full = [&](int a) { return base + L::BAR_OFF + 8 * (2 * MX_STAGES + a); };
+    auto bar_acc_empty = [&](int a) { return base + L::BAR_OFF + 8 * (2 * MX_STAGES + 2 + a); };
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(gen_base + L::MISC_OFF);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(gen_base + L::MISC_OFF + 4);
 
@@ -115,8 +121,7 @@ mx_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < MX_STAGES; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
-        mbar_init(bar_acc_full, 1);
-        mbar_init(bar_acc_empty, 8);
+        for (int a = 0; a < 2; ++a) { mbar_init(bar_acc_full(a), 1); mbar_init(bar_acc_empty(a), 8); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_proxy_async();
@@ -128,7 +133,7 @@ mx_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
     const uint32_t tmem_base = *tmem_slot;
 
     auto tile_geom = [&](int tile, int &n0, int &m0) {
-        n0 = (tile / p.m_tiles) * MX_N;
+        n0 = (tile / p.m_tiles) * p.tile_n;
         m0 = (tile % p.m_tiles) * MX_M;
     };
 
@@ -140,7 +145,7 @@ mx_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
                 int n0, m0;
                 tile_geom(tile, n0, m0);
                 const uint8_t *sfa = p.sfa + (size_t)(m0 / MX_M) * p.num_kb * 512;
-                const uint8_t *sfb = p.sfb + (size_t)(n0 / 128) * 512;
+                const uint8_t *sfb = p.sfb + (size_t)(tile / p.m_tiles) * 1024;
                 for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
                     const int s = it % MX_STAGES;
                     if (it >= MX_STAGES && !mbar_wait(bar_empty(s), ((it / MX_STAGES) - 1) & 1, abort_flag, 0x401u)) { ok = false; break; }
@@ -159,8 +164,10 @@ mx_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
             int it = 0, ti = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x, ++ti) {
-                if (ti >= 1) {
-                    if (!mbar_wait(bar_acc_empty, (ti - 1) & 1, abort_flag, 0x402u)) { ok = false; break; }
+                const int ab = ti % p.nacc;
+                const uint32_t d_tmem = tmem_base + (uint32_t)(ab * p.tile_n);
+                if (ti >= p.nacc) {   // the epilogue has drained this accumulator's previous tile
+                    if (!mbar_wait(bar_acc_empty(ab), (ti / p.nacc - 1) & 1, abort_flag, 0x402u)) { ok = false; break; }
                     tc_fence_after();
                 }
                 for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
@@ -176,38 +183,40 @@ mx_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
                     for (int kk = 0; kk < 4; ++kk) {
                         const uint64_t a_desc = smem_desc(a_tile(s) + kk * 32, 16, 1024);
                         const uint64_t b_desc = smem_desc(b_tile(s) + kk * 4096, 16384, 1024);
-                        mx_mma(tmem_base, a_desc, b_desc, idesc | ((uint32_t)kk << 4) | ((uint32_t)kk << 29), sf, sf + 4,
+                        mx_mma(d_tmem, a_desc, b_desc, idesc | ((uint32_t)kk << 4) | ((uint32_t)kk << 29), sf, sf + 4,
                                (kb > 0 || kk > 0) ? 1u : 0u);
                     }
                     tc_commit(bar_empty(s));
                 }
-                if (ok) tc_commit(bar_acc_full);
+                if (ok) tc_commit(bar_acc_full(ab));
             }
         }
     } else {
         // epilogue: a warp's tensor-memory lane quarter = 32 rows; the two sets of four warps take 128 columns each
         const int eset = (warp - 2) >> 2, q = warp & 3;
-        const int row = q * 32 + lane, cb = eset * 128;
+        const int half = p.tile_n >> 1;                     // columns per epilogue set (a multiple of 8)
+        const int row = q * 32 + lane, cb = eset * half;
         int ti = 0;
         for (int tile = blockIdx.x; tile < p.tiles; tile += gridDim.x, ++ti) {
             int n0, m0;
             tile_geom(tile, n0, m0);
             const int m = m0 + row;
             const bool m_ok = m < p.M;
-            if (!mbar_wait(bar_acc_full, ti & 1, abort_flag, 0x405u)) break;
+            const int ab = ti % p.nacc;
+            if (!mbar_wait(bar_acc_full(ab), (ti / p.nacc) & 1, abort_flag, 0x405u)) break;
             tc_fence_after();
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + cb;
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(ab * p.tile_n) + cb;
             const int esz = p.out_type == ET_F32 ? 4 : 2;
             uint8_t *orow = (uint8_t *)p.out + ((size_t)m * p.N + n0 + cb) * esz;
 #pragma unroll 1
-            for (int c0 = 0; c0 < 128; c0 += 32) {
+            for (int c0 = 0; c0 < half; c0 += 32) {
                 uint32_t v[32];
-                mx_tmem_ld32(taddr + c0, v);
+                mx_tmem_ld32(taddr + c0, v);              // (the load may run past the set's columns: those are not stored)
                 if (!m_ok) continue;
 #pragma unroll
                 for (int g = 0; g < 4; ++g) {
                     const int c = c0 + 8 * g;
-                    if (n0 + cb + c >= p.N) break;   // N is a multiple of 8 on this path
+                    if (n0 + cb + c >= p.N || c >= half) break;   // N and the set's width are multiples of 8
                     float f[8];
 #pragma unroll
                     for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(v[8 * g + j]);
@@ -234,7 +243,7 @@ mx_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_acc_empty);
+            if (lane == 0) mbar_arrive(bar_acc_empty(ab));
         }
     }
 
@@ -275,14 +284,16 @@ __global__ void __launch_bounds__(256) mx_widen_fp4_kernel(const uint4 *src, uin
 // [kblocks][rows] (operand B: rows = output columns), groups ordered [k chunk][row tile], row tiles padded to `row_tiles`.
 // Rows beyond the matrix get 127 (a scale of one; their elements are zero).  One CTA of 512 threads per group: the
 // reads follow the source's contiguous direction, the re-ordering goes through shared memory, the writes are contiguous.
+// Operand B's groups come in pairs per output tile: group 2 j + h covers the 128 columns from tile_n * j + 128 * h
+// (tile_n = 256: plain consecutive groups).
 __global__ void __launch_bounds__(512) mx_group_scales_kernel(const uint8_t *src, uint8_t *dst, int rows, int kblocks, int along_rows,
-                                                              int row_tiles, int kchunks) {
+                                                              int row_tiles, int kchunks, int tile_n) {
     __shared__ uint8_t tile[4][128];   // [block][row]
     const int grp = blockIdx.x, t = threadIdx.x;
     const int rt = along_rows ? grp / kchunks : grp % row_tiles, kc = along_rows ? grp % kchunks : grp / row_tiles;
     {
         const int rl = along_rows ? t >> 2 : t & 127, kl = along_rows ? t & 3 : t >> 7;
-        const int r = rt * 128 + rl, kb = kc * 4 + kl;
+        const int r = (along_rows ? rt * 128 : (rt >> 1) * tile_n + (rt & 1) * 128) + rl, kb = kc * 4 + kl;
         uint8_t v = 127;
         if (r < rows && kb < kblocks) v = along_rows ? src[(size_t)r * kblocks + kb] : src[(size_t)kb * rows + r];
         tile[kl][rl] = v;
@@ -295,12 +306,28 @@ inline uint64_t mx_up256(uint64_t x) { return (x + 255) / 256 * 256; }
 
 struct MxLayout {
     uint64_t a8, b8, sfa, sfb, total;
-    int m_tiles, n_tiles, n128e, kchunks;
+    int m_tiles, n_tiles, n128e, kchunks, tile_n, nacc;
 };
+int mx_sm_count() {
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    return sms;
+}
 MxLayout mx_layout(const MatmulArgs &p) {
     MxLayout l{};
     l.m_tiles = (int)((p.M + MX_M - 1) / MX_M);
-    l.n_tiles = (int)((p.N + MX_N - 1) / MX_N);
+    // 256 columns and one accumulator.  Narrower tiles leave room for a second accumulator, whose epilogue then overlaps
+    // the next tile's MMAs, but measured slower in proportion to their width (4096 x 8192 x 8192: 247 us at 256, 261 at
+    // 224, 320 at 240, 311 at 192 with two accumulators and 325 with one, 411 at 128): what bounds the kernel is the
+    // operand traffic from L2 into shared memory, (128 + tile_n) x K bytes per tile = 13.6 TB/s over all SMs at 256
+    // columns, not the tensor pipe's idle time during the epilogue.  B200_QMM_MX_TILE=<n> (a multiple of 16) and
+    // B200_QMM_MX_NACC=1 select the other forms.
+    l.tile_n = MX_N;
+    if (const char *e = getenv("B200_QMM_MX_TILE")) { const int v = atoi(e); if (v >= 32 && v <= MX_N && v % 16 == 0) l.tile_n = v; }
+    l.nacc = 2 * l.tile_n <= (int)MX_SF_COL ? 2 : 1;
+    if (const char *e = getenv("B200_QMM_MX_NACC")) { if (atoi(e) == 1) l.nacc = 1; }
+    l.n_tiles = (int)((p.N + l.tile_n - 1) / l.tile_n);
     l.n128e = 2 * l.n_tiles;
     l.kchunks = (int)(p.K / MX_BK);
     l.a8 = p.a_type == ET_E2M1 ? mx_up256((uint64_t)p.M * p.K) : 0;
@@ -350,8 +377,8 @@ cudaError_t launch_mx_native(const MatmulArgs &p, cudaStream_t s) {
     }
     const int kblocks = (int)(p.K / 32);
     {
-        mx_group_scales_kernel<<<(unsigned)(l.m_tiles * l.kchunks), 512, 0, s>>>(p.a_scale, sfa, (int)p.M, kblocks, 1, l.m_tiles, l.kchunks);
-        mx_group_scales_kernel<<<(unsigned)(l.kchunks * l.n128e), 512, 0, s>>>(p.b_scale, sfb, (int)p.N, kblocks, 0, l.n128e, l.kchunks);
+        mx_group_scales_kernel<<<(unsigned)(l.m_tiles * l.kchunks), 512, 0, s>>>(p.a_scale, sfa, (int)p.M, kblocks, 1, l.m_tiles, l.kchunks, 128);
+        mx_group_scales_kernel<<<(unsigned)(l.kchunks * l.n128e), 512, 0, s>>>(p.b_scale, sfb, (int)p.N, kblocks, 0, l.n128e, l.kchunks, l.tile_n);
         count_launch(2);
     }
     cudaError_t e = cudaGetLastError();
@@ -367,19 +394,19 @@ cudaError_t launch_mx_native(const MatmulArgs &p, cudaStream_t s) {
     mp.out = p.out; mp.out_type = p.out_type;
     mp.M = (int)p.M; mp.N = (int)p.N; mp.K = (int)p.K;
     mp.m_tiles = l.m_tiles; mp.tiles = l.m_tiles * l.n_tiles; mp.num_kb = l.kchunks;
-    mp.sfa = sfa; mp.sfb = sfb; mp.n128e = l.n128e;
+    mp.sfa = sfa; mp.sfb = sfb; mp.n128e = l.n128e; mp.tile_n = l.tile_n; mp.nacc = l.nacc;
     const int a_fmt = p.a_type == ET_E5M2 ? 1 : 0, b_fmt = p.b_type == ET_E5M2 ? 1 : 0;   // widened fp4 is e4m3
-    const uint32_t idesc = mx_idesc(a_fmt, b_fmt, MX_M, MX_N);
+    const uint32_t idesc = mx_idesc(a_fmt, b_fmt, MX_M, l.tile_n);
 
     static bool attr_set[64] = {};
-    int dev = 0, sms = 148;
+    int dev = 0;
     cudaGetDevice(&dev);
     if (!attr_set[dev & 63]) {
         e = cudaFuncSetAttribute(mx_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, MxSmem::TOTAL);
         if (e != cudaSuccess) return e;
         attr_set[dev & 63] = true;
     }
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int sms = mx_sm_count();
     const int P = mp.tiles < sms ? mp.tiles : sms;
     mx_tc_kernel<<<P, 320, MxSmem::TOTAL, s>>>(ta, tb, mp, idesc);
     count_launch();

@@ -43,6 +43,7 @@
 // Replaces the reference's k_wq_fused (cuda/src/ops/matmul.cu:337-352).
 #include <atomic>
 #include <chrono>
+#include <cmath>
 #include <mutex>
 #include <type_traits>
 
@@ -107,8 +108,9 @@ __device__ unsigned long long g_mm_prof[8][160];
 #define MM_STAMP_MAX(row) do { } while (0)
 #endif
 
-__host__ __device__ inline long long mm_share_begin(long long c, long long total, int P) { return c * total / P; }
-__host__ __device__ inline int mm_share_owner(long long u, long long total, int P) { return (int)(((u + 1) * P - 1) / total); }
+// The (tile, stage) space is cut into one contiguous share per CTA: CTA c works on units [b[c], b[c + 1]).
+constexpr int MM_MAX_CTAS = 256;
+struct MmShares { long long b[MM_MAX_CTAS + 1]; };
 
 __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
     uint32_t v;
@@ -380,7 +382,7 @@ __device__ __forceinline__ void mm_activation_producer(const MmParams &p, uint32
 
 template <bool Q8, bool BF16, int MF, bool NZ>
 __global__ void __launch_bounds__(MM_THREADS, 1)
-wq_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const MmParams p) {
+wq_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const MmParams p, const __grid_constant__ MmShares shares) {
     using L = MmSmem<MF>;
     constexpr int TN = Q8 ? 128 : 256;   // output columns per tile (the tile is 256 nibble columns wide)
     const int NS = p.ns;
@@ -399,7 +401,7 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const MmParams p) {
     const int P = gridDim.x, cta = blockIdx.x;
     if (threadIdx.x == 0) MM_STAMP(0);
     const bool has_off = p.offset != nullptr;
-    const long long ub = mm_share_begin(cta, p.total_u, P), ue = mm_share_begin(cta + 1, p.total_u, P);
+    const long long ub = shares.b[cta], ue = shares.b[cta + 1];
     const int nu = (int)(ue - ub);
     const int tile_first = (int)(ub / p.num_sb), tile_last = (int)((ue - 1) / p.num_sb);
 
@@ -677,7 +679,10 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const MmParams p) {
             constexpr int CPL = TN / 32;
             const int n = CPL * lane, n_glob = tile * TN + n;
             const bool n_ok = n_glob < p.N;
-            const int c_first = mm_share_owner(t_lo, p.total_u, P), c_last = mm_share_owner(t_hi - 1, p.total_u, P);
+            // the tile's contributors: the CTAs whose shares reach into [t_lo, t_hi) (every share has at least one unit)
+            int c_first = cta, c_last = cta;
+            while (c_first > 0 && shares.b[c_first] > t_lo) --c_first;
+            while (c_last + 1 < P && shares.b[c_last + 1] < t_hi) ++c_last;
             // A tile shared between CTAs has one 64-bit word in the workspace: this launch's key in the upper 48 bits
             // and the number of contributors that have published their partial tile in the lower 16.  The key is
             // unique to the launch, so whatever an earlier use left there never counts.  The first contributor to
@@ -977,7 +982,50 @@ struct MmPlan {
     int mf, tiles, num_sb, gsb, P;
     long long total_u;
     uint64_t slot_bytes, tag_bytes, xf_bytes;
+    MmShares shares;
 };
+
+// Shares of the (tile, stage) space.  Equal shares by default.  When there are more CTAs than tiles and a share is
+// shorter than a tile, some CTAs lie wholly inside one tile ("interior"), and such a tile then has two contributors that
+// finish at the very end of the kernel -- the interior one and the one whose share ends in the tile -- so neither finds
+// the other's partial tile published and both go through the slow hand-over, on the call's critical path.  Interior
+// shares are therefore made `stagger` stages shorter (the others correspondingly longer): the interior CTA publishes
+// early enough for the other to see it and fetch its partial tile while still working, and the tile is finished
+// without a global round trip.  B200_QMM_WQ_STAGGER=<stages> overrides (0 = equal shares).
+void mm_fill_shares(MmPlan &pl) {
+    const long long U = pl.total_u;
+    const int P = pl.P, S = pl.num_sb;
+    for (int c = 0; c <= P; ++c) pl.shares.b[c] = (long long)c * U / P;
+    double stagger = 6.0;
+    if (const char *e = getenv("B200_QMM_WQ_STAGGER")) stagger = atof(e);
+    const double even = (double)U / P;
+    if (stagger <= 0.0 || P <= pl.tiles || even >= S || even < 4.0 * stagger) return;
+    auto walk = [&](double ls, long long *b) {
+        double pos = 0.0;
+        int c = 0;
+        while (pos < (double)U - 1e-6 && c < MM_MAX_CTAS) {
+            const double rest = S - fmod(pos, (double)S);            // stages left in the current tile
+            if (b) b[c] = llround(pos);
+            pos += rest > ls + 1e-9 ? ls - stagger : ls;             // cannot reach the tile's end: interior, shorter
+            ++c;
+        }
+        return c;
+    };
+    // the shortest long share with which P CTAs cover everything
+    double lo = even, hi = even + stagger;
+    if (walk(hi, nullptr) > P) return;
+    for (int it = 0; it < 60; ++it) {
+        const double mid = 0.5 * (lo + hi);
+        if (walk(mid, nullptr) > P) lo = mid; else hi = mid;
+    }
+    long long b[MM_MAX_CTAS + 1];
+    const int used = walk(hi, b);
+    if (used != P) return;      // fewer CTAs would do: keep the equal shares
+    b[P] = U;
+    for (int c = 0; c < P; ++c)
+        if (b[c + 1] <= b[c]) return;   // every share needs at least one unit
+    for (int c = 0; c <= P; ++c) pl.shares.b[c] = b[c];
+}
 
 MmPlan mm_make_plan(const MatmulArgs &p) {
     MmPlan pl{};
@@ -1011,6 +1059,8 @@ MmPlan mm_make_plan(const MatmulArgs &p) {
         }
     }
     if (const char *e = getenv("B200_QMM_WQ_MMA_P")) { const int v = atoi(e); if (v >= 1 && v <= sms && v <= pl.total_u) pl.P = v; }
+    if (pl.P > MM_MAX_CTAS) pl.P = MM_MAX_CTAS;
+    mm_fill_shares(pl);
     pl.slot_bytes = align_up_u64((uint64_t)(pl.tiles + pl.P) * p.M * tile_n * sizeof(float), 256);
     pl.tag_bytes = align_up_u64((uint64_t)pl.tiles * sizeof(unsigned long long), 256);
     pl.xf_bytes = pl.mf == 2 ? align_up_u64((uint64_t)pl.num_sb * (2 * 2048 + 128), 256) : 0;
@@ -1045,7 +1095,7 @@ int mm_ring_slots(int M) {
 }
 
 template <bool Q8, bool BF16, int MF, bool NZ>
-cudaError_t mm_launch_one(const CUtensorMap &tw, MmParams mp, int P, cudaStream_t s) {
+cudaError_t mm_launch_one(const CUtensorMap &tw, MmParams mp, const MmShares &shares, int P, cudaStream_t s) {
     using L = MmSmem<MF>;
     static_assert(L::SLOT % 1024 == 0, "slots keep the swizzle alignment");
     mp.ns = mm_ring_slots<MF>(mp.M);
@@ -1075,7 +1125,7 @@ cudaError_t mm_launch_one(const CUtensorMap &tw, MmParams mp, int P, cudaStream_
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl >= 1 ? 1 : 0;
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tw, mp);
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tw, mp, shares);
     count_launch();
     return e != cudaSuccess ? e : cudaGetLastError();
 }
@@ -1169,8 +1219,8 @@ cudaError_t launch_wq_mma(const MatmulArgs &p, cudaStream_t s) {
     if (const char *e = getenv("B200_QMM_TEST_DROP_STAGE")) mp.test_drop = atoi(e);
 
     cudaError_t e;
-#define MM_GO(Q8_, NZ_) (pl.mf == 1 ? (bf ? mm_launch_one<Q8_, true, 1, NZ_>(tw, mp, pl.P, s) : mm_launch_one<Q8_, false, 1, NZ_>(tw, mp, pl.P, s)) \
-                                    : (bf ? mm_launch_one<Q8_, true, 2, NZ_>(tw, mp, pl.P, s) : mm_launch_one<Q8_, false, 2, NZ_>(tw, mp, pl.P, s)))
+#define MM_GO(Q8_, NZ_) (pl.mf == 1 ? (bf ? mm_launch_one<Q8_, true, 1, NZ_>(tw, mp, pl.shares, pl.P, s) : mm_launch_one<Q8_, false, 1, NZ_>(tw, mp, pl.shares, pl.P, s)) \
+                                    : (bf ? mm_launch_one<Q8_, true, 2, NZ_>(tw, mp, pl.shares, pl.P, s) : mm_launch_one<Q8_, false, 2, NZ_>(tw, mp, pl.shares, pl.P, s)))
     if (q8) e = MM_GO(true, false);
     else if (p.b_nz) e = MM_GO(false, true);
     else e = MM_GO(false, false);

@@ -540,6 +540,30 @@ def test_mx_native_block_scaled_kernel(pkg, oracle, workloads, dev, kinds, shape
                      mean_rel=1e-5 if odt == torch.float32 else 2e-3)
 
 
+def test_mx_native_tile_widths_agree(pkg, oracle, workloads, dev):
+    """The native kernel's tile width is a launch parameter (256 columns and one accumulator by default; up to 240
+    columns two accumulators fit and a tile's epilogue overlaps the next tile's MMAs).  Every form accumulates an output
+    element in the same order, so they must agree bit for bit; the shape gives every CTA three tiles and more (both
+    accumulators are reused), ragged M and N."""
+    M, K, N = 1700, 256, 8000
+    d = workloads.mx(M=M, K=K, N=N, a_fp4=False, b_fp4=True, seed=5470)
+    outs = {}
+    for width in ("240", "192", "256"):
+        with env_set("B200_QMM_MX_TILE", width):
+            outs[width] = run_mx(pkg, d, dev, torch.float32, "aclnnMatmulMxFp8")
+    torch.cuda.synchronize()
+    assert torch.equal(outs["240"], outs["256"]) and torch.equal(outs["192"], outs["256"])
+    rows = np.random.default_rng(5471).choice(M, size=96, replace=False)
+    assert_close(to_np(outs["240"])[rows], ref_mx(oracle, d)[rows], "MX 1700x256x8000, 240-column tiles")
+    small = workloads.mx(M=130, K=128, N=288, a_fp4=True, b_fp4=False, seed=5472)    # two tiles of 240: 240 + 48 columns
+    for width in ("240", "256"):
+        with env_set("B200_QMM_MX_TILE", width):
+            outs[width] = run_mx(pkg, small, dev, torch.bfloat16, "aclnnMatmulMxFp4")
+    torch.cuda.synchronize()
+    assert torch.equal(outs["240"], outs["256"])
+    assert_close(to_np(outs["240"]), ref_mx(oracle, small), "MX 130x128x288, 240-column tiles")
+
+
 def test_mx_fp4_weight_widened_at_load_time(pkg, oracle, workloads, dev):
     """aclnnTransMatmulWeight of an fp4 weight into an ACL_FORMAT_FRACTAL_NZ tensor stores one e4m3 byte per element
     (every e2m1 value is exact in e4m3); the block-scaled matmul on it gives the bits of the call on the packed
