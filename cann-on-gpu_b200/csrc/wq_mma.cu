@@ -748,9 +748,14 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const MmParams p, const 
                 bool got = mbar_try_wait(seg_done, sg & 1);
                 if (!got) {
                     const unsigned long long t0 = global_ns(), limit = p.wait_ns ? p.wait_ns : WAIT_LIMIT_NS;
+                    const bool watch = !whole && !early;
                     while (true) {
+                        // the look at the word is issued before the wait and consumed after it, so its L2 round trip
+                        // runs beside the wait instead of delaying the moment the teams' arrival is noticed
+                        unsigned long long peek = 0ull;
+                        if (watch && !early) asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(peek) : "l"(word));
                         if (mbar_try_wait_for(seg_done, sg & 1, 400u)) { got = true; break; }
-                        if (!whole && !early && others_published()) { early = true; fetch_others(); }
+                        if (watch && !early && peek == all_but_me && others_published()) { early = true; fetch_others(); }
                         if (*abort_flag) break;
                         if (global_ns() - t0 > limit) {
                             *abort_flag = 1;
@@ -985,18 +990,18 @@ struct MmPlan {
     MmShares shares;
 };
 
-// Shares of the (tile, stage) space.  Equal shares by default.  When there are more CTAs than tiles and a share is
-// shorter than a tile, some CTAs lie wholly inside one tile ("interior"), and such a tile then has two contributors that
-// finish at the very end of the kernel -- the interior one and the one whose share ends in the tile -- so neither finds
-// the other's partial tile published and both go through the slow hand-over, on the call's critical path.  Interior
-// shares are therefore made `stagger` stages shorter (the others correspondingly longer): the interior CTA publishes
-// early enough for the other to see it and fetch its partial tile while still working, and the tile is finished
-// without a global round trip.  B200_QMM_WQ_STAGGER=<stages> overrides (0 = equal shares).
+// Shares of the (tile, stage) space: equal by default.  When there are more CTAs than tiles and a share is shorter than
+// a tile, some CTAs lie wholly inside one tile ("interior"), and such a tile then has two contributors that finish at
+// the very end of the kernel -- the interior one and the one whose share ends in the tile -- so neither finds the
+// other's partial tile published and both go through the slower hand-over.  B200_QMM_WQ_STAGGER=<stages> makes the
+// interior shares that much shorter (the others correspondingly longer), so that the interior CTA publishes before the
+// other one finishes.  Measured on the 8192 x 28672 call it does not pay: 26.0 us with equal shares, 26.1-26.4 with
+// 4.5 stages, 26.5-26.6 with 6 (the longer shares cost what the quicker hand-over gains), so the default is 0.
 void mm_fill_shares(MmPlan &pl) {
     const long long U = pl.total_u;
     const int P = pl.P, S = pl.num_sb;
     for (int c = 0; c <= P; ++c) pl.shares.b[c] = (long long)c * U / P;
-    double stagger = 6.0;
+    double stagger = 0.0;
     if (const char *e = getenv("B200_QMM_WQ_STAGGER")) stagger = atof(e);
     const double even = (double)U / P;
     if (stagger <= 0.0 || P <= pl.tiles || even >= S || even < 4.0 * stagger) return;
