@@ -107,6 +107,11 @@ tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUte
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Launched with programmatic stream serialisation: everything above (barriers, tensor-memory allocation) may run
+    // while the kernel before this one in the stream is still finishing; nothing below touches global memory before
+    // that kernel has completed and its writes are visible.  Without the launch attribute both instructions do nothing.
+    if (threadIdx.x == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     // unit u -> (K slice z, tile); tiles of one K slice are consecutive and m-tiles of one weight tile
     // are adjacent, so CTAs running side by side share weight tiles in L2.
@@ -665,9 +670,22 @@ cudaError_t launch_one(const CUtensorMap &tx, const CUtensorMap &tw, const TcPar
         if (e != cudaSuccess) return e;
         attr_set[dev & 63] = true;
     }
-    kern<<<P, 320, L::TOTAL, s>>>(tx, tw, tp);
+    // Programmatic stream serialisation (see the kernel's start-up): at decode shapes the call is a few microseconds
+    // long and its start-up is a visible part of that.  B200_QMM_PDL=0 launches the plain way.
+    static const int pdl = [] { const char *e = getenv("B200_QMM_PDL"); return e ? atoi(e) : 1; }();
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)P);
+    cfg.blockDim = dim3(320);
+    cfg.dynamicSmemBytes = (size_t)L::TOTAL;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl >= 1 ? 1 : 0;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tx, tw, tp);
     count_launch();
-    return cudaGetLastError();
+    return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 template <int MODE>
