@@ -287,19 +287,19 @@ __device__ __forceinline__ void mm_store_rows(uint8_t *xf, int f, int lane, cons
     }
 }
 
-// Nine to sixteen rows: converting sixteen rows per stage in every CTA is more than two warps can keep up with, and
-// it is the same work in all of them (the activations do not depend on the tile).  One small kernel converts each
-// 128-column stage of the activations once into the layout of a slot's activation region; the main kernel then
-// copies that region with the weights.
-template <bool BF16>
+// Five to sixteen rows: converting that many rows per stage in every CTA is more than two warps can keep up with (they
+// share their schedulers with the compute warps), and it is the same work in all CTAs (the activations do not depend on
+// the tile).  One small kernel converts each 128-column stage of the activations once into the layout of a slot's
+// activation region; the main kernel then copies that region with the weights.
+template <bool BF16, int MF>
 __global__ void __launch_bounds__(32) wq_mma_activation_kernel(const uint16_t *x, uint8_t *xf_all, int M, int K) {
     pdl_launch_dependents();
     const int sbi = blockIdx.x, lane = threadIdx.x;
     constexpr int EPL = 32, V = EPL / 4, LPR = 128 / EPL;
     const int q = lane % LPR, rsub = lane / LPR, k = sbi * MM_SBK + EPL * q;
-    uint8_t *xf = xf_all + (size_t)sbi * (2 * 2048 + 128);
+    uint8_t *xf = xf_all + (size_t)sbi * (MF * 2048 + 128);
 #pragma unroll
-    for (int f = 0; f < 2; ++f) {
+    for (int f = 0; f < MF; ++f) {
         const int m = 8 * f + rsub;
         uint2 cur[V];
 #pragma unroll
@@ -310,7 +310,7 @@ __global__ void __launch_bounds__(32) wq_mma_activation_kernel(const uint16_t *x
         uint32_t h[EPL / 2];
         float up, sum;
         mm_convert_rows<BF16, EPL>(cur, h, up, sum);
-        mm_store_rows<2, EPL>(xf, f, lane, h, up, sum);
+        mm_store_rows<MF, EPL>(xf, f, lane, h, up, sum);
     }
 }
 
@@ -479,11 +479,11 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const MmParams p, const 
     } else if (warp >= 4 * MM_TEAMS + 2) {
         // ------------------------------------------------------------------ activation producers
         const int sb0 = (int)(ub - (long long)tile_first * p.num_sb), xp = warp - (4 * MM_TEAMS + 2);
-        if constexpr (MF == 2) {
+        if (p.xf != nullptr) {
             // converted once per call by wq_mma_activation_kernel: one bulk copy per stage
             if (xp == 0 && lane == 0) {
                 pdl_wait_for_prerequisites();
-                constexpr uint32_t XB = 2 * 2048 + 128;
+                constexpr uint32_t XB = MF * 2048 + 128;
                 int slot = 0, round = 0, sbi = sb0;
                 for (int i = 0; i < nu; ++i) {
                     if (round > 0 && !mm_wait(empty_bar(slot), (round - 1) & 1, abort_flag, 0x340u + slot, p.wait_ns)) break;
@@ -493,7 +493,7 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const MmParams p, const 
                     if (++sbi == p.num_sb) sbi = 0;
                 }
             }
-        } else {
+        } else if constexpr (MF == 1) {
             if (p.M == 1) mm_activation_producer<BF16, 1, 4>(p, base, NS, bars, abort_flag, sb0, nu, lane, xp);
             else if (p.M == 2) mm_activation_producer<BF16, 1, 8>(p, base, NS, bars, abort_flag, sb0, nu, lane, xp);
             else if (p.M <= 4) mm_activation_producer<BF16, 1, 16>(p, base, NS, bars, abort_flag, sb0, nu, lane, xp);
@@ -985,6 +985,7 @@ int mm_sm_count() {
 
 struct MmPlan {
     int mf, tiles, num_sb, gsb, P;
+    bool xpre;               // activations converted once per call by wq_mma_activation_kernel
     long long total_u;
     uint64_t slot_bytes, tag_bytes, xf_bytes;
     MmShares shares;
@@ -1068,7 +1069,11 @@ MmPlan mm_make_plan(const MatmulArgs &p) {
     mm_fill_shares(pl);
     pl.slot_bytes = align_up_u64((uint64_t)(pl.tiles + pl.P) * p.M * tile_n * sizeof(float), 256);
     pl.tag_bytes = align_up_u64((uint64_t)pl.tiles * sizeof(unsigned long long), 256);
-    pl.xf_bytes = pl.mf == 2 ? align_up_u64((uint64_t)pl.num_sb * (2 * 2048 + 128), 256) : 0;
+    // rows from which the activations are converted by the pre-pass instead of inside the kernel (B200_QMM_WQ_XPRE_M)
+    int xpre_m = 5;
+    if (const char *e = getenv("B200_QMM_WQ_XPRE_M")) xpre_m = atoi(e) > 0 ? atoi(e) : 1;
+    pl.xpre = pl.mf == 2 || p.M >= xpre_m;
+    pl.xf_bytes = pl.xpre ? align_up_u64((uint64_t)pl.num_sb * (pl.mf * 2048 + 128), 256) : 0;
     return pl;
 }
 
@@ -1162,12 +1167,14 @@ bool wq_mma_supported(const MatmulArgs &p) {
     return true;
 }
 
-// Three to sixteen rows on weights in the caller's layout go to the kernel that takes the activations as they are
-// (wq_rows.cu): converting that many rows per stage inside this kernel does not keep up with the weight stream.
+// Some row counts on weights in the caller's layout go to the kernel that takes the activations as they are
+// (wq_rows.cu), where it measured faster on 8192 x 28672 (us per call, this kernel / that one): 3 rows 29.8 / 32.7,
+// 4 rows 31.5 / 33.0, 5 rows 33.8 / 33.5, 6 rows 35.3 / 34.3, 8 rows 37.8 / 35.5, 9 rows 43.6 / 46.3, 12 rows 47.8 / 48.7,
+// 16 rows 53.0 / 50.5.  B200_QMM_WQ_ROWS=0 keeps everything here, =<m> sends m rows and more there.
 inline bool mm_use_rows_kernel(const MatmulArgs &p) {
-    if (p.b_nz || p.M < 3 || !wq_rows_supported(p)) return false;
-    const char *e = getenv("B200_QMM_WQ_ROWS");
-    return !(e && atoi(e) == 0);
+    if (p.b_nz || !wq_rows_supported(p)) return false;
+    if (const char *e = getenv("B200_QMM_WQ_ROWS")) return atoi(e) > 0 && p.M >= atoi(e);
+    return (p.M >= 5 && p.M <= 8) || p.M >= 13;
 }
 
 uint64_t wq_mma_workspace_bytes(const MatmulArgs &p) {
@@ -1203,10 +1210,16 @@ cudaError_t launch_wq_mma(const MatmulArgs &p, cudaStream_t s) {
     mp.tags = (unsigned long long *)((char *)p.workspace + pl.slot_bytes);
     mp.nonce = mm_next_nonce() & ~0xFFFFull;
     if (mp.nonce == 0ull) mp.nonce = 1ull << 16;
-    if (pl.mf == 2) {
+    if (pl.xpre) {
         uint8_t *xf = (uint8_t *)p.workspace + pl.slot_bytes + pl.tag_bytes;
-        if (p.a_type == ET_BF16) wq_mma_activation_kernel<true><<<pl.num_sb, 32, 0, s>>>((const uint16_t *)p.a, xf, (int)p.M, (int)p.K);
-        else wq_mma_activation_kernel<false><<<pl.num_sb, 32, 0, s>>>((const uint16_t *)p.a, xf, (int)p.M, (int)p.K);
+        const uint16_t *xa = (const uint16_t *)p.a;
+        if (pl.mf == 2) {
+            if (p.a_type == ET_BF16) wq_mma_activation_kernel<true, 2><<<pl.num_sb, 32, 0, s>>>(xa, xf, (int)p.M, (int)p.K);
+            else wq_mma_activation_kernel<false, 2><<<pl.num_sb, 32, 0, s>>>(xa, xf, (int)p.M, (int)p.K);
+        } else {
+            if (p.a_type == ET_BF16) wq_mma_activation_kernel<true, 1><<<pl.num_sb, 32, 0, s>>>(xa, xf, (int)p.M, (int)p.K);
+            else wq_mma_activation_kernel<false, 1><<<pl.num_sb, 32, 0, s>>>(xa, xf, (int)p.M, (int)p.K);
+        }
         count_launch();
         mp.xf = xf;
     }
