@@ -130,6 +130,114 @@ QMM_CLIENT_API int qmmClientWeightQuantCapture(int n, const void *const *host_x,
     return (int)e;
 }
 
+/* ---- a whole decode step of n calls -----------------------------------------------------------------
+ * The same per-call work (copy in, phase 1, phase 2, copy out) arranged the way a serving loop arranges a
+ * step of many layers: every call has its own activation and output buffer (no reuse inside the step), the
+ * host buffers of the step are one contiguous block each, and the copies are issued in groups of `per_group`
+ * calls -- the copy-in of a group is one transfer on the copy-in stream, the matmuls of the group follow on
+ * `stream` back to back (nothing between them, so each one's start-up overlaps its predecessor's end), the
+ * copy-out of the group is one transfer on the copy-out stream.  Group k+1's copy-in and group k-1's
+ * copy-out run beside group k's matmuls.  Every byte of every call still crosses the bus inside the step. */
+#define QMM_MAX_GROUPS 64
+static aclrtEvent g_ev_gin[QMM_MAX_GROUPS], g_ev_gcomp[QMM_MAX_GROUPS];
+static int g_groups_ready;
+
+static int step_setup(void) {
+    if (client_setup()) return 1;
+    if (g_groups_ready) return 0;
+    for (int k = 0; k < QMM_MAX_GROUPS; ++k)
+        if (aclrtCreateEvent(&g_ev_gin[k]) != ACL_SUCCESS || aclrtCreateEvent(&g_ev_gcomp[k]) != ACL_SUCCESS) return 1;
+    g_groups_ready = 1;
+    return 0;
+}
+
+static int enqueue_step(int n, int per_group, const void *host_x, size_t x_bytes, void *dev_x, const aclTensor *const *x,
+                        const aclTensor *const *weight, const aclTensor *const *scale, const aclTensor *const *offset,
+                        const aclTensor *const *bias, int64_t group, aclTensor *const *out, const void *dev_out, void *host_out,
+                        size_t out_bytes, void *workspace, uint64_t workspace_bytes, aclrtStream stream, int forked) {
+    aclError e;
+    if (n < 1 || per_group < 1 || (n + per_group - 1) / per_group > QMM_MAX_GROUPS) return 161002;
+    const int groups = (n + per_group - 1) / per_group;
+    if (forked) {
+        if ((e = aclrtRecordEvent(g_ev_fork, stream)) != ACL_SUCCESS) return (int)e;
+        if ((e = aclrtStreamWaitEvent(g_in, g_ev_fork)) != ACL_SUCCESS) return (int)e;
+    }
+    /* all copies in, group by group, as early as the bus allows */
+    for (int k = 0; k < groups; ++k) {
+        const int first = k * per_group, cnt = (first + per_group <= n ? per_group : n - first);
+        if ((e = aclrtMemcpyAsync((char *)dev_x + (size_t)first * x_bytes, cnt * x_bytes, (const char *)host_x + (size_t)first * x_bytes,
+                                  cnt * x_bytes, ACL_MEMCPY_HOST_TO_DEVICE, g_in)) != ACL_SUCCESS) return (int)e;
+        if ((e = aclrtRecordEvent(g_ev_gin[k], g_in)) != ACL_SUCCESS) return (int)e;
+    }
+    for (int k = 0; k < groups; ++k) {
+        const int first = k * per_group, cnt = (first + per_group <= n ? per_group : n - first);
+        if ((e = aclrtStreamWaitEvent(stream, g_ev_gin[k])) != ACL_SUCCESS) return (int)e;
+        for (int i = first; i < first + cnt; ++i) {
+            uint64_t need = 0;
+            aclOpExecutor *ex = NULL;
+            aclnnStatus st = aclnnWeightQuantBatchMatmulV2ExGetWorkspaceSize(x[i], weight[i], scale[i], offset ? offset[i] : NULL,
+                                                                             bias ? bias[i] : NULL, group, out[i], &need, &ex);
+            if (st != 0) return (int)st;
+            if (need > workspace_bytes) return 161002;
+            st = aclnnWeightQuantBatchMatmulV2Ex(workspace, workspace_bytes, ex, stream);
+            if (st != 0) return (int)st;
+        }
+        if ((e = aclrtRecordEvent(g_ev_gcomp[k], stream)) != ACL_SUCCESS) return (int)e;
+        if ((e = aclrtStreamWaitEvent(g_out, g_ev_gcomp[k])) != ACL_SUCCESS) return (int)e;
+        if ((e = aclrtMemcpyAsync((char *)host_out + (size_t)first * out_bytes, cnt * out_bytes,
+                                  (const char *)dev_out + (size_t)first * out_bytes, cnt * out_bytes, ACL_MEMCPY_DEVICE_TO_HOST,
+                                  g_out)) != ACL_SUCCESS) return (int)e;
+    }
+    if (forked) {
+        if ((e = aclrtRecordEvent(g_ev_join, g_in)) != ACL_SUCCESS) return (int)e;
+        if ((e = aclrtStreamWaitEvent(stream, g_ev_join)) != ACL_SUCCESS) return (int)e;
+        if ((e = aclrtRecordEvent(g_ev_out[0], g_out)) != ACL_SUCCESS) return (int)e;
+        if ((e = aclrtStreamWaitEvent(stream, g_ev_out[0])) != ACL_SUCCESS) return (int)e;
+    }
+    return 0;
+}
+
+/* One step of n calls, enqueued and waited for.  host_x / dev_x are [n][x_bytes], dev_out / host_out [n][out_bytes];
+ * x[i] and out[i] are the tensors over call i's slices, weight[i] / scale[i] its weights.  The calls of one step share
+ * `workspace` (they run in order on `stream`).  Returns 0 or the first status that was not success. */
+QMM_CLIENT_API int qmmClientWeightQuantStep(int n, int per_group, const void *host_x, size_t x_bytes, void *dev_x,
+                                            const aclTensor *const *x, const aclTensor *const *weight, const aclTensor *const *scale,
+                                            const aclTensor *const *offset, const aclTensor *const *bias, int64_t group,
+                                            aclTensor *const *out, const void *dev_out, void *host_out, size_t out_bytes,
+                                            void *workspace, uint64_t workspace_bytes, aclrtStream stream) {
+    if (step_setup()) return 361001;
+    const int st = enqueue_step(n, per_group, host_x, x_bytes, dev_x, x, weight, scale, offset, bias, group, out, dev_out, host_out,
+                                out_bytes, workspace, workspace_bytes, stream, 0);
+    if (st != 0) return st;
+    aclError e = aclrtSynchronizeStream(g_out);
+    if (e == ACL_SUCCESS) e = aclrtSynchronizeStream(stream);
+    if (e == ACL_SUCCESS) e = aclrtSynchronizeStream(g_in);
+    return (int)e;
+}
+
+/* The same step captured once into a model (see qmmClientWeightQuantCapture); replay with qmmClientReplay. */
+QMM_CLIENT_API int qmmClientWeightQuantStepCapture(int n, int per_group, const void *host_x, size_t x_bytes, void *dev_x,
+                                                   const aclTensor *const *x, const aclTensor *const *weight,
+                                                   const aclTensor *const *scale, const aclTensor *const *offset,
+                                                   const aclTensor *const *bias, int64_t group, aclTensor *const *out,
+                                                   const void *dev_out, void *host_out, size_t out_bytes, void *workspace,
+                                                   uint64_t workspace_bytes, aclrtStream stream, aclmdlRI *model) {
+    if (!model) return 161001;
+    *model = NULL;
+    if (step_setup()) return 361001;
+    aclError e = aclmdlRICaptureBegin(stream, ACL_MODEL_RI_CAPTURE_MODE_RELAXED);
+    if (e != ACL_SUCCESS) return (int)e;
+    const int st = enqueue_step(n, per_group, host_x, x_bytes, dev_x, x, weight, scale, offset, bias, group, out, dev_out, host_out,
+                                out_bytes, workspace, workspace_bytes, stream, 1);
+    e = aclmdlRICaptureEnd(stream, model);
+    if (st != 0) {
+        if (e == ACL_SUCCESS) aclmdlRIDestroy(*model);
+        *model = NULL;
+        return st;
+    }
+    return (int)e;
+}
+
 /* Replays a captured pass on `stream` and waits for it. */
 QMM_CLIENT_API int qmmClientReplay(aclmdlRI model, aclrtStream stream) {
     aclError e = aclmdlRIExecuteAsync(model, stream);

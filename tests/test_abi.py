@@ -44,7 +44,7 @@ def test_c_client_library_loads(pkg):
     assert os.path.exists(path), "run __graft_entry__.build()"
     ctypes.CDLL(pkg.LIB_PATH)
     client = ctypes.CDLL(path)
-    assert hasattr(client, "qmmClientWeightQuantPass")
+    assert hasattr(client, "qmmClientWeightQuantPass") and hasattr(client, "qmmClientWeightQuantStep")
 
 
 def test_hccl_library_exports(pkg):

@@ -1230,6 +1230,62 @@ def test_c_client_pipelined_pass(pkg, oracle, workloads, dev):
         assert pkg.load().aclmdlRIDestroy(model) == 0
 
 
+def test_c_client_step_of_many_calls(pkg, oracle, workloads, dev):
+    """The step form of the compiled client (the benchmark's end-to-end leg): n calls, each with its own activation and
+    output slice of contiguous host and device blocks, copies in groups on two copy streams beside the matmuls.  Every
+    call's result must come back with the bits of the plain call, for group sizes that divide n, do not divide it, and
+    exceed it; directly and from a captured model replayed with new activations in the same host block."""
+    path = os.path.join(os.path.dirname(pkg.LIB_PATH), "libqmm_client.so")
+    client = ctypes.CDLL(path)
+    client.qmmClientWeightQuantStep.restype = ctypes.c_int
+    client.qmmClientWeightQuantStepCapture.restype = ctypes.c_int
+    client.qmmClientReplay.restype = ctypes.c_int
+    M, K, N, G, n = 1, 1024, 768, 128, 7
+    sets = [workloads.w4a16(M=M, K=K, N=N, group=G, seed=7100 + i, with_offset=False, with_bias=False) for i in range(3)]
+    VP = ctypes.c_void_p
+    g = torch.Generator().manual_seed(7110)
+    hx = torch.randn((n, M, K), generator=g).to(torch.bfloat16).pin_memory()
+    hout = torch.empty((n, M, N), dtype=torch.bfloat16).pin_memory()
+    dx = torch.empty((n, M, K), dtype=torch.bfloat16, device=dev)
+    dout = torch.empty((n, M, N), dtype=torch.bfloat16, device=dev)
+    tdx, tdo = [pkg.AclTensor(dx[i]) for i in range(n)], [pkg.AclTensor(dout[i]) for i in range(n)]
+    w = [d["w"].to(dev) for d in sets]
+    sc = [d["scale"].to(dev) for d in sets]
+    tw = [pkg.AclTensor(t, pkg.ACL_INT4, (K, N)) for t in w]
+    ts = [pkg.AclTensor(t) for t in sc]
+    ws = torch.empty(64 << 20, dtype=torch.uint8, device=dev)
+    own_stream = torch.cuda.Stream(dev)
+    stream = VP(own_stream.cuda_stream)
+
+    def wanted():
+        out = torch.stack([pkg.weight_quant_matmul(hx[i].to(dev), w[i % 3], sc[i % 3], int4=True, group=G) for i in range(n)]).cpu()
+        torch.cuda.synchronize()
+        return out
+
+    def args(per_group):
+        return (ctypes.c_int(n), ctypes.c_int(per_group), VP(hx.data_ptr()), ctypes.c_size_t(M * K * 2), VP(dx.data_ptr()),
+                (VP * n)(*[VP(t.h) for t in tdx]), (VP * n)(*[VP(tw[i % 3].h) for i in range(n)]),
+                (VP * n)(*[VP(ts[i % 3].h) for i in range(n)]), None, None, ctypes.c_int64(G), (VP * n)(*[VP(t.h) for t in tdo]),
+                VP(dout.data_ptr()), VP(hout.data_ptr()), ctypes.c_size_t(M * N * 2), VP(ws.data_ptr()), ctypes.c_uint64(ws.numel()), stream)
+    want = wanted()
+    for per_group in (1, 3, 7, 50):
+        hout.zero_()
+        assert client.qmmClientWeightQuantStep(*args(per_group)) == 0
+        assert torch.equal(hout, want), per_group
+    assert client.qmmClientWeightQuantStep(*((ctypes.c_int(n), ctypes.c_int(0)) + args(1)[2:])) == 161002   # no group size
+    model = VP()
+    assert client.qmmClientWeightQuantStepCapture(*args(3), ctypes.byref(model)) == 0 and model.value
+    for rep in range(2):
+        hout.zero_()
+        assert client.qmmClientReplay(model, stream) == 0
+        assert torch.equal(hout, want), rep
+    hx.copy_(torch.randn((n, M, K), generator=g).to(torch.bfloat16))   # other activations in the same host block
+    want = wanted()
+    assert client.qmmClientReplay(model, stream) == 0
+    assert torch.equal(hout, want)
+    assert pkg.load().aclmdlRIDestroy(model) == 0
+
+
 def test_capture_replay_of_the_two_phase_call(pkg, oracle, workloads, dev):
     """aclmdlRICaptureBegin / End / ExecuteAsync around quantized matmuls, used like the reference's
     tests/test_graph.cpp:30-78: warm up, capture calls that share a caller-owned workspace (phase 1 runs
