@@ -670,6 +670,25 @@ def test_w4a16_decode_kernel_packed_weights(pkg, oracle, workloads, dev, case, M
         assert torch.equal(got, same)
 
 
+def test_decode_kernel_unequal_shares(pkg, oracle, workloads, dev):
+    """The decode kernel cuts the (tile, stage) space into one contiguous share per CTA from a table; with
+    B200_QMM_WQ_STAGGER the shares of CTAs that lie inside one tile are shorter than the others.  Any table must give
+    the oracle's result (the summation order over K changes, so not the same bits), on both weight layouts, and the
+    tiles shared by two and three CTAs must all be finished (every output written)."""
+    d = workloads.w4a16(M=2, K=8192, N=16384, group=128, seed=8700, with_offset=False)
+    K, N = d["K"], d["N"]
+    w, x, sc, bi = d["w"].to(dev), d["x"].to(dev), d["scale"].to(dev), d["bias"].to(dev)
+    packed = pkg.pack_weight_nz(w, K, N)
+    ref = ref_wq(oracle, d)
+    for stagger in ("0", "6", "3.5"):
+        with env_set("B200_QMM_WQ_STAGGER", stagger):
+            a = pkg.weight_quant_matmul(x, packed, sc, None, bi, int4=True, group=128, nz=True)
+            b = pkg.weight_quant_matmul(x, w, sc, None, bi, int4=True, group=128)
+        torch.cuda.synchronize()
+        assert torch.equal(a, b), stagger
+        assert_close(to_np(a), ref, f"decode kernel, interior shares {stagger} stages shorter")
+
+
 def test_packed_weights_large_m_and_rejections(pkg, oracle, workloads, dev):
     """More rows than the decode kernel takes: the weights are laid back into [K,N] in the workspace and the
     usual kernels run (17..128 rows: streaming kernel; more: expansion + dense).  int8 weights have no packed
