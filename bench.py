@@ -143,8 +143,8 @@ class Runner:
     """Pre-built aclTensor handles for the ring so the timed loop is phase 1 + phase 2 only.  With a
     communicator every call is followed by HcclAllGather of the output shard on the same stream."""
 
-    def __init__(self, pkg, sets, dev, passes=1, gather=None, packed=True):
-        self.pkg, self.dev, self.passes, self.gather = pkg, dev, passes, gather
+    def __init__(self, pkg, sets, dev, passes=1, gather=None, packed=True, fused=False):
+        self.pkg, self.dev, self.passes, self.gather, self.fused = pkg, dev, passes, gather, fused
         m, ns = sets[0]["M"], sets[0]["N"]
         self.out = torch.empty((m, ns), dtype=torch.bfloat16, device=dev)
         self.t_out = pkg.AclTensor(self.out)
@@ -161,9 +161,17 @@ class Runner:
         if gather is not None:
             self.hccl, self.comm, world = gather
             self.gathered = torch.empty((world, m, ns), dtype=torch.bfloat16, device=dev)
+            self.t_gathered = pkg.AclTensor(self.gathered)
+            self.hccl_path = os.path.join(os.path.dirname(pkg.LIB_PATH), "libhccl.so")
 
     def call(self, i, x_handle=None):
         tx, tw, ts, to, tb, _ = self.items[i]
+        if self.gather is not None and self.fused:
+            # the gather fused into the matmul's epilogue: peer stores from the decode kernel + a receiver kernel
+            with self.pkg.use_library(self.hccl_path):
+                self.pkg.call("aclnnB200WeightQuantMatmulAllGather", x_handle or tx, tw, ts, to, tb, ctypes.c_int64(GROUP), self.comm,
+                              self.t_gathered, workspace=self.ws, device=self.dev)
+            return
         self.pkg.call("aclnnWeightQuantBatchMatmulV2Ex", x_handle or tx, tw, ts, to, tb, ctypes.c_int64(GROUP), self.t_out,
                       workspace=self.ws, device=self.dev)
         if self.gather is not None:
@@ -711,10 +719,26 @@ def main():
             sharded["gather"] = ("HcclAllGather of the bf16 output shards after every call, same stream, through lib/libhccl.so "
                                  "(NCCL); " + ("captured in the step's CUDA graph" if captured else "direct calls (capture refused)"))
             del g_runner
+            # the same with the gather fused into the matmul (aclnnB200WeightQuantMatmulAllGather)
+            f_runner = Runner(pkg, sets, dev, passes, gather=gather, fused=True)
+            for _ in range(args.warmup):
+                f_runner.step()
+            torch.cuda.synchronize()
+            f_runner.capture()
+            for _ in range(args.warmup):
+                f_runner.replay()
+            ms_f = timed(f_runner.replay, args.steps, world, dev)
+            gather[0].aclnnB200FusedGatherCount.restype = ctypes.c_uint64
+            sharded["m1_fused_gather_us_per_call"] = round(ms_f / calls * 1e3, 3)
+            sharded["m1_fused_gather_value_gbs"] = round(calls * WEIGHT_BYTES / ms_f / 1e6, 2)
+            sharded["fused_gather"] = ("aclnnB200WeightQuantMatmulAllGather: the decode kernel stores its output rows into the peers' receive "
+                                       "windows (peer memory, 8-byte packets), a receiver kernel behind it fills the gathered tensor; "
+                                       f"{int(gather[0].aclnnB200FusedGatherCount())} calls took the fused form")
+            del f_runner
         except Exception as e:
-            sharded["m1_gathered_us_per_call"] = None
-            sharded["gather"] = "failed: " + repr(e)[:200]
-            gather = None
+            sharded.setdefault("m1_gathered_us_per_call", None)
+            sharded["gather"] = sharded.get("gather", "") + " failed: " + repr(e)[:200]
+            gather = None if "m1_gathered_us_per_call" not in sharded or sharded["m1_gathered_us_per_call"] is None else gather
     else:
         gather = None
     # prefill form of the same shard: M = 4096 rows against two of the ring's weight sets

@@ -20,6 +20,7 @@
 #include <thread>
 
 #include "hccl/hccl.h"
+#include "hccl_p2p.h"
 
 namespace {
 static_assert(sizeof(ncclUniqueId) <= HCCL_ROOT_INFO_BYTES, "root info must hold the NCCL unique id");
@@ -86,6 +87,18 @@ bool to_nccl(HcclReduceOp op, ncclRedOp_t *o) {
         case HCCL_REDUCE_MIN: *o = ncclMin; return true;
     }
     return false;
+}
+// what the peer-memory all-gather needs of the communicator
+const P2pNccl &p2p_table() {
+    static const P2pNccl t = {
+        [](void *c, int *n) { return (int)nccl().CommCount((ncclComm_t)c, n); },
+        [](void *c, int *r) { return (int)nccl().CommUserRank((ncclComm_t)c, r); },
+        [](void *c, const void *send, void *recv, size_t bytes, cudaStream_t s) {
+            return (int)nccl().AllGather(send, recv, bytes, ncclInt8, (ncclComm_t)c, s);
+        },
+        [](void *c, int *buf, cudaStream_t s) { return (int)nccl().AllReduce(buf, buf, 1, ncclInt32, ncclMin, (ncclComm_t)c, s); },
+    };
+    return t;
 }
 HcclResult from_nccl(ncclResult_t r) {
     switch (r) {
@@ -162,6 +175,7 @@ HcclResult HcclCommInitRootInfo(uint32_t nRanks, const HcclRootInfo *rootInfo, u
 HcclResult HcclCommDestroy(HcclComm comm) {
     NEED_NCCL();
     if (!comm) return HCCL_E_PTR;
+    p2p_forget(comm);
     return from_nccl(nccl().CommDestroy((ncclComm_t)comm));
 }
 
@@ -199,6 +213,16 @@ HcclResult HcclBroadcast(void *buf, uint64_t count, HcclDataType dataType, uint3
     if (!buf || !comm) return HCCL_E_PTR;
     if (!to_nccl(dataType, &dt)) return HCCL_E_NOT_SUPPORT;
     return from_nccl(nccl().Broadcast(buf, buf, count, dt, (int)root, (ncclComm_t)comm, (cudaStream_t)stream));
+}
+
+uint32_t HcclB200P2pStatus(void) { return p2p_status(); }
+// for the gathering matmul of hccl_matmul.cpp
+int hccl_gather_target(HcclComm comm, aclrtStreamH stream, P2pGatherTarget *t) {
+    if (!nccl().ok || !comm) return 0;
+    return p2p_gather_target(p2p_table(), comm, (cudaStream_t)stream, t) ? 1 : 0;
+}
+int hccl_gather_unpack(HcclComm comm, void *gathered, uint64_t elems_per_rank, aclrtStreamH stream) {
+    return p2p_unpack(p2p_table(), comm, gathered, elems_per_rank, (cudaStream_t)stream);
 }
 
 HcclResult HcclGetRankSize(HcclComm comm, uint32_t *rankSize) {

@@ -7,12 +7,14 @@
 // cuda/src/ops/matmul.cu:1304-1319, but the state travels in the executor handed back to the
 // caller instead of a process-wide map (the reference's maps are not thread-safe).
 #include <algorithm>
+#include <atomic>
 #include <cstdint>
 #include <cstdlib>
 #include <map>
 #include <mutex>
 
 #include "aclnnop/aclnn_quant_matmul_mc2.h"
+#include "hccl_p2p.h"
 
 namespace {
 
@@ -309,9 +311,120 @@ aclnnStatus norm_run(void *ws, uint64_t wsz, aclOpExecutor *e, aclrtStream s) {
     return st;
 }
 
+// ---- column shards with the gather fused into the matmul's epilogue --------------------------------------
+struct GatherExecutor {
+    const aclTensor *x = nullptr, *weight = nullptr, *scale = nullptr, *offset = nullptr, *bias = nullptr;
+    int64_t group = 0;
+    HcclComm comm = nullptr;
+    aclTensor *gathered = nullptr;
+    uint32_t nranks = 1, rank = 0;
+    int64_t rows = 0, cols = 0;        // of one shard
+};
+void free_gather(void *p) { delete static_cast<GatherExecutor *>(p); }
+std::atomic<uint64_t> g_fused_gathers{0};   // calls that took the fused form (diagnostics)
+
+// gathered[rank] as a tensor of its own: [rows, cols] over the same buffer (gathered is contiguous from its data pointer)
+aclTensor *own_shard(const GatherExecutor &g) {
+    void *data = nullptr;
+    aclDataType dt = ACL_DT_UNDEFINED;
+    if (aclGetRawTensorAddr(g.gathered, &data) != ACLNN_SUCCESS || !data || aclGetDataType(g.gathered, &dt) != ACLNN_SUCCESS) return nullptr;
+    const int64_t dims[2] = {g.rows, g.cols};
+    char *base = static_cast<char *>(data) + (size_t)g.rank * g.rows * g.cols * 2;
+    return aclCreateTensor(dims, 2, dt, nullptr, 0, ACL_FORMAT_ND, dims, 2, base);
+}
+
+aclnnStatus gather_plan(const aclTensor *x, const aclTensor *weight, const aclTensor *scale, const aclTensor *offset, const aclTensor *bias,
+                        int64_t group, HcclComm comm, aclTensor *gathered, uint64_t *ws, aclOpExecutor **ex) {
+    if (!x || !weight || !scale || !gathered || !ws || !ex) return ACLNN_ERR_PARAM_NULLPTR;
+    int64_t *gd = nullptr;
+    uint64_t gn = 0;
+    aclDataType dt = ACL_DT_UNDEFINED;
+    if (aclGetViewShape(gathered, &gd, &gn) != ACLNN_SUCCESS || gn != 3 || aclGetDataType(gathered, &dt) != ACLNN_SUCCESS) return ACLNN_ERR_PARAM_INVALID;
+    if (dt != ACL_FLOAT16 && dt != ACL_BF16) return ACLNN_ERR_PARAM_INVALID;
+    auto *g = new GatherExecutor();
+    g->x = x; g->weight = weight; g->scale = scale; g->offset = offset; g->bias = bias; g->group = group; g->comm = comm; g->gathered = gathered;
+    g->rows = gd[1]; g->cols = gd[2];
+    if (comm) {
+        if (HcclGetRankSize(comm, &g->nranks) != HCCL_SUCCESS || HcclGetRankId(comm, &g->rank) != HCCL_SUCCESS) { delete g; return ACLNN_ERR_RUNTIME_ERROR; }
+    }
+    if ((int64_t)g->nranks != gd[0]) { delete g; return ACLNN_ERR_PARAM_INVALID; }
+    // the local plan, with and without the gathering epilogue: the workspace must serve both (which one phase 2 takes
+    // depends on whether the windows can be set up, known only there)
+    aclTensor *out = own_shard(*g);
+    if (!out) { delete g; return ACLNN_ERR_PARAM_INVALID; }
+    uint64_t need_plain = 0, need_gather = 0;
+    aclOpExecutor *probe = nullptr;
+    aclnnStatus st = aclnnWeightQuantBatchMatmulV2ExGetWorkspaceSize(x, weight, scale, offset, bias, group, out, &need_plain, &probe);
+    if (st == ACLNN_SUCCESS) {
+        aclDestroyAclOpExecutor(probe);
+        aclnnB200DecodeGather fake{};
+        fake.nranks = g->nranks > 1 ? g->nranks : 2; fake.rank = 0; fake.buf_bytes = ~0ull;
+        aclnnB200SetDecodeGather(&fake);
+        st = aclnnWeightQuantBatchMatmulV2ExGetWorkspaceSize(x, weight, scale, offset, bias, group, out, &need_gather, &probe);
+        aclnnB200SetDecodeGather(nullptr);
+        if (st == ACLNN_SUCCESS) aclDestroyAclOpExecutor(probe);
+    }
+    aclDestroyTensor(out);
+    if (st != ACLNN_SUCCESS) { delete g; return st; }
+    *ws = need_plain > need_gather ? need_plain : need_gather;
+    *ex = aclnnB200CreateWrapperExecutor(g, free_gather);
+    if (!*ex) { delete g; return ACLNN_ERR_RUNTIME_ERROR; }
+    return ACLNN_SUCCESS;
+}
+
+aclnnStatus gather_run(void *ws, uint64_t wsz, aclOpExecutor *e, aclrtStream s) {
+    if (!e) return ACLNN_ERR_PARAM_NULLPTR;
+    auto *gp = static_cast<GatherExecutor *>(aclnnB200WrapperPayload(e, 1));
+    aclDestroyAclOpExecutor(e);
+    if (!gp) return ACLNN_ERR_PARAM_INVALID;
+    const GatherExecutor g = *gp;
+    delete gp;
+    aclTensor *out = own_shard(g);
+    if (!out) return ACLNN_ERR_PARAM_INVALID;
+    void *gathered_data = nullptr;
+    aclGetRawTensorAddr(g.gathered, &gathered_data);
+    // the fused form, if this communicator has its windows
+    P2pGatherTarget t{};
+    const bool windows = g.comm && g.nranks > 1 && hccl_gather_target(g.comm, s, &t) == 1;
+    if (windows) {
+        aclnnB200DecodeGather dg{};
+        for (int i = 0; i < 8; ++i) dg.peer[i] = t.peer[i];
+        dg.calls = t.calls; dg.nranks = t.nranks; dg.rank = t.rank; dg.buf_bytes = t.buf_bytes;
+        aclnnB200SetDecodeGather(&dg);
+    }
+    uint64_t need = 0;
+    aclOpExecutor *inner = nullptr;
+    aclnnStatus st = aclnnWeightQuantBatchMatmulV2ExGetWorkspaceSize(g.x, g.weight, g.scale, g.offset, g.bias, g.group, out, &need, &inner);
+    if (st == ACLNN_SUCCESS && need > wsz) { aclDestroyAclOpExecutor(inner); st = ACLNN_ERR_PARAM_INVALID; }
+    if (st == ACLNN_SUCCESS) st = aclnnWeightQuantBatchMatmulV2Ex(ws, wsz, inner, s);
+    const bool fused = windows && aclnnB200DecodeGatherConsumed() == 1;
+    if (windows) aclnnB200SetDecodeGather(nullptr);
+    aclDestroyTensor(out);
+    if (st != ACLNN_SUCCESS || !g.comm || g.nranks < 2) return st;
+    const uint64_t per_rank = (uint64_t)g.rows * (uint64_t)g.cols;
+    if (fused) {
+        g_fused_gathers.fetch_add(1);
+        return hccl_gather_unpack(g.comm, gathered_data, per_rank, s) == 0 ? ACLNN_SUCCESS : ACLNN_ERR_RUNTIME_ERROR;
+    }
+    // the plain sequence: the local shard is in place already, the library gathers in place
+    aclDataType dt = ACL_DT_UNDEFINED;
+    aclGetDataType(g.gathered, &dt);
+    char *mine = static_cast<char *>(gathered_data) + (size_t)g.rank * per_rank * 2;
+    return HcclAllGather(mine, gathered_data, per_rank, dt == ACL_BF16 ? HCCL_DATA_TYPE_BFP16 : HCCL_DATA_TYPE_FP16, g.comm, s) == HCCL_SUCCESS
+               ? ACLNN_SUCCESS : ACLNN_ERR_RUNTIME_ERROR;
+}
+
 }  // namespace
 
 extern "C" {
+
+aclnnStatus aclnnB200WeightQuantMatmulAllGatherGetWorkspaceSize(const aclTensor *x, const aclTensor *weight, const aclTensor *antiquantScale,
+        const aclTensor *antiquantOffsetOptional, const aclTensor *biasOptional, int64_t antiquantGroupSize, HcclComm comm,
+        aclTensor *gathered, uint64_t *ws, aclOpExecutor **ex) {
+    return gather_plan(x, weight, antiquantScale, antiquantOffsetOptional, biasOptional, antiquantGroupSize, comm, gathered, ws, ex);
+}
+aclnnStatus aclnnB200WeightQuantMatmulAllGather(void *ws, uint64_t wsz, aclOpExecutor *e, aclrtStream s) { return gather_run(ws, wsz, e, s); }
+uint64_t aclnnB200FusedGatherCount(void) { return g_fused_gathers.load(); }
 
 aclnnStatus aclnnQuantMatmulAllReduceAddRmsNormGetWorkspaceSize(const aclTensor *x, const aclTensor *weight, const aclTensor *scale,
         const aclTensor *residual, const aclTensor *gamma, double eps, HcclComm comm, aclTensor *y, aclTensor *residualSum,

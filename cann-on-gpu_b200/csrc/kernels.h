@@ -119,6 +119,16 @@ void wq_rows_device_status_reset();
 unsigned int tc_device_status();
 // Clears the status words of every kernel family on the current device (synchronises).
 void tc_device_status_reset();
+// Gathering epilogue of the decode kernel: the calling thread's next decode launches also store their output rows into the
+// peers' receive windows (see MmParams in wq_mma.cu).  nullptr clears.  consumed(): the thread's last launch did so.
+struct DecodeGather {
+    void *peer[8];
+    const unsigned long long *calls;
+    uint32_t nranks, rank;
+    uint64_t buf_bytes;
+};
+void wq_mma_set_gather(const DecodeGather *g);
+bool wq_mma_gather_consumed();
 void tc_reserve_sms(int n);   // the calling thread's dense-kernel plans leave n SMs free (0 = none)
 
 // Host-side tally of kernels this library has launched (diagnostics for benchmarks).

@@ -371,6 +371,11 @@ uint32_t aclnnB200DeviceStatus(void) {
     return v ? v : g_latched_status[dev].load(std::memory_order_relaxed);
 }
 void aclnnB200ReserveSms(int32_t sms) { tc_reserve_sms(sms); }
+void aclnnB200SetDecodeGather(const aclnnB200DecodeGather *g) {
+    static_assert(sizeof(aclnnB200DecodeGather) == sizeof(DecodeGather), "the public struct mirrors the kernel's");
+    wq_mma_set_gather(reinterpret_cast<const DecodeGather *>(g));
+}
+int32_t aclnnB200DecodeGatherConsumed(void) { return wq_mma_gather_consumed() ? 1 : 0; }
 
 void aclnnB200ResetDeviceStatus(void) {
     qmm::tc_device_status_reset();

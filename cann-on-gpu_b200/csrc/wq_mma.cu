@@ -58,6 +58,7 @@ constexpr int MM_W_BYTES = 16384;   // packed weights of one stage: 128 rows x 1
 constexpr int MM_TEAMS = 3;
 constexpr int MM_MAX_ROWS = 16;     // rows of one pass (two activation fragments of 8)
 constexpr int MM_XP = 2;            // activation producer warps (they take alternate stages)
+constexpr int MM_MAX_PEERS = 8;     // GPUs of a gathering epilogue
 constexpr int MM_THREADS = (4 * MM_TEAMS + 2 + MM_XP) * 32;
 
 struct MmParams {
@@ -79,6 +80,12 @@ struct MmParams {
     int weights_early;       // weights, scales and offsets may be read before the preceding kernel has completed
     unsigned long long wait_ns;   // time limit of every wait (0 = about a second)
     int test_drop;           // test hook: CTA 0 never fetches its first stage, so the wait for it runs out
+    // Gathering epilogue (column shards over several GPUs): besides p.out every finished output row is stored into each
+    // peer's receive window as 8-byte packets {two 16-bit outputs, the call's number}; the receiver polls the numbers.
+    int gather_n, gather_rank;                    // GPUs taking part (0 = no gathering), this GPU's index
+    unsigned long long gather_peer[MM_MAX_PEERS]; // every GPU's window as this process sees it
+    unsigned long long gather_buf_bytes;          // one of the window's two receive buffers (they alternate by call)
+    const unsigned long long *gather_calls;       // calls completed so far (device memory, advanced by the receiver)
 };
 
 // Shared memory of one CTA: [ring: ns slots][partial tiles: teams x M rows x 256 fp32][barriers][flag].
@@ -806,6 +813,21 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const MmParams p, const 
                 uint16_t *dst = static_cast<uint16_t *>(p.out) + (size_t)m * p.N + n_glob;
                 if constexpr (Q8) *reinterpret_cast<uint2 *>(dst) = make_uint2(o[0], o[1]);
                 else *reinterpret_cast<uint4 *>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
+                if (p.gather_n > 0) {
+                    // the same row into every peer's window: packet i of a receive buffer = outputs 2 i, 2 i + 1 of the
+                    // gathered [GPU][M][N] result.  A packet is one 8-byte store, so number and data arrive together and
+                    // no fence is needed; the number tells the receiver that the packet belongs to this call.
+                    const unsigned long long call = __ldcg(p.gather_calls) + 1ull;
+                    const size_t pkt = (((size_t)p.gather_rank * p.M + m) * p.N + n_glob) >> 1;
+                    const size_t off = (size_t)(call & 1ull) * p.gather_buf_bytes + pkt * 8;
+                    for (int g = 0; g < p.gather_n; ++g) {
+                        if (g == p.gather_rank) continue;
+                        uint2 *pk = reinterpret_cast<uint2 *>(p.gather_peer[g] + off);
+#pragma unroll
+                        for (int c = 0; c < CPL / 2; ++c)
+                            asm volatile("st.global.v2.u32 [%0], {%1, %2};" ::"l"(pk + c), "r"(o[c]), "r"((uint32_t)call) : "memory");
+                    }
+                }
             };
             if (whole) {
                 if (n_ok) {
@@ -1151,6 +1173,17 @@ extern "C" __attribute__((visibility("default"))) int aclnnB200DecodeProfile(uns
 }
 #endif
 
+namespace {
+thread_local DecodeGather tl_gather{};
+thread_local bool tl_gather_set = false, tl_gather_consumed = false;
+}  // namespace
+void wq_mma_set_gather(const DecodeGather *g) {
+    tl_gather_set = g != nullptr && g->nranks >= 2 && g->nranks <= MM_MAX_PEERS && g->rank < g->nranks;
+    if (tl_gather_set) tl_gather = *g;
+    tl_gather_consumed = false;
+}
+bool wq_mma_gather_consumed() { return tl_gather_consumed; }
+
 bool wq_mma_supported(const MatmulArgs &p) {
     if (p.epilogue != EPI_PLAIN || !p.scale || p.a_scale || p.b_scale) return false;
     if (p.batch != 1 || p.b_transposed || p.accumulate || p.M < 1 || p.M > MM_MAX_ROWS) return false;
@@ -1172,7 +1205,7 @@ bool wq_mma_supported(const MatmulArgs &p) {
 // 4 rows 31.5 / 33.0, 5 rows 33.8 / 33.5, 6 rows 35.3 / 34.3, 8 rows 37.8 / 35.5, 9 rows 43.6 / 46.3, 12 rows 47.8 / 48.7,
 // 16 rows 53.0 / 50.5.  B200_QMM_WQ_ROWS=0 keeps everything here, =<m> sends m rows and more there.
 inline bool mm_use_rows_kernel(const MatmulArgs &p) {
-    if (p.b_nz || !wq_rows_supported(p)) return false;
+    if (p.b_nz || tl_gather_set || !wq_rows_supported(p)) return false;   // the gathering epilogue lives in this kernel
     if (const char *e = getenv("B200_QMM_WQ_ROWS")) return atoi(e) > 0 && p.M >= atoi(e);
     return (p.M >= 5 && p.M <= 8) || p.M >= 13;
 }
@@ -1230,6 +1263,14 @@ cudaError_t launch_wq_mma(const MatmulArgs &p, cudaStream_t s) {
     mp.M = (int)p.M; mp.N = (int)p.N; mp.K = (int)p.K;
     mp.num_sb = pl.num_sb; mp.total_u = pl.total_u; mp.gsb = pl.gsb;
     mp.tile_n = q8 ? 128 : 256;
+    // gathering epilogue asked for by the calling thread (wq_mma_set_gather), if the receive buffers hold the result
+    if (tl_gather_set && (uint64_t)tl_gather.nranks * p.M * p.N * 4 <= tl_gather.buf_bytes && (p.N & 1) == 0) {
+        mp.gather_n = (int)tl_gather.nranks; mp.gather_rank = (int)tl_gather.rank;
+        for (int g = 0; g < mp.gather_n; ++g) mp.gather_peer[g] = (unsigned long long)(uintptr_t)tl_gather.peer[g];
+        mp.gather_buf_bytes = tl_gather.buf_bytes;
+        mp.gather_calls = tl_gather.calls;
+        tl_gather_consumed = true;
+    }
     // test hooks: B200_QMM_TEST_WAIT_LIMIT_NS=<n> gives every wait of the decode kernel n nanoseconds instead of about a
     // second; B200_QMM_TEST_DROP_STAGE=1 makes CTA 0 leave out the copy of its first stage, so that the consumers' wait
     // for it is a wait for something that never comes

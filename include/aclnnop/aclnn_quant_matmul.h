@@ -271,6 +271,20 @@ ACL_FUNC_VISIBILITY aclTensor *aclnnB200CreateRowSlice(const aclTensor *tensor, 
  * THREAD makes (both phases must see the same value) leave n SMs unused; 0 restores the default.  Used by the
  * all-reduce matmuls of libhccl.so around their row chunks. */
 ACL_FUNC_VISIBILITY void aclnnB200ReserveSms(int32_t sms);
+/* Gathering epilogue of the weight-only decode kernel (used by aclnnB200WeightQuantMatmulAllGather of libhccl.so; no
+ * counterpart in the reference).  While set, the CALLING THREAD's weight-only matmuls of up to 16 rows also store every
+ * output row into the receive windows of the other GPUs of a column-partitioned layer, as 8-byte packets {two 16-bit
+ * outputs, the call's number}: peer[i] is GPU i's window as this process sees it, two receive buffers of buf_bytes
+ * each (they alternate by call), calls the device counter of completed calls.  Both phases of a call must see the same
+ * setting; NULL clears.  aclnnB200DecodeGatherConsumed: 1 if the thread's last launch took the gathering form. */
+typedef struct aclnnB200DecodeGather {
+    void *peer[8];
+    const unsigned long long *calls;
+    uint32_t nranks, rank;
+    uint64_t buf_bytes;
+} aclnnB200DecodeGather;
+ACL_FUNC_VISIBILITY void aclnnB200SetDecodeGather(const aclnnB200DecodeGather *gather);
+ACL_FUNC_VISIBILITY int32_t aclnnB200DecodeGatherConsumed(void);
 ACL_FUNC_VISIBILITY void *aclnnB200WrapperPayload(aclOpExecutor *executor, int release);
 
 /* Diagnostics (no counterpart in the reference): number of kernels this library has launched in the

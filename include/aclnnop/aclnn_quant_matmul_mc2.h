@@ -44,6 +44,23 @@ ACL_FUNC_VISIBILITY aclnnStatus aclnnQuantMatmulAllReduceAddRmsNormGetWorkspaceS
     aclTensor *residualSum, uint64_t *workspaceSize, aclOpExecutor **executor);
 ACL_FUNC_VISIBILITY aclnnStatus aclnnQuantMatmulAllReduceAddRmsNorm(void *workspace, uint64_t workspaceSize,
     aclOpExecutor *executor, aclrtStream stream);
+/* Column-partitioned weight-only matmul with the gather of the output shards fused into its epilogue (no counterpart in
+ * the reference, which offers only the K split above; HcclAllGather, cuda/src/hccl.cu:108-113, is the unfused form).
+ * Rank r of comm holds columns [r N/g, (r+1) N/g) of the layer: weight [K, N/g], scale / offset / bias for those columns;
+ * x [M,K] is the same on every rank.  gathered is [g][M][N/g] (rank-major, contiguous, the activation type): rank r's own
+ * shard is written into gathered[r] by its matmul, and the other ranks' shards arrive through receive windows in peer
+ * memory -- the decode kernel stores every finished row straight into the peers' windows, and a small receiver kernel
+ * behind it copies them into gathered (csrc/hccl_p2p.cu).  Up to 16 rows, 16-bit activations, g <= 8 and
+ * g M N/g <= 512 Ki elements take that form; anything else (and comm windows that cannot be set up) runs the local matmul
+ * followed by HcclAllGather, with the same result.  The first call on a communicator sets the windows up collectively:
+ * make it outside stream capture.  Every rank must make the same calls in the same order. */
+ACL_FUNC_VISIBILITY aclnnStatus aclnnB200WeightQuantMatmulAllGatherGetWorkspaceSize(const aclTensor *x, const aclTensor *weight,
+    const aclTensor *antiquantScale, const aclTensor *antiquantOffsetOptional, const aclTensor *biasOptional,
+    int64_t antiquantGroupSize, HcclComm comm, aclTensor *gathered, uint64_t *workspaceSize, aclOpExecutor **executor);
+ACL_FUNC_VISIBILITY aclnnStatus aclnnB200WeightQuantMatmulAllGather(void *workspace, uint64_t workspaceSize,
+    aclOpExecutor *executor, aclrtStream stream);
+/* Diagnostics: how many of this process's aclnnB200WeightQuantMatmulAllGather calls took the fused form so far. */
+ACL_FUNC_VISIBILITY uint64_t aclnnB200FusedGatherCount(void);
 #ifdef __cplusplus
 }
 #endif

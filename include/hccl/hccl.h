@@ -27,6 +27,10 @@ HcclResult HcclReduceScatter(void *sendBuf, void *recvBuf, uint64_t recvCount, H
                              HcclReduceOp op, HcclComm comm, aclrtStreamH stream);
 HcclResult HcclBroadcast(void *buf, uint64_t count, HcclDataType dataType, uint32_t root,
                          HcclComm comm, aclrtStreamH stream);
+/* No counterpart in the reference.  The gathering matmul (aclnnB200WeightQuantMatmulAllGather,
+ * aclnnop/aclnn_quant_matmul_mc2.h) receives the other ranks' output shards through windows in peer memory; a poll for a
+ * peer's data inside its receiver kernel gives up after about a second and leaves 0x500 + the peer's rank here; 0 = none. */
+uint32_t HcclB200P2pStatus(void);
 /* reference: cuda/src/hccl.cu:164-172. */
 HcclResult HcclGetRankSize(HcclComm comm, uint32_t *rankSize);
 HcclResult HcclGetRankId(HcclComm comm, uint32_t *rank);

@@ -5,6 +5,8 @@ of the reference): rank 0 takes HcclGetRootInfo and hands the blob to the others
 then every rank calls HcclCommInitRootInfo.  Checks:
   1. column sharding: each rank multiplies its [K, N/g] shard, HcclAllGather returns [g][M][N/g], the
      interleave is the [M, N] result of the whole problem;
+  1b. the same with the gather fused into the matmul's epilogue (peer-memory receive windows), repeated, captured and
+      replayed;
   2. K-split all-reduce forms: aclnnWeightQuantMatmulAllReduce and aclnnQuantMatmulAllReduce sum the
      ranks' partial products;
   3. the same with many rows and B200_HCCL_OVERLAP_CHUNKS set, where the all-reduce of a row chunk overlaps the
@@ -68,6 +70,75 @@ def main():
     ref = oracle.wqbmm_fast(f32(full["x"]), full["w"].numpy(), True, f32(full["scale"]), f32(full["offset"]), f32(full["bias"]),
                             M, full["K"], full["N"], 128)
     assert_close(to_np(whole), ref, f"rank {rank}: gathered column shards")
+
+    # 1b. the same with the gather fused into the matmul's epilogue (aclnnB200WeightQuantMatmulAllGather): the decode
+    # kernel stores its rows into the peers' receive windows, a receiver kernel copies them into `gathered`.  Many calls in
+    # a row with changing activations (two receive buffers alternate, the call number lives on the device), one to
+    # sixteen rows, int4 in both layouts and int8 weights, a row count the decode kernel does not take (plain sequence
+    # with HcclAllGather), and a captured graph replayed -- every result against the oracle on the whole layer.
+    hccl.HcclB200P2pStatus.restype = ctypes.c_uint32
+
+    def fused_gather(d_full, xdev, gathered_t, packed=None):
+        mine_ = workloads.shard_columns(d_full, world, rank)
+        key = id(d_full)
+        if key not in dev_cache:
+            w_ = mine_["w"].to(dev)
+            if packed:
+                w_ = pkg.pack_weight_nz(w_, d_full["K"], mine_["N"])
+            dev_cache[key] = (w_, mine_["scale"].to(dev), None if mine_["offset"] is None else mine_["offset"].to(dev),
+                              None if mine_["bias"] is None else mine_["bias"].to(dev))
+        w_, sc_, of_, bi_ = dev_cache[key]
+        if d_full["int4"]:
+            tw_ = (pkg.AclTensor(w_, pkg.ACL_INT4, (d_full["K"], mine_["N"]), fmt=pkg.ACL_FORMAT_FRACTAL_NZ, storage=(w_.numel() * 2,)) if packed
+                   else pkg.AclTensor(w_, pkg.ACL_INT4, (d_full["K"], mine_["N"])))
+        else:
+            tw_ = pkg.AclTensor(w_)
+        with pkg.use_library(hccl_path):
+            pkg.call("aclnnB200WeightQuantMatmulAllGather", pkg.AclTensor(xdev), tw_, pkg.AclTensor(sc_), None if of_ is None else pkg.AclTensor(of_),
+                     None if bi_ is None else pkg.AclTensor(bi_), ctypes.c_int64(d_full["group"]), comm, pkg.AclTensor(gathered_t))
+    dev_cache = {}
+    gen = torch.Generator().manual_seed(90)
+    cases = [(workloads.w4a16(M=1, K=1024, N=512 * world, group=128, dtype=torch.bfloat16, seed=91), False),
+             (workloads.w4a16(M=2, K=2048, N=1024 * world, group=128, dtype=torch.float16, seed=92, with_offset=False), True),
+             (workloads.w4a16(M=8, K=1024, N=256 * world, group=128, dtype=torch.bfloat16, seed=93, with_bias=False), True),
+             (workloads.w4a16(M=16, K=1024, N=512 * world, group=128, dtype=torch.bfloat16, seed=94), False),
+             (workloads.w8a16(M=3, K=1024, N=256 * world, dtype=torch.float16, seed=95, with_offset=True), False),
+             (workloads.w4a16(M=40, K=1024, N=256 * world, group=128, dtype=torch.bfloat16, seed=96), False)]   # plain sequence
+    for ci, (full_c, packed) in enumerate(cases):
+        Mc, Nc = full_c["M"], full_c["N"]
+        gathered_c = torch.zeros((world, Mc, Nc // world), dtype=full_c["x"].dtype, device=dev)
+        for rep in range(3):     # new activations every time, same weights
+            xc = torch.randn((Mc, full_c["K"]), generator=gen).to(full_c["x"].dtype)
+            gathered_c.fill_(7.0)
+            fused_gather(full_c, xc.to(dev), gathered_c, packed)
+            torch.cuda.synchronize()
+            whole_c = workloads.interleave_gathered(gathered_c, world, Mc, Nc)
+            ref_c = oracle.wqbmm_fast(f32(xc), full_c["w"].numpy(), full_c["int4"], f32(full_c["scale"]), f32(full_c["offset"]),
+                                      f32(full_c["bias"]), Mc, full_c["K"], Nc, full_c["group"])
+            assert_close(to_np(whole_c), ref_c, f"rank {rank}: fused gather, case {ci} call {rep}")
+    # captured once, replayed with new activations in the same buffer
+    full_g, _ = cases[0]
+    xg = torch.zeros((1, full_g["K"]), dtype=torch.bfloat16, device=dev)
+    gathered_g = torch.zeros((world, 1, full_g["N"] // world), dtype=torch.bfloat16, device=dev)
+    side = torch.cuda.Stream(dev)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            for _ in range(3):      # three calls per replay: the receive buffers alternate inside a replay and across replays
+                fused_gather(full_g, xg, gathered_g, False)
+    for rep in range(4):
+        xh = torch.randn((1, full_g["K"]), generator=gen).to(torch.bfloat16)
+        xg.copy_(xh.to(dev))
+        torch.cuda.synchronize()
+        graph.replay()
+        torch.cuda.synchronize()
+        whole_g = workloads.interleave_gathered(gathered_g, world, 1, full_g["N"])
+        ref_g = oracle.wqbmm_fast(f32(xh), full_g["w"].numpy(), True, f32(full_g["scale"]), f32(full_g["offset"]), f32(full_g["bias"]),
+                                  1, full_g["K"], full_g["N"], 128)
+        assert_close(to_np(whole_g), ref_g, f"rank {rank}: fused gather, replay {rep}")
+    assert hccl.HcclB200P2pStatus() == 0
+    hccl.aclnnB200FusedGatherCount.restype = ctypes.c_uint64
+    assert hccl.aclnnB200FusedGatherCount() == 5 * 3 + 3, "the fused form must have run for every case the decode kernel takes"
 
     # 2. K-split all-reduce forms (reference signatures: fp16, per-channel)
     d = workloads.w8a16(M=8, K=512 * world, N=256, dtype=torch.float16, with_offset=True, seed=78)
