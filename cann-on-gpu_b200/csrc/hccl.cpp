@@ -216,6 +216,7 @@ HcclResult HcclBroadcast(void *buf, uint64_t count, HcclDataType dataType, uint3
 }
 
 uint32_t HcclB200P2pStatus(void) { return p2p_status(); }
+uint32_t HcclB200TestReceiverTimeout(uint64_t waitNs) { return p2p_test_poll_runs_out(waitNs); }
 // for the gathering matmul of hccl_matmul.cpp
 int hccl_gather_target(HcclComm comm, aclrtStreamH stream, P2pGatherTarget *t) {
     if (!nccl().ok || !comm) return 0;

@@ -55,7 +55,8 @@ __device__ __forceinline__ unsigned long long p2p_now() {
 }
 
 // gathered: [nranks][M][N] 16-bit elements; packet i of a receive buffer holds elements 2 i, 2 i + 1 of it.
-__global__ void __launch_bounds__(256) ll_unpack_kernel(const WindowView w, uint32_t *gathered, unsigned long long pairs_per_rank) {
+__global__ void __launch_bounds__(256) ll_unpack_kernel(const WindowView w, uint32_t *gathered, unsigned long long pairs_per_rank,
+                                                        unsigned long long wait_ns) {
     asm volatile("griddepcontrol.wait;" ::: "memory");   // the matmul before this kernel has completed (its workspace is free again)
     uint8_t *mine = w.win[w.rank];
     unsigned long long *calls = reinterpret_cast<unsigned long long *>(mine + win_calls_off());
@@ -74,7 +75,7 @@ __global__ void __launch_bounds__(256) ll_unpack_kernel(const WindowView w, uint
             while (true) {
                 asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(buf + i) : "memory");
                 if (v.y == (uint32_t)call) break;
-                if (p2p_now() - t0 > P2P_WAIT_NS) {
+                if (p2p_now() - t0 > wait_ns) {
                     atomicCAS(&g_p2p_status, 0u, 0x500u + (unsigned)(i / pairs_per_rank));
                     ok = false;
                     break;
@@ -198,7 +199,7 @@ int p2p_unpack(const P2pNccl &nccl, void *comm, void *gathered, uint64_t elems_p
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, ll_unpack_kernel, w->view, static_cast<uint32_t *>(gathered), pairs);
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, ll_unpack_kernel, w->view, static_cast<uint32_t *>(gathered), pairs, P2P_WAIT_NS);
     return e == cudaSuccess && cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
@@ -214,6 +215,28 @@ void p2p_forget(void *comm) {
         cudaFree(w.view.win[w.view.rank]);
     }
     g_windows.erase(it);
+}
+
+// Test of the receiver's bounded poll without a second GPU and without faulting anything: a window of two "ranks" inside
+// this process whose peer never sends, so the poll for its packets is a wait for something that never comes; it gives up
+// after wait_ns, the kernel returns and the code is in the status word (returned, and cleared again).
+unsigned int p2p_test_poll_runs_out(unsigned long long wait_ns) {
+    WindowView v{};
+    uint8_t *mine = nullptr;
+    uint32_t *gathered = nullptr;
+    if (cudaMalloc(&mine, win_bytes()) != cudaSuccess || cudaMalloc(&gathered, 2 * 16 * sizeof(uint32_t)) != cudaSuccess) return 0xFFFFFFFFu;
+    cudaMemset(mine, 0, win_bytes());
+    v.nranks = 2; v.rank = 0; v.win[0] = mine; v.win[1] = mine;
+    ll_unpack_kernel<<<1, 256>>>(v, gathered, 16, wait_ns);
+    unsigned int code = 0xFFFFFFFFu;
+    if (cudaDeviceSynchronize() == cudaSuccess) {
+        code = p2p_status();
+        const unsigned int zero = 0;
+        cudaMemcpyToSymbol(g_p2p_status, &zero, sizeof(zero));
+    }
+    cudaFree(mine);
+    cudaFree(gathered);
+    return code;
 }
 
 unsigned int p2p_status() {

@@ -30,6 +30,7 @@ int p2p_unpack(const P2pNccl &nccl, void *comm, void *gathered, uint64_t elems_p
 void p2p_forget(void *comm);
 // 0, or the code a poll for a peer's packet left when it gave up (0x500 + the peer's rank).
 unsigned int p2p_status();
+unsigned int p2p_test_poll_runs_out(unsigned long long wait_ns);
 
 // Implemented in hccl.cpp (they need its NCCL binding); used by the gathering matmul of hccl_matmul.cpp.
 extern "C" int hccl_gather_target(void *comm, void *stream, P2pGatherTarget *t);                       // 1 = available

@@ -31,6 +31,9 @@ HcclResult HcclBroadcast(void *buf, uint64_t count, HcclDataType dataType, uint3
  * aclnnop/aclnn_quant_matmul_mc2.h) receives the other ranks' output shards through windows in peer memory; a poll for a
  * peer's data inside its receiver kernel gives up after about a second and leaves 0x500 + the peer's rank here; 0 = none. */
 uint32_t HcclB200P2pStatus(void);
+/* Test hook: runs the receiver kernel on a window whose peer never sends, with a poll limit of waitNs nanoseconds, and
+ * returns the code it left (0x501) -- the failure path of the fused gather, exercised on one GPU without a fault. */
+uint32_t HcclB200TestReceiverTimeout(uint64_t waitNs);
 /* reference: cuda/src/hccl.cu:164-172. */
 HcclResult HcclGetRankSize(HcclComm comm, uint32_t *rankSize);
 HcclResult HcclGetRankId(HcclComm comm, uint32_t *rank);

@@ -1305,6 +1305,23 @@ def test_c_client_step_of_many_calls(pkg, oracle, workloads, dev):
     assert pkg.load().aclmdlRIDestroy(model) == 0
 
 
+def test_fused_gather_receiver_gives_up_on_a_silent_peer(pkg, dev):
+    """The receiver kernel of the fused gather polls the peers' packets with a time limit.  On one GPU, with a window whose
+    peer never sends, the poll runs out: the kernel returns, the status word names the peer (0x500 + rank 1), and the
+    device keeps working (nothing faulted, nothing hangs)."""
+    path = os.path.join(os.path.dirname(pkg.LIB_PATH), "libhccl.so")
+    if not os.path.exists(path):
+        pytest.skip("libhccl.so not built")
+    pkg.load()
+    hccl = ctypes.CDLL(path)
+    hccl.HcclB200TestReceiverTimeout.restype = ctypes.c_uint32
+    hccl.HcclB200P2pStatus.restype = ctypes.c_uint32
+    assert hccl.HcclB200TestReceiverTimeout(ctypes.c_uint64(200000)) == 0x501      # 200 us
+    assert hccl.HcclB200P2pStatus() == 0                                               # cleared again
+    a = torch.arange(1024, device=dev).float().sum().item()                            # the context is alive
+    assert a == 1023 * 1024 / 2
+
+
 def test_capture_replay_of_the_two_phase_call(pkg, oracle, workloads, dev):
     """aclmdlRICaptureBegin / End / ExecuteAsync around quantized matmuls, used like the reference's
     tests/test_graph.cpp:30-78: warm up, capture calls that share a caller-owned workspace (phase 1 runs
