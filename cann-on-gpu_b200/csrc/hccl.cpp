@@ -225,6 +225,9 @@ int hccl_gather_target(HcclComm comm, aclrtStreamH stream, P2pGatherTarget *t) {
 int hccl_gather_unpack(HcclComm comm, void *gathered, uint64_t elems_per_rank, aclrtStreamH stream) {
     return p2p_unpack(p2p_table(), comm, gathered, elems_per_rank, (cudaStream_t)stream);
 }
+int hccl_gather_reduce(HcclComm comm, void *out, uint64_t elems, int bf16, aclrtStreamH stream) {
+    return p2p_reduce(p2p_table(), comm, out, elems, bf16 != 0, (cudaStream_t)stream);
+}
 
 HcclResult HcclGetRankSize(HcclComm comm, uint32_t *rankSize) {
     NEED_NCCL();

@@ -30,6 +30,7 @@ struct AllReduceExecutor {
     int chunks = 1;          // row chunks whose all-reduce overlaps the next chunk's matmul
     int64_t rows = 0;
 };
+std::atomic<uint64_t> g_fused_allreduces{0};   // all-reduce matmuls that took the fused form (diagnostics)
 void free_allreduce(void *p) {
     auto *w = static_cast<AllReduceExecutor *>(p);
     if (w->inner) aclDestroyAclOpExecutor(w->inner);
@@ -143,6 +144,20 @@ aclnnStatus wrap(aclnnStatus st, aclOpExecutor *inner, HcclComm comm, const aclT
             }
         }
     }
+    // the weight-only decode kernel can send its partial result to the peers itself (run below): its plan may need a
+    // different workspace, and which form phase 2 takes is known only there
+    if (comm && weight_only) {
+        aclnnB200DecodeGather fake{};
+        fake.nranks = 2; fake.rank = 0; fake.buf_bytes = ~0ull; fake.f32 = 1;
+        aclnnB200SetDecodeGather(&fake);
+        uint64_t need = 0;
+        aclOpExecutor *probe = nullptr;
+        if (local_plan(true, x, weight, scale, offset, out, &need, &probe) == ACLNN_SUCCESS) {
+            aclDestroyAclOpExecutor(probe);
+            if (need > *ws) *ws = need;
+        }
+        aclnnB200SetDecodeGather(nullptr);
+    }
     *ex = aclnnB200CreateWrapperExecutor(w, free_allreduce);
     if (!*ex) { free_allreduce(w); return ACLNN_ERR_RUNTIME_ERROR; }
     return ACLNN_SUCCESS;
@@ -218,9 +233,40 @@ aclnnStatus run(void *ws, uint64_t wsz, aclOpExecutor *e, aclrtStream s) {
         aclDestroyAclOpExecutor(w.inner);   // the whole-problem plan only sized the workspace
         return run_chunked(w, ws, wsz, ht, s);
     }
+    // Weight-only decode shapes: the matmul kernel sends its partial rows to the peers' receive windows itself and a
+    // receiver kernel sums the ranks' unrounded fp32 partial results (rank order, rounded once) -- one-shot all-reduce over peer
+    // memory, no library collective.  Needs the communicator's windows and a plan of the decode kernel that fits the
+    // workspace; otherwise the plain sequence below.
+    P2pGatherTarget t{};
+    if (w.comm && w.weight_only && count > 0 && (dt == ACL_BF16 || dt == ACL_FLOAT16) && hccl_gather_target(w.comm, s, &t) == 1) {
+        aclnnB200DecodeGather dg{};
+        for (int i = 0; i < 8; ++i) dg.peer[i] = t.peer[i];
+        dg.calls = t.calls; dg.nranks = t.nranks; dg.rank = t.rank; dg.buf_bytes = t.buf_bytes; dg.f32 = 1;
+        aclnnB200SetDecodeGather(&dg);
+        uint64_t need = 0;
+        aclOpExecutor *again = nullptr;
+        if (local_plan(true, w.x, w.weight, w.scale, w.offset, w.out, &need, &again) == ACLNN_SUCCESS) {
+            if (need <= wsz) {
+                aclDestroyAclOpExecutor(w.inner);
+                w.inner = again;
+            } else {
+                aclDestroyAclOpExecutor(again);
+                aclnnB200SetDecodeGather(nullptr);   // the caller's workspace is too small for that plan: plain sequence
+            }
+        } else {
+            aclnnB200SetDecodeGather(nullptr);
+        }
+    }
     st = w.weight_only ? aclnnWeightQuantBatchMatmul(ws, wsz, w.inner, s) : aclnnQuantMatmul(ws, wsz, w.inner, s);
+    const bool sent = w.weight_only && aclnnB200DecodeGatherConsumed() == 1;
+    aclnnB200SetDecodeGather(nullptr);
     if (st == ACLNN_SUCCESS && w.comm && count > 0) {
-        if (HcclAllReduce(data, data, count, ht, HCCL_REDUCE_SUM, w.comm, s) != HCCL_SUCCESS) st = ACLNN_ERR_RUNTIME_ERROR;
+        if (sent) {
+            g_fused_allreduces.fetch_add(1);
+            if (hccl_gather_reduce(w.comm, data, count, dt == ACL_BF16 ? 1 : 0, s) != 0) st = ACLNN_ERR_RUNTIME_ERROR;
+        } else if (HcclAllReduce(data, data, count, ht, HCCL_REDUCE_SUM, w.comm, s) != HCCL_SUCCESS) {
+            st = ACLNN_ERR_RUNTIME_ERROR;
+        }
     }
     return st;
 }
@@ -425,6 +471,7 @@ aclnnStatus aclnnB200WeightQuantMatmulAllGatherGetWorkspaceSize(const aclTensor 
 }
 aclnnStatus aclnnB200WeightQuantMatmulAllGather(void *ws, uint64_t wsz, aclOpExecutor *e, aclrtStream s) { return gather_run(ws, wsz, e, s); }
 uint64_t aclnnB200FusedGatherCount(void) { return g_fused_gathers.load(); }
+uint64_t aclnnB200FusedAllReduceCount(void) { return g_fused_allreduces.load(); }
 
 aclnnStatus aclnnQuantMatmulAllReduceAddRmsNormGetWorkspaceSize(const aclTensor *x, const aclTensor *weight, const aclTensor *scale,
         const aclTensor *residual, const aclTensor *gamma, double eps, HcclComm comm, aclTensor *y, aclTensor *residualSum,

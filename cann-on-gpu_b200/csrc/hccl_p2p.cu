@@ -22,6 +22,8 @@
 // Failure handling: a poll gives up after about a second, records a code in a status word the host can read
 // (HcclB200P2pStatus) and the kernel returns; the gathered tensor is then incomplete.  If any rank cannot open a peer's
 // window the whole communicator keeps using NCCL (the ranks agree on that with an all-reduce).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 #include <cstdint>
@@ -35,7 +37,7 @@
 namespace {
 
 constexpr int P2P_MAX_RANKS = 8;
-constexpr size_t P2P_BUF_BYTES = 2u << 20;           // one receive buffer: packets of a whole gathered result
+constexpr size_t P2P_BUF_BYTES = 8u << 20;           // one receive buffer: packets of a whole gathered result
 constexpr unsigned long long P2P_WAIT_NS = 1000000000ull;
 
 struct WindowView {
@@ -88,6 +90,62 @@ __global__ void __launch_bounds__(256) ll_unpack_kernel(const WindowView w, uint
     if (threadIdx.x == 0) {
         __threadfence();
         if (atomicAdd(done, 1u) == gridDim.x - 1) {      // the kernel's last CTA closes the call
+            *done = 0u;
+            *calls = call;
+        }
+    }
+}
+
+// The all-reduce form of the receiver (K split over the ranks): every rank's matmul has stored its partial [M][N] result,
+// unrounded, as packets {fp32 value, call number} into slot [rank] of every rank's window, its own included.
+// out[i] = the sum over the ranks in rank order (fp32), rounded once to the 16-bit output type.  A thread takes two
+// neighbouring outputs and writes them as one 32-bit word.
+template <bool BF16>
+__global__ void __launch_bounds__(256) ll_reduce_kernel(const WindowView w, uint32_t *out, unsigned long long pairs, unsigned long long wait_ns) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    uint8_t *mine = w.win[w.rank];
+    unsigned long long *calls = reinterpret_cast<unsigned long long *>(mine + win_calls_off());
+    unsigned int *done = reinterpret_cast<unsigned int *>(calls + 1);
+    const unsigned long long call = *calls + 1;
+    const uint2 *buf = reinterpret_cast<const uint2 *>(mine + (size_t)(call & 1ull) * P2P_BUF_BYTES);
+    bool ok = true;
+    for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < pairs && ok; i += (unsigned long long)gridDim.x * blockDim.x) {
+        float acc[2] = {0.f, 0.f};
+        for (int r = 0; r < w.nranks && ok; ++r) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const uint2 *pk = buf + ((unsigned long long)r * pairs + i) * 2 + h;
+                uint2 v;
+                asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(pk) : "memory");
+                if (v.y != (uint32_t)call) {
+                    const unsigned long long t0 = p2p_now();
+                    while (true) {
+                        asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(pk) : "memory");
+                        if (v.y == (uint32_t)call) break;
+                        if (p2p_now() - t0 > wait_ns) {
+                            atomicCAS(&g_p2p_status, 0u, 0x500u + (unsigned)r);
+                            ok = false;
+                            break;
+                        }
+                    }
+                }
+                acc[h] += __uint_as_float(v.x);
+            }
+        }
+        if (ok) {
+            if constexpr (BF16) {
+                const __nv_bfloat162 hh = __floats2bfloat162_rn(acc[0], acc[1]);
+                out[i] = *reinterpret_cast<const uint32_t *>(&hh);
+            } else {
+                const __half2 hh = __floats2half2_rn(acc[0], acc[1]);
+                out[i] = *reinterpret_cast<const uint32_t *>(&hh);
+            }
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(done, 1u) == gridDim.x - 1) {
             *done = 0u;
             *calls = call;
         }
@@ -215,6 +273,26 @@ void p2p_forget(void *comm) {
         cudaFree(w.view.win[w.view.rank]);
     }
     g_windows.erase(it);
+}
+
+int p2p_reduce(const P2pNccl &nccl, void *comm, void *out, uint64_t elems, bool bf16, cudaStream_t s) {
+    Window *w = window_of(nccl, comm, s);
+    if (!w || (elems & 1) || elems * 8 * (uint64_t)w->view.nranks > P2P_BUF_BYTES || (reinterpret_cast<uintptr_t>(out) & 3)) return -1;
+    const unsigned long long pairs = elems / 2;
+    const unsigned long long want = (pairs + 511) / 512;
+    const unsigned grid = (unsigned)(want < 1 ? 1 : (want > 64 ? 64 : want));
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(256);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = bf16 ? cudaLaunchKernelEx(&cfg, ll_reduce_kernel<true>, w->view, static_cast<uint32_t *>(out), pairs, P2P_WAIT_NS)
+                               : cudaLaunchKernelEx(&cfg, ll_reduce_kernel<false>, w->view, static_cast<uint32_t *>(out), pairs, P2P_WAIT_NS);
+    return e == cudaSuccess && cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
 // Test of the receiver's bounded poll without a second GPU and without faulting anything: a window of two "ranks" inside

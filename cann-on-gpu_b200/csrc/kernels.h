@@ -126,6 +126,7 @@ struct DecodeGather {
     const unsigned long long *calls;
     uint32_t nranks, rank;
     uint64_t buf_bytes;
+    uint32_t f32, reserved;   // f32: packets carry one fp32 partial result each, also into the own window (all-reduce form)
 };
 void wq_mma_set_gather(const DecodeGather *g);
 bool wq_mma_gather_consumed();

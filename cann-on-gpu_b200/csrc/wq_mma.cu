@@ -83,6 +83,8 @@ struct MmParams {
     // Gathering epilogue (column shards over several GPUs): besides p.out every finished output row is stored into each
     // peer's receive window as 8-byte packets {two 16-bit outputs, the call's number}; the receiver polls the numbers.
     int gather_n, gather_rank;                    // GPUs taking part (0 = no gathering), this GPU's index
+    int gather_f32;                               // packets {one fp32 output, number} to every GPU, this one included (partial
+                                                  // results that the receiver sums), instead of {two 16-bit outputs, number}
     unsigned long long gather_peer[MM_MAX_PEERS]; // every GPU's window as this process sees it
     unsigned long long gather_buf_bytes;          // one of the window's two receive buffers (they alternate by call)
     const unsigned long long *gather_calls;       // calls completed so far (device memory, advanced by the receiver)
@@ -796,6 +798,7 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const MmParams p, const 
             };
             auto write_row = [&](int m, const float (&v)[CPL]) {
                 uint32_t o[CPL / 2];
+                float fo[CPL];
 #pragma unroll
                 for (int c = 0; c < CPL / 2; ++c) {
                     float lo = v[2 * c], hi = v[2 * c + 1];
@@ -803,6 +806,7 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const MmParams p, const 
                         lo += load_as_float(p.bias, BF16 ? ET_BF16 : ET_F16, n_glob + 2 * c);
                         hi += load_as_float(p.bias, BF16 ? ET_BF16 : ET_F16, n_glob + 2 * c + 1);
                     }
+                    fo[2 * c] = lo; fo[2 * c + 1] = hi;
                     if constexpr (BF16) {
                         __nv_bfloat162 t2 = __floats2bfloat162_rn(lo, hi);
                         o[c] = *reinterpret_cast<uint32_t *>(&t2);
@@ -818,14 +822,20 @@ wq_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const MmParams p, const 
                     // gathered [GPU][M][N] result.  A packet is one 8-byte store, so number and data arrive together and
                     // no fence is needed; the number tells the receiver that the packet belongs to this call.
                     const unsigned long long call = __ldcg(p.gather_calls) + 1ull;
-                    const size_t pkt = (((size_t)p.gather_rank * p.M + m) * p.N + n_glob) >> 1;
-                    const size_t off = (size_t)(call & 1ull) * p.gather_buf_bytes + pkt * 8;
+                    const size_t elem = ((size_t)p.gather_rank * p.M + m) * p.N + n_glob;
+                    const size_t off = (size_t)(call & 1ull) * p.gather_buf_bytes + (p.gather_f32 ? elem : elem >> 1) * 8;
                     for (int g = 0; g < p.gather_n; ++g) {
-                        if (g == p.gather_rank) continue;
+                        if (g == p.gather_rank && !p.gather_f32) continue;
                         uint2 *pk = reinterpret_cast<uint2 *>(p.gather_peer[g] + off);
+                        if (p.gather_f32) {
 #pragma unroll
-                        for (int c = 0; c < CPL / 2; ++c)
-                            asm volatile("st.global.v2.u32 [%0], {%1, %2};" ::"l"(pk + c), "r"(o[c]), "r"((uint32_t)call) : "memory");
+                            for (int c = 0; c < CPL; ++c)
+                                asm volatile("st.global.v2.u32 [%0], {%1, %2};" ::"l"(pk + c), "r"(__float_as_uint(fo[c])), "r"((uint32_t)call) : "memory");
+                        } else {
+#pragma unroll
+                            for (int c = 0; c < CPL / 2; ++c)
+                                asm volatile("st.global.v2.u32 [%0], {%1, %2};" ::"l"(pk + c), "r"(o[c]), "r"((uint32_t)call) : "memory");
+                        }
                     }
                 }
             };
@@ -1264,10 +1274,12 @@ cudaError_t launch_wq_mma(const MatmulArgs &p, cudaStream_t s) {
     mp.num_sb = pl.num_sb; mp.total_u = pl.total_u; mp.gsb = pl.gsb;
     mp.tile_n = q8 ? 128 : 256;
     // gathering epilogue asked for by the calling thread (wq_mma_set_gather), if the receive buffers hold the result
-    if (tl_gather_set && (uint64_t)tl_gather.nranks * p.M * p.N * 4 <= tl_gather.buf_bytes && (p.N & 1) == 0) {
+    if (tl_gather_set && (uint64_t)tl_gather.nranks * p.M * p.N * (tl_gather.f32 ? 8 : 4) <= tl_gather.buf_bytes && (p.N & 1) == 0 &&
+        !(tl_gather.f32 && p.bias)) {   // partial results must not each carry the bias
         mp.gather_n = (int)tl_gather.nranks; mp.gather_rank = (int)tl_gather.rank;
         for (int g = 0; g < mp.gather_n; ++g) mp.gather_peer[g] = (unsigned long long)(uintptr_t)tl_gather.peer[g];
         mp.gather_buf_bytes = tl_gather.buf_bytes;
+        mp.gather_f32 = tl_gather.f32 ? 1 : 0;
         mp.gather_calls = tl_gather.calls;
         tl_gather_consumed = true;
     }

@@ -282,6 +282,8 @@ typedef struct aclnnB200DecodeGather {
     const unsigned long long *calls;
     uint32_t nranks, rank;
     uint64_t buf_bytes;
+    uint32_t f32, reserved; /* f32 != 0: packets {one fp32 output, number}, stored into the own window too (partial results
+                             * that a receiver sums: the K-split all-reduce form; no bias allowed) */
 } aclnnB200DecodeGather;
 ACL_FUNC_VISIBILITY void aclnnB200SetDecodeGather(const aclnnB200DecodeGather *gather);
 ACL_FUNC_VISIBILITY int32_t aclnnB200DecodeGatherConsumed(void);

@@ -51,7 +51,7 @@ ACL_FUNC_VISIBILITY aclnnStatus aclnnQuantMatmulAllReduceAddRmsNorm(void *worksp
  * shard is written into gathered[r] by its matmul, and the other ranks' shards arrive through receive windows in peer
  * memory -- the decode kernel stores every finished row straight into the peers' windows, and a small receiver kernel
  * behind it copies them into gathered (csrc/hccl_p2p.cu).  Up to 16 rows, 16-bit activations, g <= 8 and
- * g M N/g <= 512 Ki elements take that form; anything else (and comm windows that cannot be set up) runs the local matmul
+ * g M N/g <= 2 Mi elements take that form; anything else (and comm windows that cannot be set up) runs the local matmul
  * followed by HcclAllGather, with the same result.  The first call on a communicator sets the windows up collectively:
  * make it outside stream capture.  Every rank must make the same calls in the same order. */
 ACL_FUNC_VISIBILITY aclnnStatus aclnnB200WeightQuantMatmulAllGatherGetWorkspaceSize(const aclTensor *x, const aclTensor *weight,
@@ -61,6 +61,12 @@ ACL_FUNC_VISIBILITY aclnnStatus aclnnB200WeightQuantMatmulAllGather(void *worksp
     aclOpExecutor *executor, aclrtStream stream);
 /* Diagnostics: how many of this process's aclnnB200WeightQuantMatmulAllGather calls took the fused form so far. */
 ACL_FUNC_VISIBILITY uint64_t aclnnB200FusedGatherCount(void);
+/* aclnnWeightQuantMatmulAllReduce on decode shapes (up to 16 rows, 16-bit types) takes a fused form too: the decode
+ * kernel sends its partial rows, unrounded fp32, to the receive windows and a receiver kernel sums the ranks' partial
+ * results in rank order and rounds once (a one-shot all-reduce over peer memory instead of HcclAllReduce of 16-bit
+ * partial outputs, which rounds every partial result first).  Diagnostics: how
+ * many calls of this process took that form. */
+ACL_FUNC_VISIBILITY uint64_t aclnnB200FusedAllReduceCount(void);
 #ifdef __cplusplus
 }
 #endif

@@ -151,6 +151,28 @@ def main():
     torch.cuda.synchronize()
     ref = oracle.wqbmm_fast(f32(d["x"]), d["w"].numpy(), False, f32(d["scale"]), f32(d["offset"]), None, 8, d["K"], 256, 0)
     assert_close(to_np(out), ref, f"rank {rank}: aclnnWeightQuantMatmulAllReduce")
+    # decode shapes take the fused form (the kernel sends its partial rows to the peers, a receiver sums them): again with
+    # other activations, bf16 int4 weights, one row -- and every rank must end up with the same bits
+    hccl.aclnnB200FusedAllReduceCount.restype = ctypes.c_uint64
+    assert hccl.aclnnB200FusedAllReduceCount() == 1
+    d4 = workloads.w4a16(M=1, K=1024 * world, N=2048, dtype=torch.bfloat16, per_channel=True, with_bias=False, seed=86)
+    kq = slice(rank * 1024, (rank + 1) * 1024)
+    w4_r = workloads.pack_int4(d4["w_vals"][kq].contiguous()).to(dev)
+    for rep in range(3):
+        x4 = torch.randn((1, d4["K"]), generator=torch.Generator().manual_seed(870 + rep)).to(torch.bfloat16)
+        o4 = torch.empty((1, 2048), dtype=torch.bfloat16, device=dev)
+        with pkg.use_library(hccl_path):
+            pkg.call("aclnnWeightQuantMatmulAllReduce", pkg.AclTensor(x4[:, kq].contiguous().to(dev)), pkg.AclTensor(w4_r, pkg.ACL_INT4, (1024, 2048)),
+                     pkg.AclTensor(d4["scale"].to(dev)), pkg.AclTensor(d4["offset"].to(dev)), comm, pkg.AclTensor(o4))
+        torch.cuda.synchronize()
+        ref4 = oracle.wqbmm_fast(f32(x4), d4["w"].numpy(), True, f32(d4["scale"]), f32(d4["offset"]), None, 1, d4["K"], 2048, 0)
+        assert_close(to_np(o4), ref4, f"rank {rank}: fused all-reduce, call {rep}")
+        both = torch.empty((world, 2048), dtype=torch.bfloat16, device=dev)
+        assert hccl.HcclAllGather(ctypes.c_void_p(o4.data_ptr()), ctypes.c_void_p(both.data_ptr()), ctypes.c_uint64(2048), ctypes.c_int(HCCL_BF16),
+                                  comm, stream) == 0
+        torch.cuda.synchronize()
+        assert all(torch.equal(both[r], both[0]) for r in range(world)), f"rank {rank}: the ranks' all-reduced results differ"
+    assert hccl.aclnnB200FusedAllReduceCount() == 4
 
     q = workloads.w8a8(M=16, K=256 * world, N=128, seed=79, with_pertoken=False, with_bias=False, scale_dtype=torch.float16)
     ks = slice(rank * 256, (rank + 1) * 256)
