@@ -35,21 +35,25 @@
 namespace qmm {
 namespace {
 
-constexpr int MX_M = 128, MX_N = 256, MX_BK = 128, MX_STAGES = 4;
+constexpr int MX_M = 128, MX_N = 256, MX_BK = 128;
 
+// MH = row halves of a tile: 1 = 128 rows (ring of 4 stages), 2 = 256 rows as two accumulators over one weight tile
+// (ring of 3 stages): the weight tile is then fetched once for twice the rows, which is what the kernel is short of.
+template <int MH>
 struct MxSmem {
-    static constexpr int X_BYTES = MX_M * MX_BK;            // 16 KB: 128 rows x 128 K bytes, 128-byte swizzle
+    static constexpr int STAGES = MH == 1 ? 4 : 3;
+    static constexpr int X_BYTES = MH * MX_M * MX_BK;       // 16 KB per 128 rows x 128 K bytes, 128-byte swizzle
     static constexpr int W_BYTES = MX_N * MX_BK;            // 32 KB: two boxes of 128 columns x 128 K rows
-    static constexpr int SFA_OFF = X_BYTES + W_BYTES;       // 512 B: scales of 128 rows x 4 K blocks
-    static constexpr int SFB_OFF = SFA_OFF + 512;           // 1024 B: scales of 256 columns x 4 K blocks
+    static constexpr int SFA_OFF = X_BYTES + W_BYTES;       // 512 B per 128 rows: their scales for 4 K blocks
+    static constexpr int SFB_OFF = SFA_OFF + MH * 512;      // 1024 B: scales of 256 columns x 4 K blocks
     static constexpr int STAGE_BYTES = (SFB_OFF + 1024 + 1023) / 1024 * 1024;
-    static constexpr int PAYLOAD = X_BYTES + W_BYTES + 512 + 1024;
-    static constexpr int BAR_OFF = MX_STAGES * STAGE_BYTES;
-    static constexpr int NUM_BARS = 2 * MX_STAGES + 4;
+    static constexpr int PAYLOAD = X_BYTES + W_BYTES + MH * 512 + 1024;
+    static constexpr int BAR_OFF = STAGES * STAGE_BYTES;
+    static constexpr int NUM_BARS = 2 * STAGES + 4;
     static constexpr int MISC_OFF = BAR_OFF + NUM_BARS * 8;
     static constexpr int TOTAL = MISC_OFF + 16 + 1024;
 };
-static_assert(MxSmem::TOTAL <= 232448, "shared memory budget of one CTA");
+static_assert(MxSmem<1>::TOTAL <= 232448 && MxSmem<2>::TOTAL <= 232448, "shared memory budget of one CTA");
 
 struct MxParams {
     void *out;
@@ -58,7 +62,7 @@ struct MxParams {
     int m_tiles, tiles, num_kb;     // tiles are numbered n_tile * m_tiles + m_tile; num_kb = K / 128
     int tile_n;                     // output columns per tile: 256, or less (a multiple of 16)
     int nacc;                       // accumulators in tensor memory, tile_n columns apart
-    const uint8_t *sfa;             // [m_tile][k chunk][512] scale groups of A
+    const uint8_t *sfa;             // [128-row group][k chunk][512] scale groups of A
     const uint8_t *sfb;             // [k chunk][n_tile][2][512] scale groups of B: columns tile_n * n_tile + 128 * h ...
     int n128e;                      // 2 * n_tiles
 };
@@ -102,9 +106,11 @@ __device__ __forceinline__ void mx_tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) 
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+template <int MH>
 __global__ void __launch_bounds__(320, 1)
 mx_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const MxParams p, const uint32_t idesc) {
-    using L = MxSmem;
+    using L = MxSmem<MH>;
+    constexpr int MX_STAGES = L::STAGES;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *gen_base = smem_raw + (base - smem_u32(smem_raw));
@@ -134,7 +140,7 @@ mx_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
 
     auto tile_geom = [&](int tile, int &n0, int &m0) {
         n0 = (tile / p.m_tiles) * p.tile_n;
-        m0 = (tile % p.m_tiles) * MX_M;
+        m0 = (tile % p.m_tiles) * (MH * MX_M);
     };
 
     if (warp == 0) {
@@ -144,17 +150,20 @@ mx_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
             for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x) {
                 int n0, m0;
                 tile_geom(tile, n0, m0);
-                const uint8_t *sfa = p.sfa + (size_t)(m0 / MX_M) * p.num_kb * 512;
+                const uint8_t *sfa = p.sfa + (size_t)(m0 / MX_M) * p.num_kb * 512;   // the tile's first 128-row group
                 const uint8_t *sfb = p.sfb + (size_t)(tile / p.m_tiles) * 1024;
                 for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
                     const int s = it % MX_STAGES;
                     if (it >= MX_STAGES && !mbar_wait(bar_empty(s), ((it / MX_STAGES) - 1) & 1, abort_flag, 0x401u)) { ok = false; break; }
                     mbar_expect_tx(bar_full(s), L::PAYLOAD);
                     const int k = kb * MX_BK;
-                    tma_load_2d(a_tile(s), &tm_a, bar_full(s), k, m0);
+#pragma unroll
+                    for (int h = 0; h < MH; ++h) {
+                        tma_load_2d(a_tile(s) + h * 16384, &tm_a, bar_full(s), k, m0 + h * MX_M);
+                        bulk_g2s(a_tile(s) + L::SFA_OFF + h * 512, sfa + ((size_t)h * p.num_kb + kb) * 512, 512, bar_full(s));
+                    }
                     tma_load_2d(b_tile(s), &tm_b, bar_full(s), n0, k);
                     tma_load_2d(b_tile(s) + 16384, &tm_b, bar_full(s), n0 + 128, k);
-                    bulk_g2s(a_tile(s) + L::SFA_OFF, sfa + (size_t)kb * 512, 512, bar_full(s));
                     bulk_g2s(a_tile(s) + L::SFB_OFF, sfb + (size_t)kb * p.n128e * 512, 1024, bar_full(s));
                 }
             }
@@ -174,17 +183,22 @@ mx_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
                     const int s = it % MX_STAGES;
                     if (!mbar_wait(bar_full(s), (it / MX_STAGES) & 1, abort_flag, 0x403u)) { ok = false; break; }
                     tc_fence_after();
-                    // this stage's scale groups: A (128 rows) -> 4 columns, B (256 columns) -> 8 columns
+                    // this stage's scale groups: A (128 rows) -> 4 columns (the second row half: the last 4 of the 16),
+                    // B (256 columns) -> 8 columns
                     const uint32_t sf = tmem_base + MX_SF_COL + (uint32_t)(it & 1) * 16u;
                     sf_copy(sf, a_tile(s) + L::SFA_OFF);
+                    if constexpr (MH == 2) sf_copy(sf + 12, a_tile(s) + L::SFA_OFF + 512);
                     sf_copy(sf + 4, a_tile(s) + L::SFB_OFF);
                     sf_copy(sf + 8, a_tile(s) + L::SFB_OFF + 512);
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk) {
-                        const uint64_t a_desc = smem_desc(a_tile(s) + kk * 32, 16, 1024);
                         const uint64_t b_desc = smem_desc(b_tile(s) + kk * 4096, 16384, 1024);
-                        mx_mma(d_tmem, a_desc, b_desc, idesc | ((uint32_t)kk << 4) | ((uint32_t)kk << 29), sf, sf + 4,
-                               (kb > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+                        for (int h = 0; h < MH; ++h) {     // both row halves multiply the same weight tile
+                            const uint64_t a_desc = smem_desc(a_tile(s) + h * 16384 + kk * 32, 16, 1024);
+                            mx_mma(d_tmem + (uint32_t)(h * p.tile_n), a_desc, b_desc, idesc | ((uint32_t)kk << 4) | ((uint32_t)kk << 29),
+                                   sf + (h ? 12u : 0u), sf + 4, (kb > 0 || kk > 0) ? 1u : 0u);
+                        }
                     }
                     tc_commit(bar_empty(s));
                 }
@@ -192,10 +206,12 @@ mx_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
             }
         }
     } else {
-        // epilogue: a warp's tensor-memory lane quarter = 32 rows; the two sets of four warps take 128 columns each
+        // epilogue: a warp's tensor-memory lane quarter = 32 rows.  One row half: the two sets of four warps take half of
+        // the columns each; two row halves: a set takes a row half (its accumulator) with all the columns
         const int eset = (warp - 2) >> 2, q = warp & 3;
-        const int half = p.tile_n >> 1;                     // columns per epilogue set (a multiple of 8)
-        const int row = q * 32 + lane, cb = eset * half;
+        const int half = MH == 1 ? p.tile_n >> 1 : p.tile_n;   // columns per epilogue set (a multiple of 8)
+        const int row = (MH == 2 ? eset * MX_M : 0) + q * 32 + lane, cb = MH == 1 ? eset * half : 0;
+        const uint32_t acc_off = MH == 2 ? (uint32_t)(eset * p.tile_n) : 0u;
         int ti = 0;
         for (int tile = blockIdx.x; tile < p.tiles; tile += gridDim.x, ++ti) {
             int n0, m0;
@@ -205,7 +221,7 @@ mx_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
             const int ab = ti % p.nacc;
             if (!mbar_wait(bar_acc_full(ab), (ti / p.nacc) & 1, abort_flag, 0x405u)) break;
             tc_fence_after();
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(ab * p.tile_n) + cb;
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(ab * p.tile_n) + acc_off + cb;
             const int esz = p.out_type == ET_F32 ? 4 : 2;
             uint8_t *orow = (uint8_t *)p.out + ((size_t)m * p.N + n0 + cb) * esz;
 #pragma unroll 1
@@ -306,7 +322,7 @@ inline uint64_t mx_up256(uint64_t x) { return (x + 255) / 256 * 256; }
 
 struct MxLayout {
     uint64_t a8, b8, sfa, sfb, total;
-    int m_tiles, n_tiles, n128e, kchunks, tile_n, nacc;
+    int m_tiles, n_tiles, n128e, kchunks, tile_n, nacc, mh, a_groups;
 };
 int mx_sm_count() {
     int dev = 0, sms = 148;
@@ -316,23 +332,33 @@ int mx_sm_count() {
 }
 MxLayout mx_layout(const MatmulArgs &p) {
     MxLayout l{};
-    l.m_tiles = (int)((p.M + MX_M - 1) / MX_M);
-    // 256 columns and one accumulator.  Narrower tiles leave room for a second accumulator, whose epilogue then overlaps
-    // the next tile's MMAs, but measured slower in proportion to their width (4096 x 8192 x 8192: 247 us at 256, 261 at
-    // 224, 320 at 240, 311 at 192 with two accumulators and 325 with one, 411 at 128): what bounds the kernel is the
-    // operand traffic from L2 into shared memory, (128 + tile_n) x K bytes per tile = 13.6 TB/s over all SMs at 256
-    // columns, not the tensor pipe's idle time during the epilogue.  B200_QMM_MX_TILE=<n> (a multiple of 16) and
-    // B200_QMM_MX_NACC=1 select the other forms.
-    l.tile_n = MX_N;
+    // Tile shape.  What bounds the kernel is the operand traffic from L2 into shared memory -- (rows + columns) x K bytes per
+    // tile, about 100 GB/s per SM -- not the tensor pipe (4096 x 8192 x 8192, one 128-row accumulator: 247 us at 256 columns,
+    // 261 at 224, 311 at 192 even with a second accumulator hiding the epilogue, 411 at 128).  So with more than 256 rows a
+    // tile is 256 rows x 224 columns: two accumulators (2 x 224 tensor-memory columns + the scales' 32) over ONE weight tile,
+    // a third less traffic per output (4096 x 8192 x 8192: 249 -> 225 us; 245 us at 240 columns, 255 at 192), where that
+    // does not leave SMs without a tile.  Otherwise 128 x 256 with one accumulator.
+    // B200_QMM_MX_ROWS=128|256, B200_QMM_MX_TILE=<columns, a multiple of 16>, B200_QMM_MX_NACC=1 select other forms.
+    {
+        // rounds of one tile per SM x the measured time of a K block in either form (0.55 us at 128 x 256, 0.86 us at 256 x 224)
+        const long long sms = mx_sm_count();
+        const long long t1 = ((p.M + MX_M - 1) / MX_M) * ((p.N + MX_N - 1) / MX_N), t2 = ((p.M + 2 * MX_M - 1) / (2 * MX_M)) * ((p.N + 223) / 224);
+        l.mh = p.M > 2 * MX_M && (double)((t2 + sms - 1) / sms) * 0.86 < (double)((t1 + sms - 1) / sms) * 0.55 ? 2 : 1;
+    }
+    if (const char *e = getenv("B200_QMM_MX_ROWS")) { const int v = atoi(e); if (v == 128) l.mh = 1; else if (v == 256) l.mh = 2; }
+    l.tile_n = l.mh == 2 ? 224 : MX_N;
     if (const char *e = getenv("B200_QMM_MX_TILE")) { const int v = atoi(e); if (v >= 32 && v <= MX_N && v % 16 == 0) l.tile_n = v; }
-    l.nacc = 2 * l.tile_n <= (int)MX_SF_COL ? 2 : 1;
+    if (l.mh == 2 && 2 * l.tile_n > (int)MX_SF_COL) l.tile_n = 240;      // two row halves need two accumulators in front of the scales
+    l.nacc = (l.mh == 1 && 2 * l.tile_n <= (int)MX_SF_COL) ? 2 : 1;
     if (const char *e = getenv("B200_QMM_MX_NACC")) { if (atoi(e) == 1) l.nacc = 1; }
+    l.m_tiles = (int)((p.M + l.mh * MX_M - 1) / (l.mh * MX_M));
+    l.a_groups = l.m_tiles * l.mh;                                      // 128-row scale groups of A
     l.n_tiles = (int)((p.N + l.tile_n - 1) / l.tile_n);
     l.n128e = 2 * l.n_tiles;
     l.kchunks = (int)(p.K / MX_BK);
     l.a8 = p.a_type == ET_E2M1 ? mx_up256((uint64_t)p.M * p.K) : 0;
     l.b8 = (p.b_type == ET_E2M1 && !p.b_nz) ? mx_up256((uint64_t)p.K * p.N) : 0;   // b_nz: widened once at load time
-    l.sfa = mx_up256((uint64_t)l.m_tiles * l.kchunks * 512);
+    l.sfa = mx_up256((uint64_t)l.a_groups * l.kchunks * 512);
     l.sfb = mx_up256((uint64_t)l.kchunks * l.n128e * 512);
     l.total = l.a8 + l.b8 + l.sfa + l.sfb;
     return l;
@@ -377,7 +403,7 @@ cudaError_t launch_mx_native(const MatmulArgs &p, cudaStream_t s) {
     }
     const int kblocks = (int)(p.K / 32);
     {
-        mx_group_scales_kernel<<<(unsigned)(l.m_tiles * l.kchunks), 512, 0, s>>>(p.a_scale, sfa, (int)p.M, kblocks, 1, l.m_tiles, l.kchunks, 128);
+        mx_group_scales_kernel<<<(unsigned)(l.a_groups * l.kchunks), 512, 0, s>>>(p.a_scale, sfa, (int)p.M, kblocks, 1, l.a_groups, l.kchunks, 128);
         mx_group_scales_kernel<<<(unsigned)(l.kchunks * l.n128e), 512, 0, s>>>(p.b_scale, sfb, (int)p.N, kblocks, 0, l.n128e, l.kchunks, l.tile_n);
         count_launch(2);
     }
@@ -402,13 +428,15 @@ cudaError_t launch_mx_native(const MatmulArgs &p, cudaStream_t s) {
     int dev = 0;
     cudaGetDevice(&dev);
     if (!attr_set[dev & 63]) {
-        e = cudaFuncSetAttribute(mx_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, MxSmem::TOTAL);
+        e = cudaFuncSetAttribute(mx_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, MxSmem<1>::TOTAL);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(mx_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, MxSmem<2>::TOTAL);
         if (e != cudaSuccess) return e;
         attr_set[dev & 63] = true;
     }
     const int sms = mx_sm_count();
     const int P = mp.tiles < sms ? mp.tiles : sms;
-    mx_tc_kernel<<<P, 320, MxSmem::TOTAL, s>>>(ta, tb, mp, idesc);
+    if (l.mh == 2) mx_tc_kernel<2><<<P, 320, MxSmem<2>::TOTAL, s>>>(ta, tb, mp, idesc);
+    else mx_tc_kernel<1><<<P, 320, MxSmem<1>::TOTAL, s>>>(ta, tb, mp, idesc);
     count_launch();
     return cudaGetLastError();
 }

@@ -549,15 +549,22 @@ def test_mx_native_tile_widths_agree(pkg, oracle, workloads, dev):
     d = workloads.mx(M=M, K=K, N=N, a_fp4=False, b_fp4=True, seed=5470)
     outs = {}
     for width in ("240", "192", "256"):
-        with env_set("B200_QMM_MX_TILE", width):
+        with env_set("B200_QMM_MX_TILE", width), env_set("B200_QMM_MX_ROWS", "128"):
             outs[width] = run_mx(pkg, d, dev, torch.float32, "aclnnMatmulMxFp8")
     torch.cuda.synchronize()
     assert torch.equal(outs["240"], outs["256"]) and torch.equal(outs["192"], outs["256"])
+    # 256-row tiles (two accumulators over one weight tile, the default above 256 rows), at two widths
+    for width in ("224", "160"):
+        with env_set("B200_QMM_MX_TILE", width), env_set("B200_QMM_MX_ROWS", "256"):
+            outs["rows256_" + width] = run_mx(pkg, d, dev, torch.float32, "aclnnMatmulMxFp8")
+    torch.cuda.synchronize()
+    assert torch.equal(outs["rows256_224"], outs["256"]) and torch.equal(outs["rows256_160"], outs["256"])
+    assert torch.equal(run_mx(pkg, d, dev, torch.float32, "aclnnMatmulMxFp8"), outs["256"])      # the default choice
     rows = np.random.default_rng(5471).choice(M, size=96, replace=False)
     assert_close(to_np(outs["240"])[rows], ref_mx(oracle, d)[rows], "MX 1700x256x8000, 240-column tiles")
     small = workloads.mx(M=130, K=128, N=288, a_fp4=True, b_fp4=False, seed=5472)    # two tiles of 240: 240 + 48 columns
-    for width in ("240", "256"):
-        with env_set("B200_QMM_MX_TILE", width):
+    for width, rows in (("240", "128"), ("256", "256")):     # (the 256-row form takes 240 columns where 256 are asked for)
+        with env_set("B200_QMM_MX_TILE", width), env_set("B200_QMM_MX_ROWS", rows):
             outs[width] = run_mx(pkg, small, dev, torch.bfloat16, "aclnnMatmulMxFp4")
     torch.cuda.synchronize()
     assert torch.equal(outs["240"], outs["256"])
