@@ -95,8 +95,11 @@ def test_hccl_library_exports_allreduce_matmuls(pkg):
     names = set(re.findall(r"^B200_ACLNN_QMM_ALLREDUCE\((\w+)\)", hdr, re.M)) | {"aclnnWeightQuantMatmulAllReduce",
                                                                                      "aclnnQuantMatmulAllReduceAddRmsNorm"}
     assert len(names) == 6
+    names.add("aclnnB200WeightQuantMatmulAllGather")
     for n in names:
         assert hasattr(lib, n) and hasattr(lib, n + "GetWorkspaceSize"), n
+    for n in ("aclnnB200FusedGatherCount", "aclnnB200FusedAllReduceCount", "HcclB200P2pStatus", "HcclB200TestReceiverTimeout"):
+        assert hasattr(lib, n), n
 
 
 def test_wqbmm_phase1_validation(pkg):
@@ -201,6 +204,37 @@ def test_meta_objects_round_trip(pkg):
     assert lib.aclGetViewShape(None, ctypes.byref(dims), ctypes.byref(num)) == 161001
     lib.aclDataTypeSize.restype = ctypes.c_size_t
     assert lib.aclDataTypeSize(pkg.ACL_BF16) == 2 and lib.aclDataTypeSize(pkg.ACL_INT4) == 1
+
+
+def test_gathering_matmul_phase1(pkg):
+    """Phase 1 of the column-shard matmul with the fused gather, without a communicator (one rank: gathered is [1][M][N]):
+    argument checks, a workspace that serves both forms of the decode kernel, and a plan that can be abandoned."""
+    if not os.path.exists(pkg.HCCL_PATH):
+        pytest.skip("libhccl.so not built (nccl.h absent)")
+    try:
+        hccl = ctypes.CDLL(pkg.HCCL_PATH)
+    except OSError as e:
+        pytest.skip(f"libhccl.so not loadable here: {e}")
+    lib = pkg.load()
+    M, K, N = 2, 1024, 512
+    x, w = FakeTensor(pkg, (M, K), pkg.ACL_BF16), FakeTensor(pkg, (K, N), pkg.ACL_INT4)
+    sc, g = FakeTensor(pkg, (K // 128, N), pkg.ACL_BF16), FakeTensor(pkg, (1, M, N), pkg.ACL_BF16)
+    fn = hccl.aclnnB200WeightQuantMatmulAllGatherGetWorkspaceSize
+
+    def plan(xt, wt, st, gt):
+        ws, ex = ctypes.c_uint64(0), ctypes.c_void_p(0)
+        r = fn(ctypes.c_void_p(xt.h) if xt else None, ctypes.c_void_p(wt.h), ctypes.c_void_p(st.h), None, None, ctypes.c_int64(128), None,
+               ctypes.c_void_p(gt.h) if gt else None, ctypes.byref(ws), ctypes.byref(ex))
+        return r, ws.value, ex
+    r, need, ex = plan(x, w, sc, g)
+    assert r == 0 and ex.value and need > 0
+    plain = phase1(pkg, "aclnnWeightQuantBatchMatmulV2Ex", x, w, sc, None, None, ctypes.c_int64(128), FakeTensor(pkg, (M, N), pkg.ACL_BF16))
+    assert plain[0] == 0 and need >= plain[1]
+    assert lib.aclDestroyAclOpExecutor(ex) == 0
+    assert plan(None, w, sc, g)[0] == 161001 and plan(x, w, sc, None)[0] == 161001
+    assert plan(x, w, sc, FakeTensor(pkg, (M, N), pkg.ACL_BF16))[0] == 161002            # gathered must be [ranks][M][N/ranks]
+    assert plan(x, w, sc, FakeTensor(pkg, (2, M, N), pkg.ACL_BF16))[0] == 161002         # two slots, one rank
+    assert plan(x, w, sc, FakeTensor(pkg, (1, M, N), pkg.ACL_FLOAT))[0] == 161002        # 16-bit outputs only
 
 
 def test_abandoned_collective_plan_is_released(pkg):
