@@ -425,4 +425,12 @@ cudaError_t launch_expand(const MatmulArgs &p, cudaStream_t s) {
     return launch_dense_tc(d, s);
 }
 
+cudaError_t launch_rows_bf16_to_scaled_f16(const void *x, void *xh, float *rowscale, int64_t M, int64_t K, cudaStream_t s) {
+    if (M <= 0 || K <= 0 || (K & 7)) return cudaErrorInvalidValue;
+    if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(xh) & 15)) return cudaErrorMisalignedAddress;
+    rows_bf16_to_scaled_f16_kernel<<<(unsigned)M, 256, 0, s>>>((const uint16_t *)x, (uint16_t *)xh, rowscale, (int)K);
+    count_launch();
+    return cudaGetLastError();
+}
+
 }  // namespace qmm

@@ -130,6 +130,8 @@ struct DecodeGather {
 };
 void wq_mma_set_gather(const DecodeGather *g);
 bool wq_mma_gather_consumed();
+// bf16 activations [M,K] -> fp16 with a power-of-two scale per row (xh = x / rowscale exactly; dequant.cu).
+cudaError_t launch_rows_bf16_to_scaled_f16(const void *x, void *xh, float *rowscale, int64_t M, int64_t K, cudaStream_t s);
 void tc_reserve_sms(int n);   // the calling thread's dense-kernel plans leave n SMs free (0 = none)
 
 // Host-side tally of kernels this library has launched (diagnostics for benchmarks).

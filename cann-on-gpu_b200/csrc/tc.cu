@@ -723,9 +723,12 @@ cudaError_t dispatch_mt(int mt, const CUtensorMap &tx, const CUtensorMap &tw, co
 // the switch point.
 int wq_dense_threshold(const MatmulArgs &p) {
     if (const char *e = getenv("B200_QMM_WQ_DENSE_M")) return atoi(e);
-    // Group-wise int4 under bf16 activations keeps the exact per-group fold in the streaming kernel (its
-    // pre-scaled mode would round the weights to bf16), which falls behind expansion above 64 rows.
-    if (p.a_type == ET_BF16 && p.b_type == ET_I4 && p.group < p.K) return 64;
+    // Group-wise int4 under bf16 activations with the fp16-product form switched off keeps the exact per-group fold in the
+    // streaming kernel (its pre-scaled mode would round the weights to bf16), which falls behind expansion above 64 rows.
+    if (p.a_type == ET_BF16 && p.b_type == ET_I4 && p.group < p.K) {
+        const char *v = getenv("B200_QMM_WQ_BF16_VIA_F16");
+        if (v && atoi(v) == 0) return 64;
+    }
     return 128;
 }
 bool is_wq(const MatmulArgs &p) { return p.epilogue == EPI_PLAIN && p.scale && !p.a_scale && !p.b_scale; }

@@ -54,6 +54,8 @@ __device__ unsigned int g_dbg_flags;
 #endif
 
 struct WqParams {
+    const float *row_scale;  // [M] or null: every output row is multiplied by its value (activations that came pre-scaled)
+    int cv_bf16;             // the pre-scaled mode's scale and offset rows are bf16 although the product runs in fp16
     void *out;
     float *slots;            // [tiles + P][MT][128] fp32 partial tiles
     const void *scale, *offset, *bias;
@@ -489,8 +491,12 @@ wq_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
                     if (n_ok) {
                         const float bv = p.bias ? load_as_float(p.bias, p.sc_type, n) : 0.f;
 #pragma unroll
-                        for (int c = 0; c < CT; ++c)
-                            if (m0 + cb + c < p.M) store_from_float(p.out, p.out_type, (size_t)(m0 + cb + c) * p.N + n, tot[c] + bv);
+                        for (int c = 0; c < CT; ++c) {
+                            if (m0 + cb + c < p.M) {
+                                const float rs = p.row_scale ? __ldg(p.row_scale + m0 + cb + c) : 1.f;   // the same address in every lane
+                                store_from_float(p.out, p.out_type, (size_t)(m0 + cb + c) * p.N + n, fmaf(tot[c], rs, bv));
+                            }
+                        }
                     }
                 } else {
                     float *dst = p.slots + ((size_t)(tile + cta) * MT + cb) * TILE_N + col;
@@ -561,8 +567,19 @@ wq_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
                         cur_g = g; cur_tile = tile;
                         s2[0] = __byte_perm(sraw.x, sraw.z, 0x5410); s2[1] = __byte_perm(sraw.x, sraw.z, 0x7632);
                         s2[2] = __byte_perm(sraw.y, sraw.w, 0x5410); s2[3] = __byte_perm(sraw.y, sraw.w, 0x7632);
-                        const uint32_t o2[4] = {__byte_perm(oraw.x, oraw.z, 0x5410), __byte_perm(oraw.x, oraw.z, 0x7632),
-                                                __byte_perm(oraw.y, oraw.w, 0x5410), __byte_perm(oraw.y, oraw.w, 0x7632)};
+                        uint32_t o2[4] = {__byte_perm(oraw.x, oraw.z, 0x5410), __byte_perm(oraw.x, oraw.z, 0x7632),
+                                          __byte_perm(oraw.y, oraw.w, 0x5410), __byte_perm(oraw.y, oraw.w, 0x7632)};
+                        if constexpr (!BF16) {
+                            if (p.cv_bf16) {   // bf16 tables under an fp16 product: every bf16 value in fp16's range is exact in fp16
+#pragma unroll
+                                for (int h = 0; h < 4; ++h) {
+                                    const __half2 sh = __floats2half2_rn(__uint_as_float(s2[h] << 16), __uint_as_float(s2[h] & 0xFFFF0000u));
+                                    const __half2 oh = __floats2half2_rn(__uint_as_float(o2[h] << 16), __uint_as_float(o2[h] & 0xFFFF0000u));
+                                    s2[h] = *reinterpret_cast<const uint32_t *>(&sh);
+                                    o2[h] = *reinterpret_cast<const uint32_t *>(&oh);
+                                }
+                            }
+                        }
 #pragma unroll
                         for (int h = 0; h < 4; ++h) {
                             // -(offset * scale), rounded once (the product of two 16-bit floats is exact in fp32)
@@ -728,6 +745,7 @@ __global__ void wq_finalize_kernel(WqParams p, int P) {
     float v = 0.f;
     for (int c = c_first; c <= c_last; ++c)
         v += p.slots[((size_t)(tile + c) * MT + (m % MT)) * TILE_N + (n % TILE_N)];
+    if (p.row_scale) v *= p.row_scale[m];
     if (p.bias) v += load_as_float(p.bias, p.sc_type, n);
     store_from_float(p.out, p.out_type, i, v);
 }
@@ -752,7 +770,8 @@ struct WqPlan {
     bool pre;                // converters apply scale and offset (group-wise int4, more than 16 rows)
     int cv_gsb;
     long long total_q;
-    uint64_t xtab_bytes, slot_bytes;
+    bool via;                // bf16 problem on the fp16 product: activations converted per call, rows scaled back in the epilogue
+    uint64_t xtab_bytes, slot_bytes, xh_bytes, rs_bytes;
 };
 
 WqPlan wq_make_plan(const MatmulArgs &p) {
@@ -773,11 +792,17 @@ WqPlan wq_make_plan(const MatmulArgs &p) {
     if (pl.grouped && p.b_type == ET_I4 && p.M > 32) {
         // fp16 only by default: rounding q * scale to bf16's 8 significant bits puts the bf16 output 2.1e-3
         // (mean) from the exact product, over the 2e-3 this family is held to; in fp16 it costs 2e-4.
+        // bf16 problems therefore run the pre-scaled mode on the fp16 product: the activations are converted to fp16 with a
+        // power-of-two scale per row (exact), the bf16 scale and offset rows are widened to fp16 by the converters, the
+        // epilogue multiplies the row scale back (B200_QMM_WQ_BF16_VIA_F16=0: the exact fold instead).
         const char *e = getenv("B200_QMM_WQ_PRESCALE");
-        pl.pre = e ? atoi(e) != 0 : p.a_type == ET_F16;
+        const char *v = getenv("B200_QMM_WQ_BF16_VIA_F16");
+        pl.via = !e && p.a_type == ET_BF16 && !(v && atoi(v) == 0) && p.K % 8 == 0;
+        pl.pre = e ? atoi(e) != 0 : (p.a_type == ET_F16 || pl.via);
     }
     pl.cv_gsb = pl.grouped ? (int)(p.group / SBK) : 1;
     if (pl.pre && (long long)pl.tiles * pl.num_sb >= (1ll << 31)) pl.pre = false;
+    if (!pl.pre) pl.via = false;
     if (pl.pre && p.M > 64 && (long long)pl.n_tiles * pl.num_sb >= 16LL * sm_count()) {
         // 128-row tiles: the weights are converted once for up to 128 rows (8192 x 28672 at M = 128: 165 us
         // with two 64-row tiles, 132 us with one of 128).  Its MMA ring is only two slots deep, which costs
@@ -798,7 +823,9 @@ WqPlan wq_make_plan(const MatmulArgs &p) {
     pl.P = (int)(pl.total_q < sms ? pl.total_q : sms);
     pl.entries = pl.grouped ? pl.qpt : pl.num_sb;
     pl.xtab_bytes = (p.offset && !pl.pre) ? align_up_u64((uint64_t)(pl.entries + 1) * p.M * sizeof(float), 256) : 0;
-    pl.slot_bytes = (uint64_t)(pl.tiles + pl.P) * pl.mt * TILE_N * sizeof(float);
+    pl.slot_bytes = align_up_u64((uint64_t)(pl.tiles + pl.P) * pl.mt * TILE_N * sizeof(float), 256);
+    pl.xh_bytes = pl.via ? align_up_u64((uint64_t)p.M * p.K * 2, 256) : 0;
+    pl.rs_bytes = pl.via ? align_up_u64((uint64_t)p.M * sizeof(float), 256) : 0;
     return pl;
 }
 
@@ -860,20 +887,33 @@ bool wq_tc_supported(const MatmulArgs &p) {
 
 uint64_t wq_tc_workspace_bytes(const MatmulArgs &p) {
     WqPlan pl = wq_make_plan(p);
-    return pl.xtab_bytes + pl.slot_bytes;
+    return pl.xtab_bytes + pl.slot_bytes + pl.xh_bytes + pl.rs_bytes;
 }
 
 cudaError_t launch_wq_tc(const MatmulArgs &p, cudaStream_t s) {
     const WqPlan pl = wq_make_plan(p);
-    if (p.workspace_bytes < pl.xtab_bytes + pl.slot_bytes || !p.workspace) return cudaErrorInvalidValue;
+    if (p.workspace_bytes < pl.xtab_bytes + pl.slot_bytes + pl.xh_bytes + pl.rs_bytes || !p.workspace) return cudaErrorInvalidValue;
     if ((reinterpret_cast<uintptr_t>(p.a) & 15) || (reinterpret_cast<uintptr_t>(p.b) & 15)) return cudaErrorMisalignedAddress;
     // the converters of the pre-scaled mode read scale and offset rows with 16-byte loads
     if (pl.pre && ((reinterpret_cast<uintptr_t>(p.scale) & 15) || (reinterpret_cast<uintptr_t>(p.offset) & 15)))
         return cudaErrorMisalignedAddress;
-    const bool q4 = p.b_type == ET_I4, bf = p.a_type == ET_BF16;
+    const bool q4 = p.b_type == ET_I4, bf = p.a_type == ET_BF16 && !pl.via;   // via: the product runs in fp16
+
+    // bf16 activations of the fp16-product form: converted once per call, with a power-of-two scale per row
+    char *ws0 = (char *)p.workspace;
+    const void *act = p.a;
+    const float *row_scale = nullptr;
+    if (pl.via) {
+        void *xh = ws0 + pl.xtab_bytes + pl.slot_bytes;
+        float *rs = (float *)(ws0 + pl.xtab_bytes + pl.slot_bytes + pl.xh_bytes);
+        const cudaError_t ce = launch_rows_bf16_to_scaled_f16(p.a, xh, rs, p.M, p.K, s);
+        if (ce != cudaSuccess) return ce;
+        act = xh;
+        row_scale = rs;
+    }
 
     CUtensorMap tx, tw;
-    bool ok = make_map(&tx, p.a, bf ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, p.K, p.M, p.K * 2, 64,
+    bool ok = make_map(&tx, act, bf ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, p.K, p.M, p.K * 2, 64,
                        pl.mt, CU_TENSOR_MAP_SWIZZLE_128B);
     const CUtensorMapL2promotion promo = CU_TENSOR_MAP_L2_PROMOTION_L2_256B;   // none / 128 B measured the same here
     if (q4) ok = ok && make_map(&tw, p.b, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.N / 2, p.K, p.N / 2, 64, SBK, CU_TENSOR_MAP_SWIZZLE_64B, promo);
@@ -891,6 +931,8 @@ cudaError_t launch_wq_tc(const MatmulArgs &p, cudaStream_t s) {
     wp.M = (int)p.M; wp.N = (int)p.N; wp.K = (int)p.K;
     wp.m_tiles = pl.m_tiles; wp.num_sb = pl.num_sb; wp.sbq = pl.sbq; wp.qpt = pl.qpt; wp.total_q = pl.total_q;
     wp.grouped = pl.grouped;
+    wp.row_scale = row_scale;
+    wp.cv_bf16 = pl.via ? 1 : 0;
 
     cudaError_t e;
     if (p.offset && !pl.pre) {

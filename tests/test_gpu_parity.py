@@ -788,7 +788,8 @@ def test_bench_call_w4a16_llama_gate_up_m1(pkg, oracle, workloads, dev):
     check_wq_sampled(oracle, out.cpu(), d, "bench call W4A16 g128 M=1 8192x28672", key="bench", rows=[0])
 
 
-@pytest.mark.parametrize("which,M", [(w, m) for w in ("gate_up", "down") for m in (1, 32, 512, 4096)])
+# 96 rows: beyond BASELINE's row counts, the streaming kernel's pre-scaled mode on the fp16 product
+@pytest.mark.parametrize("which,M", [(w, m) for w in ("gate_up", "down") for m in (1, 32, 96, 512, 4096)])
 def test_config4_llama70b_full_size(pkg, oracle, workloads, dev, which, M):
     """Llama-70B-shaped W4A16 group-128 projections (K=8192 N=28672 and K=28672 N=8192), bf16, at every row
     count of the configuration: all rows on eight whole 128-column blocks (first, last, seeded others), and
