@@ -43,7 +43,7 @@ import __graft_entry__ as ge  # noqa: E402
 M, K, N, GROUP = 1, 8192, 28672, 128
 RING_BYTES = 352_000_000  # a ring of weight sets holds at least this much: > 2 x 126 MB of L2
 WEIGHT_BYTES = K * N // 2
-CALLS_PER_STEP = 75       # about this many calls per step (a whole number of passes over the ring)
+CALLS_PER_STEP = 108      # about this many calls per step (a whole number of passes over the ring): 20 steps are over 50 ms
 # Algorithmic bytes of one call: packed weights + group scales + activations + output.
 ALGO_BYTES = WEIGHT_BYTES + (K // GROUP) * N * 2 + M * K * 2 + M * N * 2
 WORKLOAD = ("W4A16 group-128 weight-only matmul, Llama-70B gate/up shape: x bf16 [1,8192] @ int4 [8192,28672], "
@@ -632,7 +632,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--ring", type=int, default=0, help="weight sets in the ring (default: enough for 2 x L2)")
-    ap.add_argument("--passes", type=int, default=0, help="passes over the ring per step (default: about 75 calls per step)")
+    ap.add_argument("--passes", type=int, default=0, help="passes over the ring per step (default: about 108 calls per step)")
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-ref-cuda", action="store_true", help="skip the reference-CUDA-backend column of the sweep")
     ap.add_argument("--sweep-only", default=None, help="run only the sweep cases whose name contains this text, and nothing else; "
