@@ -9,7 +9,10 @@
 // HBM-bound: the reference reads x twice (maximum, then quantise); here a row of up to 16384 elements
 // stays in registers between the two phases, so x is read once: algorithmic bytes per row
 // D * (sizeof(x) + 1) + 4.  One CTA per row, 16-byte loads and 8/16-byte stores.
-#include "device_utils.cuh"
+#include <cstdlib>
+
+#include "kernels.h"
+#include "tc_common.cuh"
 
 namespace qmm {
 namespace {
@@ -209,6 +212,131 @@ __global__ void __launch_bounds__(THREADS) swigluquant_row_kernel(const uint16_t
     }
 }
 
+// Many long rows: persistent CTAs that stage their rows through a ring of shared-memory slots.  One thread keeps
+// SGQ_STAGES rows in flight with bulk copies (one copy per row: a and b halves are contiguous), so the loads of the
+// following rows overlap the arithmetic of this one (expf and an IEEE division per element: the issue slots are busy
+// longer than the row's bytes occupy HBM) instead of alternating with it as in the one-row-per-CTA kernel
+// ([2048, 28672] bf16: 57.5 -> 46.3 us).  The block
+// size is chosen so that CHUNKS * blockDim.x * 8 covers D with no idle lanes where D allows (14336 -> 896 threads).
+// A slot is refilled right after the row-maximum barrier, when every thread has its part of the row in registers.
+__device__ __forceinline__ void bulk_row_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+template <bool BF16, int CHUNKS, int SGQ_STAGES, bool HAS_DQ>
+__global__ void __launch_bounds__(1024) swigluquant_staged_kernel(const uint16_t *x, const float *dq, int8_t *q, float *scale_out,
+                                                                  int64_t rows, int64_t D) {
+    extern __shared__ __align__(128) uint8_t ring[];
+    __shared__ __align__(8) uint64_t full[SGQ_STAGES];
+    __shared__ float sh[2][32];
+    __shared__ int abort_flag;
+    const int tid = threadIdx.x, T = blockDim.x, nwarps = T >> 5;
+    const uint32_t row_bytes = (uint32_t)(D * 4);       // 2 D elements of 2 bytes
+    const uint32_t ring0 = smem_u32(ring);
+    if (tid == 0) {
+#pragma unroll
+        for (int s = 0; s < SGQ_STAGES; ++s) mbar_init(smem_u32(&full[s]), 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (tid == 0) {
+#pragma unroll
+        for (int s = 0; s < SGQ_STAGES; ++s) {
+            const int64_t r = blockIdx.x + (int64_t)s * gridDim.x;
+            if (r < rows) {
+                mbar_expect_tx(smem_u32(&full[s]), row_bytes);
+                bulk_row_g2s(ring0 + s * row_bytes, x + r * 2 * D, row_bytes, smem_u32(&full[s]));
+            }
+        }
+    }
+    int slot = 0;
+    uint32_t parity = 0, it = 0;
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x, ++it) {
+        const bool ok = mbar_wait(smem_u32(&full[slot]), parity, &abort_flag, 0x510u);
+        const float scl = HAS_DQ ? __ldg(dq + row) : 1.f;
+        const uint8_t *sa = ring + (size_t)slot * row_bytes;
+        float g[CHUNKS][8];
+        float amax = 0.f;
+#pragma unroll
+        for (int c = 0; c < CHUNKS; ++c) {
+            const int64_t d = ((int64_t)c * T + tid) * DQ_VEC;
+            uint4 va = make_uint4(0, 0, 0, 0), vb = make_uint4(0, 0, 0, 0);
+            if (ok && d < D) {
+                va = *reinterpret_cast<const uint4 *>(sa + d * 2);
+                vb = *reinterpret_cast<const uint4 *>(sa + (D + d) * 2);
+            }
+            float fa[8], fb[8];
+            unpack8<BF16>(va, fa);
+            unpack8<BF16>(vb, fb);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                g[c][i] = HAS_DQ ? swiglu_of(fa[i] * scl, fb[i] * scl) : swiglu_of(fa[i], fb[i]);
+                amax = fmaxf(amax, fabsf(g[c][i]));
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        float *shp = sh[it & 1];
+        if ((tid & 31) == 0) shp[tid >> 5] = amax;
+        // the barrier also says that the slot has been read by everyone, and carries a wait that gave up to all threads
+        if (__syncthreads_or(!ok)) break;
+        if (tid == 0) {
+            const int64_t nr = row + (int64_t)SGQ_STAGES * gridDim.x;
+            if (nr < rows) {
+                fence_proxy_async();
+                mbar_expect_tx(smem_u32(&full[slot]), row_bytes);
+                bulk_row_g2s(ring0 + slot * row_bytes, x + nr * 2 * D, row_bytes, smem_u32(&full[slot]));
+            }
+        }
+        float m = shp[(tid & 31) < nwarps ? (tid & 31) : 0];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        const float scale = m > 0.f ? m / 127.f : 1.f;
+        if (tid == 0) scale_out[row] = scale;
+        const float inv = 1.f / scale;
+        const int64_t ob = row * D;
+#pragma unroll
+        for (int c = 0; c < CHUNKS; ++c) {
+            const int64_t d = ((int64_t)c * T + tid) * DQ_VEC;
+            if (d >= D) continue;
+            uint32_t o[2] = {0, 0};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o[i >> 2] |= (uint32_t)(uint8_t)quant_i8_sym(g[c][i] * inv) << (8 * (i & 3));
+            *reinterpret_cast<uint2 *>(q + ob + d) = make_uint2(o[0], o[1]);
+        }
+        if (++slot == SGQ_STAGES) { slot = 0; parity ^= 1u; }
+    }
+}
+
+int dq_sm_count() {
+    static int sms[64] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    if (!sms[dev]) {
+        int n = 0;
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        sms[dev] = n > 0 ? n : 1;
+    }
+    return sms[dev];
+}
+
+template <bool BF16, int CHUNKS, int STAGES, bool HAS_DQ>
+cudaError_t launch_staged(const uint16_t *x, const float *dq, int8_t *q, float *scale_out, int64_t rows, int64_t D, int threads, cudaStream_t s) {
+    auto kernel = swigluquant_staged_kernel<BF16, CHUNKS, STAGES, HAS_DQ>;
+    const size_t smem = (size_t)STAGES * D * 4;
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err != cudaSuccess) return err;
+    int per_sm = 0;
+    err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem);
+    if (err != cudaSuccess) return err;
+    if (per_sm < 1) return cudaErrorLaunchOutOfResources;
+    const int64_t grid = std::min<int64_t>(rows, (int64_t)dq_sm_count() * per_sm);
+    kernel<<<(unsigned)grid, threads, smem, s>>>(x, dq, q, scale_out, rows, D);
+    return cudaGetLastError();
+}
+
 // Any type, any D: g is evaluated twice, the second read of the row hits L2.
 __global__ void __launch_bounds__(DQ_THREADS) swigluquant_generic_kernel(const void *x, int x_type, const float *dq, int8_t *q, float *scale_out, int64_t D) {
     __shared__ float sh[DQ_THREADS / 32];
@@ -239,6 +367,25 @@ cudaError_t launch_swiglu_quant(const void *x, int x_type, const float *dq, int8
     const bool bf = x_type == ET_BF16;
 #define SGQ(C, T) do { if (bf) swigluquant_row_kernel<true, C, T><<<g, T, 0, s>>>(x16, dq, q, scale_out, D); \
                        else swigluquant_row_kernel<false, C, T><<<g, T, 0, s>>>(x16, dq, q, scale_out, D); } while (0)
+    // rows long enough that the arithmetic matters, and several rows per SM: the staged persistent form
+    static const bool staged_on = [] { const char *e = std::getenv("B200_QMM_SGQ_STAGED"); return !e || std::atoi(e) != 0; }();
+    if (vec && staged_on && D >= 1024 && rows >= 2 * (int64_t)dq_sm_count()) {
+        // one chunk of 8 elements per thread for rows of up to 8192 elements, two above; three ring slots.  (Four chunks with
+        // one or two slots, two CTAs per SM, measured the same: the kernel is bound by instruction issue, 43 instructions per
+        // element of which 4 on the quarter-rate pipe, not by how the copies overlap.)
+        const int64_t vectors = D / DQ_VEC;
+        const int chunks = vectors <= 1024 ? 1 : 2;
+        const int threads = (int)(((vectors + chunks - 1) / chunks + 31) / 32 * 32);
+        cudaError_t err;
+#define SGS(B, C) (dq ? launch_staged<B, C, 3, true>(x16, dq, q, scale_out, rows, D, threads, s) \
+                      : launch_staged<B, C, 3, false>(x16, dq, q, scale_out, rows, D, threads, s))
+        if (chunks == 1) err = bf ? SGS(true, 1) : SGS(false, 1);
+        else err = bf ? SGS(true, 2) : SGS(false, 2);
+#undef SGS
+        if (err != cudaSuccess) return err;
+        count_launch();
+        return cudaSuccess;
+    }
     if (!vec) swigluquant_generic_kernel<<<g, DQ_THREADS, 0, s>>>(x, x_type, dq, q, scale_out, D);
     else if (D <= per) SGQ(1, 256);
     else if (D <= per * 2) SGQ(2, 256);
@@ -299,6 +446,16 @@ cudaError_t launch_dynamic_quant(const void *x, int x_type, int8_t *q, float *sc
     }
     count_launch();
     return cudaGetLastError();
+}
+
+unsigned int dynquant_device_status() {
+    unsigned int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(v)) != cudaSuccess) return 0xFFFFFFFFu;
+    return v;
+}
+void dynquant_device_status_reset() {
+    const unsigned int z = 0;
+    cudaMemcpyToSymbol(g_tc_status, &z, sizeof(z));
 }
 
 }  // namespace qmm

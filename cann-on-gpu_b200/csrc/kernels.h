@@ -115,6 +115,9 @@ uint64_t wq_rows_workspace_bytes(const MatmulArgs &p);
 cudaError_t launch_wq_rows(const MatmulArgs &p, cudaStream_t s);
 unsigned int wq_rows_device_status();
 void wq_rows_device_status_reset();
+// Activation quantisers (dynquant.cu): the staged SwiGLU quantiser waits on its row copies with a limit.
+unsigned int dynquant_device_status();
+void dynquant_device_status_reset();
 // 0, or the code of the first bounded wait that gave up on the current device (synchronises).
 unsigned int tc_device_status();
 // Clears the status words of every kernel family on the current device (synchronises).

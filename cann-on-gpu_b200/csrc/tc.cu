@@ -886,14 +886,15 @@ void tc_device_status_reset() {
     wq_mma_device_status_reset();
     mx_tc_device_status_reset();
     wq_rows_device_status_reset();
+    dynquant_device_status_reset();
 }
 
 unsigned int tc_device_status() {
     unsigned int v = 0;
     if (cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(v)) != cudaSuccess) return 0xFFFFFFFFu;
     const unsigned int w = wq_tc_device_status(), d = wq_mma_device_status(), x = mx_tc_device_status();
-    const unsigned int r = wq_rows_device_status();
-    return v ? v : (w ? w : (d ? d : (x ? x : r)));
+    const unsigned int r = wq_rows_device_status(), a = dynquant_device_status();
+    return v ? v : (w ? w : (d ? d : (x ? x : (r ? r : a))));
 }
 
 }  // namespace qmm

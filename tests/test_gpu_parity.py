@@ -1164,6 +1164,37 @@ def test_dequant_swiglu_quant(pkg, oracle, dev, dtype):
                     return_status=True) == 161002
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape,with_dq", [((600, 4096), False), ((300, 28672), False), ((320, 2192), True), ((1030, 32768), True)])
+def test_swiglu_quant_many_long_rows(pkg, oracle, dev, shape, with_dq, dtype):
+    """With at least two rows per SM and D >= 1024 the SwiGLU quantiser runs as persistent CTAs that stage rows
+    through shared memory.  Same arithmetic as the one-row-per-CTA form, so the whole call equals, bit for bit, the
+    same rows quantised in slices too short for the staged form; and the oracle's tolerance holds.  D = 1096 leaves
+    idle lanes in the last warp, D = 16384 is the longest row the staged form takes, a zero row gets scale 1."""
+    g = torch.Generator().manual_seed(6600 + shape[0])
+    rows, D = shape[0], shape[1] // 2
+    x = (torch.rand(shape, generator=g) * 6 - 3).to(dtype)
+    x[7, :] = 0
+    dq = (torch.rand(rows, generator=g) * 0.5 + 0.25).float() if with_dq else None
+    name = "aclnnDequantSwigluQuant" if with_dq else "aclnnSwiGluQuant"
+    xd = x.to(dev)
+    q, sc = pkg.swiglu_quant(xd, name=name, dequant_scale=dq.to(dev) if with_dq else None)
+    for r0 in range(0, rows, 100):
+        qs, ss = pkg.swiglu_quant(xd[r0:r0 + 100].contiguous(), name=name, dequant_scale=dq[r0:r0 + 100].to(dev) if with_dq else None)
+        assert torch.equal(q[r0:r0 + 100], qs) and torch.equal(sc.reshape(-1)[r0:r0 + 100], ss.reshape(-1)), r0
+    torch.cuda.synchronize()
+    lib = pkg.load()
+    lib.aclnnB200DeviceStatus.restype = ctypes.c_uint32
+    assert lib.aclnnB200DeviceStatus() == 0
+    take = slice(0, 64)
+    want_q, want_s = oracle.swiglu_quant(x[take].float().numpy(), dq[take].numpy() if with_dq else None)
+    qh, sh = q[take].cpu().numpy(), sc.reshape(-1)[take].cpu().numpy()
+    assert np.allclose(sh, want_s.reshape(-1), rtol=2e-6, atol=0)
+    diff = np.abs(qh.astype(int) - want_q.astype(int))
+    assert diff.max() <= 1 and (diff != 0).mean() < 1e-3
+    assert (qh[7] == 0).all() and sh[7] == 1
+
+
 def test_swiglu_quant_feeds_the_w8a8_matmul(pkg, oracle, workloads, dev):
     """gate/up output -> SwiGluQuant -> aclnnQuantMatmulV4 with the scales as pertokenScale: the matmul's
     result is bit-exact for the codes and scales the quantiser produced."""
