@@ -302,7 +302,8 @@ unsigned int p2p_test_poll_runs_out(unsigned long long wait_ns) {
     WindowView v{};
     uint8_t *mine = nullptr;
     uint32_t *gathered = nullptr;
-    if (cudaMalloc(&mine, win_bytes()) != cudaSuccess || cudaMalloc(&gathered, 2 * 16 * sizeof(uint32_t)) != cudaSuccess) return 0xFFFFFFFFu;
+    if (cudaMalloc(&mine, win_bytes()) != cudaSuccess) return 0xFFFFFFFFu;
+    if (cudaMalloc(&gathered, 2 * 16 * sizeof(uint32_t)) != cudaSuccess) { cudaFree(mine); return 0xFFFFFFFFu; }
     cudaMemset(mine, 0, win_bytes());
     v.nranks = 2; v.rank = 0; v.win[0] = mine; v.win[1] = mine;
     ll_unpack_kernel<<<1, 256>>>(v, gathered, 16, wait_ns);
