@@ -63,7 +63,7 @@ static int enqueue_pass(int n, const void *const *host_x, size_t x_bytes, void *
         aclnnStatus st = aclnnWeightQuantBatchMatmulV2ExGetWorkspaceSize(x[b], weight[i], scale[i], offset ? offset[i] : NULL,
                                                                          bias ? bias[i] : NULL, group, out[b], &need, &ex);
         if (st != 0) return (int)st;
-        if (need > workspace_bytes) return 161002;
+        if (need > workspace_bytes) { aclDestroyAclOpExecutor(ex); return 161002; }
         st = aclnnWeightQuantBatchMatmulV2Ex(workspace, workspace_bytes, ex, stream);
         if (st != 0) return (int)st;
         if ((e = aclrtRecordEvent(g_ev_comp[b], stream)) != ACL_SUCCESS) return (int)e;
@@ -178,7 +178,7 @@ static int enqueue_step(int n, int per_group, const void *host_x, size_t x_bytes
             aclnnStatus st = aclnnWeightQuantBatchMatmulV2ExGetWorkspaceSize(x[i], weight[i], scale[i], offset ? offset[i] : NULL,
                                                                              bias ? bias[i] : NULL, group, out[i], &need, &ex);
             if (st != 0) return (int)st;
-            if (need > workspace_bytes) return 161002;
+            if (need > workspace_bytes) { aclDestroyAclOpExecutor(ex); return 161002; }
             st = aclnnWeightQuantBatchMatmulV2Ex(workspace, workspace_bytes, ex, stream);
             if (st != 0) return (int)st;
         }
