@@ -24,6 +24,14 @@ __device__ __forceinline__ int8_t quant_i8(float v) {
     const int q = (int)rintf(v);
     return (int8_t)(q < -128 ? -128 : (q > 127 ? 127 : q));
 }
+// Four 32-bit integers -> four signed bytes, each clamped to [-128, 127], q0 in the lowest byte.  With __float2int_rn in
+// front this is quant_i8 of four values: round to nearest even, clamp, NaN -> 0.
+__device__ __forceinline__ uint32_t pack4_s8(int q0, int q1, int q2, int q3) {
+    uint32_t hi, r;
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(q3), "r"(q2), "r"(0));
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(q1), "r"(q0), "r"(hi));
+    return r;
+}
 
 template <int THREADS>
 __device__ __forceinline__ float block_max_t(float v, float *sh) {
@@ -78,16 +86,16 @@ __global__ void __launch_bounds__(THREADS) dynquant_row_kernel(const uint16_t *x
         const int64_t d = ((int64_t)c * THREADS + threadIdx.x) * DQ_VEC;
         if (d >= D) continue;
         const uint32_t w[4] = {v[c].x, v[c].y, v[c].z, v[c].w};
-        uint32_t o[2] = {0, 0};
+        int qi[8];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             float lo, hi;
             if constexpr (BF16) { lo = __uint_as_float(w[i] << 16); hi = __uint_as_float(w[i] & 0xFFFF0000u); }
             else { lo = __half2float(__ushort_as_half((unsigned short)(w[i] & 0xFFFFu))); hi = __half2float(__ushort_as_half((unsigned short)(w[i] >> 16))); }
-            const uint32_t b0 = (uint8_t)quant_i8(lo * inv), b1 = (uint8_t)quant_i8(hi * inv);
-            o[i >> 1] |= (b0 | (b1 << 8)) << (16 * (i & 1));
+            qi[2 * i] = __float2int_rn(lo * inv);
+            qi[2 * i + 1] = __float2int_rn(hi * inv);
         }
-        *reinterpret_cast<uint2 *>(q + base + d) = make_uint2(o[0], o[1]);
+        *reinterpret_cast<uint2 *>(q + base + d) = make_uint2(pack4_s8(qi[0], qi[1], qi[2], qi[3]), pack4_s8(qi[4], qi[5], qi[6], qi[7]));
     }
 }
 
@@ -131,10 +139,10 @@ __global__ void __launch_bounds__(256) mxquant_vec_kernel(const uint16_t *x, int
     const float sc = mx_block_scale(amax);
     if (in && (threadIdx.x & (LPB - 1)) == 0) scale_out[i0 / (8 * LPB)] = sc;
     const float inv = 1.f / sc;
-    uint32_t o[2] = {0, 0};
+    int qi[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) o[i >> 2] |= (uint32_t)(uint8_t)quant_i8(f[i] * inv) << (8 * (i & 3));
-    if (in) *reinterpret_cast<uint2 *>(q + i0) = make_uint2(o[0], o[1]);
+    for (int i = 0; i < 8; ++i) qi[i] = __float2int_rn(f[i] * inv);
+    if (in) *reinterpret_cast<uint2 *>(q + i0) = make_uint2(pack4_s8(qi[0], qi[1], qi[2], qi[3]), pack4_s8(qi[4], qi[5], qi[6], qi[7]));
 }
 
 // Any type, any block size: one CTA per block.
@@ -219,13 +227,6 @@ __global__ void __launch_bounds__(THREADS) swigluquant_row_kernel(const uint16_t
 // ([2048, 28672] bf16: 57.5 -> 43.2 us).  The block
 // size is chosen so that CHUNKS * blockDim.x * 8 covers D with no idle lanes where D allows (14336 -> 896 threads).
 // A slot is refilled right after the row-maximum barrier, when every thread has its part of the row in registers.
-// Four 32-bit integers -> four signed bytes (saturating), q0 in the lowest byte.
-__device__ __forceinline__ uint32_t pack4_s8(int q0, int q1, int q2, int q3) {
-    uint32_t hi, r;
-    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(q3), "r"(q2), "r"(0));
-    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(q1), "r"(q0), "r"(hi));
-    return r;
-}
 __device__ __forceinline__ void bulk_row_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
